@@ -1,0 +1,51 @@
+/*
+ * Entry points of libgmm_b200.so that have no counterpart in the reference's headers: a status read-back for the
+ * asynchronous second-phase calls, and flat (handle-free) launchers for bindings that do not want to build
+ * aclTensor objects.  Plain C ABI: pointers, sizes and a CUDA stream passed as void*.
+ */
+#ifndef B200_GMM_B200_H
+#define B200_GMM_B200_H
+#include "aclnn/aclnn_base.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Library version, major*10000 + minor*100 + patch. */
+ACL_FUNC_VISIBILITY int32_t gmmB200Version(void);
+
+/* The second-phase calls only enqueue work, so a device-side problem (a bounded wait that ran out) cannot be
+ * returned by them.  This call waits for `stream`, copies the 4-word status record that the kernels keep at the
+ * start of `workspace` and returns ACLNN_SUCCESS when it is clean, ACLNN_ERR_RUNTIME_ERROR otherwise.
+ * record[0] = code (0 clean, 1 wait timed out), record[1] = CTA, record[2] = waiting role, record[3] = detail.
+ * `record` may be null.  Plays the role of the reference's aclrtSynchronizeStream + error query after
+ * aclnnGroupedMatmulV4 (gmm/grouped_matmul/examples/test_aclnn_grouped_matmul.cpp:180-196). */
+ACL_FUNC_VISIBILITY aclnnStatus gmmB200CheckStatus(const void *workspace, uint64_t workspaceSize, aclrtStream stream,
+                                                  int32_t record[4]);
+
+/* Flat form of aclnnGroupedMatmulV4 for the W8A8 path (same arithmetic, same validation of sizes).
+ * scaleDtype / biasDtype / yDtype use aclDataType codes; bias may be null (biasDtype ignored);
+ * weightTransposed != 0 means the weight is stored [E, N, K]. */
+ACL_FUNC_VISIBILITY aclnnStatus gmmB200GroupedMatmulW8A8WorkspaceSize(int64_t m, int64_t k, int64_t n, int64_t e,
+                                                                     int32_t yDtype, uint64_t *workspaceSize);
+ACL_FUNC_VISIBILITY aclnnStatus gmmB200GroupedMatmulW8A8(const void *x, const void *weight, const void *scale,
+                                                        int32_t scaleDtype, const void *perTokenScale, const void *bias,
+                                                        int32_t biasDtype, const void *groupList, int64_t groupListLen,
+                                                        int32_t groupListType, int64_t m, int64_t k, int64_t n, int64_t e,
+                                                        int32_t weightTransposed, int32_t actType, void *y, int32_t yDtype,
+                                                        void *workspace, uint64_t workspaceSize, aclrtStream stream);
+
+/* Flat form of aclnnGroupedMatmulSwigluQuant. */
+ACL_FUNC_VISIBILITY aclnnStatus gmmB200GroupedMatmulSwigluQuantWorkspaceSize(int64_t m, int64_t k, int64_t n, int64_t e,
+                                                                            uint64_t *workspaceSize);
+ACL_FUNC_VISIBILITY aclnnStatus gmmB200GroupedMatmulSwigluQuant(const void *x, const void *weight, const void *weightScale,
+                                                               int32_t weightScaleDtype, const void *xScale,
+                                                               const void *groupList, int64_t groupListLen, int64_t m,
+                                                               int64_t k, int64_t n, int64_t e, void *output,
+                                                               void *outputScale, void *workspace, uint64_t workspaceSize,
+                                                               aclrtStream stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_GMM_B200_H */

@@ -1,0 +1,8 @@
+"""B200-native grouped int8 GEMM operators behind the aclnn two-phase C API.
+
+``grouped_matmul_v4`` and ``grouped_matmul_swiglu_quant`` mirror the reference operators
+``aclnnGroupedMatmulV4`` (W8A8 per-token mode) and ``aclnnGroupedMatmulSwigluQuant``; both go through the
+C-ABI library ``libgmm_b200.so`` and run hand-written sm_100a kernels.  There is no CPU fallback.
+"""
+from .acl import (AclnnError, grouped_matmul_swiglu_quant, grouped_matmul_v4, check_status)  # noqa: F401
+from ._lib import LIB_PATH, lib  # noqa: F401

@@ -1,0 +1,70 @@
+// Internal interface between the aclnn-compatible host layer and the CUDA launchers.
+// Nothing here is exported; the public C ABI lives in include/.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace gmm {
+
+// Data-type codes follow aclDataType (include/aclnn/aclnn_base.h).
+enum : int { kF32 = 0, kF16 = 1, kI8 = 2, kI32 = 3, kI64 = 9, kBF16 = 27, kNone = -1 };
+
+enum : int {
+    kModeDequantBf16 = 0,  // grouped_matmul W8A8: int32 -> (acc*w_scale)*x_scale -> bf16
+    kModeSwigluQuant = 1,  // grouped_matmul_swiglu_quant: (acc*x_scale)*w_scale -> SwiGLU -> int8 requant
+    kModeInt32 = 2,        // grouped_matmul with an int32 result: raw accumulators
+};
+
+enum : int { kPathSm100 = 0, kPathSimt = 1 };
+
+// Kernel status word (4 x int32 at the start of the workspace).  code 0 = clean.
+enum : int { kStatusOk = 0, kStatusWaitTimeout = 1, kStatusBadSchedule = 2 };
+
+struct Problem {
+    const int8_t *x = nullptr;          // [M, K]
+    const int8_t *w = nullptr;          // [E, K, N], or [E, N, K] when w_trans
+    const void *w_scale = nullptr;      // [E, N] f32 / bf16 / f16
+    int w_scale_dtype = kF32;
+    const float *x_scale = nullptr;     // [M] per-token scale (may be null for mode kModeInt32)
+    const void *bias = nullptr;         // [E, N] int32 or bf16, optional
+    int bias_dtype = kNone;
+    const int64_t *group_list = nullptr;
+    int gl_len = 0;
+    int gl_type = 0;                    // 0 = running total, 1 = per-group count
+    int64_t M = 0, K = 0, N = 0, E = 0;
+    int w_trans = 0;
+    int act_type = 0;                   // 0 none, 1 relu
+    int mode = kModeDequantBf16;
+    void *out0 = nullptr;               // y (bf16 / int32) or q (int8 [M, N/2])
+    void *out1 = nullptr;               // q_scale f32 [M] (swiglu only)
+};
+
+struct Plan {
+    int path = kPathSimt;
+    int num_sms = 0;
+    size_t ws_bytes = 0;
+    size_t off_status = 0, off_amax = 0, off_stage = 0, off_done = 0;
+    size_t zero_bytes = 0;              // leading bytes of the workspace cleared at launch
+    bool maps_ready = false;
+    alignas(64) CUtensorMap map_x;
+    alignas(64) CUtensorMap map_w;
+};
+
+// Host only: choose the kernel path and the workspace layout.  Never touches the device.
+void make_plan(const Problem &p, Plan *plan);
+// Enqueue the operator on `stream`.  Returns cudaSuccess or the first CUDA error.
+cudaError_t launch(const Problem &p, Plan &plan, void *workspace, size_t workspace_bytes, cudaStream_t stream);
+
+// gmm_sm100.cu
+bool sm100_shape_ok(const Problem &p);
+cudaError_t sm100_encode_maps(const Problem &p, Plan &plan);
+cudaError_t sm100_launch(const Problem &p, Plan &plan, void *workspace, cudaStream_t stream);
+// gmm_simt.cu
+cudaError_t simt_launch(const Problem &p, Plan &plan, void *workspace, cudaStream_t stream);
+cudaError_t quant_rows_launch(const Problem &p, const float *stage, const unsigned *amax_bits, cudaStream_t stream);
+
+int device_sm_count();
+
+}  // namespace gmm

@@ -1,0 +1,247 @@
+// CUDA-core kernels of the grouped int8 GEMM path:
+//   * quant_rows_kernel  - second pass of grouped_matmul_swiglu_quant on the tensor-core path: per-row
+//                          scale from the row maximum, then fp32 -> fp16 -> int8.
+//   * gmm_simt_*_kernel  - complete operators for shapes the TMA path cannot take (K or N not a multiple of
+//                          16 bytes, unaligned pointers).  The reference accepts such shapes (its own unit
+//                          tests use K=5, N=10), so they run here on the GPU instead of being rejected.
+// plus the plan / launch glue shared by both paths.
+//
+// Arithmetic follows gmm/grouped_matmul/op_kernel/grouped_matmul_quant_mixcore.h:248-315 and
+// gmm/grouped_matmul_swiglu_quant/op_kernel/grouped_matmul_swiglu_quant.h:367-513 step for step: every fp32
+// operation is separately rounded (no fused multiply-add), bf16 and fp16 casts round to nearest even.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "gmm_common.h"
+
+namespace gmm {
+namespace {
+
+constexpr unsigned kTouched = 0x80000000u;  // marks a row of the staging buffer as written
+
+__device__ __forceinline__ float load_scale1(const void *p, int dtype, size_t i)
+{
+    if (dtype == kF32) return __ldg(reinterpret_cast<const float *>(p) + i);
+    const uint16_t h = __ldg(reinterpret_cast<const uint16_t *>(p) + i);
+    if (dtype == kBF16) return __uint_as_float((uint32_t)h << 16);
+    return __half2float(__ushort_as_half(h));
+}
+
+// q = int8(rint(half(S * (1 / (amax / 127)))))  -- CastFp32ToInt8Template,
+// gmm/grouped_matmul_swiglu_quant/op_kernel/grouped_matmul_swiglu_quant_utils.h:308-316; NaN -> 0, saturating.
+__device__ __forceinline__ int quant1(float s, float rcp)
+{
+    const __half h = __float2half_rn(__fmul_rn(s, rcp));
+    int q = __half2int_rn(h);
+    return max(-128, min(127, q));
+}
+
+// One warp per row.  amax_bits[row] = float bits of max|S| with the top bit set once any tile wrote the row.
+__global__ void __launch_bounds__(256) quant_rows_kernel(const float *__restrict__ stage, const unsigned *__restrict__ amax_bits,
+                                                          int8_t *__restrict__ q, float *__restrict__ q_scale, int M, int H)
+{
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= M) return;
+    const unsigned bits = amax_bits[row];
+    if (!(bits & kTouched)) return;  // row not covered by group_list: outputs stay untouched
+    const float amax = __uint_as_float(bits & ~kTouched);
+    const float qs = __fdiv_rn(amax, 127.0f);
+    const float rcp = __fdiv_rn(1.0f, qs);
+    if (lane == 0) q_scale[row] = qs;
+    const float4 *src = reinterpret_cast<const float4 *>(stage + (size_t)row * H);
+    uint4 *dst = reinterpret_cast<uint4 *>(q + (size_t)row * H);
+    for (int c = lane; c < H / 16; c += 32) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float4 v = src[c * 4 + i];
+            w[i] = (uint32_t)(quant1(v.x, rcp) & 0xff) | ((uint32_t)(quant1(v.y, rcp) & 0xff) << 8) |
+                   ((uint32_t)(quant1(v.z, rcp) & 0xff) << 16) | ((uint32_t)(quant1(v.w, rcp) & 0xff) << 24);
+        }
+        dst[c] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
+// Locate the group of row m.  Same row-range rules as the tensor-core scheduler (group_list semantics of
+// gmm/grouped_matmul/op_kernel/grouped_matmul_utils.h:243-257, clipped to [0, M]).
+__device__ int find_group(const int64_t *gl, int L, int type, int M, int m)
+{
+    long long prev = 0, run = 0;
+    for (int g = 0; g < L; ++g) {
+        const int v = (int)gl[g];
+        long long start, rows;
+        if (type == 0) { start = prev; rows = (long long)v - prev; prev = v; }
+        else { start = run; rows = v; if (v > 0) run += v; }
+        if (rows < 0) rows = 0;
+        if (start < 0) { rows += start; start = 0; if (rows < 0) rows = 0; }
+        if (start > M) { start = M; rows = 0; }
+        if (start + rows > M) rows = M - start;
+        if (m >= start && m < start + rows) return g;
+    }
+    return -1;
+}
+
+struct SimtParams {
+    const int8_t *x, *w;
+    const void *w_scale;
+    int w_scale_dtype;
+    const float *x_scale;
+    const void *bias;
+    int bias_dtype;
+    const int64_t *gl;
+    int gl_len, gl_type;
+    int M, K, N;
+    long long wsk, wsn;  // weight element (k, n) of a group sits at k*wsk + n*wsn
+    int act_type, mode;
+    void *out0;
+    float *out1;
+};
+
+// One CTA per row; threads stride over the output columns.
+__global__ void __launch_bounds__(256) gmm_simt_kernel(const SimtParams p)
+{
+    __shared__ int s_g;
+    const int m = blockIdx.x;
+    if (threadIdx.x == 0) s_g = find_group(p.gl, p.gl_len, p.gl_type, p.M, m);
+    __syncthreads();
+    const int g = s_g;
+    if (g < 0) return;
+    const int8_t *xr = p.x + (size_t)m * p.K;
+    const int8_t *wg = p.w + (size_t)g * p.K * p.N;
+    const float xs = p.x_scale ? p.x_scale[m] : 1.0f;
+    for (int n = threadIdx.x; n < p.N; n += blockDim.x) {
+        int acc = 0;
+        for (int k = 0; k < p.K; ++k) acc += (int)xr[k] * (int)wg[k * p.wsk + n * p.wsn];
+        if (p.bias_dtype == kI32) acc += reinterpret_cast<const int *>(p.bias)[(size_t)g * p.N + n];
+        if (p.mode == kModeInt32) {
+            reinterpret_cast<int *>(p.out0)[(size_t)m * p.N + n] = acc;
+            continue;
+        }
+        float t = __fmul_rn(__int2float_rn(acc), load_scale1(p.w_scale, p.w_scale_dtype, (size_t)g * p.N + n));
+        if (p.x_scale) t = __fmul_rn(t, xs);
+        if (p.bias_dtype == kBF16) t = __fadd_rn(t, load_scale1(p.bias, kBF16, (size_t)g * p.N + n));
+        if (p.act_type == 1) t = t > 0.0f ? t : 0.0f;
+        reinterpret_cast<__nv_bfloat16 *>(p.out0)[(size_t)m * p.N + n] = __float2bfloat16_rn(t);
+    }
+}
+
+// One CTA per row; S for the whole row is held in shared memory (N/2 <= 5120 floats).
+__global__ void __launch_bounds__(256) swiglu_simt_kernel(const SimtParams p)
+{
+    extern __shared__ float s_row[];
+    __shared__ int s_g;
+    __shared__ float s_red[8];
+    const int m = blockIdx.x, H = p.N / 2;
+    if (threadIdx.x == 0) s_g = find_group(p.gl, p.gl_len, 0, p.M, m);
+    __syncthreads();
+    const int g = s_g;
+    if (g < 0) return;
+    const int8_t *xr = p.x + (size_t)m * p.K;
+    const int8_t *wg = p.w + (size_t)g * p.K * p.N;
+    const float xs = p.x_scale[m];
+    float amax = 0.0f;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        int a0 = 0, a1 = 0;
+        for (int k = 0; k < p.K; ++k) {
+            const int xv = xr[k];
+            a0 += xv * (int)wg[k * p.wsk + j * p.wsn];
+            a1 += xv * (int)wg[k * p.wsk + (j + H) * p.wsn];
+        }
+        const float a = __fmul_rn(__fmul_rn(__int2float_rn(a0), xs), load_scale1(p.w_scale, p.w_scale_dtype, (size_t)g * p.N + j));
+        const float b = __fmul_rn(__fmul_rn(__int2float_rn(a1), xs), load_scale1(p.w_scale, p.w_scale_dtype, (size_t)g * p.N + H + j));
+        const float sw = __fdiv_rn(a, __fadd_rn(1.0f, expf(-a)));
+        const float s = __fmul_rn(b, sw);
+        s_row[j] = s;
+        amax = fmaxf(amax, fabsf(s));
+    }
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = s_red[0];
+    for (int i = 1; i < (int)(blockDim.x >> 5); ++i) amax = fmaxf(amax, s_red[i]);
+    const float qs = __fdiv_rn(amax, 127.0f);
+    const float rcp = __fdiv_rn(1.0f, qs);
+    if (threadIdx.x == 0) p.out1[m] = qs;
+    int8_t *qrow = reinterpret_cast<int8_t *>(p.out0) + (size_t)m * H;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) qrow[j] = (int8_t)quant1(s_row[j], rcp);
+}
+
+}  // namespace
+
+int device_sm_count()
+{
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (dev < 0 || dev >= 64) return 0;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+void make_plan(const Problem &p, Plan *plan)
+{
+    plan->path = sm100_shape_ok(p) ? kPathSm100 : kPathSimt;
+    plan->off_status = 0;
+    size_t off = 256;
+    plan->off_amax = off;
+    if (p.mode == kModeSwigluQuant && plan->path == kPathSm100) {
+        off += align_up((size_t)p.M * 4, 256);
+        plan->zero_bytes = off;
+        plan->off_stage = off;
+        off += align_up((size_t)p.M * (size_t)(p.N / 2) * 4, 256);
+    } else {
+        plan->zero_bytes = off;
+        plan->off_stage = off;
+    }
+    plan->ws_bytes = off;
+    plan->maps_ready = false;
+}
+
+cudaError_t quant_rows_launch(const Problem &p, const float *stage, const unsigned *amax_bits, cudaStream_t stream)
+{
+    const int warps = 8;
+    const int grid = (int)((p.M + warps - 1) / warps);
+    quant_rows_kernel<<<grid, warps * 32, 0, stream>>>(stage, amax_bits, reinterpret_cast<int8_t *>(p.out0),
+                                                       reinterpret_cast<float *>(p.out1), (int)p.M, (int)(p.N / 2));
+    return cudaGetLastError();
+}
+
+cudaError_t simt_launch(const Problem &p, Plan &, void *, cudaStream_t stream)
+{
+    SimtParams sp;
+    sp.x = p.x; sp.w = p.w; sp.w_scale = p.w_scale; sp.w_scale_dtype = p.w_scale_dtype; sp.x_scale = p.x_scale;
+    sp.bias = p.bias; sp.bias_dtype = p.bias ? p.bias_dtype : kNone;
+    sp.gl = p.group_list; sp.gl_len = p.gl_len; sp.gl_type = p.gl_type;
+    sp.M = (int)p.M; sp.K = (int)p.K; sp.N = (int)p.N;
+    sp.wsk = p.w_trans ? 1 : p.N;
+    sp.wsn = p.w_trans ? p.K : 1;
+    sp.act_type = p.act_type; sp.mode = p.mode; sp.out0 = p.out0; sp.out1 = reinterpret_cast<float *>(p.out1);
+    if (p.M <= 0) return cudaSuccess;
+    if (p.mode == kModeSwigluQuant) {
+        const size_t smem = (size_t)(p.N / 2) * sizeof(float);
+        swiglu_simt_kernel<<<(int)p.M, 256, smem, stream>>>(sp);
+    } else {
+        gmm_simt_kernel<<<(int)p.M, 256, 0, stream>>>(sp);
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t launch(const Problem &p, Plan &plan, void *workspace, size_t workspace_bytes, cudaStream_t stream)
+{
+    if (workspace_bytes < plan.ws_bytes || (plan.ws_bytes && !workspace)) return cudaErrorInvalidValue;
+    if (plan.zero_bytes) {
+        cudaError_t e = cudaMemsetAsync(workspace, 0, plan.zero_bytes, stream);
+        if (e != cudaSuccess) return e;
+    }
+    if (plan.path == kPathSm100) return sm100_launch(p, plan, workspace, stream);
+    return simt_launch(p, plan, workspace, stream);
+}
+
+}  // namespace gmm

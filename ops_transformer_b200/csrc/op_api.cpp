@@ -1,0 +1,500 @@
+// Host side of the two operators: the aclnn two-phase entry points (parameter validation, executor
+// construction, launch) and the flat entry points declared in include/gmm_b200.h.
+//
+// Validation order and status codes follow the reference's op_api layer:
+//   gmm/grouped_matmul/op_host/op_api/aclnn_grouped_matmul.cpp
+//       CheckNotNull :303-311, CheckCommonParam :1883-1916, CheckUnusedParams :1373-1386,
+//       CheckFunctionQuantParams :786-812, CheckGroupedMatmulQuant :678-700, CheckQuantParamsDtype :642-676,
+//       CheckPerTokenScale :556-588, SplitMSingleXSingleWeightSingleY :1021-1053, CheckGroupListCommonTensor :339-361
+//   gmm/grouped_matmul_swiglu_quant/op_host/op_api/aclnn_grouped_matmul_swiglu_quant.cpp
+//       CheckNotNull :75-105, CheckInputOutDims_A8W8 :108-125, CheckInputOutShape_A8W8 :149-213, CheckDtypeValid :304-324
+// restricted to the int8 x int8 path.  The first phase is host only and never reads group_list; the second
+// phase enqueues on the caller's CUDA stream and returns.
+#include <cstring>
+
+#include "acl_shim.h"
+#include "aclnnop/aclnn_grouped_matmul_swiglu_quant.h"
+#include "aclnnop/aclnn_grouped_matmul_v4.h"
+#include "gmm_b200.h"
+
+namespace gmm {
+void register_executor(aclOpExecutor *e);
+bool claim_executor(aclOpExecutor *e);
+
+namespace {
+
+constexpr int64_t kMaxGroupListLen = 1024;   // MAX_GROUP_LIST_SIZE_TENSOR, aclnn_grouped_matmul.cpp:52
+constexpr int64_t kMaxInnerAxis = 65535;     // aclnn_grouped_matmul.cpp:53
+constexpr int64_t kSwigluNLimit = 10240;     // N_LIMIT, aclnn_grouped_matmul_swiglu_quant.cpp:39
+constexpr int64_t kSwigluKLimit = 65536;     // K_LIMIT_A8W8, :37
+
+#define GMM_REQUIRE(cond, code, ...)                   \
+    do {                                               \
+        if (!(cond)) return fail((code), __VA_ARGS__); \
+    } while (0)
+
+bool is_private_format(aclFormat f) { return f == ACL_FORMAT_FRACTAL_NZ || f == ACL_FORMAT_FRACTAL_Z || f == ACL_FORMAT_NC1HWC0; }
+
+// Same test as IsTransposeLastTwoDims (gmm/grouped_matmul/op_host/op_api/aclnn_grouped_matmul_util.cpp:16-33).
+bool is_transposed_last_two(const aclTensor *t)
+{
+    const size_t r = t->rank();
+    if (r < 2) return false;
+    const size_t d1 = r - 1, d2 = r - 2;
+    if (t->strides[d2] == 1 && t->strides[d1] == t->dim(d2)) {
+        int64_t acc = t->dim(d1) * t->dim(d2);
+        for (size_t b = r - 2; b-- > 0;) {
+            if (t->strides[b] != acc) return false;
+            acc *= t->dim(b);
+        }
+        return true;
+    }
+    return false;
+}
+
+aclOpExecutor *new_executor(const char *name)
+{
+    aclOpExecutor *e = new (std::nothrow) aclOpExecutor();
+    if (e) e->op_name = name;
+    return e;
+}
+
+aclnnStatus finish_phase1(aclOpExecutor *e, uint64_t *workspaceSize, aclOpExecutor **executor)
+{
+    *workspaceSize = e->kind == aclOpExecutor::kNoop ? 0 : e->plan.ws_bytes;
+    register_executor(e);
+    *executor = e;
+    return ACLNN_SUCCESS;
+}
+
+}  // namespace
+
+aclnnStatus run_executor(const char *op_name, void *workspace, uint64_t workspace_size, aclOpExecutor *executor,
+                         aclrtStream stream)
+{
+    clear_error();
+    GMM_REQUIRE(executor != nullptr, ACLNN_ERR_PARAM_NULLPTR, "%s: executor must not be nullptr.", op_name);
+    GMM_REQUIRE(claim_executor(executor), ACLNN_ERR_PARAM_INVALID,
+                "%s: executor is not live; an executor can be run once and only after its GetWorkspaceSize call.", op_name);
+    aclnnStatus rc = ACLNN_SUCCESS;
+    if (std::strcmp(executor->op_name, op_name) != 0) {
+        rc = fail(ACLNN_ERR_PARAM_INVALID, "%s: executor was built by %s.", op_name, executor->op_name);
+    } else if (executor->kind == aclOpExecutor::kGmm) {
+        if (workspace_size < executor->plan.ws_bytes) {
+            rc = fail(ACLNN_ERR_PARAM_INVALID, "%s: workspaceSize %llu is smaller than the %llu bytes required.", op_name,
+                      (unsigned long long)workspace_size, (unsigned long long)executor->plan.ws_bytes);
+        } else if (executor->plan.ws_bytes && !workspace) {
+            rc = fail(ACLNN_ERR_PARAM_NULLPTR, "%s: workspace must not be nullptr.", op_name);
+        } else {
+            cudaError_t ce = launch(executor->problem, executor->plan, workspace, workspace_size, static_cast<cudaStream_t>(stream));
+            if (ce != cudaSuccess)
+                rc = fail(ACLNN_ERR_INNER, "%s: kernel launch failed: %s", op_name, cudaGetErrorString(ce));
+        }
+    }
+    delete executor;
+    return rc;
+}
+
+}  // namespace gmm
+
+using namespace gmm;
+
+extern "C" {
+
+int32_t gmmB200Version(void) { return 100; }
+
+aclnnStatus aclnnGroupedMatmulV4GetWorkspaceSize(
+    const aclTensorList *x, const aclTensorList *weight, const aclTensorList *biasOptional,
+    const aclTensorList *scaleOptional, const aclTensorList *offsetOptional,
+    const aclTensorList *antiquantScaleOptional, const aclTensorList *antiquantOffsetOptional,
+    const aclTensorList *perTokenScaleOptional, const aclTensor *groupListOptional,
+    const aclTensorList *activationInputOptional, const aclTensorList *activationQuantScaleOptional,
+    const aclTensorList *activationQuantOffsetOptional, int64_t splitItem, int64_t groupType, int64_t groupListType,
+    int64_t actType, aclTensorList *out, aclTensorList *activationFeatureOutOptional,
+    aclTensorList *dynQuantScaleOutOptional, uint64_t *workspaceSize, aclOpExecutor **executor)
+{
+    static const char *kOp = "aclnnGroupedMatmulV4";
+    clear_error();
+    // CheckNotNull
+    GMM_REQUIRE(x != nullptr, ACLNN_ERR_PARAM_NULLPTR, "x must not be nullptr.");
+    GMM_REQUIRE(!x->items.empty(), ACLNN_ERR_PARAM_INVALID, "x must not be empty tensorlist.");
+    GMM_REQUIRE(weight != nullptr, ACLNN_ERR_PARAM_NULLPTR, "weight must not be nullptr.");
+    GMM_REQUIRE(!weight->items.empty(), ACLNN_ERR_PARAM_INVALID, "weight must not be empty tensorlist.");
+    GMM_REQUIRE(out != nullptr, ACLNN_ERR_PARAM_NULLPTR, "y must not be nullptr.");
+    GMM_REQUIRE(!out->items.empty(), ACLNN_ERR_PARAM_INVALID, "y must not be empty tensorlist.");
+    GMM_REQUIRE(workspaceSize != nullptr, ACLNN_ERR_PARAM_NULLPTR, "workspaceSize must not be nullptr.");
+    GMM_REQUIRE(executor != nullptr, ACLNN_ERR_PARAM_NULLPTR, "executor must not be nullptr.");
+
+    // CheckCommonParam
+    GMM_REQUIRE(groupType != 1, ACLNN_ERR_PARAM_INVALID, "Not support split n dim now, groupType can not be 1.");
+    GMM_REQUIRE(groupType == 0 || groupType == 2 || groupType == -1, ACLNN_ERR_PARAM_INVALID,
+                "groupType only support -1/0/2 now, but given groupType is %lld", (long long)groupType);
+    if (splitItem == 2 || splitItem == 3)
+        GMM_REQUIRE(groupType != -1, ACLNN_ERR_PARAM_INVALID, "When splitItem is 2/3, groupType can not be -1.");
+    GMM_REQUIRE(groupListOptional == nullptr || groupListOptional->rank() == (groupListType == 2 ? 2u : 1u),
+                ACLNN_ERR_PARAM_INVALID, "groupList dim only support 1 (2 only when groupListType is 2), but now is %zu.",
+                groupListOptional->rank());
+    GMM_REQUIRE(actType >= 0, ACLNN_ERR_PARAM_INVALID, "actType must be larger or equal to 0");
+    GMM_REQUIRE(actType != GMM_ACT_TYPE_GELU_ERR_FUNC, ACLNN_ERR_PARAM_INVALID, "Activation function not support GELU_ERR_FUNC now.");
+    GMM_REQUIRE(actType <= GMM_ACT_TYPE_SILU, ACLNN_ERR_PARAM_INVALID, "Activation function only support RELU/GELU_TANH/FASTGELU/SILU.");
+    GMM_REQUIRE(groupListType == 0 || groupListType == 1, ACLNN_ERR_PARAM_INVALID,
+                "groupListType should be 0 or 1 (the sparse type 2 is not supported on this platform).");
+
+    // CheckUnusedParams
+    GMM_REQUIRE(activationInputOptional == nullptr, ACLNN_ERR_PARAM_INVALID, "activationInputOptional must be nullptr.");
+    GMM_REQUIRE(activationQuantScaleOptional == nullptr, ACLNN_ERR_PARAM_INVALID, "activationQuantScaleOptional must be nullptr.");
+    GMM_REQUIRE(activationQuantOffsetOptional == nullptr, ACLNN_ERR_PARAM_INVALID, "activationQuantOffsetOptional must be nullptr.");
+    GMM_REQUIRE(activationFeatureOutOptional == nullptr, ACLNN_ERR_PARAM_INVALID, "activationFeatureOutOptional must be nullptr.");
+    GMM_REQUIRE(dynQuantScaleOutOptional == nullptr, ACLNN_ERR_PARAM_INVALID, "dynQuantScaleOutOptional must be nullptr.");
+
+    // Scope of this build: one x, one weight, one y, rows split along M.
+    GMM_REQUIRE(groupType == 0, ACLNN_ERR_PARAM_INVALID, "this build supports groupType 0 (split M) only, got %lld.", (long long)groupType);
+    GMM_REQUIRE(x->items.size() == 1 && weight->items.size() == 1 && out->items.size() == 1, ACLNN_ERR_PARAM_INVALID,
+                "this build supports single-tensor x, weight and y only (sizes %zu, %zu, %zu).", x->items.size(),
+                weight->items.size(), out->items.size());
+    GMM_REQUIRE(splitItem == 2 || splitItem == 3, ACLNN_ERR_PARAM_INVALID,
+                "When y is not separated, splitItem should be 2/3, but current splitItem is %lld.", (long long)splitItem);
+    const aclTensor *tx = x->items[0], *tw = weight->items[0], *ty = out->items[0];
+    GMM_REQUIRE(tx && tw && ty, ACLNN_ERR_PARAM_INVALID, "x[0], weight[0] and y[0] must not be null.");
+
+    // CheckFunctionParams: the int8 x int8 family.
+    GMM_REQUIRE(tx->dtype == ACL_INT8 && tw->dtype == ACL_INT8, ACLNN_ERR_PARAM_INVALID,
+                "this build supports int8 x with int8 weight only.");
+    GMM_REQUIRE(ty->dtype == ACL_BF16 || ty->dtype == ACL_INT32, ACLNN_ERR_PARAM_INVALID,
+                "Expect yDtype is int32 or bfloat16 in quant case on this build (int8 and float16 results are not implemented).");
+    const aclTensor *tbias = nullptr;
+    if (biasOptional != nullptr && !biasOptional->items.empty()) {
+        GMM_REQUIRE(biasOptional->items.size() == 1 && biasOptional->items[0], ACLNN_ERR_PARAM_INVALID, "bias must hold one tensor.");
+        tbias = biasOptional->items[0];
+        GMM_REQUIRE(tbias->dtype == ACL_INT32 || tbias->dtype == ACL_BF16, ACLNN_ERR_PARAM_INVALID,
+                    "GMM: bias dtype does not match with required dtype int32 or bfloat16.");
+    }
+    const bool int32_out = ty->dtype == ACL_INT32;
+    const aclTensor *tscale = nullptr, *tpts = nullptr;
+    if (!int32_out) {
+        // CheckGroupedMatmulQuant
+        GMM_REQUIRE(offsetOptional == nullptr, ACLNN_ERR_PARAM_INVALID, "GMM: offset must be nullptr in quant, but now is not nullptr.");
+        GMM_REQUIRE(scaleOptional != nullptr, ACLNN_ERR_PARAM_INVALID, "GMM: scale must not be nullptr in quant, but now is nullptr.");
+        GMM_REQUIRE(scaleOptional->items.size() == 1 && scaleOptional->items[0], ACLNN_ERR_PARAM_INVALID, "Invalid scale.");
+        tscale = scaleOptional->items[0];
+        // Reference pairs (bf16 scale, bf16 y); fp32 scale with a bf16 result is accepted as an extension
+        // (the kernel converts every scale to fp32, grouped_matmul_quant_mixcore.h:262).
+        GMM_REQUIRE(tscale->dtype == ACL_BF16 || tscale->dtype == ACL_FLOAT, ACLNN_ERR_PARAM_INVALID,
+                    "quant case supports scale data type bfloat16 or float32 with output data type bfloat16.");
+        if (perTokenScaleOptional != nullptr) {
+            GMM_REQUIRE(perTokenScaleOptional->items.size() == 1, ACLNN_ERR_PARAM_INVALID,
+                        "perTokenScaleOptional size[%zu] must be 1 and equal with x size[1].", perTokenScaleOptional->items.size());
+            tpts = perTokenScaleOptional->items[0];
+            GMM_REQUIRE(tpts != nullptr, ACLNN_ERR_PARAM_INVALID, "perTokenScaleOptional[0] must not be nullptr, but now is nullptr.");
+            GMM_REQUIRE(tpts->dtype == ACL_FLOAT, ACLNN_ERR_PARAM_INVALID, "per-token quant case only support perTokenScale with data type float32.");
+            GMM_REQUIRE(tpts->rank() == 1, ACLNN_ERR_PARAM_INVALID,
+                        "perTokenScaleOptional dim num must be 1 when x is single tensor, but now is %zu.", tpts->rank());
+        }
+        GMM_REQUIRE(antiquantScaleOptional == nullptr && antiquantOffsetOptional == nullptr, ACLNN_ERR_PARAM_INVALID,
+                    "Detected quant, but antiquant inputs is not empty!");
+    }
+    GMM_REQUIRE(actType == GMM_ACT_TYPE_NONE || actType == GMM_ACT_TYPE_RELU, ACLNN_ERR_PARAM_INVALID,
+                "this build implements actType NONE and RELU only, got %lld.", (long long)actType);
+
+    // SplitMSingleXSingleWeightSingleY: dims and shapes x(m,k), weight(e,k,n), y(m,n).
+    GMM_REQUIRE(!is_private_format(tx->format) && !is_private_format(ty->format), ACLNN_ERR_PARAM_INVALID, "Invalid format.");
+    GMM_REQUIRE(!is_private_format(tw->format), ACLNN_ERR_PARAM_INVALID, "weight format FRACTAL_NZ is not supported by this build.");
+    GMM_REQUIRE(tx->rank() == 2, ACLNN_ERR_PARAM_INVALID, "x[0] dim num should be 2 in this case, but now is %zu.", tx->rank());
+    GMM_REQUIRE(tw->rank() == 3, ACLNN_ERR_PARAM_INVALID, "weight[0] dim num should be 3 in this case, but now is %zu.", tw->rank());
+    GMM_REQUIRE(ty->rank() == 2, ACLNN_ERR_PARAM_INVALID, "y[0] dim num should be 2 in this case, but now is %zu.", ty->rank());
+    const int64_t M = tx->dim(0), K = tx->dim(1), E = tw->dim(0), N = tw->dim(2);
+    GMM_REQUIRE(tw->dim(1) == K, ACLNN_ERR_PARAM_INVALID, "k dim value of x and weight is not matched.");
+    GMM_REQUIRE(ty->dim(0) == M, ACLNN_ERR_PARAM_INVALID, "m dim value of x and y is not matched.");
+    GMM_REQUIRE(ty->dim(1) == N, ACLNN_ERR_PARAM_INVALID, "n dim value of weight and y is not matched.");
+    GMM_REQUIRE(K <= kMaxInnerAxis && N <= kMaxInnerAxis, ACLNN_ERR_PARAM_INVALID, "inner axis of x / weight must not exceed %lld.", (long long)kMaxInnerAxis);
+    // CheckGroupListCommonTensor
+    GMM_REQUIRE(groupListOptional != nullptr, ACLNN_ERR_PARAM_INVALID, "groupListOptional(tensor) is required in this case, but get nullptr.");
+    const int64_t glLen = groupListOptional->dim(0);
+    GMM_REQUIRE(glLen <= kMaxGroupListLen, ACLNN_ERR_PARAM_INVALID,
+                "When groupList type is tensor, size of groupList %lld should be less than or equal to %lld.", (long long)glLen, (long long)kMaxGroupListLen);
+    GMM_REQUIRE((glLen == E && E > 1) || E == 1, ACLNN_ERR_PARAM_INVALID,
+                "When groupList is not null, size of groupList(tensor) %lld should be equal to weight dim 0 %lld with groupType 0.", (long long)glLen, (long long)E);
+    GMM_REQUIRE(groupListOptional->dtype == ACL_INT64, ACLNN_ERR_PARAM_INVALID, "Invalid dtype: Only int64 is supported for groupList.");
+    if (tscale) {
+        GMM_REQUIRE(tscale->rank() == 2 && tscale->dim(0) == E && tscale->dim(1) == N, ACLNN_ERR_PARAM_INVALID, "scale shape must be [%lld, %lld].", (long long)E, (long long)N);
+    }
+    if (tpts) {
+        GMM_REQUIRE(tpts->dim(0) == M, ACLNN_ERR_PARAM_INVALID, "MDim[%lld] of perTokenScaleOptional should be equal with MDim[%lld] of x.", (long long)tpts->dim(0), (long long)M);
+    }
+    if (tbias) {
+        GMM_REQUIRE(tbias->rank() == 2 && tbias->dim(0) == E && tbias->dim(1) == N, ACLNN_ERR_PARAM_INVALID, "bias shape must be [%lld, %lld].", (long long)E, (long long)N);
+    }
+
+    aclOpExecutor *e = new_executor(kOp);
+    GMM_REQUIRE(e != nullptr, ACLNN_ERR_INNER_CREATE_EXECUTOR, "cannot create executor.");
+    // Empty tensors: nothing to launch (CheckZeroShape, aclnn_grouped_matmul.cpp:1535-1548).
+    if (M == 0 || N == 0 || glLen == 0) return finish_phase1(e, workspaceSize, executor);
+
+    const bool w_trans = !tw->contiguous() && is_transposed_last_two(tw);
+    if (!(tx->contiguous() && ty->contiguous() && (tw->contiguous() || w_trans) && groupListOptional->contiguous() &&
+          (!tscale || tscale->contiguous()) && (!tpts || tpts->contiguous()) && (!tbias || tbias->contiguous()))) {
+        delete e;
+        return fail(ACLNN_ERR_PARAM_INVALID, "this build needs contiguous tensors (a transposed weight view excepted).");
+    }
+    Problem &p = e->problem;
+    p.x = static_cast<const int8_t *>(tensor_ptr(tx));
+    p.w = static_cast<const int8_t *>(tensor_ptr(tw));
+    p.w_scale = tscale ? tensor_ptr(tscale) : nullptr;
+    p.w_scale_dtype = tscale ? (int)tscale->dtype : kF32;
+    p.x_scale = tpts ? static_cast<const float *>(tensor_ptr(tpts)) : nullptr;
+    p.bias = tbias ? tensor_ptr(tbias) : nullptr;
+    p.bias_dtype = tbias ? (int)tbias->dtype : kNone;
+    p.group_list = static_cast<const int64_t *>(tensor_ptr(groupListOptional));
+    p.gl_len = (int)(E == 1 ? 1 : glLen);
+    p.gl_type = (int)groupListType;
+    p.M = M; p.K = K; p.N = N; p.E = E;
+    p.w_trans = w_trans ? 1 : 0;
+    p.act_type = (int)actType;
+    p.mode = int32_out ? kModeInt32 : kModeDequantBf16;
+    p.out0 = tensor_ptr(ty);
+    e->kind = aclOpExecutor::kGmm;
+    make_plan(p, &e->plan);
+    return finish_phase1(e, workspaceSize, executor);
+}
+
+aclnnStatus aclnnGroupedMatmulV4(void *workspace, uint64_t workspaceSize, aclOpExecutor *executor, aclrtStream stream)
+{
+    return run_executor("aclnnGroupedMatmulV4", workspace, workspaceSize, executor, stream);
+}
+
+aclnnStatus aclnnGroupedMatmulSwigluQuantGetWorkspaceSize(const aclTensor *x, const aclTensor *weight, const aclTensor *bias,
+                                                          const aclTensor *offset, const aclTensor *weightScale,
+                                                          const aclTensor *xScale, const aclTensor *groupList,
+                                                          aclTensor *output, aclTensor *outputScale, aclTensor *outputOffset,
+                                                          uint64_t *workspaceSize, aclOpExecutor **executor)
+{
+    static const char *kOp = "aclnnGroupedMatmulSwigluQuant";
+    clear_error();
+    (void)bias; (void)offset; (void)outputOffset;  // accepted and ignored, as in the reference (:86-104)
+    // OP_CHECK_COMM_INPUT + CheckNotNull
+    GMM_REQUIRE(workspaceSize != nullptr, ACLNN_ERR_PARAM_NULLPTR, "workspaceSize must not be nullptr.");
+    GMM_REQUIRE(executor != nullptr, ACLNN_ERR_PARAM_NULLPTR, "executor must not be nullptr.");
+    GMM_REQUIRE(x != nullptr, ACLNN_ERR_PARAM_NULLPTR, "x must not be nullptr.");
+    GMM_REQUIRE(weight != nullptr, ACLNN_ERR_PARAM_NULLPTR, "weight must not be nullptr.");
+    GMM_REQUIRE(weightScale != nullptr, ACLNN_ERR_PARAM_NULLPTR, "weightScale must not be nullptr.");
+    GMM_REQUIRE(xScale != nullptr, ACLNN_ERR_PARAM_NULLPTR, "xScale must not be nullptr.");
+    GMM_REQUIRE(groupList != nullptr, ACLNN_ERR_PARAM_NULLPTR, "groupList must not be nullptr.");
+    GMM_REQUIRE(output != nullptr, ACLNN_ERR_PARAM_NULLPTR, "output must not be nullptr.");
+    GMM_REQUIRE(outputScale != nullptr, ACLNN_ERR_PARAM_NULLPTR, "outputScale must not be nullptr.");
+    // CheckInputOutDims_A8W8
+    GMM_REQUIRE(x->rank() == 2, ACLNN_ERR_PARAM_INVALID, "x dim num should be 2, but now is %zu.", x->rank());
+    GMM_REQUIRE(!is_private_format(weight->format), ACLNN_ERR_PARAM_INVALID,
+                "weight storage format FRACTAL_NZ is not supported by this build; pass the ND [E, K, N] tensor.");
+    GMM_REQUIRE(weight->rank() == 3, ACLNN_ERR_PARAM_INVALID, "weight dim num should be 3, but now is %zu.", weight->rank());
+    GMM_REQUIRE(weightScale->rank() == 2, ACLNN_ERR_PARAM_INVALID, "weightScale dim num should be 2, but now is %zu.", weightScale->rank());
+    GMM_REQUIRE(xScale->rank() == 1, ACLNN_ERR_PARAM_INVALID, "xScale dim num should be 1, but now is %zu.", xScale->rank());
+    GMM_REQUIRE(groupList->rank() == 1, ACLNN_ERR_PARAM_INVALID, "groupList dim num should be 1, but now is %zu.", groupList->rank());
+    GMM_REQUIRE(output->rank() == 2, ACLNN_ERR_PARAM_INVALID, "output dim num should be 2, but now is %zu.", output->rank());
+    GMM_REQUIRE(outputScale->rank() == 1, ACLNN_ERR_PARAM_INVALID, "outputScale dim num should be 1, but now is %zu.", outputScale->rank());
+    // CheckInputOutShape_A8W8
+    const int64_t M = x->dim(0), K = x->dim(1), N = weightScale->dim(1), E = weight->dim(0);
+    GMM_REQUIRE(N % 2 == 0, ACLNN_ERR_PARAM_INVALID, "aclnnGroupedMatmulSwiGluQuant, N is %lld , not an even number.", (long long)N);
+    GMM_REQUIRE(weight->dim(1) == K && weight->dim(2) == N, ACLNN_ERR_PARAM_INVALID, "weight shape must be [%lld, %lld, %lld].", (long long)E, (long long)K, (long long)N);
+    GMM_REQUIRE(weightScale->dim(0) == E, ACLNN_ERR_PARAM_INVALID, "weightScale shape must be [%lld, %lld].", (long long)E, (long long)N);
+    GMM_REQUIRE(xScale->dim(0) == M, ACLNN_ERR_PARAM_INVALID, "xScale shape must be [%lld].", (long long)M);
+    GMM_REQUIRE(output->dim(0) == M && output->dim(1) == N / 2, ACLNN_ERR_PARAM_INVALID, "output shape must be [%lld, %lld].", (long long)M, (long long)(N / 2));
+    GMM_REQUIRE(outputScale->dim(0) == M, ACLNN_ERR_PARAM_INVALID, "outputScale shape must be [%lld].", (long long)M);
+    const int64_t glLen = groupList->dim(0);
+    GMM_REQUIRE(glLen <= E, ACLNN_ERR_PARAM_INVALID,
+                "Length of 'groupList' out of range (expected to be in range of [1, %lld], but got %lld)", (long long)E, (long long)glLen);
+    GMM_REQUIRE(N <= kSwigluNLimit, ACLNN_ERR_PARAM_INVALID, "N(%lld) is greater than %lld.", (long long)N, (long long)kSwigluNLimit);
+    GMM_REQUIRE(K < kSwigluKLimit, ACLNN_ERR_PARAM_INVALID, "The tail axis dimension of input0(x) is %lld, which need lower than %lld.", (long long)K, (long long)kSwigluKLimit);
+    // CheckDtypeValid
+    GMM_REQUIRE(x->dtype == ACL_INT8, ACLNN_ERR_PARAM_INVALID, "x dtype must be int8.");
+    GMM_REQUIRE(weight->dtype == ACL_INT8, ACLNN_ERR_PARAM_INVALID, "weight dtype must be int8 (the int4 path is not part of this build).");
+    GMM_REQUIRE(weightScale->dtype == ACL_FLOAT || weightScale->dtype == ACL_FLOAT16 || weightScale->dtype == ACL_BF16,
+                ACLNN_ERR_PARAM_INVALID, "weightScale dtype must be float32, float16 or bfloat16.");
+    GMM_REQUIRE(xScale->dtype == ACL_FLOAT, ACLNN_ERR_PARAM_INVALID, "xScale dtype must be float32.");
+    GMM_REQUIRE(groupList->dtype == ACL_INT64, ACLNN_ERR_PARAM_INVALID, "groupList dtype must be int64.");
+    GMM_REQUIRE(output->dtype == ACL_INT8, ACLNN_ERR_PARAM_INVALID, "output dtype must be int8.");
+    GMM_REQUIRE(outputScale->dtype == ACL_FLOAT, ACLNN_ERR_PARAM_INVALID, "outputScale dtype must be float32.");
+    GMM_REQUIRE(!is_private_format(x->format) && !is_private_format(output->format), ACLNN_ERR_PARAM_INVALID,
+                "x / output Format Not support Private Format.");
+    GMM_REQUIRE(glLen <= kMaxGroupListLen, ACLNN_ERR_PARAM_INVALID, "groupList longer than %lld.", (long long)kMaxGroupListLen);
+
+    aclOpExecutor *e = new_executor(kOp);
+    GMM_REQUIRE(e != nullptr, ACLNN_ERR_INNER_CREATE_EXECUTOR, "cannot create executor.");
+    // Empty tensors (aclnn_grouped_matmul_swiglu_quant.cpp:425-429)
+    if (output->empty() || groupList->empty() || outputScale->empty()) return finish_phase1(e, workspaceSize, executor);
+    if (!(x->contiguous() && weight->contiguous() && weightScale->contiguous() && xScale->contiguous() &&
+          groupList->contiguous() && output->contiguous() && outputScale->contiguous())) {
+        delete e;
+        return fail(ACLNN_ERR_PARAM_INVALID, "this build needs contiguous tensors.");
+    }
+    Problem &p = e->problem;
+    p.x = static_cast<const int8_t *>(tensor_ptr(x));
+    p.w = static_cast<const int8_t *>(tensor_ptr(weight));
+    p.w_scale = tensor_ptr(weightScale);
+    p.w_scale_dtype = (int)weightScale->dtype;
+    p.x_scale = static_cast<const float *>(tensor_ptr(xScale));
+    p.group_list = static_cast<const int64_t *>(tensor_ptr(groupList));
+    p.gl_len = (int)glLen;
+    p.gl_type = 0;
+    p.M = M; p.K = K; p.N = N; p.E = E;
+    p.mode = kModeSwigluQuant;
+    p.out0 = tensor_ptr(output);
+    p.out1 = tensor_ptr(outputScale);
+    e->kind = aclOpExecutor::kGmm;
+    make_plan(p, &e->plan);
+    return finish_phase1(e, workspaceSize, executor);
+}
+
+aclnnStatus aclnnGroupedMatmulSwigluQuant(void *workspace, uint64_t workspaceSize, aclOpExecutor *executor, aclrtStream stream)
+{
+    return run_executor("aclnnGroupedMatmulSwigluQuant", workspace, workspaceSize, executor, stream);
+}
+
+aclnnStatus gmmB200CheckStatus(const void *workspace, uint64_t workspaceSize, aclrtStream stream, int32_t record[4])
+{
+    clear_error();
+    int32_t rec[4] = {0, 0, 0, 0};
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t ce;
+    if (workspace && workspaceSize >= sizeof(rec)) {
+        ce = cudaMemcpyAsync(rec, workspace, sizeof(rec), cudaMemcpyDeviceToHost, s);
+        if (ce != cudaSuccess) return fail(ACLNN_ERR_RUNTIME_ERROR, "status copy failed: %s", cudaGetErrorString(ce));
+    }
+    ce = cudaStreamSynchronize(s);
+    if (ce != cudaSuccess) return fail(ACLNN_ERR_RUNTIME_ERROR, "stream failed: %s", cudaGetErrorString(ce));
+    if (record) std::memcpy(record, rec, sizeof(rec));
+    if (rec[0] != 0)
+        return fail(ACLNN_ERR_RUNTIME_ERROR, "kernel reported status %d (CTA %d, role %d, detail %d)", rec[0], rec[1], rec[2], rec[3]);
+    return ACLNN_SUCCESS;
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// Flat entry points
+// ------------------------------------------------------------------------------------------------------------
+
+static aclnnStatus flat_sizes_ok(int64_t m, int64_t k, int64_t n, int64_t e)
+{
+    GMM_REQUIRE(m >= 0 && k > 0 && n > 0 && e > 0, ACLNN_ERR_PARAM_INVALID, "m, k, n, e must be positive (m may be 0).");
+    GMM_REQUIRE(k <= kMaxInnerAxis && n <= kMaxInnerAxis, ACLNN_ERR_PARAM_INVALID, "k and n must not exceed %lld.", (long long)kMaxInnerAxis);
+    return ACLNN_SUCCESS;
+}
+
+// Workspace for any pointer alignment: the tensor-core layout is a superset of the CUDA-core one.
+static uint64_t flat_ws(int64_t m, int64_t k, int64_t n, int64_t e, int mode)
+{
+    Problem p;
+    p.x = reinterpret_cast<const int8_t *>(uintptr_t(256));
+    p.w = p.x; p.w_scale = p.x; p.out0 = const_cast<int8_t *>(p.x);
+    p.M = m; p.K = k; p.N = n; p.E = e; p.gl_len = 1; p.mode = mode;
+    Plan a;
+    make_plan(p, &a);
+    uint64_t best = a.ws_bytes;
+    p.x = reinterpret_cast<const int8_t *>(uintptr_t(1));  // forces the CUDA-core path
+    make_plan(p, &a);
+    return best > a.ws_bytes ? best : a.ws_bytes;
+}
+
+aclnnStatus gmmB200GroupedMatmulW8A8WorkspaceSize(int64_t m, int64_t k, int64_t n, int64_t e, int32_t yDtype, uint64_t *workspaceSize)
+{
+    clear_error();
+    GMM_REQUIRE(workspaceSize != nullptr, ACLNN_ERR_PARAM_NULLPTR, "workspaceSize must not be nullptr.");
+    aclnnStatus rc = flat_sizes_ok(m, k, n, e);
+    if (rc != ACLNN_SUCCESS) return rc;
+    GMM_REQUIRE(yDtype == ACL_BF16 || yDtype == ACL_INT32, ACLNN_ERR_PARAM_INVALID, "yDtype must be bfloat16 or int32.");
+    *workspaceSize = flat_ws(m, k, n, e, yDtype == ACL_INT32 ? kModeInt32 : kModeDequantBf16);
+    return ACLNN_SUCCESS;
+}
+
+aclnnStatus gmmB200GroupedMatmulW8A8(const void *x, const void *weight, const void *scale, int32_t scaleDtype,
+                                     const void *perTokenScale, const void *bias, int32_t biasDtype, const void *groupList,
+                                     int64_t groupListLen, int32_t groupListType, int64_t m, int64_t k, int64_t n, int64_t e,
+                                     int32_t weightTransposed, int32_t actType, void *y, int32_t yDtype, void *workspace,
+                                     uint64_t workspaceSize, aclrtStream stream)
+{
+    clear_error();
+    GMM_REQUIRE(x && weight && groupList && y, ACLNN_ERR_PARAM_NULLPTR, "x, weight, groupList and y must not be nullptr.");
+    aclnnStatus rc = flat_sizes_ok(m, k, n, e);
+    if (rc != ACLNN_SUCCESS) return rc;
+    GMM_REQUIRE(yDtype == ACL_BF16 || yDtype == ACL_INT32, ACLNN_ERR_PARAM_INVALID, "yDtype must be bfloat16 or int32.");
+    if (yDtype == ACL_BF16) {
+        GMM_REQUIRE(scale != nullptr, ACLNN_ERR_PARAM_NULLPTR, "scale must not be nullptr for a bfloat16 result.");
+        GMM_REQUIRE(scaleDtype == ACL_BF16 || scaleDtype == ACL_FLOAT, ACLNN_ERR_PARAM_INVALID, "scaleDtype must be bfloat16 or float32.");
+    }
+    GMM_REQUIRE(!bias || biasDtype == ACL_INT32 || biasDtype == ACL_BF16, ACLNN_ERR_PARAM_INVALID, "biasDtype must be int32 or bfloat16.");
+    GMM_REQUIRE(groupListType == 0 || groupListType == 1, ACLNN_ERR_PARAM_INVALID, "groupListType should be 0 or 1.");
+    GMM_REQUIRE(groupListLen >= 0 && groupListLen <= e && groupListLen <= kMaxGroupListLen, ACLNN_ERR_PARAM_INVALID,
+                "groupListLen %lld out of range [0, min(e, %lld)].", (long long)groupListLen, (long long)kMaxGroupListLen);
+    GMM_REQUIRE(actType == 0 || actType == 1, ACLNN_ERR_PARAM_INVALID, "actType must be 0 (none) or 1 (relu).");
+    if (m == 0 || groupListLen == 0) return ACLNN_SUCCESS;
+    Problem p;
+    p.x = static_cast<const int8_t *>(x);
+    p.w = static_cast<const int8_t *>(weight);
+    p.w_scale = scale; p.w_scale_dtype = scaleDtype;
+    p.x_scale = static_cast<const float *>(perTokenScale);
+    p.bias = bias; p.bias_dtype = bias ? biasDtype : kNone;
+    p.group_list = static_cast<const int64_t *>(groupList);
+    p.gl_len = (int)groupListLen; p.gl_type = groupListType;
+    p.M = m; p.K = k; p.N = n; p.E = e;
+    p.w_trans = weightTransposed ? 1 : 0;
+    p.act_type = actType;
+    p.mode = yDtype == ACL_INT32 ? kModeInt32 : kModeDequantBf16;
+    p.out0 = y;
+    Plan plan;
+    make_plan(p, &plan);
+    GMM_REQUIRE(workspaceSize >= plan.ws_bytes, ACLNN_ERR_PARAM_INVALID, "workspaceSize %llu is smaller than the %llu bytes required.",
+                (unsigned long long)workspaceSize, (unsigned long long)plan.ws_bytes);
+    GMM_REQUIRE(workspace != nullptr, ACLNN_ERR_PARAM_NULLPTR, "workspace must not be nullptr.");
+    cudaError_t ce = launch(p, plan, workspace, workspaceSize, static_cast<cudaStream_t>(stream));
+    if (ce != cudaSuccess) return fail(ACLNN_ERR_INNER, "kernel launch failed: %s", cudaGetErrorString(ce));
+    return ACLNN_SUCCESS;
+}
+
+aclnnStatus gmmB200GroupedMatmulSwigluQuantWorkspaceSize(int64_t m, int64_t k, int64_t n, int64_t e, uint64_t *workspaceSize)
+{
+    clear_error();
+    GMM_REQUIRE(workspaceSize != nullptr, ACLNN_ERR_PARAM_NULLPTR, "workspaceSize must not be nullptr.");
+    aclnnStatus rc = flat_sizes_ok(m, k, n, e);
+    if (rc != ACLNN_SUCCESS) return rc;
+    GMM_REQUIRE(n % 2 == 0 && n <= kSwigluNLimit && k < kSwigluKLimit, ACLNN_ERR_PARAM_INVALID, "n must be even and <= %lld, k < %lld.",
+                (long long)kSwigluNLimit, (long long)kSwigluKLimit);
+    *workspaceSize = flat_ws(m, k, n, e, kModeSwigluQuant);
+    return ACLNN_SUCCESS;
+}
+
+aclnnStatus gmmB200GroupedMatmulSwigluQuant(const void *x, const void *weight, const void *weightScale, int32_t weightScaleDtype,
+                                            const void *xScale, const void *groupList, int64_t groupListLen, int64_t m, int64_t k,
+                                            int64_t n, int64_t e, void *output, void *outputScale, void *workspace,
+                                            uint64_t workspaceSize, aclrtStream stream)
+{
+    clear_error();
+    GMM_REQUIRE(x && weight && weightScale && xScale && groupList && output && outputScale, ACLNN_ERR_PARAM_NULLPTR,
+                "x, weight, weightScale, xScale, groupList, output and outputScale must not be nullptr.");
+    aclnnStatus rc = flat_sizes_ok(m, k, n, e);
+    if (rc != ACLNN_SUCCESS) return rc;
+    GMM_REQUIRE(n % 2 == 0 && n <= kSwigluNLimit && k < kSwigluKLimit, ACLNN_ERR_PARAM_INVALID, "n must be even and <= %lld, k < %lld.",
+                (long long)kSwigluNLimit, (long long)kSwigluKLimit);
+    GMM_REQUIRE(weightScaleDtype == ACL_FLOAT || weightScaleDtype == ACL_FLOAT16 || weightScaleDtype == ACL_BF16, ACLNN_ERR_PARAM_INVALID,
+                "weightScaleDtype must be float32, float16 or bfloat16.");
+    GMM_REQUIRE(groupListLen >= 0 && groupListLen <= e && groupListLen <= kMaxGroupListLen, ACLNN_ERR_PARAM_INVALID,
+                "groupListLen %lld out of range [0, min(e, %lld)].", (long long)groupListLen, (long long)kMaxGroupListLen);
+    if (m == 0 || groupListLen == 0) return ACLNN_SUCCESS;
+    Problem p;
+    p.x = static_cast<const int8_t *>(x);
+    p.w = static_cast<const int8_t *>(weight);
+    p.w_scale = weightScale; p.w_scale_dtype = weightScaleDtype;
+    p.x_scale = static_cast<const float *>(xScale);
+    p.group_list = static_cast<const int64_t *>(groupList);
+    p.gl_len = (int)groupListLen; p.gl_type = 0;
+    p.M = m; p.K = k; p.N = n; p.E = e;
+    p.mode = kModeSwigluQuant;
+    p.out0 = output; p.out1 = outputScale;
+    Plan plan;
+    make_plan(p, &plan);
+    GMM_REQUIRE(workspaceSize >= plan.ws_bytes, ACLNN_ERR_PARAM_INVALID, "workspaceSize %llu is smaller than the %llu bytes required.",
+                (unsigned long long)workspaceSize, (unsigned long long)plan.ws_bytes);
+    GMM_REQUIRE(workspace != nullptr, ACLNN_ERR_PARAM_NULLPTR, "workspace must not be nullptr.");
+    cudaError_t ce = launch(p, plan, workspace, workspaceSize, static_cast<cudaStream_t>(stream));
+    if (ce != cudaSuccess) return fail(ACLNN_ERR_INNER, "kernel launch failed: %s", cudaGetErrorString(ce));
+    return ACLNN_SUCCESS;
+}
+
+}  // extern "C"

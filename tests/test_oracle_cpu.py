@@ -1,0 +1,177 @@
+"""CPU checks of the oracle itself: against what the reference's own tests pin (group_list semantics from the
+operator README, workspace byte counts and tiling keys from the tiling unit tests), against an independent
+numpy formulation, against the committed golden fixtures, and of each rounding rule on hand-picked values."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from ops_transformer_b200 import synth
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+# ---- what the reference pins -----------------------------------------------------------------------------
+
+def test_group_list_readme_example(oracle):
+    # gmm/grouped_matmul_swiglu_quant/README.md:38-48: groupList=[3,4,4,6] -> rows [0,3) [3,4) [4,4) [4,6)
+    rs, rc = oracle.group_layout([3, 4, 4, 6], 0, 6)
+    assert rs.tolist() == [0, 3, 4, 4] and rc.tolist() == [3, 1, 0, 2]
+    # README.md:50-57: groupList=[12,14,18] with 30 rows -> rows 18.. are never written
+    rs, rc = oracle.group_layout([12, 14, 18], 0, 30)
+    assert int(rs[-1] + rc[-1]) == 18
+
+
+def test_group_list_count_type(oracle):
+    # aclnn_grouped_matmul_v4.h:55-57: groupListType 1 = per-group counts
+    rs, rc = oracle.group_layout([64, 32, 96, 64], 1, 256)
+    assert rs.tolist() == [0, 64, 96, 192] and rc.tolist() == [64, 32, 96, 64]
+    rs0, rc0 = oracle.group_layout(np.cumsum([64, 32, 96, 64]), 0, 256)
+    assert rs0.tolist() == rs.tolist() and rc0.tolist() == rc.tolist()
+
+
+def test_group_list_is_clipped_to_the_tensor(oracle):
+    rs, rc = oracle.group_layout([5, 3, 40], 0, 20)       # not monotone, overshoots M
+    assert rc.tolist() == [5, 0, 17] and (rs + rc).max() <= 20
+    rs, rc = oracle.group_layout([5, -3, 40], 1, 20)
+    assert rc.tolist() == [5, 0, 15] and rs.tolist() == [0, 5, 5]
+
+
+def test_reference_workspace_known_answers(oracle):
+    # tests/ut/op_host/test_grouped_matmul_swiglu_quant_tiling.cpp:70, :99 (A8W8 cases) of the reference
+    assert oracle.ref_swiglu_workspace_bytes(16, 512) == 16809984
+    assert oracle.ref_swiglu_workspace_bytes(16, 4096) == 17039360
+    assert oracle.ref_swiglu_tiling_key(16, 512) == 0 and oracle.ref_swiglu_tiling_key(16, 4096) == 0
+    # key 1 iff m > 2*mLimit; at N=4096 mLimit = 2048 (grouped_matmul_swiglu_quant_tiling.cpp:211, :232)
+    assert oracle.ref_swiglu_tiling_key(4096, 4096) == 0 and oracle.ref_swiglu_tiling_key(4097, 4096) == 1
+    assert oracle.ref_swiglu_workspace_bytes(32768, 4096) == 16 * 2**20 + 64 * 2**20
+
+
+# ---- rounding rules ----------------------------------------------------------------------------------------
+
+def test_bf16_round_to_nearest_even(oracle):
+    L = oracle.lib()
+    assert L.oracle_f32_to_bf16(1.0) == 0x3F80
+    assert L.oracle_f32_to_bf16(np.float32(1.00390625)) == 0x3F80        # 1 + 2^-8: tie -> even (down)
+    assert L.oracle_f32_to_bf16(np.float32(1.01171875)) == 0x3F82        # 1 + 3*2^-8: tie -> even (up)
+    assert L.oracle_f32_to_bf16(float(np.nextafter(np.float32(1.00390625), np.float32(2)))) == 0x3F81  # just above the tie
+    vals = np.random.default_rng(0).standard_normal(4096).astype(np.float32) * 1e3
+    import torch
+    exp = torch.from_numpy(vals).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+    assert np.array_equal(oracle.f32_to_bf16_bits(vals), exp)
+    assert all(L.oracle_f32_to_bf16(float(v)) == int(e) for v, e in zip(vals[:512], exp[:512]))
+
+
+def test_fp16_then_int8_double_rounding(oracle):
+    L = oracle.lib()
+    vals = np.concatenate([np.random.default_rng(1).uniform(-130, 130, 20000), [0.5, 1.5, 2.5, -0.5, -2.5, 126.5, 127.49,
+                          126.96875, 0.49999997, 1e-8, -1e-8, 65519.0, 65520.0, 1e9, 5.96e-8, 2.98e-8, 3.0e-8]]).astype(np.float32)
+    for v in vals:
+        h = L.oracle_f32_to_f16(float(v))
+        assert h == int(np.float32(v).astype(np.float16).view(np.uint16)), v
+        if abs(float(v)) < 1000:
+            q = L.oracle_f16_to_i8(h)
+            e = int(np.clip(np.rint(np.float32(np.float16(v))), -128, 127))
+            assert q == e, (v, q, e)
+    # double rounding differs from a single rounding: 0.50024 -> half 0.5 -> 0, although rint(0.50024) = 1
+    assert L.oracle_f16_to_i8(L.oracle_f32_to_f16(0.50024)) == 0 and round(0.50024) == 1
+    assert L.oracle_f16_to_i8(0x7E00) == 0  # NaN -> 0
+
+
+# ---- against the independent numpy formulation ---------------------------------------------------------------
+
+@pytest.mark.parametrize("gl_type", [0, 1])
+def test_gmm_matches_numpy_formulation(oracle, gl_type):
+    rng = np.random.default_rng(3)
+    M, K, N, E = 70, 133, 48, 5
+    x = synth.int8_tensor((M, K), 3, 1)
+    w = synth.int8_tensor((E, K, N), 3, 2)
+    ws = synth.scale_tensor((E, N), 3, 3)
+    xs = synth.scale_tensor((M,), 3, 4)
+    counts = np.array([10, 0, 33, 1, 20])
+    gl = synth.group_list_from_counts(counts, gl_type)
+    r = oracle.gmm_w8a8(x, w, ws, xs, gl, gl_type, want_acc=True, want_pre=True)
+    acc, pre, y = oracle.np_gmm_w8a8(x, w, ws, xs, gl, gl_type)
+    n = int(counts.sum())
+    assert np.array_equal(r["acc"][:n], acc[:n]) and np.array_equal(r["pre"][:n], pre[:n]) and np.array_equal(r["y"][:n], y[:n])
+    assert (r["y"][n:] == 0).all()
+    # int32 bias joins the accumulator; bf16 bias is added in fp32 after both scales; relu before the cast
+    b32 = rng.integers(-5000, 5000, size=(E, N)).astype(np.int32)
+    r = oracle.gmm_w8a8(x, w, ws, xs, gl, gl_type, bias=b32, want_acc=True)
+    acc, pre, y = oracle.np_gmm_w8a8(x, w, ws, xs, gl, gl_type, bias_i32=b32)
+    assert np.array_equal(r["acc"][:n], acc[:n]) and np.array_equal(r["y"][:n], y[:n])
+    bf = oracle.f32_to_bf16_bits(rng.uniform(-30, 30, size=(E, N)).astype(np.float32))
+    r = oracle.gmm_w8a8(x, w, ws, xs, gl, gl_type, bias=bf, act_type=1)
+    acc, pre, y = oracle.np_gmm_w8a8(x, w, ws, xs, gl, gl_type, bias_f32=oracle.bf16_bits_to_f32(bf), relu=True)
+    assert np.array_equal(r["y"][:n], y[:n])
+    # transposed storage gives the same numbers
+    rt = oracle.gmm_w8a8(x, np.ascontiguousarray(w.transpose(0, 2, 1)), ws, xs, gl, gl_type, w_trans=True)
+    r0 = oracle.gmm_w8a8(x, w, ws, xs, gl, gl_type)
+    assert np.array_equal(rt["y"], r0["y"])
+
+
+def test_gmm_scale_order_is_weight_then_token(oracle):
+    # (acc*w_scale)*x_scale and (acc*x_scale)*w_scale differ in the last bit for some inputs; the two operators
+    # use opposite orders (grouped_matmul_quant_mixcore.h:262,300 vs grouped_matmul_swiglu_quant.h:392,450).
+    x = synth.int8_tensor((64, 256), 5, 1)
+    w = synth.int8_tensor((1, 256, 64), 5, 2)
+    ws = synth.scale_tensor((1, 64), 5, 3)
+    xs = synth.scale_tensor((64,), 5, 4)
+    r = oracle.gmm_w8a8(x, w, ws, xs, [64], 0, want_acc=True, want_pre=True)
+    a = r["acc"].astype(np.float32)
+    assert np.array_equal(r["pre"], (a * ws[0][None, :]) * xs[:, None])
+    other = (a * xs[:, None]) * ws[0][None, :]
+    assert np.count_nonzero(other != r["pre"]) > 0
+
+
+def test_swiglu_matches_numpy_formulation(oracle):
+    M, K, N, E = 90, 200, 96, 4
+    x = synth.int8_tensor((M, K), 6, 1)
+    w = synth.int8_tensor((E, K, N), 6, 2)
+    ws = synth.scale_tensor((E, N), 6, 3)
+    xs = synth.scale_tensor((M,), 6, 4)
+    gl = [20, 20, 75, 80]
+    r = oracle.swiglu_quant(x, w, ws, xs, gl, want_acc=True, want_s=True)
+    q, qs, S = oracle.np_swiglu_quant(x, w, ws, xs, gl)
+    acc = np.zeros((M, N), np.int64)
+    for g, (s, n) in enumerate(oracle.np_group_ranges(gl, 0, M)):
+        acc[s:s + n] = x[s:s + n].astype(np.int64) @ w[g].astype(np.int64)
+    assert np.array_equal(r["acc"][:80], acc[:80])
+    # exp differs between libm and numpy by an ulp or two: 1e-6 on the scales, 1 LSB on a few outputs
+    assert np.max(np.abs(S[:80] - r["s"][:80]) / np.maximum(np.abs(S[:80]), 1e-30)) < 1e-6
+    assert np.max(np.abs(qs[:80] - r["q_scale"][:80]) / qs[:80]) < 1e-6
+    d = np.abs(q[:80].astype(int) - r["q"][:80].astype(int))
+    assert d.max() <= 1 and np.count_nonzero(d) <= 2
+    assert (r["q"][80:] == 0).all() and (r["q_scale"][80:] == 0).all()
+    # exact identities of the quantisation step given the oracle's own S
+    s = r["s"][:80]
+    amax = np.abs(s).max(axis=1)
+    assert np.array_equal(r["q_scale"][:80], amax / np.float32(127.0))
+    assert (np.abs(r["q"][:80]).max(axis=1) == 127).all()
+
+
+def test_swiglu_zero_row_maps_nan_to_zero(oracle):
+    x = np.zeros((4, 32), np.int8)
+    w = synth.int8_tensor((1, 32, 32), 7, 2)
+    ws = synth.scale_tensor((1, 32), 7, 3)
+    xs = synth.scale_tensor((4,), 7, 4)
+    r = oracle.swiglu_quant(x, w, ws, xs, [4])
+    assert (r["q_scale"] == 0).all() and (r["q"] == 0).all()
+
+
+# ---- committed golden fixtures ---------------------------------------------------------------------------------
+
+def test_golden_fixtures(oracle):
+    with open(os.path.join(GOLDEN, "manifest.json")) as f:
+        manifest = json.load(f)
+    assert manifest["cases"], "no golden cases"
+    for case in manifest["cases"]:
+        d = np.load(os.path.join(GOLDEN, case["file"]))
+        x, w, ws, xs, gl = d["x"], d["w"], d["w_scale"], d["x_scale"], d["group_list"]
+        if case["op"] == "grouped_matmul":
+            r = oracle.gmm_w8a8(x, w, ws, xs, gl, int(case["group_list_type"]), want_acc=True)
+            assert np.array_equal(r["acc"], d["acc"]) and np.array_equal(r["y"], d["y_bf16_bits"])
+        else:
+            r = oracle.swiglu_quant(x, w, ws, xs, gl)
+            assert np.array_equal(r["q"], d["q"]) and np.array_equal(r["q_scale"], d["q_scale"])

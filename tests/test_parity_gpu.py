@@ -1,0 +1,284 @@
+"""Parity of the CUDA path (through the C ABI) against the CPU oracle on identical seeded inputs.
+
+Bars: int32 accumulators bit-exact; bf16 results within rtol 4e-3 / atol 1e-2 of the oracle (they are in fact
+expected to be bit-identical, which is asserted too); per-token requant scales within 1e-6 relative; int8
+requant values identical except at most 1 LSB on at most 0.01 % of elements; rows that group_list does not
+cover keep their previous contents.
+"""
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+
+from ops_transformer_b200 import synth  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+BF16_RTOL, BF16_ATOL = 4e-3, 1e-2
+QSCALE_RTOL = 1e-6
+Q_LSB_FRACTION = 1e-4
+
+
+def _dev():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    return torch.device("cuda:0")
+
+
+def _bf16_bits(t):
+    return t.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def make_inputs(M, K, N, E, seed=0):
+    x = synth.int8_tensor((M, K), seed, 1)
+    w = synth.int8_tensor((E, K, N), seed, 2)
+    ws = synth.scale_tensor((E, N), seed, 3)
+    xs = synth.scale_tensor((M,), seed, 4)
+    return x, w, ws, xs
+
+
+def check_gmm(oracle, x, w, ws, xs, gl, gl_type=0, bias=None, act_type=0, w_trans=False, out_dtype="bf16",
+              scale_bf16=False, expect_exact=True):
+    import ops_transformer_b200 as ops
+    dev = _dev()
+    M, K = x.shape
+    E = w.shape[0]
+    N = w.shape[2]
+    gl = np.asarray(gl, np.int64)
+    if scale_bf16:
+        ws_bits = oracle.f32_to_bf16_bits(ws)
+        ws_o = ws_bits
+        ws_t = torch.from_numpy(ws_bits.view(np.int16)).to(dev).view(torch.bfloat16)
+    else:
+        ws_o = ws
+        ws_t = torch.from_numpy(ws).to(dev)
+    w_o = np.ascontiguousarray(w.transpose(0, 2, 1)) if w_trans else w
+    bias_t = None
+    bias_o = None
+    if bias is not None:
+        if bias.dtype == np.int32:
+            bias_o = bias
+            bias_t = torch.from_numpy(bias).to(dev)
+        else:  # bf16 bits
+            bias_o = bias
+            bias_t = torch.from_numpy(bias.view(np.int16)).to(dev).view(torch.bfloat16)
+    ref = oracle.gmm_w8a8(x, w_o, ws_o, xs, gl, gl_type, bias=bias_o, act_type=act_type, w_trans=w_trans,
+                          y_dtype=out_dtype, want_acc=True)
+    xt = torch.from_numpy(x).to(dev)
+    if w_trans:
+        wt = torch.from_numpy(w_o).to(dev).transpose(1, 2)  # view [E, K, N] with strides (N*K, 1, K)
+    else:
+        wt = torch.from_numpy(w).to(dev)
+    xst = torch.from_numpy(xs).to(dev) if xs is not None else None
+    glt = torch.from_numpy(gl).to(dev)
+    tdt = torch.bfloat16 if out_dtype == "bf16" else torch.int32
+    sentinel = 0x7fc1 if out_dtype == "bf16" else -123456789
+    if out_dtype == "bf16":
+        out = torch.full((M, N), 0, dtype=torch.int16, device=dev)
+        out.fill_(np.int16(np.uint16(sentinel).view(np.int16)).item())
+        out = out.view(torch.bfloat16)
+    else:
+        out = torch.full((M, N), sentinel, dtype=torch.int32, device=dev)
+    y, wsb = ops.grouped_matmul_v4(xt, wt, ws_t if out_dtype == "bf16" else None, xst if out_dtype == "bf16" else None,
+                                   glt, bias=bias_t, group_list_type=gl_type, act_type=act_type, out=out,
+                                   out_dtype=tdt, return_workspace=True)
+    ops.check_status(wsb)
+    rs, rc = oracle.group_layout(gl[: E if E > 1 else 1], gl_type, M)
+    covered = np.zeros(M, bool)
+    for s, r in zip(rs, rc):
+        covered[s:s + r] = True
+    if out_dtype == "int32":
+        got = y.cpu().numpy()
+        assert np.array_equal(got[covered], ref["y"][covered]), "int32 accumulators differ"
+        assert (got[~covered] == sentinel).all(), "rows outside group_list were written"
+        return
+    got_bits = _bf16_bits(y)
+    got = oracle.bf16_bits_to_f32(got_bits)
+    exp = oracle.bf16_bits_to_f32(ref["y"])
+    err = np.abs(got[covered] - exp[covered])
+    assert (err <= BF16_ATOL + BF16_RTOL * np.abs(exp[covered])).all(), f"bf16 max err {err.max()}"
+    assert (got_bits[~covered] == sentinel).all(), "rows outside group_list were written"
+    if expect_exact:
+        nbad = int(np.count_nonzero(got_bits[covered] != ref["y"][covered]))
+        assert nbad == 0, f"{nbad} bf16 values are not bit-identical to the oracle"
+
+
+def check_swiglu(oracle, x, w, ws, xs, gl, ws_dtype="f32"):
+    import ops_transformer_b200 as ops
+    dev = _dev()
+    M, K = x.shape
+    N = w.shape[2]
+    H = N // 2
+    gl = np.asarray(gl, np.int64)
+    if ws_dtype == "bf16":
+        bits = oracle.f32_to_bf16_bits(ws)
+        ws_o = bits
+        ws_t = torch.from_numpy(bits.view(np.int16)).to(dev).view(torch.bfloat16)
+    elif ws_dtype == "f16":
+        ws_o = ws.astype(np.float16)
+        ws_t = torch.from_numpy(ws_o).to(dev)
+    else:
+        ws_o = ws
+        ws_t = torch.from_numpy(ws).to(dev)
+    ref = oracle.swiglu_quant(x, w, ws_o, xs, gl)
+    q0 = torch.full((M, H), -77, dtype=torch.int8, device=dev)
+    qs0 = torch.full((M,), -5.0, dtype=torch.float32, device=dev)
+    q, qs, wsb = ops.grouped_matmul_swiglu_quant(torch.from_numpy(x).to(dev), torch.from_numpy(w).to(dev), ws_t,
+                                                 torch.from_numpy(xs).to(dev), torch.from_numpy(gl).to(dev), output=q0,
+                                                 output_scale=qs0, return_workspace=True)
+    ops.check_status(wsb)
+    rs, rc = oracle.group_layout(gl, 0, M)
+    covered = np.zeros(M, bool)
+    for s, r in zip(rs, rc):
+        covered[s:s + r] = True
+    qg, qsg = q.cpu().numpy(), qs.cpu().numpy()
+    assert (qg[~covered] == -77).all() and (qsg[~covered] == -5.0).all(), "rows outside group_list were written"
+    if covered.any():
+        rel = np.abs(qsg[covered] - ref["q_scale"][covered]) / np.abs(ref["q_scale"][covered])
+        assert rel.max() <= QSCALE_RTOL, f"q_scale max rel err {rel.max()}"
+        d = np.abs(qg[covered].astype(np.int32) - ref["q"][covered].astype(np.int32))
+        assert d.max() <= 1, f"int8 outputs differ by {d.max()} LSB"
+        frac = np.count_nonzero(d) / d.size
+        assert frac <= Q_LSB_FRACTION, f"{frac:.2e} of int8 outputs differ by 1 LSB"
+
+
+# ----------------------------------------------------------------------------------------------------------
+# grouped_matmul W8A8
+# ----------------------------------------------------------------------------------------------------------
+
+def test_gmm_single_tile_int32(oracle):
+    x, w, ws, xs = make_inputs(128, 128, 256, 1, seed=1)
+    check_gmm(oracle, x, w, ws, xs, [128], out_dtype="int32")
+
+
+def test_gmm_single_tile_bf16(oracle):
+    x, w, ws, xs = make_inputs(128, 128, 256, 1, seed=2)
+    check_gmm(oracle, x, w, ws, xs, [128])
+
+
+def test_gmm_single_tile_transposed_weight(oracle):
+    x, w, ws, xs = make_inputs(128, 256, 256, 1, seed=3)
+    check_gmm(oracle, x, w, ws, xs, [128], w_trans=True, out_dtype="int32")
+
+
+@pytest.mark.parametrize("gl_type", [0, 1])
+def test_gmm_config1_cpu_golden_case(oracle, gl_type):
+    c = synth.CONFIGS["c1"]
+    counts = np.asarray(c["counts"])
+    x, w, ws, xs = make_inputs(int(counts.sum()), c["K"], c["N"], c["E"], seed=0)
+    check_gmm(oracle, x, w, ws, xs, synth.group_list_from_counts(counts, gl_type), gl_type)
+    check_gmm(oracle, x, w, ws, xs, synth.group_list_from_counts(counts, gl_type), gl_type, out_dtype="int32")
+
+
+def test_gmm_ragged_groups_and_tails(oracle):
+    counts = [0, 5, 130, 0, 1, 257]
+    M = sum(counts) + 9  # 9 trailing rows not covered
+    x, w, ws, xs = make_inputs(M, 144, 272, len(counts), seed=4)  # K and N not multiples of the tile
+    check_gmm(oracle, x, w, ws, xs, np.cumsum(counts), 0)
+    check_gmm(oracle, x, w, ws, xs, counts, 1, out_dtype="int32")
+
+
+def test_gmm_bf16_scale_reference_dtype_pair(oracle):
+    # the reference's own aclnn case: x[84,5120] w[4,5120,2560], bf16 scale, group list {50,65,69,84}
+    x, w, ws, xs = make_inputs(84, 5120, 2560, 4, seed=5)
+    check_gmm(oracle, x, w, ws, xs, [50, 65, 69, 84], 0, scale_bf16=True)
+
+
+def test_gmm_reference_kernel_ut_shapes(oracle):
+    counts = [40, 40] + [20] * 14
+    x, w, ws, xs = make_inputs(360, 1024, 8192, 16, seed=6)
+    check_gmm(oracle, x, w, ws, xs, counts, 1, scale_bf16=True)
+    x, w, ws, xs = make_inputs(360, 8192, 1024, 16, seed=7)
+    check_gmm(oracle, x, w, ws, xs, counts, 1, scale_bf16=True)
+
+
+def test_gmm_unaligned_shapes_take_the_cuda_core_path(oracle):
+    # K=5, N=10 (not 16-byte aligned) are legal in the reference's kernel tests
+    x, w, ws, xs = make_inputs(16, 5, 10, 2, seed=8)
+    check_gmm(oracle, x, w, ws, xs, [8, 8], 1, scale_bf16=True)
+    x, w, ws, xs = make_inputs(16, 10, 10, 2, seed=9)
+    check_gmm(oracle, x, w, ws, xs, [8, 8], 1, act_type=1)
+
+
+def test_gmm_bias_and_relu(oracle):
+    counts = [70, 0, 200]
+    x, w, ws, xs = make_inputs(270, 256, 512, 3, seed=10)
+    b32 = np.random.default_rng(11).integers(-100000, 100000, size=(3, 512)).astype(np.int32)
+    check_gmm(oracle, x, w, ws, xs, np.cumsum(counts), 0, bias=b32)
+    check_gmm(oracle, x, w, ws, xs, np.cumsum(counts), 0, bias=b32, out_dtype="int32")
+    bbf = oracle.f32_to_bf16_bits(np.random.default_rng(12).uniform(-50, 50, size=(3, 512)).astype(np.float32))
+    check_gmm(oracle, x, w, ws, xs, np.cumsum(counts), 0, bias=bbf, act_type=1)
+
+
+def test_gmm_transposed_weight_multi_group(oracle):
+    counts = [100, 37, 300]
+    x, w, ws, xs = make_inputs(437, 512, 768, 3, seed=13)
+    check_gmm(oracle, x, w, ws, xs, np.cumsum(counts), 0, w_trans=True)
+
+
+def test_gmm_many_tiles_more_than_sms(oracle):
+    counts = [513, 1000, 129, 0, 700]
+    x, w, ws, xs = make_inputs(sum(counts), 256, 1024, 5, seed=14)
+    check_gmm(oracle, x, w, ws, xs, np.cumsum(counts), 0)
+
+
+def test_gmm_max_group_count(oracle):
+    E = 1024
+    counts = np.zeros(E, np.int64)
+    counts[[0, 17, 500, 1023]] = [3, 129, 1, 64]
+    x = synth.int8_tensor((int(counts.sum()), 128), 15, 1)
+    w = synth.int8_tensor((E, 128, 32), 15, 2)
+    ws = synth.scale_tensor((E, 32), 15, 3)
+    xs = synth.scale_tensor((int(counts.sum()),), 15, 4)
+    check_gmm(oracle, x, w, ws, xs, counts, 1)
+    check_gmm(oracle, x, w, ws, xs, np.cumsum(counts), 0)
+
+
+# ----------------------------------------------------------------------------------------------------------
+# grouped_matmul_swiglu_quant
+# ----------------------------------------------------------------------------------------------------------
+
+def test_swiglu_reference_small_case(oracle):
+    # m=16, k=256, n=512, e=4 (the reference's kernel unit test shape)
+    x, w, ws, xs = make_inputs(16, 256, 512, 4, seed=20)
+    check_swiglu(oracle, x, w, ws, xs, [4, 8, 12, 16])
+
+
+def test_swiglu_reference_api_case(oracle):
+    x, w, ws, xs = make_inputs(192, 2048, 2048, 4, seed=21)
+    check_swiglu(oracle, x, w, ws, xs, [24, 48, 72, 96])  # rows 96.. stay untouched
+
+
+def test_swiglu_config1_shape(oracle):
+    x, w, ws, xs = make_inputs(256, 1024, 2048, 4, seed=0)
+    check_swiglu(oracle, x, w, ws, xs, np.cumsum([64, 32, 96, 64]))
+
+
+def test_swiglu_ragged_empty_groups_short_list(oracle):
+    counts = [0, 3, 0, 131, 260]
+    x, w, ws, xs = make_inputs(sum(counts) + 5, 144, 608, 8, seed=22)  # list shorter than E, K/N tails
+    check_swiglu(oracle, x, w, ws, xs, np.cumsum(counts))
+
+
+@pytest.mark.parametrize("ws_dtype", ["bf16", "f16"])
+def test_swiglu_half_precision_weight_scale(oracle, ws_dtype):
+    x, w, ws, xs = make_inputs(200, 512, 1024, 2, seed=23)
+    check_swiglu(oracle, x, w, ws, xs, [120, 200], ws_dtype=ws_dtype)
+
+
+def test_swiglu_unaligned_takes_cuda_core_path(oracle):
+    x, w, ws, xs = make_inputs(20, 24, 36, 2, seed=24)
+    check_swiglu(oracle, x, w, ws, xs, [7, 20])
+
+
+def test_swiglu_deepseek_width_few_rows(oracle):
+    # decode-like: full K=7168 / N=4096 with a handful of rows per expert, some experts empty
+    counts = [3, 0, 17, 1, 0, 40]
+    x, w, ws, xs = make_inputs(sum(counts), 7168, 4096, 6, seed=25)
+    check_swiglu(oracle, x, w, ws, xs, np.cumsum(counts))
+
+
+def test_gmm_deepseek_down_width_few_rows(oracle):
+    counts = [3, 0, 17, 1, 0, 40]
+    x, w, ws, xs = make_inputs(sum(counts), 2048, 7168, 6, seed=26)
+    check_gmm(oracle, x, w, ws, xs, np.cumsum(counts), 0)
