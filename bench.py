@@ -1,0 +1,355 @@
+#!/usr/bin/env python
+"""Benchmark of the grouped int8 GEMM hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One "step" is one pass of the hot path over one batch of synthetic input (seeded, DeepSeek-V3 shaped; no
+dataset or checkpoint is involved).  At N=1 the default workload is the DeepSeek-V3 prefill gate/up projection
+through grouped_matmul_swiglu_quant: 4096 tokens x top-8 over 32 local experts = 32768 rows, K=7168, N=4096.
+At N>1 (launched under torchrun, one rank per GPU) the workload is the expert-parallel FFN: 256 experts split
+over the ranks, 16384 tokens per rank, rows exchanged with NCCL all-to-all, swiglu_quant then the down GEMM,
+results returned by all-to-all.  Rank 0 prints one JSON line.
+
+`--impl reference` times the reference's CPU golden path instead: the CPU restatement of the reference kernels
+(oracle/) with all host threads, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+FALLBACK_HBM_GBS = 6650.0
+FALLBACK_BF16_TFLOPS = 1590.0
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm_gbs=float(p["hbm_gbs"]), bf16_tflops=float(p["bf16_tflops"]),
+                    bf16_tflops_sustained=float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), source="measured")
+    return dict(hbm_gbs=FALLBACK_HBM_GBS, bf16_tflops=FALLBACK_BF16_TFLOPS, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+# ------------------------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------------------------
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+        self.t0 = self.t1 = None
+        self.stamps = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def mark_begin(self):
+        self.t0 = time.time()
+
+    def mark_end(self):
+        self.t1 = time.time()
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"], samples=0)
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        rows = [l for (t, l) in self.lines if self.t0 is not None and self.t0 - 0.05 <= t <= (self.t1 or t) + 0.25]
+        if not rows:
+            rows = [l for (_, l) in self.lines]
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for l in rows:
+            f = [c.strip() for c in l.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return dict(sm_mhz=float(np.median(sm)) if sm else None, sm_max_mhz=max(mx) if mx else None,
+                    reasons=sorted(reasons), samples=len(sm))
+
+
+# ------------------------------------------------------------------------------------------------------------
+# workloads
+# ------------------------------------------------------------------------------------------------------------
+
+def gen_device_inputs(torch, dev, M, K, N, E, seed):
+    g = torch.Generator(device=dev)
+    g.manual_seed(seed)
+    x = torch.randint(-127, 128, (M, K), dtype=torch.int8, device=dev, generator=g)
+    w = torch.randint(-127, 128, (E, K, N), dtype=torch.int8, device=dev, generator=g)
+    ws = torch.empty((E, N), dtype=torch.float32, device=dev).uniform_(1e-3, 1e-2, generator=g)
+    xs = torch.empty((M,), dtype=torch.float32, device=dev).uniform_(1e-3, 1e-2, generator=g)
+    return x, w, ws, xs
+
+
+def cpu_sample_swiglu(counts, K, N, rows_per_expert, seed):
+    """Bounded CPU sample of the swiglu workload: the first `rows_per_expert` rows of every expert."""
+    from ops_transformer_b200 import synth
+    c = np.minimum(np.asarray(counts), rows_per_expert)
+    M = int(c.sum())
+    E = len(c)
+    x = synth.int8_tensor((M, K), seed, 1)
+    w = synth.int8_tensor((E, K, N), seed, 2)
+    ws = synth.scale_tensor((E, N), seed, 3)
+    xs = synth.scale_tensor((M,), seed, 4)
+    return x, w, ws, xs, np.cumsum(c)
+
+
+def run_reference_arm(args):
+    """The reference's CPU golden path (CPU restatement of its kernels) on a bounded sample of the N=1 workload."""
+    from oracle import oracle as O
+    from ops_transformer_b200 import synth
+    O.build()
+    cfg = synth.CONFIGS["c2"]
+    counts = synth.config_counts("c2", 0)
+    K, N = cfg["K"], cfg["N"]
+    rows_per_expert = 64
+    x, w, ws, xs, gl = cpu_sample_swiglu(counts, K, N, rows_per_expert, 0)
+    M = x.shape[0]
+    ops_per_step = 2.0 * M * K * N
+    for _ in range(args.warmup if args.warmup < 2 else 1):
+        O.swiglu_quant(x, w, ws, xs, gl)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        O.swiglu_quant(x, w, ws, xs, gl)
+    dt = (time.perf_counter() - t0) / args.steps
+    tops = ops_per_step / dt / 1e12
+    sample = f"first {rows_per_expert} rows of each of the 32 experts ({M} of 32768 rows), full K and N, per step"
+    line = {
+        "impl": "reference", "metric": "int8 GMM+SwiGLU-quant TOPS", "value": tops, "unit": "TOPS", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": {"workload": "c2: DeepSeek-V3 prefill gate/up, grouped_matmul_swiglu_quant, 32768 rows, 32 experts, K=7168, N=4096",
+                   "sample": sample},
+        "cpu_baseline": {"value": tops, "unit": "TOPS", "cores": O.num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": tops, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def cpu_baseline_sample(seconds_budget=15.0):
+    from oracle import oracle as O
+    from ops_transformer_b200 import synth
+    O.build()
+    cfg = synth.CONFIGS["c2"]
+    counts = synth.config_counts("c2", 0)
+    rows_per_expert = 64
+    x, w, ws, xs, gl = cpu_sample_swiglu(counts, cfg["K"], cfg["N"], rows_per_expert, 0)
+    M = x.shape[0]
+    t0 = time.perf_counter()
+    reps = 0
+    while True:
+        O.swiglu_quant(x, w, ws, xs, gl)
+        reps += 1
+        if time.perf_counter() - t0 > seconds_budget or reps >= 5:
+            break
+    dt = (time.perf_counter() - t0) / reps
+    return {"value": 2.0 * M * cfg["K"] * cfg["N"] / dt / 1e12, "unit": "TOPS", "cores": O.num_threads(), "kind": "port",
+            "sample": f"first {rows_per_expert} rows of each expert ({M} of 32768 rows), full K/N, {reps} repetitions"}
+
+
+def bench_single(args):
+    import ctypes as C
+
+    import torch
+
+    import ops_transformer_b200 as ops
+    from ops_transformer_b200 import _lib, synth
+
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    L = _lib.lib()
+    name = args.workload or "c2"
+    cfg = synth.CONFIGS[name]
+    counts = synth.config_counts(name, 0)
+    E, K, N = cfg["E"], cfg["K"], cfg["N"]
+    M = int(counts.sum())
+    swiglu = name in ("c2", "c4_swiglu", "c2_small", "c4_swiglu_small")
+    x, w, ws, xs = gen_device_inputs(torch, dev, M, K, N, E, 0)
+    gl = torch.from_numpy(np.cumsum(counts)).to(dev)
+    nonempty = int((counts > 0).sum())
+    if swiglu:
+        out0 = torch.empty((M, N // 2), dtype=torch.int8, device=dev)
+        out1 = torch.empty((M,), dtype=torch.float32, device=dev)
+        out_bytes = M * (N // 2) + M * 4
+    else:
+        out0 = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+        out1 = None
+        out_bytes = M * N * 2
+    ops_per_step = 2.0 * M * K * N
+    alg_bytes = M * K + nonempty * K * N + nonempty * N * 4 + M * 4 + out_bytes + E * 8
+
+    def step():
+        if swiglu:
+            return ops.grouped_matmul_swiglu_quant(x, w, ws, xs, gl, output=out0, output_scale=out1, return_workspace=True)[-1]
+        return ops.grouped_matmul_v4(x, w, ws, xs, gl, out=out0, return_workspace=True)[-1]
+
+    # L2 policy: for the prefill workloads one step streams > 1 GB, far more than the 126 MB L2; for the small
+    # decode workloads a 256 MB buffer is rewritten between timed steps.
+    flush = None
+    if alg_bytes < 4 * 126e6:
+        flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+
+    for _ in range(max(args.warmup, 3)):
+        wsb = step()
+    ops.check_status(wsb)
+
+    # kernel-only events (recorded by the library around the tensor-core kernel) + whole-step events
+    k_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    s_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    for a, b in k_ev:
+        a.record(); b.record()  # materialise the handles
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    sampler.start()
+    time.sleep(0.3)
+    torch.cuda.synchronize()
+    sampler.mark_begin()
+    for i in range(args.steps):
+        if flush is not None:
+            flush.fill_(i & 0xff)
+        L.gmmB200SetTimingEvents(C.c_void_p(k_ev[i][0].cuda_event), C.c_void_p(k_ev[i][1].cuda_event))
+        s_ev[i][0].record()
+        step()
+        s_ev[i][1].record()
+    L.gmmB200SetTimingEvents(None, None)
+    torch.cuda.synchronize()
+    sampler.mark_end()
+    clocks = sampler.stop()
+    step_ms = [a.elapsed_time(b) for a, b in s_ev]
+    kern_ms = [a.elapsed_time(b) for a, b in k_ev]
+    ms = float(np.mean(step_ms))
+    kms = float(np.mean(kern_ms))
+    ops.check_status(wsb)
+
+    # end to end through the public API with host buffers: pinned H2D of the step's inputs, the two-phase call,
+    # D2H of the results, all inside the timed region.
+    hx = torch.empty_like(x, device="cpu").pin_memory(); hx.copy_(x)
+    hxs = torch.empty_like(xs, device="cpu").pin_memory(); hxs.copy_(xs)
+    hgl = torch.empty_like(gl, device="cpu").pin_memory(); hgl.copy_(gl)
+    ho0 = torch.empty_like(out0, device="cpu").pin_memory()
+    ho1 = torch.empty_like(out1, device="cpu").pin_memory() if out1 is not None else None
+    dx, dxs, dgl = torch.empty_like(x), torch.empty_like(xs), torch.empty_like(gl)
+
+    def e2e_step():
+        dx.copy_(hx, non_blocking=True); dxs.copy_(hxs, non_blocking=True); dgl.copy_(hgl, non_blocking=True)
+        if swiglu:
+            ops.grouped_matmul_swiglu_quant(dx, w, ws, dxs, dgl, output=out0, output_scale=out1)
+            ho0.copy_(out0, non_blocking=True); ho1.copy_(out1, non_blocking=True)
+        else:
+            ops.grouped_matmul_v4(dx, w, ws, dxs, dgl, out=out0)
+            ho0.copy_(out0, non_blocking=True)
+        torch.cuda.synchronize()
+
+    e2e_step()
+    e_steps = max(3, min(args.steps, 10))
+    t0 = time.perf_counter()
+    for _ in range(e_steps):
+        e2e_step()
+    e2e_ms = (time.perf_counter() - t0) / e_steps * 1e3
+    h2d = hx.numel() + hxs.numel() * 4 + hgl.numel() * 8
+    d2h = ho0.numel() * ho0.element_size() + (ho1.numel() * 4 if ho1 is not None else 0)
+
+    peaks = measured_peaks()
+    int8_peak = 2.0 * peaks["bf16_tflops"]  # tcgen05 int8 runs at twice the bf16 rate; bf16 burst is what was measured
+    t_tensor = ops_per_step / (int8_peak * 1e12)
+    t_hbm = alg_bytes / (peaks["hbm_gbs"] * 1e9)
+    if t_tensor >= t_hbm:
+        roof = {"bound": "tensor", "achieved": ops_per_step / (kms * 1e-3) / 1e12, "peak": int8_peak, "unit": "TFLOP/s",
+                "peak_basis": f"2 x bf16 burst of {peaks['source']} ({peaks['bf16_tflops']} TFLOP/s); int8 ops counted as 2 per multiply-add"}
+    else:
+        roof = {"bound": "hbm", "achieved": alg_bytes / (kms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "peak_basis": f"copy bandwidth, {peaks['source']}"}
+    roof["frac"] = roof["achieved"] / roof["peak"]
+    roof["traffic"] = None
+    roof["kernel"] = "gmm_w8a8_sm100_kernel"
+    roof["kernel_ms"] = kms
+    roof["algorithmic_bytes"] = alg_bytes
+    roof["algorithmic_ops"] = ops_per_step
+
+    tops = ops_per_step / (ms * 1e-3) / 1e12
+    line = {
+        "metric": "int8 GMM+SwiGLU-quant TOPS" if swiglu else "int8 GMM W8A8 TOPS",
+        "value": tops, "unit": "TOPS", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
+        "data": "synthetic",
+        "config": {"workload": f"{name}: E={E} K={K} N={N} rows={M} non-empty experts={nonempty}",
+                   "l2": "inputs larger than L2" if flush is None else "256 MB flush write between steps",
+                   "tokens_per_s": (cfg.get("tokens", 0) / (ms * 1e-3)) if cfg.get("tokens") else None},
+        "roofline": roof,
+        "e2e": {"value": ops_per_step / (e2e_ms * 1e-3) / 1e12, "unit": "TOPS", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
+        "gpu_launches": (2 if swiglu else 1) * args.steps,
+        "clocks": clocks,
+        "pct_of_nominal_int8_peak": tops / 4500.0 * 100.0,
+    }
+    if not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline_sample()
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=None, help="c2 (default at N=1), c3, c4_swiglu, c4_down")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    if args.impl == "reference":
+        if rank == 0:
+            run_reference_arm(args)
+        return
+    if args.gpus > 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        from ops_transformer_b200 import ep
+        ep.bench_main(args)
+        return
+    bench_single(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -23,6 +23,12 @@ ACL_FUNC_VISIBILITY int32_t gmmB200Version(void);
 ACL_FUNC_VISIBILITY aclnnStatus gmmB200CheckStatus(const void *workspace, uint64_t workspaceSize, aclrtStream stream,
                                                   int32_t record[4]);
 
+/* Measurement hook: while both events (cudaEvent_t, created by the caller) are set, every launch records
+ * `startEvent` right before and `stopEvent` right after the tensor-core GEMM kernel on the launch stream, so a
+ * benchmark can time that kernel alone inside a multi-kernel operator.  Pass null to switch it off.  Process
+ * wide and not thread safe; meant for benchmarks.  No counterpart in the reference. */
+ACL_FUNC_VISIBILITY void gmmB200SetTimingEvents(void *startEvent, void *stopEvent);
+
 /* Flat form of aclnnGroupedMatmulV4 for the W8A8 path (same arithmetic, same validation of sizes).
  * scaleDtype / biasDtype / yDtype use aclDataType codes; bias may be null (biasDtype ignored);
  * weightTransposed != 0 means the weight is stored [E, N, K]. */

@@ -26,7 +26,7 @@ EXPORTED_SYMBOLS = [
     "aclDestroyIntArray", "aclDestroyAclOpExecutor", "aclGetRecentErrMsg",
     "aclnnGroupedMatmulV4GetWorkspaceSize", "aclnnGroupedMatmulV4",
     "aclnnGroupedMatmulSwigluQuantGetWorkspaceSize", "aclnnGroupedMatmulSwigluQuant",
-    "gmmB200Version", "gmmB200CheckStatus", "gmmB200GroupedMatmulW8A8WorkspaceSize", "gmmB200GroupedMatmulW8A8",
+    "gmmB200Version", "gmmB200CheckStatus", "gmmB200SetTimingEvents", "gmmB200GroupedMatmulW8A8WorkspaceSize", "gmmB200GroupedMatmulW8A8",
     "gmmB200GroupedMatmulSwigluQuantWorkspaceSize", "gmmB200GroupedMatmulSwigluQuant",
 ]
 
@@ -58,6 +58,8 @@ def _load():
     L.aclnnGroupedMatmulSwigluQuantGetWorkspaceSize.argtypes = [p] * 10 + [C.POINTER(u64), C.POINTER(p)]
     L.aclnnGroupedMatmulSwigluQuant.argtypes = [p, u64, p, p]
     L.gmmB200CheckStatus.argtypes = [p, u64, p, C.POINTER(i32)]
+    L.gmmB200SetTimingEvents.argtypes = [p, p]
+    L.gmmB200SetTimingEvents.restype = None
     L.gmmB200GroupedMatmulW8A8WorkspaceSize.argtypes = [i64, i64, i64, i64, i32, C.POINTER(u64)]
     L.gmmB200GroupedMatmulW8A8.argtypes = [p, p, p, i32, p, p, i32, p, i64, i32, i64, i64, i64, i64, i32, i32, p, i32, p, u64, p]
     L.gmmB200GroupedMatmulSwigluQuantWorkspaceSize.argtypes = [i64, i64, i64, i64, C.POINTER(u64)]

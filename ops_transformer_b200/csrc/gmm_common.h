@@ -61,6 +61,8 @@ cudaError_t launch(const Problem &p, Plan &plan, void *workspace, size_t workspa
 bool sm100_shape_ok(const Problem &p);
 cudaError_t sm100_encode_maps(const Problem &p, Plan &plan);
 cudaError_t sm100_launch(const Problem &p, Plan &plan, void *workspace, cudaStream_t stream);
+// Optional pair of events recorded right before / after the tensor-core kernel (nullptr = off).
+void set_timing_events(cudaEvent_t start, cudaEvent_t stop);
 // gmm_simt.cu
 cudaError_t simt_launch(const Problem &p, Plan &plan, void *workspace, cudaStream_t stream);
 cudaError_t quant_rows_launch(const Problem &p, const float *stage, const unsigned *amax_bits, cudaStream_t stream);

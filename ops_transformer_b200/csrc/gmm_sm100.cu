@@ -629,7 +629,15 @@ cudaError_t launch_variant(const Plan &plan, const KParams &kp, cudaStream_t str
     return cudaGetLastError();
 }
 
+cudaEvent_t g_ev_start = nullptr, g_ev_stop = nullptr;
+
 }  // namespace
+
+void set_timing_events(cudaEvent_t start, cudaEvent_t stop)
+{
+    g_ev_start = start;
+    g_ev_stop = stop;
+}
 
 // The tcgen05 path needs 16-byte aligned row pitches for TMA (K for x; N or K for the weight), 16-byte
 // aligned base pointers and, for SwiGLU, a half width that keeps the second box aligned.
@@ -706,12 +714,14 @@ cudaError_t sm100_launch(const Problem &p, Plan &plan, void *workspace, cudaStre
 
     cudaError_t e;
     const bool mn = !p.w_trans;
+    if (g_ev_start) cudaEventRecord(g_ev_start, stream);
     if (p.mode == kModeSwigluQuant)
         e = mn ? launch_variant<kModeSwigluQuant, true>(plan, kp, stream) : launch_variant<kModeSwigluQuant, false>(plan, kp, stream);
     else if (p.mode == kModeInt32)
         e = mn ? launch_variant<kModeInt32, true>(plan, kp, stream) : launch_variant<kModeInt32, false>(plan, kp, stream);
     else
         e = mn ? launch_variant<kModeDequantBf16, true>(plan, kp, stream) : launch_variant<kModeDequantBf16, false>(plan, kp, stream);
+    if (g_ev_stop) cudaEventRecord(g_ev_stop, stream);
     if (e != cudaSuccess) return e;
     if (p.mode == kModeSwigluQuant)
         e = quant_rows_launch(p, reinterpret_cast<const float *>(ws + plan.off_stage), kp.amax_bits, stream);

@@ -103,6 +103,11 @@ extern "C" {
 
 int32_t gmmB200Version(void) { return 100; }
 
+void gmmB200SetTimingEvents(void *startEvent, void *stopEvent)
+{
+    set_timing_events(static_cast<cudaEvent_t>(startEvent), static_cast<cudaEvent_t>(stopEvent));
+}
+
 aclnnStatus aclnnGroupedMatmulV4GetWorkspaceSize(
     const aclTensorList *x, const aclTensorList *weight, const aclTensorList *biasOptional,
     const aclTensorList *scaleOptional, const aclTensorList *offsetOptional,

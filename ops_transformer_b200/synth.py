@@ -52,6 +52,11 @@ CONFIGS = {
     "c3": dict(E=32, K=2048, N=7168, tokens=4096, top_k=8, routing="softmax"),
     "c4_swiglu": dict(E=256, K=7168, N=4096, tokens=128, top_k=8, routing="zipf"),
     "c4_down": dict(E=256, K=2048, N=7168, tokens=128, top_k=8, routing="zipf"),
+    # Reduced cases of the same kernels for profiler captures (a few hundred MB on the device, still > L2).
+    "c2_small": dict(E=8, K=7168, N=4096, tokens=1024, top_k=8, routing="softmax"),
+    "c3_small": dict(E=8, K=2048, N=7168, tokens=1024, top_k=8, routing="softmax"),
+    "c4_swiglu_small": dict(E=32, K=7168, N=4096, tokens=16, top_k=8, routing="zipf"),
+    "c4_down_small": dict(E=32, K=2048, N=7168, tokens=16, top_k=8, routing="zipf"),
 }
 
 
