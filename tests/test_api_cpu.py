@@ -1,0 +1,238 @@
+"""Host-side behaviour of the C ABI that needs no GPU: the library loads and exports every declared symbol, and
+the first-phase calls return the reference's status codes for valid and invalid parameter sets (the cases follow
+gmm/grouped_matmul/tests/utest_aclnn/ts_aclnn_grouped_matmul.cpp and
+gmm/grouped_matmul_swiglu_quant/tests/ut/op_host/op_api/test_aclnn_grouped_matmul_swiglu_quant.cpp of the reference).
+Phase 1 never dereferences tensor data, so host tensors stand in for device tensors here."""
+import ctypes as C
+import os
+import re
+
+import pytest
+import torch
+
+from ops_transformer_b200 import _lib, acl
+
+OK, NULLPTR, INVALID = 0, 161001, 161002
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol(gmm_lib):
+    declared = set()
+    for d, _, files in os.walk(os.path.join(ROOT, "include")):
+        for f in files:
+            text = open(os.path.join(d, f)).read()
+            text = re.sub(r"#define ACL_FUNC_VISIBILITY.*", "", text)
+            declared |= set(re.findall(r"ACL_FUNC_VISIBILITY[^;(]*?\b(\w+)\s*\(", text))
+    assert declared, "no declarations found"
+    assert declared == set(_lib.EXPORTED_SYMBOLS)
+    for name in declared:
+        assert hasattr(gmm_lib, name), f"{name} is declared but not exported"
+    assert gmm_lib.gmmB200Version() >= 100
+
+
+def _v4_phase1(x, w, scale, pts, gl, out, bias=None, split_item=3, group_type=0, gl_type=0, act=0, extra=None):
+    L = _lib.lib()
+    mk = lambda t: acl.create_tensor_list([t]) if t is not None else None  # noqa: E731
+    hx, hw, hb, hs, hp, hy = mk(x), mk(w), mk(bias), mk(scale), mk(pts), mk(out)
+    hg = acl.create_tensor(gl) if gl is not None else None
+    size, ex = C.c_uint64(123), C.c_void_p(0)
+    args = [hx, hw, hb, hs, None, None, None, hp, hg, None, None, None, split_item, group_type, gl_type, act, hy, None, None]
+    if extra:
+        for k, v in extra.items():
+            args[k] = v
+    rc = L.aclnnGroupedMatmulV4GetWorkspaceSize(*args, C.byref(size), C.byref(ex))
+    if rc == OK:
+        assert L.aclDestroyAclOpExecutor(ex) == OK
+    for h in (hx, hw, hb, hs, hp, hy):
+        if h:
+            L.aclDestroyTensorList(h)
+    if hg:
+        L.aclDestroyTensor(hg)
+    return rc, size.value
+
+
+def _v4_tensors(M=84, K=5120, N=2560, E=4, scale_dtype=torch.bfloat16, out_dtype=torch.bfloat16):
+    return dict(x=torch.empty((M, K), dtype=torch.int8), w=torch.empty((E, K, N), dtype=torch.int8),
+                scale=torch.empty((E, N), dtype=scale_dtype), pts=torch.empty((M,), dtype=torch.float32),
+                gl=torch.tensor([50, 65, 69, 84][:E], dtype=torch.int64), out=torch.empty((M, N), dtype=out_dtype))
+
+
+def test_v4_reference_valid_case():
+    # Test_GMMV4_04 of the reference: int8, bf16 scale, fp32 per-token scale, bf16 out, group list {50,65,69,84}
+    rc, size = _v4_phase1(**_v4_tensors())
+    assert rc == OK and size >= 256 and size % 256 == 0
+    rc, _ = _v4_phase1(**_v4_tensors(scale_dtype=torch.float32))  # fp32 scale with bf16 result: accepted extension
+    assert rc == OK
+    rc, _ = _v4_phase1(**_v4_tensors(), gl_type=1)
+    assert rc == OK
+
+
+def test_v4_null_and_empty_arguments():
+    t = _v4_tensors()
+    assert _v4_phase1(**{**t, "x": None})[0] == NULLPTR
+    assert _v4_phase1(**{**t, "w": None})[0] == NULLPTR
+    assert _v4_phase1(**{**t, "out": None})[0] == NULLPTR
+    assert _v4_phase1(**{**t, "gl": None})[0] == INVALID      # required group list missing -> invalid, not nullptr
+    assert _v4_phase1(**{**t, "scale": None})[0] == INVALID   # quant case without scale
+    L = _lib.lib()
+    hx = acl.create_tensor_list([t["x"]])
+    rc = L.aclnnGroupedMatmulV4GetWorkspaceSize(hx, hx, None, None, None, None, None, None, None, None, None, None, 3, 0, 0, 0, hx,
+                                                None, None, None, None)
+    assert rc == NULLPTR  # workspaceSize / executor pointers missing
+    L.aclDestroyTensorList(hx)
+
+
+@pytest.mark.parametrize("kw", [
+    dict(group_type=1), dict(group_type=5), dict(group_type=-1), dict(split_item=0), dict(split_item=1),
+    dict(gl_type=2), dict(gl_type=7), dict(act=-1), dict(act=3), dict(act=6),
+])
+def test_v4_invalid_attributes(kw):
+    assert _v4_phase1(**_v4_tensors(), **kw)[0] == INVALID
+
+
+def test_v4_invalid_shapes_and_dtypes():
+    t = _v4_tensors()
+    assert _v4_phase1(**{**t, "x": torch.empty((84, 5000), dtype=torch.int8)})[0] == INVALID          # K mismatch
+    assert _v4_phase1(**{**t, "out": torch.empty((80, 2560), dtype=torch.bfloat16)})[0] == INVALID    # M mismatch
+    assert _v4_phase1(**{**t, "out": torch.empty((84, 2000), dtype=torch.bfloat16)})[0] == INVALID    # N mismatch
+    assert _v4_phase1(**{**t, "out": torch.empty((84, 2560), dtype=torch.float32)})[0] == INVALID     # y dtype
+    assert _v4_phase1(**{**t, "pts": torch.empty((84,), dtype=torch.float16)})[0] == INVALID          # per-token dtype
+    assert _v4_phase1(**{**t, "pts": torch.empty((80,), dtype=torch.float32)})[0] == INVALID
+    assert _v4_phase1(**{**t, "pts": torch.empty((84, 1), dtype=torch.float32)})[0] == INVALID
+    assert _v4_phase1(**{**t, "gl": torch.tensor([50, 65, 84], dtype=torch.int64)})[0] == INVALID     # len != E
+    assert _v4_phase1(**{**t, "gl": torch.tensor([50, 65, 69, 84], dtype=torch.int32)})[0] == INVALID
+    assert _v4_phase1(**{**t, "gl": torch.zeros((4, 1), dtype=torch.int64)})[0] == INVALID
+    assert _v4_phase1(**{**t, "scale": torch.empty((4, 2560), dtype=torch.int64)})[0] == INVALID
+    assert _v4_phase1(**{**t, "scale": torch.empty((4, 100), dtype=torch.bfloat16)})[0] == INVALID
+    assert _v4_phase1(**{**t, "x": torch.empty((84, 5120), dtype=torch.float16)})[0] == INVALID       # other dtype families
+    assert _v4_phase1(**{**t, "bias": torch.empty((4, 2560), dtype=torch.float32)})[0] == INVALID
+    assert _v4_phase1(**{**t, "bias": torch.empty((4, 2560), dtype=torch.int32)})[0] == OK
+    big = _v4_tensors(M=4, K=65536, N=16, E=1)
+    assert _v4_phase1(**big)[0] == INVALID                                                              # inner axis > 65535
+    hx = acl.create_tensor_list([t["x"]])
+    for slot in (4, 5, 6, 9, 10, 11, 17, 18):  # offset, antiquant*, activation*, dynQuant* must be null
+        assert _v4_phase1(**t, extra={slot: hx})[0] == INVALID
+    _lib.lib().aclDestroyTensorList(hx)
+
+
+def test_v4_int32_result_needs_no_scales_and_empty_input_needs_no_workspace():
+    t = _v4_tensors(out_dtype=torch.int32)
+    assert _v4_phase1(**{**t, "scale": None, "pts": None})[0] == OK
+    e = _v4_tensors(M=0)
+    rc, size = _v4_phase1(**e)
+    assert rc == OK and size == 0
+
+
+def test_v4_transposed_weight_view_and_unaligned_shapes():
+    t = _v4_tensors()
+    wt = torch.empty((4, 2560, 5120), dtype=torch.int8).transpose(1, 2)
+    assert _v4_phase1(**{**t, "w": wt})[0] == OK
+    # K=5, N=10 (the reference kernel UT shape): accepted, served by the CUDA-core kernels
+    u = dict(x=torch.empty((16, 5), dtype=torch.int8), w=torch.empty((2, 5, 10), dtype=torch.int8),
+             scale=torch.empty((2, 10), dtype=torch.bfloat16), pts=torch.empty((16,), dtype=torch.float32),
+             gl=torch.tensor([8, 8], dtype=torch.int64), out=torch.empty((16, 10), dtype=torch.bfloat16))
+    assert _v4_phase1(**u, gl_type=1)[0] == OK
+    # a strided x is refused with a message rather than silently misread
+    xs = torch.empty((84, 2 * 5120), dtype=torch.int8)[:, ::2]
+    assert _v4_phase1(**{**t, "x": xs})[0] == INVALID
+    assert "contiguous" in _lib.last_error()
+
+
+def _sw_phase1(x, w, ws, xs, gl, q, qs, fmt_w=_lib.ACL_FORMAT_ND, null=()):
+    L = _lib.lib()
+    hs = dict(x=x, w=w, ws=ws, xs=xs, gl=gl, q=q, qs=qs)
+    h = {k: (acl.create_tensor(v, fmt=fmt_w if k == "w" else _lib.ACL_FORMAT_ND) if (v is not None and k not in null) else None)
+         for k, v in hs.items()}
+    size, ex = C.c_uint64(7), C.c_void_p(0)
+    rc = L.aclnnGroupedMatmulSwigluQuantGetWorkspaceSize(h["x"], h["w"], None, None, h["ws"], h["xs"], h["gl"], h["q"], h["qs"], None,
+                                                         C.byref(size), C.byref(ex))
+    if rc == OK:
+        assert L.aclDestroyAclOpExecutor(ex) == OK
+    for v in h.values():
+        if v:
+            L.aclDestroyTensor(v)
+    return rc, size.value
+
+
+def _sw_tensors(m=192, k=2048, n=2048, e=4, ws_dtype=torch.float32):
+    return dict(x=torch.empty((m, k), dtype=torch.int8), w=torch.empty((e, k, n), dtype=torch.int8),
+                ws=torch.empty((e, n), dtype=ws_dtype), xs=torch.empty((m,), dtype=torch.float32),
+                gl=torch.tensor([24 * (i + 1) for i in range(e)], dtype=torch.int64),
+                q=torch.empty((m, n // 2), dtype=torch.int8), qs=torch.empty((m,), dtype=torch.float32))
+
+
+def test_swiglu_valid_cases():
+    for dt in (torch.float32, torch.float16, torch.bfloat16):
+        rc, size = _sw_phase1(**_sw_tensors(ws_dtype=dt))
+        assert rc == OK and size > 192 * 1024 * 4
+    t = _sw_tensors()
+    assert _sw_phase1(**{**t, "gl": torch.tensor([10, 20], dtype=torch.int64)})[0] == OK   # list shorter than E is legal
+
+
+def test_swiglu_reference_api_ut_case_is_rejected():
+    # the reference's op_api UT passes an int64 weightScale and an [m, n] output: neither is valid for A8W8
+    t = _sw_tensors()
+    assert _sw_phase1(**{**t, "ws": torch.empty((4, 2048), dtype=torch.int64)})[0] == INVALID
+    assert _sw_phase1(**{**t, "q": torch.empty((192, 2048), dtype=torch.int8)})[0] == INVALID
+
+
+def test_swiglu_null_arguments():
+    t = _sw_tensors()
+    for name in ("x", "w", "ws", "xs", "gl", "q", "qs"):
+        assert _sw_phase1(**t, null=(name,))[0] == NULLPTR
+
+
+def test_swiglu_invalid_shapes_dtypes_limits():
+    t = _sw_tensors()
+    assert _sw_phase1(**{**t, "x": torch.empty((192, 2048, 1), dtype=torch.int8)})[0] == INVALID
+    assert _sw_phase1(**{**t, "w": torch.empty((4, 2000, 2048), dtype=torch.int8)})[0] == INVALID
+    assert _sw_phase1(**{**t, "xs": torch.empty((100,), dtype=torch.float32)})[0] == INVALID
+    assert _sw_phase1(**{**t, "xs": torch.empty((192,), dtype=torch.float16)})[0] == INVALID
+    assert _sw_phase1(**{**t, "qs": torch.empty((192,), dtype=torch.float16)})[0] == INVALID
+    assert _sw_phase1(**{**t, "q": torch.empty((192, 1024), dtype=torch.int32)})[0] == INVALID
+    assert _sw_phase1(**{**t, "gl": torch.tensor([1, 2, 3, 4, 5], dtype=torch.int64)})[0] == INVALID   # longer than E
+    assert _sw_phase1(**{**t, "gl": torch.tensor([1, 2, 3, 4], dtype=torch.int32)})[0] == INVALID
+    odd = _sw_tensors(m=8, k=64, n=34)
+    odd["ws"] = torch.empty((4, 33), dtype=torch.float32)
+    assert _sw_phase1(**odd)[0] == INVALID                                                                  # N odd
+    assert _sw_phase1(**_sw_tensors(m=4, k=64, n=10242, e=1))[0] == INVALID                                 # N > 10240
+    assert _sw_phase1(**_sw_tensors(m=2, k=65536, n=32, e=1))[0] == INVALID                                 # K >= 65536
+    assert _sw_phase1(**t, fmt_w=_lib.ACL_FORMAT_FRACTAL_NZ)[0] == INVALID                                  # NZ storage not built
+    e = _sw_tensors(m=0)
+    rc, size = _sw_phase1(**e)
+    assert rc == OK and size == 0
+
+
+def test_second_phase_host_checks():
+    L = _lib.lib()
+    assert L.aclnnGroupedMatmulV4(None, 0, None, None) == NULLPTR
+    assert L.aclnnGroupedMatmulSwigluQuant(None, 0, None, None) == NULLPTR
+    # an executor built by one operator cannot be run by the other, and cannot be run twice
+    t = _sw_tensors(m=0)
+    h = {k: acl.create_tensor(v) for k, v in t.items()}
+    size, ex = C.c_uint64(0), C.c_void_p(0)
+    assert L.aclnnGroupedMatmulSwigluQuantGetWorkspaceSize(h["x"], h["w"], None, None, h["ws"], h["xs"], h["gl"], h["q"], h["qs"], None,
+                                                           C.byref(size), C.byref(ex)) == OK
+    assert L.aclnnGroupedMatmulV4(None, 0, ex, None) == INVALID
+    assert L.aclnnGroupedMatmulSwigluQuant(None, 0, ex, None) == INVALID          # consumed by the failed call above
+    assert L.aclnnGroupedMatmulSwigluQuantGetWorkspaceSize(h["x"], h["w"], None, None, h["ws"], h["xs"], h["gl"], h["q"], h["qs"], None,
+                                                           C.byref(size), C.byref(ex)) == OK
+    assert L.aclnnGroupedMatmulSwigluQuant(None, 0, ex, None) == OK               # empty problem: nothing to launch
+    assert L.aclnnGroupedMatmulSwigluQuant(None, 0, ex, None) == INVALID          # single use
+    for v in h.values():
+        L.aclDestroyTensor(v)
+
+
+def test_flat_entry_points_validate_on_the_host():
+    L = _lib.lib()
+    size = C.c_uint64(0)
+    assert L.gmmB200GroupedMatmulSwigluQuantWorkspaceSize(32768, 7168, 4096, 32, C.byref(size)) == OK
+    assert size.value >= 32768 * 2048 * 4
+    assert L.gmmB200GroupedMatmulSwigluQuantWorkspaceSize(16, 64, 33, 1, C.byref(size)) == INVALID
+    assert L.gmmB200GroupedMatmulW8A8WorkspaceSize(256, 1024, 2048, 4, _lib.ACL_BF16, C.byref(size)) == OK and size.value == 256
+    assert L.gmmB200GroupedMatmulW8A8WorkspaceSize(256, 1024, 2048, 4, _lib.ACL_FLOAT16, C.byref(size)) == INVALID
+    one = C.c_void_p(256)
+    assert L.gmmB200GroupedMatmulW8A8(None, one, one, 0, one, None, 0, one, 1, 0, 1, 16, 16, 1, 0, 0, one, 27, one, 256, None) == NULLPTR
+    assert L.gmmB200GroupedMatmulW8A8(one, one, one, 0, one, None, 0, one, 2, 0, 1, 16, 16, 1, 0, 0, one, 27, one, 256, None) == INVALID
+    assert L.gmmB200GroupedMatmulSwigluQuant(one, one, one, 0, one, one, 1, 4, 16, 32, 1, one, one, one, 16, None) == INVALID  # workspace too small
+    assert "workspaceSize" in _lib.last_error()
