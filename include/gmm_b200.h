@@ -51,6 +51,29 @@ ACL_FUNC_VISIBILITY aclnnStatus gmmB200GroupedMatmulSwigluQuant(const void *x, c
                                                                void *outputScale, void *workspace, uint64_t workspaceSize,
                                                                aclrtStream stream);
 
+/* grouped_matmul_swiglu_quant without any device allocation.  This entry point has no counterpart in the reference.
+ *
+ * For callers that cannot allocate at the point of the call - a server whose memory pool is frozen after warm-up,
+ * a plugin living inside another runtime's arena, a loop that cannot afford the device-wide synchronisation that
+ * cudaMalloc / cudaFree imply.  The operator's scratch memory is a fixed array of
+ * GMM_B200_NO_ALLOC_SCRATCH_BYTES inside the library image, which every GPU that loads the library keeps until the
+ * process ends.  Same arguments and results as gmmB200GroupedMatmulSwigluQuant minus the workspace.
+ *   - Limit: the scratch needed is 256 + 4*m (rounded up to 256) + 4*m*(n/2) bytes; a larger problem is rejected
+ *     with ACLNN_ERR_PARAM_INVALID and a message (e.g. at n = 4096, m = 4096 rows fit and m = 8192 do not).
+ *   - The first call on each device looks up the array's device address (once, with that device current); make that
+ *     first call before any stream capture begins.
+ *   - All calls share the one array and it keeps the previous call's contents; the part that must start at zero is
+ *     cleared on `stream` by every call.  Two calls that can overlap on the GPU (different streams, no ordering
+ *     between them) race on it: order them, or use the workspace variant for one of them.
+ * Neither this call nor anything it calls allocates or frees device memory. */
+#define GMM_B200_NO_ALLOC_SCRATCH_BYTES (32u * 1024u * 1024u + 64u * 1024u)
+ACL_FUNC_VISIBILITY uint64_t gmmB200NoAllocScratchBytes(void);
+ACL_FUNC_VISIBILITY aclnnStatus gmmB200GroupedMatmulSwigluQuantNoAlloc(const void *x, const void *weight, const void *weightScale,
+                                                                      int32_t weightScaleDtype, const void *xScale,
+                                                                      const void *groupList, int64_t groupListLen, int64_t m,
+                                                                      int64_t k, int64_t n, int64_t e, void *output,
+                                                                      void *outputScale, aclrtStream stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -28,6 +28,7 @@ EXPORTED_SYMBOLS = [
     "aclnnGroupedMatmulSwigluQuantGetWorkspaceSize", "aclnnGroupedMatmulSwigluQuant",
     "gmmB200Version", "gmmB200CheckStatus", "gmmB200SetTimingEvents", "gmmB200GroupedMatmulW8A8WorkspaceSize", "gmmB200GroupedMatmulW8A8",
     "gmmB200GroupedMatmulSwigluQuantWorkspaceSize", "gmmB200GroupedMatmulSwigluQuant",
+    "gmmB200NoAllocScratchBytes", "gmmB200GroupedMatmulSwigluQuantNoAlloc",
 ]
 
 
@@ -64,6 +65,8 @@ def _load():
     L.gmmB200GroupedMatmulW8A8.argtypes = [p, p, p, i32, p, p, i32, p, i64, i32, i64, i64, i64, i64, i32, i32, p, i32, p, u64, p]
     L.gmmB200GroupedMatmulSwigluQuantWorkspaceSize.argtypes = [i64, i64, i64, i64, C.POINTER(u64)]
     L.gmmB200GroupedMatmulSwigluQuant.argtypes = [p, p, p, i32, p, p, i64, i64, i64, i64, i64, p, p, p, u64, p]
+    L.gmmB200NoAllocScratchBytes.restype = u64
+    L.gmmB200GroupedMatmulSwigluQuantNoAlloc.argtypes = [p, p, p, i32, p, p, i64, i64, i64, i64, i64, p, p, p]
     return L
 
 
