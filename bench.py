@@ -338,13 +338,16 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, help="c2 (default at N=1), c3, c4_swiglu, c4_down")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ep-tokens", type=int, default=16384, help="tokens per GPU of the expert-parallel workload")
+    ap.add_argument("--ep-chunks", type=int, default=4, help="token chunks pipelined against the exchange")
+    ap.add_argument("--ep-phases", action="store_true", help="also report serialised per-phase times (diagnostic)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     if args.impl == "reference":
         if rank == 0:
             run_reference_arm(args)
         return
-    if args.gpus > 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
+    if args.gpus > 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1 or args.workload == "c5":
         from ops_transformer_b200 import ep
         ep.bench_main(args)
         return
