@@ -31,15 +31,20 @@ ACL_FUNC_VISIBILITY void gmmB200SetTimingEvents(void *startEvent, void *stopEven
 
 /* Flat form of aclnnGroupedMatmulV4 for the W8A8 path (same arithmetic, same validation of sizes).
  * scaleDtype / biasDtype / yDtype use aclDataType codes; bias may be null (biasDtype ignored);
- * weightTransposed != 0 means the weight is stored [E, N, K]. */
+ * weightTransposed != 0 means the weight is stored [E, N, K].
+ * outRowIndex (optional, int64 [m] on the device, may be null): result row r is written to row outRowIndex[r] of y
+ * instead of row r, which lets a caller fold the un-permute that follows the down projection of an MoE layer into the
+ * GEMM (the row scatter of the reference's GroupedMatmulFinalizeRouting, gmm/grouped_matmul_finalize_routing/README.md:11-14,
+ * without its weighting).  The indices must be a permutation onto rows of y; they are not checked. */
 ACL_FUNC_VISIBILITY aclnnStatus gmmB200GroupedMatmulW8A8WorkspaceSize(int64_t m, int64_t k, int64_t n, int64_t e,
                                                                      int32_t yDtype, uint64_t *workspaceSize);
 ACL_FUNC_VISIBILITY aclnnStatus gmmB200GroupedMatmulW8A8(const void *x, const void *weight, const void *scale,
                                                         int32_t scaleDtype, const void *perTokenScale, const void *bias,
                                                         int32_t biasDtype, const void *groupList, int64_t groupListLen,
                                                         int32_t groupListType, int64_t m, int64_t k, int64_t n, int64_t e,
-                                                        int32_t weightTransposed, int32_t actType, void *y, int32_t yDtype,
-                                                        void *workspace, uint64_t workspaceSize, aclrtStream stream);
+                                                        int32_t weightTransposed, int32_t actType, const void *outRowIndex,
+                                                        void *y, int32_t yDtype, void *workspace, uint64_t workspaceSize,
+                                                        aclrtStream stream);
 
 /* Flat form of aclnnGroupedMatmulSwigluQuant. */
 ACL_FUNC_VISIBILITY aclnnStatus gmmB200GroupedMatmulSwigluQuantWorkspaceSize(int64_t m, int64_t k, int64_t n, int64_t e,
@@ -58,7 +63,7 @@ ACL_FUNC_VISIBILITY aclnnStatus gmmB200GroupedMatmulSwigluQuant(const void *x, c
  * cudaMalloc / cudaFree imply.  The operator's scratch memory is a fixed array of
  * GMM_B200_NO_ALLOC_SCRATCH_BYTES inside the library image, which every GPU that loads the library keeps until the
  * process ends.  Same arguments and results as gmmB200GroupedMatmulSwigluQuant minus the workspace.
- *   - Limit: the scratch needed is 256 + 4*m (rounded up to 256) + 4*m*(n/2) bytes; a larger problem is rejected
+ *   - Limit: the scratch needed is about 4*m*(n/2) + 4*m + 4*(m/128 + groupListLen) + 1 KiB bytes; a larger problem is rejected
  *     with ACLNN_ERR_PARAM_INVALID and a message (e.g. at n = 4096, m = 4096 rows fit and m = 8192 do not).
  *   - The first call on each device looks up the array's device address (once, with that device current); make that
  *     first call before any stream capture begins.

@@ -47,7 +47,8 @@ def needs_build() -> bool:
 def build_library(force: bool = False, verbose: bool = False) -> str:
     if not force and not needs_build():
         return LIB_PATH
-    cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + [
+    extra = os.environ.get("GMM_B200_NVCC_EXTRA", "").split()  # e.g. -DGMM_DEBUG_KNOBS for kernel experiments
+    cmd = [_nvcc()] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + [
         "-I", os.path.join(ROOT, "include"), "-I", CSRC, "-o", LIB_PATH,
     ] + [os.path.join(CSRC, s) for s in SOURCES]
     env = dict(os.environ)

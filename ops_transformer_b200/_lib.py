@@ -62,7 +62,7 @@ def _load():
     L.gmmB200SetTimingEvents.argtypes = [p, p]
     L.gmmB200SetTimingEvents.restype = None
     L.gmmB200GroupedMatmulW8A8WorkspaceSize.argtypes = [i64, i64, i64, i64, i32, C.POINTER(u64)]
-    L.gmmB200GroupedMatmulW8A8.argtypes = [p, p, p, i32, p, p, i32, p, i64, i32, i64, i64, i64, i64, i32, i32, p, i32, p, u64, p]
+    L.gmmB200GroupedMatmulW8A8.argtypes = [p, p, p, i32, p, p, i32, p, i64, i32, i64, i64, i64, i64, i32, i32, p, p, i32, p, u64, p]
     L.gmmB200GroupedMatmulSwigluQuantWorkspaceSize.argtypes = [i64, i64, i64, i64, C.POINTER(u64)]
     L.gmmB200GroupedMatmulSwigluQuant.argtypes = [p, p, p, i32, p, p, i64, i64, i64, i64, i64, p, p, p, u64, p]
     L.gmmB200NoAllocScratchBytes.restype = u64

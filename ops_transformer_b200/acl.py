@@ -97,12 +97,17 @@ def grouped_matmul_v4(x: torch.Tensor, weight: torch.Tensor, scale: Optional[tor
                       bias: Optional[torch.Tensor] = None, split_item: int = 3, group_type: int = 0,
                       group_list_type: int = 0, act_type: int = 0, out: Optional[torch.Tensor] = None,
                       out_dtype: torch.dtype = torch.bfloat16, stream=None, workspace: Optional[torch.Tensor] = None,
-                      return_workspace: bool = False):
+                      return_workspace: bool = False, out_row_index: Optional[torch.Tensor] = None):
     """y = bf16((x @ weight[e]) * scale[e] * per_token_scale) per expert row range (W8A8), or the raw int32
-    accumulators when ``out_dtype`` is torch.int32.  Rows not covered by ``group_list`` keep their contents."""
+    accumulators when ``out_dtype`` is torch.int32.  Rows not covered by ``group_list`` keep their contents.
+    ``out_row_index`` (int64 [M], an extension of this library) scatters result row r to row out_row_index[r]; it
+    goes through the flat entry point gmmB200GroupedMatmulW8A8."""
     L = _lib.lib()
     if out is None:
         out = torch.empty((x.shape[0], weight.shape[2]), dtype=out_dtype, device=x.device)
+    if out_row_index is not None:
+        return _grouped_matmul_flat(x, weight, scale, per_token_scale, group_list, bias, group_list_type, act_type, out,
+                                    out_row_index, stream, workspace, return_workspace)
     lists = []
     try:
         hx = create_tensor_list([x]); lists.append(hx)
@@ -140,6 +145,34 @@ def grouped_matmul_v4(x: torch.Tensor, weight: torch.Tensor, scale: Optional[tor
     finally:
         for h in lists:
             L.aclDestroyTensorList(h)
+    return (out, workspace) if return_workspace else out
+
+
+def _grouped_matmul_flat(x, weight, scale, per_token_scale, group_list, bias, group_list_type, act_type, out, out_row_index,
+                         stream, workspace, return_workspace):
+    L = _lib.lib()
+    M, K = x.shape
+    E, _, N = weight.shape
+    trans = (not weight.is_contiguous()) and weight.transpose(1, 2).is_contiguous()
+    for t in (x, scale, per_token_scale, group_list, bias, out, out_row_index):
+        if t is not None and not t.is_contiguous():
+            raise ValueError("the flat entry point needs contiguous tensors")
+    if out_row_index.dtype != torch.int64 or out_row_index.numel() != M:
+        raise ValueError("out_row_index must be int64 [M]")
+    ydt = _DTYPES[out.dtype]
+    size = C.c_uint64(0)
+    rc = L.gmmB200GroupedMatmulW8A8WorkspaceSize(M, K, N, E, ydt, C.byref(size))
+    if rc != ACLNN_SUCCESS:
+        raise AclnnError(rc, "gmmB200GroupedMatmulW8A8WorkspaceSize")
+    if workspace is None:
+        workspace = _WS.get(x.device, size.value)
+    p = lambda t: C.c_void_p(t.data_ptr()) if t is not None else None  # noqa: E731
+    rc = L.gmmB200GroupedMatmulW8A8(p(x), p(weight), p(scale), _DTYPES[scale.dtype] if scale is not None else 0, p(per_token_scale),
+                                    p(bias), _DTYPES[bias.dtype] if bias is not None else 0, p(group_list), group_list.numel(),
+                                    group_list_type, M, K, N, E, int(trans), act_type, p(out_row_index), p(out), ydt, p(workspace),
+                                    workspace.numel(), C.c_void_p(_stream_handle(stream)))
+    if rc != ACLNN_SUCCESS:
+        raise AclnnError(rc, "gmmB200GroupedMatmulW8A8")
     return (out, workspace) if return_workspace else out
 
 

@@ -39,6 +39,7 @@ struct Problem {
     int mode = kModeDequantBf16;
     void *out0 = nullptr;               // y (bf16 / int32) or q (int8 [M, N/2])
     void *out1 = nullptr;               // q_scale f32 [M] (swiglu only)
+    const int64_t *out_row_index = nullptr;  // optional [M]: result row r goes to row out_row_index[r] (grouped_matmul only)
 };
 
 struct Plan {
@@ -65,7 +66,6 @@ cudaError_t sm100_launch(const Problem &p, Plan &plan, void *workspace, cudaStre
 void set_timing_events(cudaEvent_t start, cudaEvent_t stop);
 // gmm_simt.cu
 cudaError_t simt_launch(const Problem &p, Plan &plan, void *workspace, cudaStream_t stream);
-cudaError_t quant_rows_launch(const Problem &p, const float *stage, const unsigned *amax_bits, cudaStream_t stream);
 
 int device_sm_count();
 

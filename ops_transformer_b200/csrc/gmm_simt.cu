@@ -1,7 +1,5 @@
 // CUDA-core kernels of the grouped int8 GEMM path:
-//   * quant_rows_kernel  - second pass of grouped_matmul_swiglu_quant on the tensor-core path: per-row
-//                          scale from the row maximum, then fp32 -> fp16 -> int8.
-//   * gmm_simt_*_kernel  - complete operators for shapes the TMA path cannot take (K or N not a multiple of
+//   * gmm_simt_kernel, swiglu_simt_kernel - complete operators for shapes the TMA path cannot take (K or N not a multiple of
 //                          16 bytes, unaligned pointers).  The reference accepts such shapes (its own unit
 //                          tests use K=5, N=10), so they run here on the GPU instead of being rejected.
 // plus the plan / launch glue shared by both paths.
@@ -16,8 +14,6 @@
 
 namespace gmm {
 namespace {
-
-constexpr unsigned kTouched = 0x80000000u;  // marks a row of the staging buffer as written
 
 __device__ __forceinline__ float load_scale1(const void *p, int dtype, size_t i)
 {
@@ -34,33 +30,6 @@ __device__ __forceinline__ int quant1(float s, float rcp)
     const __half h = __float2half_rn(__fmul_rn(s, rcp));
     int q = __half2int_rn(h);
     return max(-128, min(127, q));
-}
-
-// One warp per row.  amax_bits[row] = float bits of max|S| with the top bit set once any tile wrote the row.
-__global__ void __launch_bounds__(256) quant_rows_kernel(const float *__restrict__ stage, const unsigned *__restrict__ amax_bits,
-                                                          int8_t *__restrict__ q, float *__restrict__ q_scale, int M, int H)
-{
-    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    const int lane = threadIdx.x & 31;
-    if (row >= M) return;
-    const unsigned bits = amax_bits[row];
-    if (!(bits & kTouched)) return;  // row not covered by group_list: outputs stay untouched
-    const float amax = __uint_as_float(bits & ~kTouched);
-    const float qs = __fdiv_rn(amax, 127.0f);
-    const float rcp = __fdiv_rn(1.0f, qs);
-    if (lane == 0) q_scale[row] = qs;
-    const float4 *src = reinterpret_cast<const float4 *>(stage + (size_t)row * H);
-    uint4 *dst = reinterpret_cast<uint4 *>(q + (size_t)row * H);
-    for (int c = lane; c < H / 16; c += 32) {
-        uint32_t w[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float4 v = src[c * 4 + i];
-            w[i] = (uint32_t)(quant1(v.x, rcp) & 0xff) | ((uint32_t)(quant1(v.y, rcp) & 0xff) << 8) |
-                   ((uint32_t)(quant1(v.z, rcp) & 0xff) << 16) | ((uint32_t)(quant1(v.w, rcp) & 0xff) << 24);
-        }
-        dst[c] = make_uint4(w[0], w[1], w[2], w[3]);
-    }
 }
 
 // Locate the group of row m.  Same row-range rules as the tensor-core scheduler (group_list semantics of
@@ -96,6 +65,7 @@ struct SimtParams {
     int act_type, mode;
     void *out0;
     float *out1;
+    const long long *out_row_index;
 };
 
 // One CTA per row; threads stride over the output columns.
@@ -110,19 +80,20 @@ __global__ void __launch_bounds__(256) gmm_simt_kernel(const SimtParams p)
     const int8_t *xr = p.x + (size_t)m * p.K;
     const int8_t *wg = p.w + (size_t)g * p.K * p.N;
     const float xs = p.x_scale ? p.x_scale[m] : 1.0f;
+    const size_t orow = p.out_row_index ? (size_t)p.out_row_index[m] : (size_t)m;
     for (int n = threadIdx.x; n < p.N; n += blockDim.x) {
         int acc = 0;
         for (int k = 0; k < p.K; ++k) acc += (int)xr[k] * (int)wg[k * p.wsk + n * p.wsn];
         if (p.bias_dtype == kI32) acc += reinterpret_cast<const int *>(p.bias)[(size_t)g * p.N + n];
         if (p.mode == kModeInt32) {
-            reinterpret_cast<int *>(p.out0)[(size_t)m * p.N + n] = acc;
+            reinterpret_cast<int *>(p.out0)[orow * p.N + n] = acc;
             continue;
         }
         float t = __fmul_rn(__int2float_rn(acc), load_scale1(p.w_scale, p.w_scale_dtype, (size_t)g * p.N + n));
         if (p.x_scale) t = __fmul_rn(t, xs);
         if (p.bias_dtype == kBF16) t = __fadd_rn(t, load_scale1(p.bias, kBF16, (size_t)g * p.N + n));
         if (p.act_type == 1) t = t > 0.0f ? t : 0.0f;
-        reinterpret_cast<__nv_bfloat16 *>(p.out0)[(size_t)m * p.N + n] = __float2bfloat16_rn(t);
+        reinterpret_cast<__nv_bfloat16 *>(p.out0)[orow * p.N + n] = __float2bfloat16_rn(t);
     }
 }
 
@@ -193,6 +164,8 @@ void make_plan(const Problem &p, Plan *plan)
     plan->off_amax = off;
     if (p.mode == kModeSwigluQuant && plan->path == kPathSm100) {
         off += align_up((size_t)p.M * 4, 256);
+        plan->off_done = off;  // one counter per 128-row block; every group can add one partial block
+        off += align_up(((size_t)(p.M + 127) / 128 + (size_t)p.gl_len + 1) * 4, 256);
         plan->zero_bytes = off;
         plan->off_stage = off;
         off += align_up((size_t)p.M * (size_t)(p.N / 2) * 4, 256);
@@ -202,15 +175,6 @@ void make_plan(const Problem &p, Plan *plan)
     }
     plan->ws_bytes = off;
     plan->maps_ready = false;
-}
-
-cudaError_t quant_rows_launch(const Problem &p, const float *stage, const unsigned *amax_bits, cudaStream_t stream)
-{
-    const int warps = 8;
-    const int grid = (int)((p.M + warps - 1) / warps);
-    quant_rows_kernel<<<grid, warps * 32, 0, stream>>>(stage, amax_bits, reinterpret_cast<int8_t *>(p.out0),
-                                                       reinterpret_cast<float *>(p.out1), (int)p.M, (int)(p.N / 2));
-    return cudaGetLastError();
 }
 
 cudaError_t simt_launch(const Problem &p, Plan &, void *, cudaStream_t stream)
@@ -223,6 +187,7 @@ cudaError_t simt_launch(const Problem &p, Plan &, void *, cudaStream_t stream)
     sp.wsk = p.w_trans ? 1 : p.N;
     sp.wsn = p.w_trans ? p.K : 1;
     sp.act_type = p.act_type; sp.mode = p.mode; sp.out0 = p.out0; sp.out1 = reinterpret_cast<float *>(p.out1);
+    sp.out_row_index = reinterpret_cast<const long long *>(p.out_row_index);
     if (p.M <= 0) return cudaSuccess;
     if (p.mode == kModeSwigluQuant) {
         const size_t smem = (size_t)(p.N / 2) * sizeof(float);

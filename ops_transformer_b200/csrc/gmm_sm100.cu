@@ -13,10 +13,17 @@
 //   swiglu_quant         : columns [0,128) come from weight columns n0.. (activated half), columns [128,256)
 //                          from N/2+n0.. (linear half), so SwiGLU is tile-local and a tile yields 128 outputs.
 // Warp roles (320 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2-9 = epilogue.
+// Epilogue: the tile's per-column scales are staged in shared memory while the MMAs run; bf16 results are
+// transposed through shared memory so that stores cover whole 64-byte row segments (optionally scattered by a row
+// index); SwiGLU values go to an fp32 staging buffer with a per-row atomic max, and once all N tiles of a
+// 128-row block have done so (a counter per block) every CTA that worked on the block requantises its share of
+// the block's rows to int8, one tile later, while the data is still in L2.
 // Every wait on an mbarrier is bounded; on expiry the CTA records a status word, all roles leave their loops,
 // outstanding copies are drained with a second bounded wait, TMEM is released and the kernel returns.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+
+#include <cstddef>
 
 #include "gmm_common.h"
 
@@ -39,11 +46,17 @@ constexpr int TMEM_COLS = 512;
 constexpr long long WAIT_LIMIT_CYCLES = 1ll << 31;   // about a second
 constexpr long long DRAIN_LIMIT_CYCLES = 1ll << 24;  // a few milliseconds
 
+constexpr int EPI_THREADS = 32 * EPI_WARPS;
+constexpr int SCALE_BUFS = 3;          // an epilogue thread can run at most two tiles ahead of another one
+constexpr int OUT_STAGE_BYTES = 2048;  // per epilogue warp: 32 rows x 64 bytes of packed bf16
+
 struct Shared {
     uint64_t full[STAGES];
     uint64_t empty[STAGES];
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
+    uint64_t scale_ready[SCALE_BUFS];  // all epilogue threads have stored their column's scale
+    uint64_t tile_sync[2];             // [0] every epilogue thread fenced its stores, [1] an earlier row block is complete
     uint32_t tmem_base;
     int abort_flag;
     int total_tiles;
@@ -51,9 +64,13 @@ struct Shared {
     int row_start[MAX_GROUPS];
     int rows[MAX_GROUPS];
     int tile_start[MAX_GROUPS + 1];
+    alignas(16) float scales[SCALE_BUFS][BN];  // dequant scale of every accumulator column of the tile (read as float4)
+    alignas(16) uint8_t out_stage[EPI_WARPS][OUT_STAGE_BYTES];
 };
 
 constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + sizeof(Shared);
+static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
+static_assert(offsetof(Shared, scales) % 16 == 0 && offsetof(Shared, out_stage) % 16 == 0, "vector accesses need 16-byte alignment");
 
 struct KParams {
     const int64_t *group_list;
@@ -69,7 +86,11 @@ struct KParams {
     int bias_dtype;
     int act_type;
     void *out;            // y (bf16 / int32) or the fp32 SwiGLU staging [M, N/2]
-    unsigned *amax_bits;  // [M] row max of |S| as float bits, top bit set once written (swiglu)
+    const long long *out_row_index;  // optional: result row r is written to row out_row_index[r] (bf16 / int32 modes)
+    unsigned *amax_bits;  // [M] row max of |S| as float bits (swiglu)
+    int *rb_counter;      // per 128-row block: number of N tiles that have stored their part (swiglu)
+    int8_t *q_out;        // int8 [M, N/2] (swiglu)
+    float *q_scale_out;   // fp32 [M] (swiglu)
     int *status;
 };
 
@@ -318,40 +339,119 @@ __device__ __forceinline__ Tile decode_tile(const Shared *sh, int t, int n_tiles
 // Epilogue helpers
 // ---------------------------------------------------------------------------------------------------------
 
-__device__ __forceinline__ void load_scales8(const void *p, int dtype, size_t i, float (&s)[8])
+__device__ __forceinline__ float load_scale1(const void *p, int dtype, size_t i)
 {
-    if (dtype == kF32) {
-        const float4 a = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p) + i));
-        const float4 b = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p) + i) + 1);
-        s[0] = a.x; s[1] = a.y; s[2] = a.z; s[3] = a.w; s[4] = b.x; s[5] = b.y; s[6] = b.z; s[7] = b.w;
-    } else {
-        const uint4 r = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(p) + i));
-        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            if (dtype == kBF16) {
-                s[2 * j] = __uint_as_float(w[j] << 16);
-                s[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
-            } else {
-                const __half2 h = *reinterpret_cast<const __half2 *>(&w[j]);
-                s[2 * j] = __low2float(h);
-                s[2 * j + 1] = __high2float(h);
-            }
-        }
-    }
+    if (dtype == kF32) return __ldg(reinterpret_cast<const float *>(p) + i);
+    const uint16_t h = __ldg(reinterpret_cast<const uint16_t *>(p) + i);
+    if (dtype == kBF16) return __uint_as_float((uint32_t)h << 16);
+    return __half2float(__ushort_as_half(h));
 }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi)
 {
-    const __nv_bfloat16 a = __float2bfloat16_rn(lo), b = __float2bfloat16_rn(hi);
-    return (uint32_t)__bfloat16_as_ushort(a) | ((uint32_t)__bfloat16_as_ushort(b) << 16);
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);  // one cvt.rn.bf16x2.f32, round to nearest even
+    return *reinterpret_cast<const uint32_t *>(&v);
+}
+
+__device__ __forceinline__ int ld_acquire_gpu(const int *p)
+{
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// q = int8(rint(half(S * (1 / (amax / 127)))))  -- CastFp32ToInt8Template,
+// gmm/grouped_matmul_swiglu_quant/op_kernel/grouped_matmul_swiglu_quant_utils.h:308-316; NaN -> 0, saturating.
+__device__ __forceinline__ uint32_t quant1(float s, float rcp)
+{
+    const __half h = __float2half_rn(__fmul_rn(s, rcp));
+    const int q = max(-128, min(127, __half2int_rn(h)));
+    return (uint32_t)q & 0xffu;
+}
+__device__ __forceinline__ uint32_t quant4(float4 v, float rcp)
+{
+    return quant1(v.x, rcp) | (quant1(v.y, rcp) << 8) | (quant1(v.z, rcp) << 16) | (quant1(v.w, rcp) << 24);
+}
+
+// Second half of grouped_matmul_swiglu_quant for rows [r_begin, r_end) of a finished row block (all of its N tiles
+// have stored S and the row maxima): per row  qs = amax / 127, r = 1 / qs, q = int8(half(S * r))
+// (gmm/grouped_matmul_swiglu_quant/op_kernel/grouped_matmul_swiglu_quant.h:496-503).  S and amax were written by
+// other SMs, so they are read through L2 (ld.global.cg).  One warp per row, 16 outputs per lane and step.
+__device__ void requant_rows(const KParams &p, int r_begin, int r_end, int te)
+{
+    const int warp_e = te >> 5, lane = te & 31;
+    const int H = p.half_n;
+    const int pieces = H >> 4;
+    const float *stage = reinterpret_cast<const float *>(p.out);
+    for (int grow = r_begin + warp_e; grow < r_end; grow += EPI_WARPS) {
+        const float amax = __uint_as_float(__ldcg(p.amax_bits + grow));
+        const float qs = __fdiv_rn(amax, 127.0f);
+        const float rcp = __fdiv_rn(1.0f, qs);
+        if (lane == 0) p.q_scale_out[grow] = qs;
+        const float4 *src = reinterpret_cast<const float4 *>(stage + (size_t)grow * H);
+        uint4 *dst = reinterpret_cast<uint4 *>(p.q_out + (size_t)grow * H);
+        int c = lane;
+        for (; c + 32 < pieces; c += 64) {  // two pieces (eight 16-byte loads) per lane in flight
+            const float4 a0 = __ldcg(src + c * 4 + 0), a1 = __ldcg(src + c * 4 + 1), a2 = __ldcg(src + c * 4 + 2), a3 = __ldcg(src + c * 4 + 3);
+            const float4 b0 = __ldcg(src + (c + 32) * 4 + 0), b1 = __ldcg(src + (c + 32) * 4 + 1), b2 = __ldcg(src + (c + 32) * 4 + 2),
+                         b3 = __ldcg(src + (c + 32) * 4 + 3);
+            dst[c] = make_uint4(quant4(a0, rcp), quant4(a1, rcp), quant4(a2, rcp), quant4(a3, rcp));
+            dst[c + 32] = make_uint4(quant4(b0, rcp), quant4(b1, rcp), quant4(b2, rcp), quant4(b3, rcp));
+        }
+        for (; c < pieces; c += 32) {
+            const float4 a0 = __ldcg(src + c * 4 + 0), a1 = __ldcg(src + c * 4 + 1), a2 = __ldcg(src + c * 4 + 2), a3 = __ldcg(src + c * 4 + 3);
+            dst[c] = make_uint4(quant4(a0, rcp), quant4(a1, rcp), quant4(a2, rcp), quant4(a3, rcp));
+        }
+    }
+}
+
+// A tile whose SwiGLU part is stored and whose share of the requantisation is still owed.
+struct Pending {
+    int valid, rb, r_begin, r_end;
+};
+
+// Wait (bounded) until every N tile of the row block has stored its part, then requantise this CTA's share of rows.
+// Thread 0 of the epilogue polls the block's counter; the others wait on tile_sync[1].  Returns false on abort.
+__device__ bool settle_pending(const KParams &p, Shared *sh, Pending &pd, uint32_t &settle_it, int te)
+{
+    if (!pd.valid) return true;
+    pd.valid = 0;
+    if (te == 0) {
+        bool ok = true;
+        if (ld_acquire_gpu(p.rb_counter + pd.rb) < p.n_tiles) {
+            const long long t0 = clock64();
+            while (ld_acquire_gpu(p.rb_counter + pd.rb) < p.n_tiles) {
+                if (*(volatile int *)&sh->abort_flag) { ok = false; break; }
+                if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                    *(volatile int *)&sh->abort_flag = 1;
+                    if (atomicCAS(p.status, kStatusOk, kStatusWaitTimeout) == kStatusOk) {
+                        p.status[1] = (int)blockIdx.x;
+                        p.status[2] = 700;
+                        p.status[3] = pd.rb;
+                    }
+                    ok = false;
+                    break;
+                }
+            }
+        }
+        if (ok) {
+            __threadfence();
+            mbar_arrive(&sh->tile_sync[1]);
+        }
+    }
+    if (!mbar_wait(&sh->tile_sync[1], settle_it & 1u, sh, p.status, 601)) return false;
+    ++settle_it;
+    requant_rows(p, pd.r_begin, pd.r_end, te);
+    return true;
 }
 
 // ---------------------------------------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------------------------------------
 
-template <int MODE, bool B_MN_MAJOR>
+// PLAIN: no bias, no activation, per-token scale present, no row scatter - the common case, compiled without
+// the per-element tests for those options.
+template <int MODE, bool B_MN_MAJOR, bool PLAIN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const KParams p)
 {
@@ -370,8 +470,11 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&sh->acc_full[b], 1);
-            mbar_init(&sh->acc_empty[b], 32 * EPI_WARPS);
+            mbar_init(&sh->acc_empty[b], EPI_THREADS);
         }
+        for (int b = 0; b < SCALE_BUFS; ++b) mbar_init(&sh->scale_ready[b], EPI_THREADS);
+        mbar_init(&sh->tile_sync[0], EPI_THREADS);
+        mbar_init(&sh->tile_sync[1], 1);
         sh->abort_flag = 0;
         sh->total_tiles = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -468,61 +571,82 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         // ------------------------------ epilogue: warp -> (TMEM lane quarter, column half) ------------------------------
         const int quarter = warp & 3;
         const int chalf = (warp - 2) >> 2;
-        const int r = quarter * 32 + lane;  // row inside the tile == TMEM lane
-        int buf = 0;
-        uint32_t acc_phase = 0;
-        for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+        const int te = (int)threadIdx.x - 64;  // 0 .. EPI_THREADS-1
+        const int r = quarter * 32 + lane;     // row inside the tile == TMEM lane
+        uint8_t *my_stage = sh->out_stage[warp - 2];
+        int buf = 0, it = 0;
+        uint32_t acc_phase = 0, settle_it = 0;
+        Pending pend = {0, 0, 0, 0};
+        bool ok = true;
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
             const Tile tl = decode_tile(sh, t, p.n_tiles, L);
             const bool valid = r < tl.rows;
             const bool warp_has_rows = quarter * 32 < tl.rows;
             const int grow = tl.row0 + r;
+            const size_t sbase = (size_t)tl.g * p.N;
+            const int n0 = MODE == kModeSwigluQuant ? tl.n_idx * (BN / 2) : tl.n_idx * BN;
+
+            // Stage this tile's per-column scales in shared memory; the loads overlap the wait for the MMAs.
+            const int sb = it % SCALE_BUFS;
+            if (MODE != kModeInt32) {
+                int col;
+                bool in_range;
+                if (MODE == kModeSwigluQuant) {
+                    const int j = te < BN / 2 ? te : te - BN / 2;
+                    in_range = n0 + j < p.half_n;
+                    col = (te < BN / 2 ? 0 : p.half_n) + n0 + j;
+                } else {
+                    col = n0 + te;
+                    in_range = col < p.N;
+                }
+                sh->scales[sb][te] = in_range ? load_scale1(p.w_scale, p.w_scale_dtype, sbase + col) : 0.0f;
+                mbar_arrive(&sh->scale_ready[sb]);
+            }
             const float xs = (valid && p.x_scale) ? __ldg(p.x_scale + grow) : 1.0f;
+            long long out_row = grow;
+            if (MODE != kModeSwigluQuant && !PLAIN && p.out_row_index && valid) out_row = __ldg(p.out_row_index + grow);
+            if (MODE != kModeInt32 && !mbar_wait(&sh->scale_ready[sb], (uint32_t)(it / SCALE_BUFS) & 1u, sh, p.status, 500 + sb)) break;
             if (!mbar_wait(&sh->acc_full[buf], acc_phase, sh, p.status, 400 + buf)) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * BN;
+            const float *tsc = sh->scales[sb];
 
             if (warp_has_rows) {
                 if (MODE == kModeSwigluQuant) {
-                    const int n0 = tl.n_idx * (BN / 2);
                     float amax = 0.0f;
                     float *srow = reinterpret_cast<float *>(p.out) + (size_t)grow * p.half_n;
-                    const size_t sbase = (size_t)tl.g * p.N;
 #pragma unroll 1
                     for (int c = chalf * 2; c < chalf * 2 + 2; ++c) {
+                        if (n0 + c * 32 >= p.half_n) break;
                         uint32_t va[32], vb[32];
                         tmem_ld32(taddr + c * 32, va);
                         tmem_ld32(taddr + BN / 2 + c * 32, vb);
                         tmem_ld_wait();
 #pragma unroll
-                        for (int j8 = 0; j8 < 4; ++j8) {
-                            const int col = n0 + c * 32 + j8 * 8;
+                        for (int j4 = 0; j4 < 8; ++j4) {
+                            const int col = n0 + c * 32 + j4 * 4;
                             if (col < p.half_n) {
-                                float sa[8], sb[8], o[8];
-                                load_scales8(p.w_scale, p.w_scale_dtype, sbase + col, sa);
-                                load_scales8(p.w_scale, p.w_scale_dtype, sbase + p.half_n + col, sb);
+                                const float4 sa = *reinterpret_cast<const float4 *>(tsc + c * 32 + j4 * 4);
+                                const float4 sg = *reinterpret_cast<const float4 *>(tsc + BN / 2 + c * 32 + j4 * 4);
+                                const float sav[4] = {sa.x, sa.y, sa.z, sa.w}, sgv[4] = {sg.x, sg.y, sg.z, sg.w};
+                                float o[4];
 #pragma unroll
-                                for (int j = 0; j < 8; ++j) {
+                                for (int j = 0; j < 4; ++j) {
                                     // (acc * x_scale) * w_scale, then S = gate * (act / (1 + exp(-act)))
-                                    float a = __fmul_rn(__fmul_rn(__int2float_rn((int)va[j8 * 8 + j]), xs), sa[j]);
-                                    float b = __fmul_rn(__fmul_rn(__int2float_rn((int)vb[j8 * 8 + j]), xs), sb[j]);
+                                    const float a = __fmul_rn(__fmul_rn(__int2float_rn((int)va[j4 * 4 + j]), xs), sav[j]);
+                                    const float b = __fmul_rn(__fmul_rn(__int2float_rn((int)vb[j4 * 4 + j]), xs), sgv[j]);
                                     const float den = __fadd_rn(1.0f, expf(-a));
                                     const float sw = __fdiv_rn(a, den);
-                                    const float s = __fmul_rn(b, sw);
-                                    o[j] = s;
-                                    amax = fmaxf(amax, fabsf(s));
+                                    const float sv = __fmul_rn(b, sw);
+                                    o[j] = sv;
+                                    amax = fmaxf(amax, fabsf(sv));
                                 }
-                                if (valid) {
-                                    float4 *dst = reinterpret_cast<float4 *>(srow + col);
-                                    dst[0] = make_float4(o[0], o[1], o[2], o[3]);
-                                    dst[1] = make_float4(o[4], o[5], o[6], o[7]);
-                                }
+                                if (valid) *reinterpret_cast<float4 *>(srow + col) = make_float4(o[0], o[1], o[2], o[3]);
                             }
                         }
                     }
-                    if (valid) atomicMax(p.amax_bits + grow, __float_as_uint(amax) | 0x80000000u);  // top bit: row written
-                } else {
-                    const int n0 = tl.n_idx * BN;
-                    const size_t sbase = (size_t)tl.g * p.N;
+                    if (valid) atomicMax(p.amax_bits + grow, __float_as_uint(amax));
+                } else if (MODE == kModeInt32) {
 #pragma unroll 1
                     for (int c = chalf * 4; c < chalf * 4 + 4; ++c) {
                         if (n0 + c * 32 >= p.N) break;
@@ -530,49 +654,72 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                         tmem_ld32(taddr + c * 32, v);
                         tmem_ld_wait();
 #pragma unroll
-                        for (int j8 = 0; j8 < 4; ++j8) {
-                            const int col = n0 + c * 32 + j8 * 8;
-                            if (col < p.N) {
-                                int acc[8];
+                        for (int j4 = 0; j4 < 8; ++j4) {
+                            const int col = n0 + c * 32 + j4 * 4;
+                            if (col < p.N && valid) {
+                                int acc[4];
 #pragma unroll
-                                for (int j = 0; j < 8; ++j) acc[j] = (int)v[j8 * 8 + j];
-                                if (p.bias_dtype == kI32) {
-                                    const int4 b0 = __ldg(reinterpret_cast<const int4 *>(reinterpret_cast<const int *>(p.bias) + sbase + col));
-                                    const int4 b1 = __ldg(reinterpret_cast<const int4 *>(reinterpret_cast<const int *>(p.bias) + sbase + col) + 1);
-                                    acc[0] += b0.x; acc[1] += b0.y; acc[2] += b0.z; acc[3] += b0.w;
-                                    acc[4] += b1.x; acc[5] += b1.y; acc[6] += b1.z; acc[7] += b1.w;
+                                for (int j = 0; j < 4; ++j) {
+                                    acc[j] = (int)v[j4 * 4 + j];
+                                    if (!PLAIN && p.bias_dtype == kI32) acc[j] += __ldg(reinterpret_cast<const int *>(p.bias) + sbase + col + j);
                                 }
-                                if (MODE == kModeInt32) {
-                                    if (valid) {
-                                        int4 *dst = reinterpret_cast<int4 *>(reinterpret_cast<int *>(p.out) + (size_t)grow * p.N + col);
-                                        dst[0] = make_int4(acc[0], acc[1], acc[2], acc[3]);
-                                        dst[1] = make_int4(acc[4], acc[5], acc[6], acc[7]);
-                                    }
-                                } else {
-                                    float sc[8], o[8];
-                                    load_scales8(p.w_scale, p.w_scale_dtype, sbase + col, sc);
-                                    float bf[8];
-                                    if (p.bias_dtype == kBF16) load_scales8(p.bias, kBF16, sbase + col, bf);
-#pragma unroll
-                                    for (int j = 0; j < 8; ++j) {
-                                        // (acc * w_scale) * x_scale, optional bf16 bias, optional relu, bf16 RNE
-                                        float tv = __fmul_rn(__int2float_rn(acc[j]), sc[j]);
-                                        if (p.x_scale) tv = __fmul_rn(tv, xs);
-                                        if (p.bias_dtype == kBF16) tv = __fadd_rn(tv, bf[j]);
-                                        if (p.act_type == 1) tv = tv > 0.0f ? tv : 0.0f;
-                                        o[j] = tv;
-                                    }
-                                    if (valid) {
-                                        uint4 pk;
-                                        pk.x = pack_bf16x2(o[0], o[1]);
-                                        pk.y = pack_bf16x2(o[2], o[3]);
-                                        pk.z = pack_bf16x2(o[4], o[5]);
-                                        pk.w = pack_bf16x2(o[6], o[7]);
-                                        *reinterpret_cast<uint4 *>(reinterpret_cast<uint16_t *>(p.out) + (size_t)grow * p.N + col) = pk;
-                                    }
-                                }
+                                *reinterpret_cast<int4 *>(reinterpret_cast<int *>(p.out) + (size_t)out_row * p.N + col) =
+                                    make_int4(acc[0], acc[1], acc[2], acc[3]);
                             }
                         }
+                    }
+                } else {
+                    uint16_t *out = reinterpret_cast<uint16_t *>(p.out);
+#pragma unroll 1
+                    for (int c = chalf * 4; c < chalf * 4 + 4; ++c) {
+                        if (n0 + c * 32 >= p.N) break;
+                        uint32_t v[32];
+                        tmem_ld32(taddr + c * 32, v);
+                        tmem_ld_wait();
+                        uint32_t pk[16];
+#pragma unroll
+                        for (int j4 = 0; j4 < 8; ++j4) {
+                            const float4 s4 = *reinterpret_cast<const float4 *>(tsc + c * 32 + j4 * 4);
+                            const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
+                            float o[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                // (acc * w_scale) * x_scale, optional bf16 bias, optional relu, then bf16 RNE
+                                const int cc = c * 32 + j4 * 4 + j;
+                                int acc = (int)v[j4 * 4 + j];
+                                if (PLAIN) {
+                                    o[j] = __fmul_rn(__fmul_rn(__int2float_rn(acc), sv[j]), xs);
+                                } else {
+                                    const bool in_n = n0 + cc < p.N;
+                                    if (p.bias_dtype == kI32 && in_n) acc += __ldg(reinterpret_cast<const int *>(p.bias) + sbase + n0 + cc);
+                                    float tv = __fmul_rn(__int2float_rn(acc), sv[j]);
+                                    if (p.x_scale) tv = __fmul_rn(tv, xs);
+                                    if (p.bias_dtype == kBF16 && in_n)
+                                        tv = __fadd_rn(tv, __uint_as_float((uint32_t)__ldg(reinterpret_cast<const uint16_t *>(p.bias) + sbase + n0 + cc) << 16));
+                                    if (p.act_type == 1) tv = tv > 0.0f ? tv : 0.0f;
+                                    o[j] = tv;
+                                }
+                            }
+                            pk[j4 * 2] = pack_bf16x2(o[0], o[1]);
+                            pk[j4 * 2 + 1] = pack_bf16x2(o[2], o[3]);
+                        }
+                        // Transpose through shared memory so that four lanes write 64 contiguous bytes of one row.
+#pragma unroll
+                        for (int pc = 0; pc < 4; ++pc)
+                            *reinterpret_cast<uint4 *>(my_stage + lane * 64 + (((pc ^ (lane >> 1)) & 3) << 4)) =
+                                make_uint4(pk[pc * 4], pk[pc * 4 + 1], pk[pc * 4 + 2], pk[pc * 4 + 3]);
+                        __syncwarp();
+                        const int pc = lane & 3;
+                        const int col = n0 + c * 32 + pc * 8;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int rr = i * 8 + (lane >> 2);
+                            const uint4 val = *reinterpret_cast<const uint4 *>(my_stage + rr * 64 + (((pc ^ (rr >> 1)) & 3) << 4));
+                            long long orow = tl.row0 + quarter * 32 + rr;
+                            if (!PLAIN) orow = __shfl_sync(0xffffffffu, out_row, rr);
+                            if (quarter * 32 + rr < tl.rows && col < p.N) *reinterpret_cast<uint4 *>(out + (size_t)orow * p.N + col) = val;
+                        }
+                        __syncwarp();
                     }
                 }
             }
@@ -580,7 +727,21 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             mbar_arrive(&sh->acc_empty[buf]);
             buf ^= 1;
             if (buf == 0) acc_phase ^= 1u;
+
+            if (MODE == kModeSwigluQuant) {
+                // Publish this tile's part of its row block, then settle what is owed for the previous tile.
+                __threadfence();
+                mbar_arrive(&sh->tile_sync[0]);
+                if (!mbar_wait(&sh->tile_sync[0], (uint32_t)it & 1u, sh, p.status, 600)) break;
+                if (te == 0) atomicAdd(p.rb_counter + t / p.n_tiles, 1);
+                ok = settle_pending(p, sh, pend, settle_it, te);
+                pend.valid = 1;
+                pend.rb = t / p.n_tiles;
+                pend.r_begin = tl.row0 + (int)((long long)tl.rows * tl.n_idx / p.n_tiles);
+                pend.r_end = tl.row0 + (int)((long long)tl.rows * (tl.n_idx + 1) / p.n_tiles);
+            }
         }
+        if (MODE == kModeSwigluQuant && ok && !*(volatile int *)&sh->abort_flag) settle_pending(p, sh, pend, settle_it, te);
     }
 
     __syncthreads();
@@ -612,10 +773,10 @@ EncodeTiledFn encode_fn()
     return fn;
 }
 
-template <int MODE, bool B_MN>
+template <int MODE, bool B_MN, bool PLAIN>
 cudaError_t launch_variant(const Plan &plan, const KParams &kp, cudaStream_t stream)
 {
-    auto kern = gmm_w8a8_sm100_kernel<MODE, B_MN>;
+    auto kern = gmm_w8a8_sm100_kernel<MODE, B_MN, PLAIN>;
     // Once per device and instantiation; the attribute is idempotent, so a race only repeats the call.
     static unsigned long long done_mask = 0;
     int dev = 0;
@@ -649,8 +810,9 @@ bool sm100_shape_ok(const Problem &p)
     if (p.M <= 0 || p.M > 0x7fffffffll / 2 || p.K > 0x7fffffffll || p.N > 0x7fffffffll) return false;
     if ((reinterpret_cast<uintptr_t>(p.x) & 15) || (reinterpret_cast<uintptr_t>(p.w) & 15)) return false;
     if (reinterpret_cast<uintptr_t>(p.out0) & 15) return false;
-    if (reinterpret_cast<uintptr_t>(p.w_scale) & 15) return false;
-    if (p.bias && (reinterpret_cast<uintptr_t>(p.bias) & 15)) return false;
+    if (reinterpret_cast<uintptr_t>(p.w_scale) & 3) return false;
+    if (p.bias && (reinterpret_cast<uintptr_t>(p.bias) & 3)) return false;
+    if (p.mode == kModeSwigluQuant && (!p.out1 || (reinterpret_cast<uintptr_t>(p.out1) & 3))) return false;
     return true;
 }
 
@@ -710,21 +872,26 @@ cudaError_t sm100_launch(const Problem &p, Plan &plan, void *workspace, cudaStre
     kp.act_type = p.act_type;
     kp.status = reinterpret_cast<int *>(ws + plan.off_status);
     kp.amax_bits = reinterpret_cast<unsigned *>(ws + plan.off_amax);
+    kp.rb_counter = reinterpret_cast<int *>(ws + plan.off_done);
+    kp.out_row_index = reinterpret_cast<const long long *>(p.out_row_index);
+    kp.q_out = reinterpret_cast<int8_t *>(p.out0);
+    kp.q_scale_out = reinterpret_cast<float *>(p.out1);
     kp.out = p.mode == kModeSwigluQuant ? static_cast<void *>(ws + plan.off_stage) : p.out0;
 
     cudaError_t e;
     const bool mn = !p.w_trans;
+    const bool plain = !p.bias && p.act_type == 0 && !p.out_row_index && (p.mode != kModeDequantBf16 || p.x_scale);
     if (g_ev_start) cudaEventRecord(g_ev_start, stream);
     if (p.mode == kModeSwigluQuant)
-        e = mn ? launch_variant<kModeSwigluQuant, true>(plan, kp, stream) : launch_variant<kModeSwigluQuant, false>(plan, kp, stream);
+        e = mn ? launch_variant<kModeSwigluQuant, true, true>(plan, kp, stream) : launch_variant<kModeSwigluQuant, false, true>(plan, kp, stream);
     else if (p.mode == kModeInt32)
-        e = mn ? launch_variant<kModeInt32, true>(plan, kp, stream) : launch_variant<kModeInt32, false>(plan, kp, stream);
+        e = mn ? (plain ? launch_variant<kModeInt32, true, true>(plan, kp, stream) : launch_variant<kModeInt32, true, false>(plan, kp, stream))
+               : (plain ? launch_variant<kModeInt32, false, true>(plan, kp, stream) : launch_variant<kModeInt32, false, false>(plan, kp, stream));
     else
-        e = mn ? launch_variant<kModeDequantBf16, true>(plan, kp, stream) : launch_variant<kModeDequantBf16, false>(plan, kp, stream);
+        e = mn ? (plain ? launch_variant<kModeDequantBf16, true, true>(plan, kp, stream) : launch_variant<kModeDequantBf16, true, false>(plan, kp, stream))
+               : (plain ? launch_variant<kModeDequantBf16, false, true>(plan, kp, stream)
+                        : launch_variant<kModeDequantBf16, false, false>(plan, kp, stream));
     if (g_ev_stop) cudaEventRecord(g_ev_stop, stream);
-    if (e != cudaSuccess) return e;
-    if (p.mode == kModeSwigluQuant)
-        e = quant_rows_launch(p, reinterpret_cast<const float *>(ws + plan.off_stage), kp.amax_bits, stream);
     return e;
 }
 

@@ -388,8 +388,8 @@ static uint64_t flat_ws(int64_t m, int64_t k, int64_t n, int64_t e, int mode)
 {
     Problem p;
     p.x = reinterpret_cast<const int8_t *>(uintptr_t(256));
-    p.w = p.x; p.w_scale = p.x; p.out0 = const_cast<int8_t *>(p.x);
-    p.M = m; p.K = k; p.N = n; p.E = e; p.gl_len = 1; p.mode = mode;
+    p.w = p.x; p.w_scale = p.x; p.out0 = const_cast<int8_t *>(p.x); p.out1 = p.out0;
+    p.M = m; p.K = k; p.N = n; p.E = e; p.gl_len = (int)(e < kMaxGroupListLen ? e : kMaxGroupListLen); p.mode = mode;
     Plan a;
     make_plan(p, &a);
     uint64_t best = a.ws_bytes;
@@ -412,8 +412,8 @@ aclnnStatus gmmB200GroupedMatmulW8A8WorkspaceSize(int64_t m, int64_t k, int64_t 
 aclnnStatus gmmB200GroupedMatmulW8A8(const void *x, const void *weight, const void *scale, int32_t scaleDtype,
                                      const void *perTokenScale, const void *bias, int32_t biasDtype, const void *groupList,
                                      int64_t groupListLen, int32_t groupListType, int64_t m, int64_t k, int64_t n, int64_t e,
-                                     int32_t weightTransposed, int32_t actType, void *y, int32_t yDtype, void *workspace,
-                                     uint64_t workspaceSize, aclrtStream stream)
+                                     int32_t weightTransposed, int32_t actType, const void *outRowIndex, void *y, int32_t yDtype,
+                                     void *workspace, uint64_t workspaceSize, aclrtStream stream)
 {
     clear_error();
     GMM_REQUIRE(x && weight && groupList && y, ACLNN_ERR_PARAM_NULLPTR, "x, weight, groupList and y must not be nullptr.");
@@ -443,6 +443,7 @@ aclnnStatus gmmB200GroupedMatmulW8A8(const void *x, const void *weight, const vo
     p.act_type = actType;
     p.mode = yDtype == ACL_INT32 ? kModeInt32 : kModeDequantBf16;
     p.out0 = y;
+    p.out_row_index = static_cast<const int64_t *>(outRowIndex);
     Plan plan;
     make_plan(p, &plan);
     GMM_REQUIRE(workspaceSize >= plan.ws_bytes, ACLNN_ERR_PARAM_INVALID, "workspaceSize %llu is smaller than the %llu bytes required.",

@@ -234,6 +234,30 @@ def test_gmm_max_group_count(oracle):
     check_gmm(oracle, x, w, ws, xs, np.cumsum(counts), 0)
 
 
+def test_gmm_row_scatter_extension(oracle):
+    # result row r lands in row perm[r]: the un-permute after the down projection folded into the epilogue
+    import ops_transformer_b200 as ops
+    dev = _dev()
+    counts = [150, 3, 200]
+    M = sum(counts)
+    x, w, ws, xs = make_inputs(M, 256, 528, 3, seed=16)
+    gl = np.cumsum(counts)
+    perm = np.random.default_rng(17).permutation(M).astype(np.int64)
+    ref = oracle.gmm_w8a8(x, w, ws, xs, gl, 0)["y"]
+    for dt, odt in ((torch.bfloat16, "bf16"), (torch.int32, "int32")):
+        y = ops.grouped_matmul_v4(torch.from_numpy(x).to(dev), torch.from_numpy(w).to(dev),
+                                  torch.from_numpy(ws).to(dev) if odt == "bf16" else None,
+                                  torch.from_numpy(xs).to(dev) if odt == "bf16" else None, torch.from_numpy(gl).to(dev),
+                                  out_dtype=dt, out_row_index=torch.from_numpy(perm).to(dev))
+        torch.cuda.synchronize()
+        if odt == "bf16":
+            got = _bf16_bits(y)
+            assert np.array_equal(got[perm], ref)
+        else:
+            refi = oracle.gmm_w8a8(x, w, ws, xs, gl, 0, y_dtype="int32")["y"]
+            assert np.array_equal(y.cpu().numpy()[perm], refi)
+
+
 # ----------------------------------------------------------------------------------------------------------
 # grouped_matmul_swiglu_quant
 # ----------------------------------------------------------------------------------------------------------
@@ -276,6 +300,23 @@ def test_swiglu_deepseek_width_few_rows(oracle):
     counts = [3, 0, 17, 1, 0, 40]
     x, w, ws, xs = make_inputs(sum(counts), 7168, 4096, 6, seed=25)
     check_swiglu(oracle, x, w, ws, xs, np.cumsum(counts))
+
+
+def test_swiglu_many_row_blocks_and_tiles(oracle):
+    # more tiles than SMs and several row blocks per expert: exercises the row-block completion counters
+    counts = [700, 0, 1300, 129, 512]
+    x, w, ws, xs = make_inputs(sum(counts) + 3, 256, 2048, 5, seed=27)
+    check_swiglu(oracle, x, w, ws, xs, np.cumsum(counts))
+
+
+def test_swiglu_repeated_calls_reuse_workspace(oracle):
+    # the same workspace is used by consecutive calls of different shapes; counters and maxima must be reset
+    x, w, ws, xs = make_inputs(400, 384, 1024, 3, seed=28)
+    check_swiglu(oracle, x, w, ws, xs, [100, 250, 400])
+    x, w, ws, xs = make_inputs(90, 128, 512, 2, seed=29)
+    check_swiglu(oracle, x, w, ws, xs, [40, 90])
+    x, w, ws, xs = make_inputs(400, 384, 1024, 3, seed=30)
+    check_swiglu(oracle, x, w, ws, xs, [10, 20, 390])
 
 
 def test_gmm_deepseek_down_width_few_rows(oracle):
