@@ -10,6 +10,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+
 #include "gmm_common.h"
 
 namespace gmm {
@@ -159,6 +161,13 @@ static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 void make_plan(const Problem &p, Plan *plan)
 {
     plan->path = sm100_shape_ok(p) ? kPathSm100 : kPathSimt;
+    // CTA pairs halve the weight traffic per SM but waste up to 255 rows at the end of every group, so they are
+    // used when groups are long on average.  GMM_B200_CTAS=1|2 overrides the choice (for measurements).
+    plan->ctas = (p.gl_len > 0 && p.M / p.gl_len >= 384) ? 2 : 1;
+    if (const char *e = getenv("GMM_B200_CTAS")) {
+        if (e[0] == '1') plan->ctas = 1;
+        if (e[0] == '2') plan->ctas = 2;
+    }
     plan->off_status = 0;
     size_t off = 256;
     plan->off_amax = off;

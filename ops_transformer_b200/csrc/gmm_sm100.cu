@@ -33,12 +33,25 @@ namespace {
 constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BK = 128;
-constexpr int STAGES = 4;
 constexpr int UMMA_K = 32;
-constexpr int A_STAGE = BM * BK;
-constexpr int B_STAGE = BN * BK;
-constexpr int B_HALF = B_STAGE / 2;
-constexpr int STAGE_BYTES = A_STAGE + B_STAGE;
+constexpr int A_STAGE = BM * BK;        // 128 rows x 128 bytes of K
+constexpr int B_BOX = 128 * BK;         // one weight box: 128 N-columns x 128 bytes of K
+constexpr int PIPE_BYTES = 196608;      // shared memory given to the TMA ring
+constexpr int MAX_STAGES = 6;
+
+// CTAS = 1: one CTA computes a 128 x 256 tile; it stages A (16 KB) and both weight boxes (32 KB) per K block, 4 stages.
+// CTAS = 2: a pair of CTAs (one cluster) computes a 256 x 256 tile with cta_group::2 MMAs; each CTA stages its own 128
+//           rows of A and ONE weight box (its half of the 256 columns), so a K block costs 32 KB per SM and the ring
+//           holds 6 stages.  The pair's even CTA issues the MMAs for both.
+template <int CTAS>
+struct Cfg {
+    static constexpr int kBoxes = 2 / CTAS;                 // weight boxes staged per CTA and K block
+    static constexpr int kStageBytes = A_STAGE + kBoxes * B_BOX;
+    static constexpr int kStages = PIPE_BYTES / kStageBytes;
+    static constexpr int kTileM = BM * CTAS;
+    static constexpr uint32_t kTxBytes = (uint32_t)kStageBytes * CTAS;  // bytes landing per stage, both CTAs together
+};
+static_assert(Cfg<1>::kStages == 4 && Cfg<2>::kStages == 6 && Cfg<2>::kStages <= MAX_STAGES, "stage arithmetic");
 constexpr int MAX_GROUPS = 1024;
 constexpr int EPI_WARPS = 8;                 // two warps per TMEM lane quarter, each takes half of the columns
 constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;
@@ -51,8 +64,8 @@ constexpr int SCALE_BUFS = 3;          // an epilogue thread can run at most two
 constexpr int OUT_STAGE_BYTES = 2048;  // per epilogue warp: 32 rows x 64 bytes of packed bf16
 
 struct Shared {
-    uint64_t full[STAGES];
-    uint64_t empty[STAGES];
+    uint64_t full[MAX_STAGES];
+    uint64_t empty[MAX_STAGES];
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
     uint64_t scale_ready[SCALE_BUFS];  // all epilogue threads have stored their column's scale
@@ -68,7 +81,7 @@ struct Shared {
     alignas(16) uint8_t out_stage[EPI_WARPS][OUT_STAGE_BYTES];
 };
 
-constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + sizeof(Shared);
+constexpr size_t SMEM_BYTES = 1024 + (size_t)PIPE_BYTES + sizeof(Shared);
 static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
 static_assert(offsetof(Shared, scales) % 16 == 0 && offsetof(Shared, out_stage) % 16 == 0, "vector accesses need 16-byte alignment");
 
@@ -170,6 +183,44 @@ __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, i
         ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
         : "memory");
 }
+// Pair (cta_group::2) forms: the copy lands in the executing CTA's shared memory, the byte count is credited to the
+// mbarrier at `bar_cluster_addr`, a shared::cluster address that may belong to the other CTA of the pair.
+__device__ __forceinline__ void tma_load_2d_pair(void *dst, const CUtensorMap *map, int c0, int c1, uint32_t bar_cluster_addr)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(c0), "r"(c1), "r"(bar_cluster_addr)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(void *dst, const CUtensorMap *map, int c0, int c1, int c2, uint32_t bar_cluster_addr)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(c0), "r"(c1), "r"(c2), "r"(bar_cluster_addr)
+        : "memory");
+}
+// shared::cluster address of `p` (a location in this CTA's shared memory) as seen in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(const void *p, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(p)), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_cta_rank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 __device__ __forceinline__ void prefetch_map(const CUtensorMap *map)
 {
     asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)map) : "memory");
@@ -178,15 +229,22 @@ __device__ __forceinline__ void prefetch_map(const CUtensorMap *map)
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+template <int CTAS>
 __device__ __forceinline__ void tmem_alloc(uint32_t *dst_smem, uint32_t cols)
 {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (CTAS == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    } else {  // issued by the same warp of both CTAs of the pair, with the same shared-memory offset
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
 }
+template <int CTAS>
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols)
 {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+    if (CTAS == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+    else asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
 }
 
 // D[tmem] (+)= A[smem] * B[smem], int8 x int8 -> int32, issued by one thread.
@@ -205,6 +263,24 @@ __device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64
 __device__ __forceinline__ void umma_commit(uint64_t *bar)
 {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Pair forms.  The MMA reads A and its half of B from both CTAs' shared memory (same offsets) and writes each CTA's
+// 128 accumulator rows to that CTA's TMEM.  The commit takes a shared::cluster address, so it can arrive on a
+// barrier of either CTA; it is issued once per CTA of the pair.
+__device__ __forceinline__ void umma_i8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr)
+{
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
 
 // 32 lanes x 32 consecutive columns of 32-bit values: thread i of the warp receives row (lane base + i).
@@ -239,10 +315,10 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
 
 // Instruction descriptor for kind::i8: D = S32 (2 at bit 4), A = B = signed 8-bit (1 at bits 7 and 10),
 // A K-major, B major per flag (bit 16), N >> 3 at bit 17, M >> 4 at bit 24.
-__host__ __device__ constexpr uint32_t make_idesc(bool b_mn_major)
+__host__ __device__ constexpr uint32_t make_idesc(bool b_mn_major, int m)
 {
     return (2u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) |
-           ((uint32_t)(BM >> 4) << 24);
+           ((uint32_t)(m >> 4) << 24);
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -252,7 +328,7 @@ __host__ __device__ constexpr uint32_t make_idesc(bool b_mn_major)
 // Row ranges follow GetSplitValueFromGroupList (gmm/grouped_matmul/op_kernel/grouped_matmul_utils.h:243-257):
 // type 0 = running total, type 1 = count, values narrowed to int32; groups with no rows are skipped
 // (grouped_matmul.h:263).  Ranges are clipped to [0, M] so a malformed list cannot address other memory.
-__device__ void build_schedule(Shared *sh, const KParams &p)
+__device__ void build_schedule(Shared *sh, const KParams &p, int tile_m)
 {
     const int tid = threadIdx.x, L = p.gl_len;
     for (int g = tid; g < L; g += NUM_THREADS) {
@@ -294,7 +370,7 @@ __device__ void build_schedule(Shared *sh, const KParams &p)
             if (start + rows > p.M) rows = p.M - start;
             sh->row_start[g] = (int)start;
             sh->rows[g] = (int)rows;
-            tsum += (int)((rows + BM - 1) / BM) * p.n_tiles;
+            tsum += (int)((rows + tile_m - 1) / tile_m) * p.n_tiles;
         }
         int incl = tsum;
         for (int o = 1; o < 32; o <<= 1) {
@@ -304,7 +380,7 @@ __device__ void build_schedule(Shared *sh, const KParams &p)
         int run = incl - tsum;
         for (int g = lo; g < hi; ++g) {
             sh->tile_start[g] = run;
-            run += ((sh->rows[g] + BM - 1) / BM) * p.n_tiles;
+            run += ((sh->rows[g] + tile_m - 1) / tile_m) * p.n_tiles;
         }
         if (lane == 31) {
             sh->tile_start[L] = incl;
@@ -318,7 +394,7 @@ struct Tile {
     int g, row0, rows, n_idx;
 };
 
-__device__ __forceinline__ Tile decode_tile(const Shared *sh, int t, int n_tiles, int L)
+__device__ __forceinline__ Tile decode_tile(const Shared *sh, int t, int n_tiles, int L, int tile_m)
 {
     int lo = 0, hi = L;  // largest g in [0, L) with tile_start[g] <= t
     while (hi - lo > 1) {
@@ -330,8 +406,8 @@ __device__ __forceinline__ Tile decode_tile(const Shared *sh, int t, int n_tiles
     Tile tl;
     tl.g = lo;
     tl.n_idx = local - mb * n_tiles;
-    tl.row0 = sh->row_start[lo] + mb * BM;
-    tl.rows = min(BM, sh->rows[lo] - mb * BM);
+    tl.row0 = sh->row_start[lo] + mb * tile_m;
+    tl.rows = min(tile_m, sh->rows[lo] - mb * tile_m);
     return tl;
 }
 
@@ -412,15 +488,15 @@ struct Pending {
 
 // Wait (bounded) until every N tile of the row block has stored its part, then requantise this CTA's share of rows.
 // Thread 0 of the epilogue polls the block's counter; the others wait on tile_sync[1].  Returns false on abort.
-__device__ bool settle_pending(const KParams &p, Shared *sh, Pending &pd, uint32_t &settle_it, int te)
+__device__ bool settle_pending(const KParams &p, Shared *sh, Pending &pd, uint32_t &settle_it, int te, int target)
 {
     if (!pd.valid) return true;
     pd.valid = 0;
     if (te == 0) {
         bool ok = true;
-        if (ld_acquire_gpu(p.rb_counter + pd.rb) < p.n_tiles) {
+        if (ld_acquire_gpu(p.rb_counter + pd.rb) < target) {
             const long long t0 = clock64();
-            while (ld_acquire_gpu(p.rb_counter + pd.rb) < p.n_tiles) {
+            while (ld_acquire_gpu(p.rb_counter + pd.rb) < target) {
                 if (*(volatile int *)&sh->abort_flag) { ok = false; break; }
                 if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
                     *(volatile int *)&sh->abort_flag = 1;
@@ -450,27 +526,32 @@ __device__ bool settle_pending(const KParams &p, Shared *sh, Pending &pd, uint32
 // ---------------------------------------------------------------------------------------------------------
 
 // PLAIN: no bias, no activation, per-token scale present, no row scatter - the common case, compiled without
-// the per-element tests for those options.
-template <int MODE, bool B_MN_MAJOR, bool PLAIN>
+// the per-element tests for those options.  CTAS: 1 = one CTA per tile, 2 = a cluster of two CTAs per 256-row tile.
+template <int MODE, bool B_MN_MAJOR, bool PLAIN, int CTAS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const KParams p)
 {
+    using C = Cfg<CTAS>;
+    constexpr int STAGES = C::kStages;
+    constexpr int STAGE_BYTES = C::kStageBytes;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint8_t *smem_a = smem;
-    uint8_t *smem_b = smem + STAGES * A_STAGE;
-    Shared *sh = reinterpret_cast<Shared *>(smem + STAGES * STAGE_BYTES);
+    Shared *sh = reinterpret_cast<Shared *>(smem + PIPE_BYTES);
+    // stage s: A at smem + s * STAGE_BYTES, weight box(es) right behind it
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = CTAS == 2 ? cluster_cta_rank() : 0u;  // position in the pair; rank 0 issues the MMAs
+    const int unit = CTAS == 2 ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;   // tile-processing unit (CTA or pair)
+    const int n_units = CTAS == 2 ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(&sh->full[s], 1);
+            mbar_init(&sh->full[s], 1);   // pair: only rank 0's is used; its producer arrives, both CTAs' copies credit it
             mbar_init(&sh->empty[s], 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&sh->acc_full[b], 1);
-            mbar_init(&sh->acc_empty[b], EPI_THREADS);
+            mbar_init(&sh->acc_empty[b], EPI_WARPS * CTAS);  // one arrival per epilogue warp of every CTA of the unit
         }
         for (int b = 0; b < SCALE_BUFS; ++b) mbar_init(&sh->scale_ready[b], EPI_THREADS);
         mbar_init(&sh->tile_sync[0], EPI_THREADS);
@@ -482,10 +563,11 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         prefetch_map(&map_w);
     }
     if (warp == 1) {
-        tmem_alloc(&sh->tmem_base, TMEM_COLS);
+        tmem_alloc<CTAS>(&sh->tmem_base, TMEM_COLS);
         tc_fence_before();
     }
-    build_schedule(sh, p);  // ends with __syncthreads()
+    build_schedule(sh, p, C::kTileM);  // ends with __syncthreads()
+    if (CTAS == 2) cluster_sync_all();  // the partner's barriers exist before anything is sent to them
     tc_fence_after();
 
     const int total_tiles = sh->total_tiles;
@@ -499,70 +581,95 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             uint32_t phase = 0;
             long long issued = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-                const Tile tl = decode_tile(sh, t, p.n_tiles, L);
+            // pair: rank 0's full barriers as shared::cluster addresses (barriers are 8 bytes apart)
+            const uint32_t full_rank0 = CTAS == 2 ? map_to_cta(&sh->full[0], 0) : 0u;
+            for (int t = unit; t < total_tiles && ok; t += n_units) {
+                const Tile tl = decode_tile(sh, t, p.n_tiles, L, C::kTileM);
+                const int my_row0 = tl.row0 + (int)rank * BM;
                 int n0, n1;
                 if (MODE == kModeSwigluQuant) { n0 = tl.n_idx * (BN / 2); n1 = p.half_n + n0; }
                 else { n0 = tl.n_idx * BN; n1 = n0 + BN / 2; }
+                const int nb = rank == 0 ? n0 : n1;  // pair: the weight box this CTA contributes
                 for (int kb = 0; kb < p.num_k_blocks; ++kb) {
                     if (!mbar_wait(&sh->empty[stage], phase ^ 1u, sh, p.status, 100 + stage)) { ok = false; break; }
-                    mbar_arrive_expect_tx(&sh->full[stage], STAGE_BYTES);
-                    tma_load_2d(smem_a + stage * A_STAGE, &map_x, kb * BK, tl.row0, &sh->full[stage]);
-                    uint8_t *bdst = smem_b + stage * B_STAGE;
-                    if (B_MN_MAJOR) {  // weight [E, K, N]: map dims {N, K, E}
-                        tma_load_3d(bdst, &map_w, n0, kb * BK, tl.g, &sh->full[stage]);
-                        tma_load_3d(bdst + B_HALF, &map_w, n1, kb * BK, tl.g, &sh->full[stage]);
-                    } else {           // weight [E, N, K]: map dims {K, N, E}
-                        tma_load_3d(bdst, &map_w, kb * BK, n0, tl.g, &sh->full[stage]);
-                        tma_load_3d(bdst + B_HALF, &map_w, kb * BK, n1, tl.g, &sh->full[stage]);
+                    uint8_t *adst = smem + stage * STAGE_BYTES;
+                    uint8_t *bdst = adst + A_STAGE;
+                    if (CTAS == 1) {
+                        mbar_arrive_expect_tx(&sh->full[stage], C::kTxBytes);
+                        tma_load_2d(adst, &map_x, kb * BK, my_row0, &sh->full[stage]);
+                        if (B_MN_MAJOR) {  // weight [E, K, N]: map dims {N, K, E}
+                            tma_load_3d(bdst, &map_w, n0, kb * BK, tl.g, &sh->full[stage]);
+                            tma_load_3d(bdst + B_BOX, &map_w, n1, kb * BK, tl.g, &sh->full[stage]);
+                        } else {           // weight [E, N, K]: map dims {K, N, E}
+                            tma_load_3d(bdst, &map_w, kb * BK, n0, tl.g, &sh->full[stage]);
+                            tma_load_3d(bdst + B_BOX, &map_w, kb * BK, n1, tl.g, &sh->full[stage]);
+                        }
+                    } else {
+                        if (rank == 0) mbar_arrive_expect_tx(&sh->full[stage], C::kTxBytes);
+                        tma_load_2d_pair(adst, &map_x, kb * BK, my_row0, full_rank0 + (uint32_t)stage * 8u);
+                        if (B_MN_MAJOR) tma_load_3d_pair(bdst, &map_w, nb, kb * BK, tl.g, full_rank0 + (uint32_t)stage * 8u);
+                        else tma_load_3d_pair(bdst, &map_w, kb * BK, nb, tl.g, full_rank0 + (uint32_t)stage * 8u);
                     }
                     ++issued;
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
-            if (!ok || *(volatile int *)&sh->abort_flag) {
+            if ((!ok || *(volatile int *)&sh->abort_flag) && rank == 0) {
                 // Drain: give the copies already issued a bounded chance to land before the CTA leaves.
                 const int n = (int)(issued < STAGES ? issued : STAGES);
-                int s = stage;
+                int s2 = stage;
                 uint32_t ph = phase;
                 for (int i = 0; i < n; ++i) {
-                    if (--s < 0) { s = STAGES - 1; ph ^= 1u; }
-                    const uint32_t a = smem_u32(&sh->full[s]);
+                    if (--s2 < 0) { s2 = STAGES - 1; ph ^= 1u; }
+                    const uint32_t a = smem_u32(&sh->full[s2]);
                     const long long t0 = clock64();
                     while (!mbar_try_wait(a, ph) && clock64() - t0 < DRAIN_LIMIT_CYCLES) {}
                 }
             }
         }
     } else if (warp == 1) {
-        // ------------------------------ MMA issuer ------------------------------
-        if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(B_MN_MAJOR);
+        // ------------------------------ MMA issuer (rank 0 of the unit) ------------------------------
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = make_idesc(B_MN_MAJOR, C::kTileM);
             int stage = 0;
             uint32_t phase = 0;
             int buf = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+            const uint32_t empty_peer = CTAS == 2 ? map_to_cta(&sh->empty[0], 1) : 0u;       // the partner's barriers
+            const uint32_t acc_full_peer = CTAS == 2 ? map_to_cta(&sh->acc_full[0], 1) : 0u;
+            for (int t = unit; t < total_tiles && ok; t += n_units) {
                 if (!mbar_wait(&sh->acc_empty[buf], acc_phase ^ 1u, sh, p.status, 200 + buf)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)buf * BN;
                 for (int kb = 0; kb < p.num_k_blocks; ++kb) {
                     if (!mbar_wait(&sh->full[stage], phase, sh, p.status, 300 + stage)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t a_addr = smem_u32(smem_a + stage * A_STAGE);
-                    const uint32_t b_addr = smem_u32(smem_b + stage * B_STAGE);
+                    const uint32_t a_addr = smem_u32(smem + stage * STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + A_STAGE;
 #pragma unroll
                     for (int j = 0; j < BK / UMMA_K; ++j) {
                         const uint64_t a_desc = make_smem_desc(a_addr + j * UMMA_K, 16, 1024);
-                        const uint64_t b_desc = B_MN_MAJOR ? make_smem_desc(b_addr + j * UMMA_K * 128, B_HALF, 1024)
+                        const uint64_t b_desc = B_MN_MAJOR ? make_smem_desc(b_addr + j * UMMA_K * 128, B_BOX, 1024)
                                                            : make_smem_desc(b_addr + j * UMMA_K, 16, 1024);
-                        umma_i8(d_tmem, a_desc, b_desc, idesc, (kb | j) != 0 ? 1u : 0u);
+                        if (CTAS == 1) umma_i8(d_tmem, a_desc, b_desc, idesc, (kb | j) != 0 ? 1u : 0u);
+                        else umma_i8_pair(d_tmem, a_desc, b_desc, idesc, (kb | j) != 0 ? 1u : 0u);
                     }
-                    umma_commit(&sh->empty[stage]);
+                    if (CTAS == 1) {
+                        umma_commit(&sh->empty[stage]);
+                    } else {  // the stage is free in both CTAs once these MMAs have read it
+                        umma_commit_pair(smem_u32(&sh->empty[stage]));
+                        umma_commit_pair(empty_peer + (uint32_t)stage * 8u);
+                    }
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
                 if (!ok) break;
-                umma_commit(&sh->acc_full[buf]);
+                if (CTAS == 1) {
+                    umma_commit(&sh->acc_full[buf]);
+                } else {
+                    umma_commit_pair(smem_u32(&sh->acc_full[buf]));
+                    umma_commit_pair(acc_full_peer + (uint32_t)buf * 8u);
+                }
                 buf ^= 1;
                 if (buf == 0) acc_phase ^= 1u;
             }
@@ -578,11 +685,14 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         uint32_t acc_phase = 0, settle_it = 0;
         Pending pend = {0, 0, 0, 0};
         bool ok = true;
-        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
-            const Tile tl = decode_tile(sh, t, p.n_tiles, L);
-            const bool valid = r < tl.rows;
-            const bool warp_has_rows = quarter * 32 < tl.rows;
-            const int grow = tl.row0 + r;
+        const uint32_t acc_empty_rank0 = CTAS == 2 ? map_to_cta(&sh->acc_empty[0], 0) : 0u;
+        for (int t = unit; t < total_tiles && ok; t += n_units, ++it) {
+            const Tile tl = decode_tile(sh, t, p.n_tiles, L, C::kTileM);
+            const int my_row0 = tl.row0 + (int)rank * BM;                 // this CTA's 128 rows of the tile
+            const int my_rows = max(0, min(BM, tl.rows - (int)rank * BM));
+            const bool valid = r < my_rows;
+            const bool warp_has_rows = quarter * 32 < my_rows;
+            const int grow = my_row0 + r;
             const size_t sbase = (size_t)tl.g * p.N;
             const int n0 = MODE == kModeSwigluQuant ? tl.n_idx * (BN / 2) : tl.n_idx * BN;
 
@@ -715,16 +825,20 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                         for (int i = 0; i < 4; ++i) {
                             const int rr = i * 8 + (lane >> 2);
                             const uint4 val = *reinterpret_cast<const uint4 *>(my_stage + rr * 64 + (((pc ^ (rr >> 1)) & 3) << 4));
-                            long long orow = tl.row0 + quarter * 32 + rr;
+                            long long orow = my_row0 + quarter * 32 + rr;
                             if (!PLAIN) orow = __shfl_sync(0xffffffffu, out_row, rr);
-                            if (quarter * 32 + rr < tl.rows && col < p.N) *reinterpret_cast<uint4 *>(out + (size_t)orow * p.N + col) = val;
+                            if (quarter * 32 + rr < my_rows && col < p.N) *reinterpret_cast<uint4 *>(out + (size_t)orow * p.N + col) = val;
                         }
                         __syncwarp();
                     }
                 }
             }
             tc_fence_before();
-            mbar_arrive(&sh->acc_empty[buf]);
+            __syncwarp();
+            if (lane == 0) {  // the accumulator buffer may be overwritten once every epilogue warp of the unit has read it
+                if (CTAS == 1) mbar_arrive(&sh->acc_empty[buf]);
+                else mbar_arrive_cluster(acc_empty_rank0 + (uint32_t)buf * 8u);
+            }
             buf ^= 1;
             if (buf == 0) acc_phase ^= 1u;
 
@@ -734,21 +848,25 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                 mbar_arrive(&sh->tile_sync[0]);
                 if (!mbar_wait(&sh->tile_sync[0], (uint32_t)it & 1u, sh, p.status, 600)) break;
                 if (te == 0) atomicAdd(p.rb_counter + t / p.n_tiles, 1);
-                ok = settle_pending(p, sh, pend, settle_it, te);
+                const int shares = p.n_tiles * CTAS;  // every CTA that worked on the row block requantises one share of its rows
+                ok = settle_pending(p, sh, pend, settle_it, te, shares);
+                const int share = tl.n_idx * CTAS + (int)rank;
                 pend.valid = 1;
                 pend.rb = t / p.n_tiles;
-                pend.r_begin = tl.row0 + (int)((long long)tl.rows * tl.n_idx / p.n_tiles);
-                pend.r_end = tl.row0 + (int)((long long)tl.rows * (tl.n_idx + 1) / p.n_tiles);
+                pend.r_begin = tl.row0 + (int)((long long)tl.rows * share / shares);
+                pend.r_end = tl.row0 + (int)((long long)tl.rows * (share + 1) / shares);
             }
         }
-        if (MODE == kModeSwigluQuant && ok && !*(volatile int *)&sh->abort_flag) settle_pending(p, sh, pend, settle_it, te);
+        if (MODE == kModeSwigluQuant && ok && !*(volatile int *)&sh->abort_flag)
+            settle_pending(p, sh, pend, settle_it, te, p.n_tiles * CTAS);
     }
 
     __syncthreads();
+    if (CTAS == 2) cluster_sync_all();  // neither CTA leaves, or frees TMEM, while the other can still reach into it
     if (warp == 1) {
         __syncwarp();
         tc_fence_after();
-        tmem_dealloc(tmem_base, TMEM_COLS);
+        tmem_dealloc<CTAS>(tmem_base, TMEM_COLS);
     }
 }
 
@@ -773,10 +891,10 @@ EncodeTiledFn encode_fn()
     return fn;
 }
 
-template <int MODE, bool B_MN, bool PLAIN>
+template <int MODE, bool B_MN, bool PLAIN, int CTAS>
 cudaError_t launch_variant(const Plan &plan, const KParams &kp, cudaStream_t stream)
 {
-    auto kern = gmm_w8a8_sm100_kernel<MODE, B_MN, PLAIN>;
+    auto kern = gmm_w8a8_sm100_kernel<MODE, B_MN, PLAIN, CTAS>;
     // Once per device and instantiation; the attribute is idempotent, so a race only repeats the call.
     static unsigned long long done_mask = 0;
     int dev = 0;
@@ -786,8 +904,25 @@ cudaError_t launch_variant(const Plan &plan, const KParams &kp, cudaStream_t str
         if (e != cudaSuccess) return e;
         done_mask |= 1ull << (dev & 63);
     }
-    kern<<<plan.num_sms, NUM_THREADS, SMEM_BYTES, stream>>>(plan.map_x, plan.map_w, kp);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(CTAS == 2 ? (plan.num_sms & ~1) : plan.num_sms), 1, 1);
+    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CTAS;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = CTAS == 2 ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, plan.map_x, plan.map_w, kp);
+}
+
+template <int MODE, bool B_MN, bool PLAIN>
+cudaError_t launch_ctas(const Plan &plan, const KParams &kp, cudaStream_t stream)
+{
+    return plan.ctas == 2 ? launch_variant<MODE, B_MN, PLAIN, 2>(plan, kp, stream) : launch_variant<MODE, B_MN, PLAIN, 1>(plan, kp, stream);
 }
 
 cudaEvent_t g_ev_start = nullptr, g_ev_stop = nullptr;
@@ -862,6 +997,7 @@ cudaError_t sm100_launch(const Problem &p, Plan &plan, void *workspace, cudaStre
     kp.K = (int)p.K;
     kp.N = (int)p.N;
     kp.half_n = (int)(p.N / 2);
+    if (plan.ctas != 2) plan.ctas = 1;
     kp.n_tiles = p.mode == kModeSwigluQuant ? (int)((p.N / 2 + BN / 2 - 1) / (BN / 2)) : (int)((p.N + BN - 1) / BN);
     kp.num_k_blocks = (int)((p.K + BK - 1) / BK);
     kp.w_scale = p.w_scale;
@@ -883,14 +1019,14 @@ cudaError_t sm100_launch(const Problem &p, Plan &plan, void *workspace, cudaStre
     const bool plain = !p.bias && p.act_type == 0 && !p.out_row_index && (p.mode != kModeDequantBf16 || p.x_scale);
     if (g_ev_start) cudaEventRecord(g_ev_start, stream);
     if (p.mode == kModeSwigluQuant)
-        e = mn ? launch_variant<kModeSwigluQuant, true, true>(plan, kp, stream) : launch_variant<kModeSwigluQuant, false, true>(plan, kp, stream);
+        e = mn ? launch_ctas<kModeSwigluQuant, true, true>(plan, kp, stream) : launch_ctas<kModeSwigluQuant, false, true>(plan, kp, stream);
     else if (p.mode == kModeInt32)
-        e = mn ? (plain ? launch_variant<kModeInt32, true, true>(plan, kp, stream) : launch_variant<kModeInt32, true, false>(plan, kp, stream))
-               : (plain ? launch_variant<kModeInt32, false, true>(plan, kp, stream) : launch_variant<kModeInt32, false, false>(plan, kp, stream));
+        e = mn ? (plain ? launch_ctas<kModeInt32, true, true>(plan, kp, stream) : launch_ctas<kModeInt32, true, false>(plan, kp, stream))
+               : (plain ? launch_ctas<kModeInt32, false, true>(plan, kp, stream) : launch_ctas<kModeInt32, false, false>(plan, kp, stream));
     else
-        e = mn ? (plain ? launch_variant<kModeDequantBf16, true, true>(plan, kp, stream) : launch_variant<kModeDequantBf16, true, false>(plan, kp, stream))
-               : (plain ? launch_variant<kModeDequantBf16, false, true>(plan, kp, stream)
-                        : launch_variant<kModeDequantBf16, false, false>(plan, kp, stream));
+        e = mn ? (plain ? launch_ctas<kModeDequantBf16, true, true>(plan, kp, stream) : launch_ctas<kModeDequantBf16, true, false>(plan, kp, stream))
+               : (plain ? launch_ctas<kModeDequantBf16, false, true>(plan, kp, stream)
+                        : launch_ctas<kModeDequantBf16, false, false>(plan, kp, stream));
     if (g_ev_stop) cudaEventRecord(g_ev_stop, stream);
     return e;
 }
