@@ -48,7 +48,7 @@ def measured_peaks():
 # ------------------------------------------------------------------------------------------------------------
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+    """Samples nvidia-smi clocks and throttle reasons every 50 ms while the timed region runs."""
 
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -62,7 +62,7 @@ class ClockSampler:
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50",
                                           "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -325,6 +325,13 @@ def bench_single(args):
         "clocks": clocks,
         "pct_of_nominal_int8_peak": tops / 4500.0 * 100.0,
     }
+    if name == "c2" and not args.no_ep:
+        # the expert-parallel workload (config 5) on this one GPU: the reference point of the multi-GPU lines
+        from ops_transformer_b200 import ep
+        del x, w, ws, xs, out0, out1, dx, hx, ho0
+        torch.cuda.empty_cache()
+        line["ep"] = {"workload": "c5 on one GPU: 256 local experts, 16384 tokens, top-8, swiglu_quant then down GEMM",
+                      **ep.one_gpu_summary(args, dev)}
     if not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline_sample()
     print(json.dumps(line))
@@ -333,13 +340,18 @@ def bench_single(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=400)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, help="c2 (default at N=1), c3, c4_swiglu, c4_down")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-ep", action="store_true", help="N=1: skip the one-GPU run of the expert-parallel workload")
     ap.add_argument("--ep-tokens", type=int, default=16384, help="tokens per GPU of the expert-parallel workload")
-    ap.add_argument("--ep-chunks", type=int, default=4, help="token chunks pipelined against the exchange")
+    ap.add_argument("--ep-chunks", type=int, default=0, help="token chunks pipelined against the exchange (0 = by world size)")
+    ap.add_argument("--ep-reserve-sms", type=int, default=-1, help="SMs left free for the exchange kernels (-1 = automatic)")
+    ap.add_argument("--ep-impl", default="fused", choices=["fused", "nccl"],
+                    help="fused: rows move by peer stores inside our kernels; nccl: NCCL all-to-all around the operators")
+    ap.add_argument("--ep-skip-n1", action="store_true", help="N>1: skip rank 0's one-GPU run of the same workload")
     ap.add_argument("--ep-phases", action="store_true", help="also report serialised per-phase times (diagnostic)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

@@ -23,6 +23,12 @@ ACL_FUNC_VISIBILITY int32_t gmmB200Version(void);
 ACL_FUNC_VISIBILITY aclnnStatus gmmB200CheckStatus(const void *workspace, uint64_t workspaceSize, aclrtStream stream,
                                                   int32_t record[4]);
 
+/* The GEMM kernels are persistent and normally launch one CTA per SM.  A caller that overlaps them with other work on
+ * the same GPU (for example the collectives of an expert-parallel layer, whose kernels need a few SMs to make progress)
+ * can cap the number of CTAs; 0 restores the default.  Process wide.  No counterpart in the reference, where the
+ * AI-core count comes from the platform (gmm/grouped_matmul/op_host/op_tiling/grouped_matmul_tiling.cpp:908-918). */
+ACL_FUNC_VISIBILITY void gmmB200SetSmLimit(int32_t maxCtas);
+
 /* Measurement hook: while both events (cudaEvent_t, created by the caller) are set, every launch records
  * `startEvent` right before and `stopEvent` right after the tensor-core GEMM kernel on the launch stream, so a
  * benchmark can time that kernel alone inside a multi-kernel operator.  Pass null to switch it off.  Process
@@ -35,7 +41,12 @@ ACL_FUNC_VISIBILITY void gmmB200SetTimingEvents(void *startEvent, void *stopEven
  * outRowIndex (optional, int64 [m] on the device, may be null): result row r is written to row outRowIndex[r] of y
  * instead of row r, which lets a caller fold the un-permute that follows the down projection of an MoE layer into the
  * GEMM (the row scatter of the reference's GroupedMatmulFinalizeRouting, gmm/grouped_matmul_finalize_routing/README.md:11-14,
- * without its weighting).  The indices must be a permutation onto rows of y; they are not checked. */
+ * without its weighting).  The indices must be a permutation onto rows of y; they are not checked.
+ * outPeers / numPeers (optional, bf16 result only): with numPeers in [1, 8], outRowIndex[r] = (gpu << 40) | row and the
+ * row is stored into outPeers[gpu] (a [rows, n] bf16 buffer that may live on another GPU of the node, see
+ * gmmB200PeerImport) instead of y: the return all-to-all of an expert-parallel layer folded into the GEMM epilogue,
+ * the role of the reference's GroupedMatMulAlltoAllv (mc2/grouped_mat_mul_allto_allv/README.md:12-24).  The caller
+ * orders the GPUs (a barrier after the kernels) before anyone reads those buffers. */
 ACL_FUNC_VISIBILITY aclnnStatus gmmB200GroupedMatmulW8A8WorkspaceSize(int64_t m, int64_t k, int64_t n, int64_t e,
                                                                      int32_t yDtype, uint64_t *workspaceSize);
 ACL_FUNC_VISIBILITY aclnnStatus gmmB200GroupedMatmulW8A8(const void *x, const void *weight, const void *scale,
@@ -43,8 +54,31 @@ ACL_FUNC_VISIBILITY aclnnStatus gmmB200GroupedMatmulW8A8(const void *x, const vo
                                                         int32_t biasDtype, const void *groupList, int64_t groupListLen,
                                                         int32_t groupListType, int64_t m, int64_t k, int64_t n, int64_t e,
                                                         int32_t weightTransposed, int32_t actType, const void *outRowIndex,
-                                                        void *y, int32_t yDtype, void *workspace, uint64_t workspaceSize,
-                                                        aclrtStream stream);
+                                                        void *const *outPeers, int32_t numPeers, void *y, int32_t yDtype,
+                                                        void *workspace, uint64_t workspaceSize, aclrtStream stream);
+
+/* Buffers that other GPUs of the node can write into (CUDA IPC).  PeerAlloc/PeerFree own device memory of the calling
+ * process; PeerExport fills a 64-byte handle that another process passes to PeerImport to obtain a device pointer to the
+ * same memory (peer access is enabled on first use); PeerRelease drops an imported mapping.  Set-up calls, not for the
+ * hot path.  They stand in for the HCCL window memory the reference's mc2 operators obtain from
+ * AscendC::GetHcclContext (mc2/moe_distribute_dispatch_v2/op_kernel/moe_distribute_dispatch_v2.h:317-319). */
+ACL_FUNC_VISIBILITY aclnnStatus gmmB200PeerAlloc(uint64_t bytes, void **devPtr);
+ACL_FUNC_VISIBILITY aclnnStatus gmmB200PeerFree(void *devPtr);
+ACL_FUNC_VISIBILITY aclnnStatus gmmB200PeerExport(const void *devPtr, void *handle64);
+ACL_FUNC_VISIBILITY aclnnStatus gmmB200PeerImport(const void *handle64, void **devPtr);
+ACL_FUNC_VISIBILITY aclnnStatus gmmB200PeerRelease(void *devPtr);
+
+/* Expert-parallel dispatch of already quantised token rows: send row i is token srcToken[i] of x (int8 [tokens, hidden],
+ * scale xScale[tokens]) and is stored as row (dest[i] & (2^40-1)) of GPU (dest[i] >> 40)'s activation buffer peerX[gpu]
+ * (int8 [capacity, hidden]) with its scale in peerScale[gpu]; dest[i] < 0 skips the row.  One pass of stores over NVLink
+ * replaces gather + all-to-all + re-ordering (reference: MoeDistributeDispatchV2 with quantMode 2 followed by
+ * MoeReRouting, mc2/moe_distribute_dispatch_v2/README.md:167-186, moe/moe_re_routing/README.md:12-26).  Rows whose
+ * destination is beyond `capacity` are dropped and counted in *overflowCounter (int32 on the device, cleared by the
+ * caller).  The caller orders the GPUs (a barrier) before the receivers read. */
+ACL_FUNC_VISIBILITY aclnnStatus gmmB200EpDispatch(const void *x, const void *xScale, const void *srcToken, const void *dest,
+                                                 int64_t rows, int64_t hidden, int64_t capacity, void *const *peerX,
+                                                 void *const *peerScale, int32_t numPeers, void *overflowCounter,
+                                                 aclrtStream stream);
 
 /* Flat form of aclnnGroupedMatmulSwigluQuant. */
 ACL_FUNC_VISIBILITY aclnnStatus gmmB200GroupedMatmulSwigluQuantWorkspaceSize(int64_t m, int64_t k, int64_t n, int64_t e,

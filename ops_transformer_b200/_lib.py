@@ -26,9 +26,10 @@ EXPORTED_SYMBOLS = [
     "aclDestroyIntArray", "aclDestroyAclOpExecutor", "aclGetRecentErrMsg",
     "aclnnGroupedMatmulV4GetWorkspaceSize", "aclnnGroupedMatmulV4",
     "aclnnGroupedMatmulSwigluQuantGetWorkspaceSize", "aclnnGroupedMatmulSwigluQuant",
-    "gmmB200Version", "gmmB200CheckStatus", "gmmB200SetTimingEvents", "gmmB200GroupedMatmulW8A8WorkspaceSize", "gmmB200GroupedMatmulW8A8",
+    "gmmB200Version", "gmmB200CheckStatus", "gmmB200SetTimingEvents", "gmmB200SetSmLimit", "gmmB200GroupedMatmulW8A8WorkspaceSize", "gmmB200GroupedMatmulW8A8",
     "gmmB200GroupedMatmulSwigluQuantWorkspaceSize", "gmmB200GroupedMatmulSwigluQuant",
     "gmmB200NoAllocScratchBytes", "gmmB200GroupedMatmulSwigluQuantNoAlloc",
+    "gmmB200PeerAlloc", "gmmB200PeerFree", "gmmB200PeerExport", "gmmB200PeerImport", "gmmB200PeerRelease", "gmmB200EpDispatch",
 ]
 
 
@@ -61,10 +62,18 @@ def _load():
     L.gmmB200CheckStatus.argtypes = [p, u64, p, C.POINTER(i32)]
     L.gmmB200SetTimingEvents.argtypes = [p, p]
     L.gmmB200SetTimingEvents.restype = None
+    L.gmmB200SetSmLimit.argtypes = [i32]
+    L.gmmB200SetSmLimit.restype = None
     L.gmmB200GroupedMatmulW8A8WorkspaceSize.argtypes = [i64, i64, i64, i64, i32, C.POINTER(u64)]
-    L.gmmB200GroupedMatmulW8A8.argtypes = [p, p, p, i32, p, p, i32, p, i64, i32, i64, i64, i64, i64, i32, i32, p, p, i32, p, u64, p]
+    L.gmmB200GroupedMatmulW8A8.argtypes = [p, p, p, i32, p, p, i32, p, i64, i32, i64, i64, i64, i64, i32, i32, p, p, i32, p, i32, p, u64, p]
     L.gmmB200GroupedMatmulSwigluQuantWorkspaceSize.argtypes = [i64, i64, i64, i64, C.POINTER(u64)]
     L.gmmB200GroupedMatmulSwigluQuant.argtypes = [p, p, p, i32, p, p, i64, i64, i64, i64, i64, p, p, p, u64, p]
+    L.gmmB200PeerAlloc.argtypes = [u64, C.POINTER(p)]
+    L.gmmB200PeerFree.argtypes = [p]
+    L.gmmB200PeerExport.argtypes = [p, p]
+    L.gmmB200PeerImport.argtypes = [p, C.POINTER(p)]
+    L.gmmB200PeerRelease.argtypes = [p]
+    L.gmmB200EpDispatch.argtypes = [p, p, p, p, i64, i64, i64, C.POINTER(p), C.POINTER(p), i32, p, p]
     L.gmmB200NoAllocScratchBytes.restype = u64
     L.gmmB200GroupedMatmulSwigluQuantNoAlloc.argtypes = [p, p, p, i32, p, p, i64, i64, i64, i64, i64, p, p, p]
     return L

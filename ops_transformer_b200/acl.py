@@ -97,17 +97,18 @@ def grouped_matmul_v4(x: torch.Tensor, weight: torch.Tensor, scale: Optional[tor
                       bias: Optional[torch.Tensor] = None, split_item: int = 3, group_type: int = 0,
                       group_list_type: int = 0, act_type: int = 0, out: Optional[torch.Tensor] = None,
                       out_dtype: torch.dtype = torch.bfloat16, stream=None, workspace: Optional[torch.Tensor] = None,
-                      return_workspace: bool = False, out_row_index: Optional[torch.Tensor] = None):
+                      return_workspace: bool = False, out_row_index: Optional[torch.Tensor] = None,
+                      out_peers: Optional[Sequence[int]] = None):
     """y = bf16((x @ weight[e]) * scale[e] * per_token_scale) per expert row range (W8A8), or the raw int32
     accumulators when ``out_dtype`` is torch.int32.  Rows not covered by ``group_list`` keep their contents.
     ``out_row_index`` (int64 [M], an extension of this library) scatters result row r to row out_row_index[r]; it
     goes through the flat entry point gmmB200GroupedMatmulW8A8."""
     L = _lib.lib()
-    if out is None:
+    if out is None and not out_peers:
         out = torch.empty((x.shape[0], weight.shape[2]), dtype=out_dtype, device=x.device)
     if out_row_index is not None:
         return _grouped_matmul_flat(x, weight, scale, per_token_scale, group_list, bias, group_list_type, act_type, out,
-                                    out_row_index, stream, workspace, return_workspace)
+                                    out_row_index, stream, workspace, return_workspace, out_peers)
     lists = []
     try:
         hx = create_tensor_list([x]); lists.append(hx)
@@ -149,7 +150,9 @@ def grouped_matmul_v4(x: torch.Tensor, weight: torch.Tensor, scale: Optional[tor
 
 
 def _grouped_matmul_flat(x, weight, scale, per_token_scale, group_list, bias, group_list_type, act_type, out, out_row_index,
-                         stream, workspace, return_workspace):
+                         stream, workspace, return_workspace, out_peers=None):
+    """Flat entry point.  ``out_peers`` (device addresses, one [rows, N] bf16 buffer per GPU) makes out_row_index hold
+    (gpu << 40) | row; ``out`` may then be None."""
     L = _lib.lib()
     M, K = x.shape
     E, _, N = weight.shape
@@ -159,7 +162,9 @@ def _grouped_matmul_flat(x, weight, scale, per_token_scale, group_list, bias, gr
             raise ValueError("the flat entry point needs contiguous tensors")
     if out_row_index.dtype != torch.int64 or out_row_index.numel() != M:
         raise ValueError("out_row_index must be int64 [M]")
-    ydt = _DTYPES[out.dtype]
+    ydt = _DTYPES[out.dtype] if out is not None else ACL_BF16
+    n_peers = len(out_peers) if out_peers else 0
+    peers = (C.c_void_p * max(n_peers, 1))(*[C.c_void_p(a) for a in (out_peers or [])])
     size = C.c_uint64(0)
     rc = L.gmmB200GroupedMatmulW8A8WorkspaceSize(M, K, N, E, ydt, C.byref(size))
     if rc != ACLNN_SUCCESS:
@@ -169,7 +174,7 @@ def _grouped_matmul_flat(x, weight, scale, per_token_scale, group_list, bias, gr
     p = lambda t: C.c_void_p(t.data_ptr()) if t is not None else None  # noqa: E731
     rc = L.gmmB200GroupedMatmulW8A8(p(x), p(weight), p(scale), _DTYPES[scale.dtype] if scale is not None else 0, p(per_token_scale),
                                     p(bias), _DTYPES[bias.dtype] if bias is not None else 0, p(group_list), group_list.numel(),
-                                    group_list_type, M, K, N, E, int(trans), act_type, p(out_row_index), p(out), ydt, p(workspace),
+                                    group_list_type, M, K, N, E, int(trans), act_type, p(out_row_index), peers if n_peers else None, n_peers, p(out), ydt, p(workspace),
                                     workspace.numel(), C.c_void_p(_stream_handle(stream)))
     if rc != ACLNN_SUCCESS:
         raise AclnnError(rc, "gmmB200GroupedMatmulW8A8")

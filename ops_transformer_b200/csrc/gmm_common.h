@@ -40,6 +40,8 @@ struct Problem {
     void *out0 = nullptr;               // y (bf16 / int32) or q (int8 [M, N/2])
     void *out1 = nullptr;               // q_scale f32 [M] (swiglu only)
     const int64_t *out_row_index = nullptr;  // optional [M]: result row r goes to row out_row_index[r] (grouped_matmul only)
+    void *out_peers[8] = {nullptr};          // with num_peers > 0: out_row_index = (gpu << 40) | row, one result buffer per gpu
+    int num_peers = 0;
 };
 
 struct Plan {
@@ -69,5 +71,7 @@ void set_timing_events(cudaEvent_t start, cudaEvent_t stop);
 cudaError_t simt_launch(const Problem &p, Plan &plan, void *workspace, cudaStream_t stream);
 
 int device_sm_count();
+// Caps the number of CTAs the persistent kernels launch (0 = one per SM).
+void set_sm_limit(int n);
 
 }  // namespace gmm

@@ -142,6 +142,10 @@ __global__ void __launch_bounds__(256) swiglu_simt_kernel(const SimtParams p)
 
 }  // namespace
 
+static int g_sm_limit = 0;
+
+void set_sm_limit(int n) { g_sm_limit = n > 0 ? n : 0; }
+
 int device_sm_count()
 {
     static int cached[64] = {0};
@@ -153,6 +157,7 @@ int device_sm_count()
         if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
         cached[dev] = n;
     }
+    if (g_sm_limit > 0 && g_sm_limit < cached[dev]) return g_sm_limit;
     return cached[dev];
 }
 

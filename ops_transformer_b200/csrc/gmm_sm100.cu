@@ -60,6 +60,7 @@ constexpr long long WAIT_LIMIT_CYCLES = 1ll << 31;   // about a second
 constexpr long long DRAIN_LIMIT_CYCLES = 1ll << 24;  // a few milliseconds
 
 constexpr int EPI_THREADS = 32 * EPI_WARPS;
+enum : int { kEpiPlain = 0, kEpiScatter = 1, kEpiGeneric = 2 };
 constexpr int SCALE_BUFS = 3;          // an epilogue thread can run at most two tiles ahead of another one
 constexpr int OUT_STAGE_BYTES = 2048;  // per epilogue warp: 32 rows x 64 bytes of packed bf16
 
@@ -100,6 +101,8 @@ struct KParams {
     int act_type;
     void *out;            // y (bf16 / int32) or the fp32 SwiGLU staging [M, N/2]
     const long long *out_row_index;  // optional: result row r is written to row out_row_index[r] (bf16 / int32 modes)
+    void *out_peers[8];              // bf16 mode with num_peers > 0: out_row_index = (gpu << 40) | row, base per gpu here
+    int num_peers;
     unsigned *amax_bits;  // [M] row max of |S| as float bits (swiglu)
     int *rb_counter;      // per 128-row block: number of N tiles that have stored their part (swiglu)
     int8_t *q_out;        // int8 [M, N/2] (swiglu)
@@ -525,12 +528,16 @@ __device__ bool settle_pending(const KParams &p, Shared *sh, Pending &pd, uint32
 // The kernel
 // ---------------------------------------------------------------------------------------------------------
 
-// PLAIN: no bias, no activation, per-token scale present, no row scatter - the common case, compiled without
-// the per-element tests for those options.  CTAS: 1 = one CTA per tile, 2 = a cluster of two CTAs per 256-row tile.
-template <int MODE, bool B_MN_MAJOR, bool PLAIN, int CTAS>
+// EPI selects the epilogue variant: kEpiPlain = no bias, no activation, per-token scale present, rows stored in place
+// (the common case, compiled without per-element tests for the options); kEpiScatter = the same arithmetic with the
+// result rows scattered through out_row_index, optionally into other GPUs' memory; kEpiGeneric = every option
+// tested at run time.  CTAS: 1 = one CTA per tile, 2 = a cluster of two CTAs per 256-row tile.
+template <int MODE, bool B_MN_MAJOR, int EPI, int CTAS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const KParams p)
 {
+    constexpr bool PLAIN = EPI != kEpiGeneric;   // lean arithmetic
+    constexpr bool SCATTER = EPI != kEpiPlain;  // rows go where out_row_index says
     using C = Cfg<CTAS>;
     constexpr int STAGES = C::kStages;
     constexpr int STAGE_BYTES = C::kStageBytes;
@@ -714,7 +721,7 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             }
             const float xs = (valid && p.x_scale) ? __ldg(p.x_scale + grow) : 1.0f;
             long long out_row = grow;
-            if (MODE != kModeSwigluQuant && !PLAIN && p.out_row_index && valid) out_row = __ldg(p.out_row_index + grow);
+            if (MODE != kModeSwigluQuant && SCATTER && p.out_row_index && valid) out_row = __ldg(p.out_row_index + grow);
             if (MODE != kModeInt32 && !mbar_wait(&sh->scale_ready[sb], (uint32_t)(it / SCALE_BUFS) & 1u, sh, p.status, 500 + sb)) break;
             if (!mbar_wait(&sh->acc_full[buf], acc_phase, sh, p.status, 400 + buf)) break;
             tc_fence_after();
@@ -826,8 +833,15 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                             const int rr = i * 8 + (lane >> 2);
                             const uint4 val = *reinterpret_cast<const uint4 *>(my_stage + rr * 64 + (((pc ^ (rr >> 1)) & 3) << 4));
                             long long orow = my_row0 + quarter * 32 + rr;
-                            if (!PLAIN) orow = __shfl_sync(0xffffffffu, out_row, rr);
-                            if (quarter * 32 + rr < my_rows && col < p.N) *reinterpret_cast<uint4 *>(out + (size_t)orow * p.N + col) = val;
+                            uint16_t *obase = out;
+                            if (SCATTER) {
+                                orow = __shfl_sync(0xffffffffu, out_row, rr);
+                                if (p.num_peers > 0) {  // high bits: which GPU's buffer, low 40 bits: row in it
+                                    obase = reinterpret_cast<uint16_t *>(p.out_peers[(int)(orow >> 40) & 7]);
+                                    orow &= (1ll << 40) - 1;
+                                }
+                            }
+                            if (quarter * 32 + rr < my_rows && col < p.N) *reinterpret_cast<uint4 *>(obase + (size_t)orow * p.N + col) = val;
                         }
                         __syncwarp();
                     }
@@ -859,6 +873,7 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         }
         if (MODE == kModeSwigluQuant && ok && !*(volatile int *)&sh->abort_flag)
             settle_pending(p, sh, pend, settle_it, te, p.n_tiles * CTAS);
+        if (SCATTER && p.num_peers > 0) __threadfence_system();  // rows stored into other GPUs' memory
     }
 
     __syncthreads();
@@ -891,10 +906,10 @@ EncodeTiledFn encode_fn()
     return fn;
 }
 
-template <int MODE, bool B_MN, bool PLAIN, int CTAS>
+template <int MODE, bool B_MN, int EPI, int CTAS>
 cudaError_t launch_variant(const Plan &plan, const KParams &kp, cudaStream_t stream)
 {
-    auto kern = gmm_w8a8_sm100_kernel<MODE, B_MN, PLAIN, CTAS>;
+    auto kern = gmm_w8a8_sm100_kernel<MODE, B_MN, EPI, CTAS>;
     // Once per device and instantiation; the attribute is idempotent, so a race only repeats the call.
     static unsigned long long done_mask = 0;
     int dev = 0;
@@ -919,10 +934,18 @@ cudaError_t launch_variant(const Plan &plan, const KParams &kp, cudaStream_t str
     return cudaLaunchKernelEx(&cfg, kern, plan.map_x, plan.map_w, kp);
 }
 
-template <int MODE, bool B_MN, bool PLAIN>
+template <int MODE, bool B_MN, int EPI>
 cudaError_t launch_ctas(const Plan &plan, const KParams &kp, cudaStream_t stream)
 {
-    return plan.ctas == 2 ? launch_variant<MODE, B_MN, PLAIN, 2>(plan, kp, stream) : launch_variant<MODE, B_MN, PLAIN, 1>(plan, kp, stream);
+    return plan.ctas == 2 ? launch_variant<MODE, B_MN, EPI, 2>(plan, kp, stream) : launch_variant<MODE, B_MN, EPI, 1>(plan, kp, stream);
+}
+
+template <int MODE, bool B_MN>
+cudaError_t launch_epi(int epi, const Plan &plan, const KParams &kp, cudaStream_t stream)
+{
+    if (epi == kEpiPlain) return launch_ctas<MODE, B_MN, kEpiPlain>(plan, kp, stream);
+    if (epi == kEpiScatter) return launch_ctas<MODE, B_MN, kEpiScatter>(plan, kp, stream);
+    return launch_ctas<MODE, B_MN, kEpiGeneric>(plan, kp, stream);
 }
 
 cudaEvent_t g_ev_start = nullptr, g_ev_stop = nullptr;
@@ -986,7 +1009,7 @@ cudaError_t sm100_launch(const Problem &p, Plan &plan, void *workspace, cudaStre
         cudaError_t e = sm100_encode_maps(p, plan);
         if (e != cudaSuccess) return e;
     }
-    if (plan.num_sms <= 0) plan.num_sms = device_sm_count();
+    plan.num_sms = device_sm_count();
     if (plan.num_sms <= 0) return cudaErrorNoDevice;
     uint8_t *ws = static_cast<uint8_t *>(workspace);
     KParams kp;
@@ -1016,17 +1039,18 @@ cudaError_t sm100_launch(const Problem &p, Plan &plan, void *workspace, cudaStre
 
     cudaError_t e;
     const bool mn = !p.w_trans;
-    const bool plain = !p.bias && p.act_type == 0 && !p.out_row_index && (p.mode != kModeDequantBf16 || p.x_scale);
+    const bool lean = !p.bias && p.act_type == 0 && (p.mode != kModeDequantBf16 || p.x_scale);
+    const int epi = !lean ? kEpiGeneric : (p.out_row_index ? kEpiScatter : kEpiPlain);
+    kp.num_peers = p.mode == kModeDequantBf16 ? p.num_peers : 0;
+    for (int i = 0; i < 8; ++i) kp.out_peers[i] = i < kp.num_peers ? p.out_peers[i] : nullptr;
+    if (kp.num_peers > 0 && epi != kEpiScatter) return cudaErrorInvalidValue;
     if (g_ev_start) cudaEventRecord(g_ev_start, stream);
     if (p.mode == kModeSwigluQuant)
-        e = mn ? launch_ctas<kModeSwigluQuant, true, true>(plan, kp, stream) : launch_ctas<kModeSwigluQuant, false, true>(plan, kp, stream);
+        e = mn ? launch_ctas<kModeSwigluQuant, true, kEpiPlain>(plan, kp, stream) : launch_ctas<kModeSwigluQuant, false, kEpiPlain>(plan, kp, stream);
     else if (p.mode == kModeInt32)
-        e = mn ? (plain ? launch_ctas<kModeInt32, true, true>(plan, kp, stream) : launch_ctas<kModeInt32, true, false>(plan, kp, stream))
-               : (plain ? launch_ctas<kModeInt32, false, true>(plan, kp, stream) : launch_ctas<kModeInt32, false, false>(plan, kp, stream));
+        e = mn ? launch_epi<kModeInt32, true>(epi, plan, kp, stream) : launch_epi<kModeInt32, false>(epi, plan, kp, stream);
     else
-        e = mn ? (plain ? launch_ctas<kModeDequantBf16, true, true>(plan, kp, stream) : launch_ctas<kModeDequantBf16, true, false>(plan, kp, stream))
-               : (plain ? launch_ctas<kModeDequantBf16, false, true>(plan, kp, stream)
-                        : launch_ctas<kModeDequantBf16, false, false>(plan, kp, stream));
+        e = mn ? launch_epi<kModeDequantBf16, true>(epi, plan, kp, stream) : launch_epi<kModeDequantBf16, false>(epi, plan, kp, stream);
     if (g_ev_stop) cudaEventRecord(g_ev_stop, stream);
     return e;
 }

@@ -103,6 +103,8 @@ extern "C" {
 
 int32_t gmmB200Version(void) { return 100; }
 
+void gmmB200SetSmLimit(int32_t maxCtas) { set_sm_limit(maxCtas); }
+
 void gmmB200SetTimingEvents(void *startEvent, void *stopEvent)
 {
     set_timing_events(static_cast<cudaEvent_t>(startEvent), static_cast<cudaEvent_t>(stopEvent));
@@ -412,14 +414,22 @@ aclnnStatus gmmB200GroupedMatmulW8A8WorkspaceSize(int64_t m, int64_t k, int64_t 
 aclnnStatus gmmB200GroupedMatmulW8A8(const void *x, const void *weight, const void *scale, int32_t scaleDtype,
                                      const void *perTokenScale, const void *bias, int32_t biasDtype, const void *groupList,
                                      int64_t groupListLen, int32_t groupListType, int64_t m, int64_t k, int64_t n, int64_t e,
-                                     int32_t weightTransposed, int32_t actType, const void *outRowIndex, void *y, int32_t yDtype,
-                                     void *workspace, uint64_t workspaceSize, aclrtStream stream)
+                                     int32_t weightTransposed, int32_t actType, const void *outRowIndex, void *const *outPeers,
+                                     int32_t numPeers, void *y, int32_t yDtype, void *workspace, uint64_t workspaceSize,
+                                     aclrtStream stream)
 {
     clear_error();
-    GMM_REQUIRE(x && weight && groupList && y, ACLNN_ERR_PARAM_NULLPTR, "x, weight, groupList and y must not be nullptr.");
+    GMM_REQUIRE(x && weight && groupList && (y || numPeers > 0), ACLNN_ERR_PARAM_NULLPTR, "x, weight, groupList and y must not be nullptr.");
     aclnnStatus rc = flat_sizes_ok(m, k, n, e);
     if (rc != ACLNN_SUCCESS) return rc;
     GMM_REQUIRE(yDtype == ACL_BF16 || yDtype == ACL_INT32, ACLNN_ERR_PARAM_INVALID, "yDtype must be bfloat16 or int32.");
+    GMM_REQUIRE(numPeers >= 0 && numPeers <= 8, ACLNN_ERR_PARAM_INVALID, "numPeers must be in [0, 8].");
+    if (numPeers > 0) {
+        GMM_REQUIRE(outPeers && outRowIndex && yDtype == ACL_BF16 && !bias && actType == 0 && perTokenScale, ACLNN_ERR_PARAM_INVALID,
+                    "peer output needs outPeers, outRowIndex, a bfloat16 result, a per-token scale, no bias and no activation.");
+        for (int i = 0; i < numPeers; ++i)
+            GMM_REQUIRE(outPeers[i] && !(reinterpret_cast<uintptr_t>(outPeers[i]) & 15), ACLNN_ERR_PARAM_INVALID, "outPeers[%d] is null or unaligned.", i);
+    }
     if (yDtype == ACL_BF16) {
         GMM_REQUIRE(scale != nullptr, ACLNN_ERR_PARAM_NULLPTR, "scale must not be nullptr for a bfloat16 result.");
         GMM_REQUIRE(scaleDtype == ACL_BF16 || scaleDtype == ACL_FLOAT, ACLNN_ERR_PARAM_INVALID, "scaleDtype must be bfloat16 or float32.");
@@ -442,8 +452,10 @@ aclnnStatus gmmB200GroupedMatmulW8A8(const void *x, const void *weight, const vo
     p.w_trans = weightTransposed ? 1 : 0;
     p.act_type = actType;
     p.mode = yDtype == ACL_INT32 ? kModeInt32 : kModeDequantBf16;
-    p.out0 = y;
+    p.out0 = y ? y : outPeers[0];
     p.out_row_index = static_cast<const int64_t *>(outRowIndex);
+    p.num_peers = numPeers;
+    for (int i = 0; i < numPeers; ++i) p.out_peers[i] = outPeers[i];
     Plan plan;
     make_plan(p, &plan);
     GMM_REQUIRE(workspaceSize >= plan.ws_bytes, ACLNN_ERR_PARAM_INVALID, "workspaceSize %llu is smaller than the %llu bytes required.",

@@ -78,6 +78,14 @@ class ExpertParallelFFN:
         self.chunks = chunks
         self.compute = compute or self._gpu_compute
         self.timers = None  # set to a dict to collect per-phase wall times (synchronises after every phase)
+        self.trace = None   # set to a list to collect (label, CUDA event) marks without synchronising
+
+    def _mark(self, label):
+        """Diagnostic trace: with self.trace set to a list, record a CUDA event on the current stream (no sync)."""
+        if self.trace is not None and torch.cuda.is_available():
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self.trace.append((label, ev))
 
     def _tick(self, name, t0):
         """Diagnostic timing: with timers enabled, wait for the device and add the phase's wall time."""
@@ -91,15 +99,14 @@ class ExpertParallelFFN:
         return t1
 
     # -- step 4 on the GPU: the two operators through the C ABI ------------------------------------------------
-    def _gpu_compute(self, x, xs, group_list):
+    def _gpu_compute(self, x, xs, group_list, out_row_index):
+        """gate/up GEMM + SwiGLU + requant, then the down GEMM; with ``out_row_index`` the down GEMM scatters its
+        result rows (row r -> row out_row_index[r]) so that no separate un-permute pass is needed."""
         from . import acl
         q, qs = acl.grouped_matmul_swiglu_quant(x, self.w1, self.w1_scale, xs, group_list)
-        return acl.grouped_matmul_v4(q, self.w2, self.w2_scale, qs, group_list, group_list_type=0)
+        return acl.grouped_matmul_v4(q, self.w2, self.w2_scale, qs, group_list, group_list_type=0, out_row_index=out_row_index)
 
     def _a2a(self, out, inp, out_splits, in_splits, async_op=False):
-        if self.world == 1:
-            out.copy_(inp)
-            return None
         return dist.all_to_all_single(out, inp, out_splits, in_splits, group=self.group, async_op=async_op)
 
     def forward(self, x: torch.Tensor, x_scale: torch.Tensor, topk_ids: torch.Tensor) -> List[dict]:
@@ -109,10 +116,26 @@ class ExpertParallelFFN:
         G, E, C = self.world, self.e_local, self.chunks
         T = x.shape[0]
         dev = x.device
+        use_cuda = dev.type == "cuda"
         t = time.perf_counter()
+        self._mark("start")
         bounds = [T * c // C for c in range(C + 1)]
         plans = [dispatch_plan(topk_ids[bounds[c]:bounds[c + 1]], self.n_experts, G) for c in range(C)]
         t = self._tick("plan", t)
+
+        if G == 1:
+            # One rank: nothing to exchange, rows sorted by expert are already expert major.
+            results = []
+            for c, p in enumerate(plans):
+                tok = p.src_token + bounds[c]
+                sx = x.index_select(0, tok)
+                ss = x_scale.index_select(0, tok)
+                t = self._tick("gather_send", t)
+                group_list = torch.cumsum(p.send_counts.reshape(-1), 0).to(torch.int64)
+                y = self.compute(sx, ss, group_list, None)
+                t = self._tick("gemms", t)
+                results.append({"y": y, "plan": p, "rows_computed": int(sx.shape[0])})
+            return results
 
         # counts of all chunks in one small exchange; the split sizes are needed on the host
         send_counts = torch.stack([p.send_counts for p in plans], 1).contiguous()      # [G(dst), C, E]
@@ -120,10 +143,8 @@ class ExpertParallelFFN:
         self._a2a(recv_counts, send_counts, None, None)
         send_h = send_counts.sum(2).cpu()   # [G, C] rows to each rank
         recv_h = recv_counts.sum(2).cpu()   # [G, C] rows from each rank
-        recv_counts_h = recv_counts.cpu()
         t = self._tick("counts_exchange", t)
-
-        use_cuda = dev.type == "cuda"
+        self._mark("counts_done")
 
         # dispatch of every chunk is issued up front; compute of chunk c starts when its rows have landed
         inflight = []
@@ -136,8 +157,8 @@ class ExpertParallelFFN:
             rx = torch.empty((n_recv, x.shape[1]), dtype=x.dtype, device=dev)
             rs = torch.empty((n_recv,), dtype=x_scale.dtype, device=dev)
             in_sp, out_sp = send_h[:, c].tolist(), recv_h[:, c].tolist()
-            w1 = self._a2a(rx, sx, out_sp, in_sp, async_op=use_cuda and G > 1)
-            w2 = self._a2a(rs, ss, out_sp, in_sp, async_op=use_cuda and G > 1)
+            w1 = self._a2a(rx, sx, out_sp, in_sp, async_op=use_cuda)
+            w2 = self._a2a(rs, ss, out_sp, in_sp, async_op=use_cuda)
             inflight.append((rx, rs, w1, w2, sx, ss, in_sp, out_sp))
             if self.timers is not None:
                 for w in (w1, w2):
@@ -152,107 +173,375 @@ class ExpertParallelFFN:
             for w in (w1, w2):
                 if w is not None:
                     w.wait()
-            dst, group_list = reorder_index(recv_counts[:, c, :], n_rows=int(rx.shape[0]))
-            if G > 1:
-                xs_sorted = torch.empty_like(rx); xs_sorted.index_copy_(0, dst, rx)
-                ss_sorted = torch.empty_like(rs); ss_sorted.index_copy_(0, dst, rs)
-            else:
-                xs_sorted, ss_sorted = rx, rs   # one source: already expert major
+            self._mark(f"c{c}_dispatch_landed")
+            n_rows = int(rx.shape[0])
+            dst, group_list = reorder_index(recv_counts[:, c, :], n_rows=n_rows)
+            # inverse permutation: expert-major position -> position as received (source-rank major)
+            inv = torch.empty_like(dst)
+            inv[dst] = torch.arange(n_rows, device=dev)
+            xs_sorted = rx.index_select(0, inv)
+            ss_sorted = rs.index_select(0, inv)
             t = self._tick("reorder_in", t)
-            y = self.compute(xs_sorted, ss_sorted, group_list)
+            self._mark(f"c{c}_reordered")
+            # the down projection writes result row r straight to row inv[r], i.e. back in source-rank-major order
+            y_back = self.compute(xs_sorted, ss_sorted, group_list, inv)
             t = self._tick("gemms", t)
-            y_back = y.index_select(0, dst) if G > 1 else y
-            t = self._tick("reorder_out", t)
-            out = torch.empty((sx.shape[0], y.shape[1]), dtype=y.dtype, device=dev)
-            w3 = self._a2a(out, y_back, in_sp, out_sp, async_op=use_cuda and G > 1)
+            self._mark(f"c{c}_gemms_done")
+            out = torch.empty((sx.shape[0], y_back.shape[1]), dtype=y_back.dtype, device=dev)
+            w3 = self._a2a(out, y_back, in_sp, out_sp, async_op=use_cuda)
             if self.timers is not None and w3 is not None:
                 w3.wait()
             t = self._tick("a2a_return", t)
             returns.append(w3)
-            results.append({"y": out, "plan": p, "rows_computed": int(rx.shape[0]), "keep": (y_back, sx, ss)})
-        for w in returns:
+            results.append({"y": out, "plan": p, "rows_computed": n_rows, "keep": (y_back, sx, ss, xs_sorted, ss_sorted)})
+        for c, w in enumerate(returns):
             if w is not None:
                 w.wait()
+            self._mark(f"c{c}_return_landed")
         return results
 
 
+ROW_BITS = 40  # a destination is (gpu << ROW_BITS) | row
+
+
+def fused_maps(all_counts: torch.Tensor, rank: int, n_send: int, capacity: int):
+    """Row maps of the peer-memory pipeline, from the all-gathered count tensor all_counts[src, dst, e] (rows that rank
+    src sends to local expert e of rank dst).  No value is read on the host.
+
+    Returns (send_dest [n_send], ret_dest [capacity], group_list [E], n_recv [1]):
+      send_dest[i]  where send row i of this rank (rows sorted by global expert) lands: (dst << 40) | row in dst's
+                    expert-major activation buffer (MoeReRouting's DstOffset, moe/moe_re_routing/README.md:12-26);
+      ret_dest[p]   where the result of activation row p of this rank goes back: (src << 40) | row in src's result
+                    buffer, i.e. the position the row had in src's send order (-1 for rows beyond n_recv);
+      group_list    running totals of rows per local expert of this rank.
+    """
+    G, _, E = all_counts.shape
+    dev = all_counts.device
+    c = all_counts.to(torch.int64)
+    tot = c.sum(0)                                                    # [dst, e] rows of expert e on dst
+    expert_off = torch.cumsum(tot, 1) - tot                           # [dst, e] start of expert e in dst's buffer
+    src_off = torch.cumsum(c, 0) - c                                  # [src, dst, e] rows of lower ranks inside the expert
+    send_flat = c.reshape(G, G * E)
+    send_start = (torch.cumsum(send_flat, 1) - send_flat).reshape(G, G, E)   # [src, dst, e] start in src's send order
+
+    # sender side: segments of my send order are (dst, e) in this order
+    seg_len = c[rank].reshape(-1)
+    seg_end = torch.cumsum(seg_len, 0)
+    i = torch.arange(n_send, device=dev)
+    seg = torch.searchsorted(seg_end, i, right=True).clamp_(max=G * E - 1)
+    within = i - (seg_end[seg] - seg_len[seg])
+    base = (expert_off + src_off[rank]).reshape(-1)                   # [(dst, e)]
+    dst_rank = seg // E
+    send_dest = (dst_rank << ROW_BITS) | (base[seg] + within)
+    send_dest = torch.where(i < seg_end[-1], send_dest, torch.full_like(send_dest, -1))
+
+    # receiver side: my activation buffer is ordered (e, src)
+    rlen = c[:, rank, :].t().reshape(-1)                              # [(e, src)]
+    rend = torch.cumsum(rlen, 0)
+    p = torch.arange(capacity, device=dev)
+    rseg = torch.searchsorted(rend, p, right=True).clamp_(max=G * E - 1)
+    rwithin = p - (rend[rseg] - rlen[rseg])
+    src = rseg % G
+    e = rseg // G
+    back = send_start[:, rank, :].t().reshape(-1)                     # [(e, src)] start of that segment in src's send order
+    ret_dest = (src << ROW_BITS) | (back[rseg] + rwithin)
+    ret_dest = torch.where(p < rend[-1], ret_dest, torch.full_like(ret_dest, -1))
+    del e
+    group_list = torch.cumsum(tot[rank], 0)
+    return send_dest, ret_dest, group_list, rend[-1:].clone()
+
+
+class FusedExpertParallelFFN:
+    """Expert-parallel FFN over peer memory: no collective moves token rows.
+
+      1. rows sorted by expert (as in ExpertParallelFFN); the per-(rank, expert) counts are all-gathered (a few KB),
+      2. one dispatch kernel stores every row straight into its place in the owning GPU's expert-major buffer
+         (gather + exchange + re-order in one pass of NVLink stores),
+      3. a barrier orders the GPUs, then grouped_matmul_swiglu_quant and grouped_matmul run on the local experts; the
+         down projection's epilogue stores each result row into the buffer of the GPU that sent the token,
+      4. a second barrier; every rank then finds its results, in send order, in its own result buffer.
+
+    Nothing is read back to the host during a step.  Buffers are sized for `capacity` received rows per rank; rows
+    beyond it are dropped and counted (``overflow``), so capacity must cover the worst expected imbalance.
+    """
+
+    def __init__(self, n_experts: int, hidden: int, hidden_out: int, w1, w1_scale, w2, w2_scale, *, tokens: int, top_k: int,
+                 capacity: int, group=None):
+        from .peer import PeerBuffer
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.n_experts, self.e_local = n_experts, n_experts // self.world
+        self.hidden, self.hidden_out = hidden, hidden_out
+        self.w1, self.w1_scale, self.w2, self.w2_scale = w1, w1_scale, w2, w2_scale
+        self.n_send = tokens * top_k
+        self.capacity = capacity
+        self.buf_x = PeerBuffer(capacity * hidden, group)
+        self.buf_s = PeerBuffer(capacity * 4, group)
+        self.buf_y = PeerBuffer(self.n_send * hidden_out * 2, group)
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.act = self.buf_x.view(torch.int8, (capacity, hidden))
+        self.act_scale = self.buf_s.view(torch.float32, (capacity,))
+        self.result = self.buf_y.view(torch.bfloat16, (self.n_send, hidden_out))
+        self.overflow = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._token = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.trace = None   # set to a list to collect (label, CUDA event) marks without synchronising
+
+    def _mark(self, label):
+        if self.trace is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self.trace.append((label, ev))
+
+    def _barrier(self):
+        """Stream-ordered barrier across the ranks: completes on this rank's stream only after every rank's earlier
+        work on its stream (the kernels that store into peer memory) has finished."""
+        if self.world > 1:
+            dist.all_reduce(self._token, group=self.group)
+
+    def forward(self, x: torch.Tensor, x_scale: torch.Tensor, topk_ids: torch.Tensor):
+        import ctypes as C
+
+        from . import _lib, acl
+        L = _lib.lib()
+        G, E = self.world, self.e_local
+        self._mark("start")
+        plan = dispatch_plan(topk_ids, self.n_experts, G)
+        self._mark("plan")
+        if G > 1:
+            allc = torch.empty((G, G, E), dtype=plan.send_counts.dtype, device=x.device)
+            dist.all_gather_into_tensor(allc, plan.send_counts.contiguous(), group=self.group)
+        else:
+            allc = plan.send_counts.reshape(1, 1, E)
+        self._mark("counts_gathered")
+        send_dest, ret_dest, group_list, _ = fused_maps(allc, self.rank, self.n_send, self.capacity)
+        self._mark("maps")
+        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        p = lambda t: C.c_void_p(t.data_ptr())  # noqa: E731
+        rc = L.gmmB200EpDispatch(p(x), p(x_scale), p(plan.src_token), p(send_dest), self.n_send, self.hidden, self.capacity,
+                                 self.buf_x.ptr_array(), self.buf_s.ptr_array(), G, p(self.overflow), stream)
+        if rc != 0:
+            raise acl.AclnnError(rc, "gmmB200EpDispatch")
+        self._mark("dispatch_kernel")
+        self._barrier()   # all rows for my experts have landed
+        self._mark("barrier1")
+        q, qs = acl.grouped_matmul_swiglu_quant(self.act, self.w1, self.w1_scale, self.act_scale, group_list)
+        self._mark("swiglu_quant")
+        acl.grouped_matmul_v4(q, self.w2, self.w2_scale, qs, group_list, group_list_type=0, out_row_index=ret_dest,
+                              out_peers=self.buf_y.ptrs, out=None)
+        self._mark("down_gemm")
+        self._barrier()   # every rank's results have landed, and everyone is done reading its activation buffer
+        self._mark("barrier2")
+        return {"y": self.result, "plan": plan, "group_list": group_list}
+
+    def close(self):
+        for b in (self.buf_x, self.buf_s, self.buf_y):
+            b.close()
+
+
 # ----------------------------------------------------------------------------------------------------------------
-# benchmark entry (bench.py --gpus N under torchrun, or N = 1)
+# benchmark entry (bench.py --gpus N under torchrun, or --workload c5 on one GPU)
 # ----------------------------------------------------------------------------------------------------------------
 
-def bench_main(args):
-    import json
-    import time
+N_EXPERTS, HIDDEN, INTER, TOP_K = 256, 7168, 2048, 8
 
+
+def default_chunks(world: int) -> int:
+    """Token chunks per step of the NCCL variant: enough rows per local expert and chunk to keep the GEMM tiles full."""
+    return {1: 1, 2: 1, 4: 2}.get(world, 4)
+
+
+def one_gpu_summary(args, dev):
+    """The expert-parallel workload on one GPU (all 256 experts local): tokens/s, ms per step and TOPS."""
+    T = args.ep_tokens
+    d1 = _make_rank_data(dev, 1, 0, T)
+    f1, _, _ = _build_ffn(args, d1, T, 1)
+    ms1, _, rows1 = _timed_steps(f1, d1, max(3, min(args.steps, 10)), 3, 1)
+    out = {"ms_per_step": ms1, "tokens_per_s": T / (ms1 * 1e-3),
+           "tops": rows1 * 2.0 * (HIDDEN * 2 * INTER + INTER * HIDDEN) / (ms1 * 1e-3) / 1e12}
+    if hasattr(f1, "close"):
+        f1.close()
+    del f1, d1
+    torch.cuda.empty_cache()
+    return out
+
+
+def _make_rank_data(dev, world, rank, tokens):
+    """Seeded synthetic weights of this rank's experts and this rank's tokens (DeepSeek-V3 shapes)."""
     import numpy as np
 
     from . import synth
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    n_experts, H, I, top_k, T = 256, 7168, 2048, 8, args.ep_tokens
-    e_local = n_experts // world
+    e_local = N_EXPERTS // world
     g = torch.Generator(device=dev)
     g.manual_seed(1234 + rank)
-    w1 = torch.randint(-127, 128, (e_local, H, 2 * I), dtype=torch.int8, device=dev, generator=g)
-    w2 = torch.randint(-127, 128, (e_local, I, H), dtype=torch.int8, device=dev, generator=g)
-    w1s = torch.empty((e_local, 2 * I), dtype=torch.float32, device=dev).uniform_(1e-3, 1e-2, generator=g)
-    w2s = torch.empty((e_local, H), dtype=torch.float32, device=dev).uniform_(1e-3, 1e-2, generator=g)
-    x = torch.randint(-127, 128, (T, H), dtype=torch.int8, device=dev, generator=g)
-    xs = torch.empty((T,), dtype=torch.float32, device=dev).uniform_(1e-3, 1e-2, generator=g)
-    _, top = synth.topk_softmax_counts(T, n_experts, top_k, seed=rank, idx=7)
-    topk = torch.from_numpy(top.astype(np.int64)).to(dev)
+    d = {}
+    d["w1"] = torch.randint(-127, 128, (e_local, HIDDEN, 2 * INTER), dtype=torch.int8, device=dev, generator=g)
+    d["w2"] = torch.randint(-127, 128, (e_local, INTER, HIDDEN), dtype=torch.int8, device=dev, generator=g)
+    d["w1s"] = torch.empty((e_local, 2 * INTER), dtype=torch.float32, device=dev).uniform_(1e-3, 1e-2, generator=g)
+    d["w2s"] = torch.empty((e_local, HIDDEN), dtype=torch.float32, device=dev).uniform_(1e-3, 1e-2, generator=g)
+    d["x"] = torch.randint(-127, 128, (tokens, HIDDEN), dtype=torch.int8, device=dev, generator=g)
+    d["xs"] = torch.empty((tokens,), dtype=torch.float32, device=dev).uniform_(1e-3, 1e-2, generator=g)
+    _, top = synth.topk_softmax_counts(tokens, N_EXPERTS, TOP_K, seed=rank, idx=7)
+    d["topk"] = torch.from_numpy(top.astype(np.int64)).to(dev)
+    return d
 
-    ffn = ExpertParallelFFN(n_experts, w1, w1s, w2, w2s, chunks=args.ep_chunks)
-    for _ in range(max(args.warmup, 3)):
-        res = ffn.forward(x, xs, topk)
+
+def _build_ffn(args, d, tokens, world):
+    if args.ep_impl == "fused":
+        ffn = FusedExpertParallelFFN(N_EXPERTS, HIDDEN, HIDDEN, d["w1"], d["w1s"], d["w2"], d["w2s"], tokens=tokens, top_k=TOP_K,
+                                     capacity=2 * tokens * TOP_K)
+        return ffn, "dispatch by peer stores, results stored into the owners' buffers by the down-GEMM epilogue", 3
+    chunks = args.ep_chunks if args.ep_chunks > 0 else default_chunks(world)
+    reserve = args.ep_reserve_sms if args.ep_reserve_sms >= 0 else (16 if world > 1 and chunks > 1 else 0)
+    if reserve > 0:
+        # leave a few SMs to the all-to-all kernels so that they can run beside the persistent GEMM kernels
+        from . import _lib
+        n_sm = torch.cuda.get_device_properties(d["x"].device).multi_processor_count
+        _lib.lib().gmmB200SetSmLimit(max(2, n_sm - reserve))
+    ffn = ExpertParallelFFN(N_EXPERTS, d["w1"], d["w1s"], d["w2"], d["w2s"], chunks=chunks)
+    return ffn, f"NCCL all-to-all around the operators, {chunks} chunk(s), {reserve} SMs left to the exchange", 2 * chunks
+
+
+def _rows_of(res):
+    if isinstance(res, dict):
+        return int(res["group_list"][-1].item())
+    return sum(r["rows_computed"] for r in res)
+
+
+def _timed_steps(ffn, d, steps, warmup, world):
+    import time
+    for _ in range(max(warmup, 3)):
+        res = ffn.forward(d["x"], d["xs"], d["topk"])
     torch.cuda.synchronize()
-    rows_local = sum(r["rows_computed"] for r in res)
+    rows = _rows_of(res)
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0 = time.perf_counter()
     ev0.record()
-    for _ in range(args.steps):
-        res = ffn.forward(x, xs, topk)
+    for _ in range(steps):
+        ffn.forward(d["x"], d["xs"], d["topk"])
     ev1.record()
     torch.cuda.synchronize()
-    wall = (time.perf_counter() - t0) / args.steps * 1e3
-    ms = ev0.elapsed_time(ev1) / args.steps
-    stats = torch.tensor([ms, float(rows_local)], dtype=torch.float64, device=dev)
+    wall = (time.perf_counter() - t0) / steps * 1e3
+    return ev0.elapsed_time(ev1) / steps, wall, rows
+
+
+def _e2e_steps(ffn, d, steps):
+    """The same step through the public classes with host buffers: pinned H2D of tokens, scales and routing, the
+    FFN, D2H of the result rows, every step."""
+    import time
+    hx = torch.empty_like(d["x"], device="cpu").pin_memory(); hx.copy_(d["x"])
+    hs = torch.empty_like(d["xs"], device="cpu").pin_memory(); hs.copy_(d["xs"])
+    ht = torch.empty_like(d["topk"], device="cpu").pin_memory(); ht.copy_(d["topk"])
+    dx, ds, dt = torch.empty_like(d["x"]), torch.empty_like(d["xs"]), torch.empty_like(d["topk"])
+    host_out = None
+
+    def step():
+        nonlocal host_out
+        dx.copy_(hx, non_blocking=True); ds.copy_(hs, non_blocking=True); dt.copy_(ht, non_blocking=True)
+        res = ffn.forward(dx, ds, dt)
+        ys = [res["y"]] if isinstance(res, dict) else [r["y"] for r in res]
+        if host_out is None:
+            host_out = [torch.empty_like(y, device="cpu").pin_memory() for y in ys]
+        for h, y in zip(host_out, ys):
+            h.copy_(y, non_blocking=True)
+        torch.cuda.synchronize()
+
+    step()
+    if dist.is_initialized():
+        dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    ms = (time.perf_counter() - t0) / steps * 1e3
+    h2d = hx.numel() + hs.numel() * 4 + ht.numel() * 8
+    d2h = sum(h.numel() * h.element_size() for h in host_out)
+    return ms, h2d, d2h
+
+
+def bench_main(args):
+    import json
+    import os as _os
+    import sys as _sys
+
+    _sys.path.insert(0, _os.path.dirname(_os.path.dirname(_os.path.abspath(__file__))))
+    from bench import ClockSampler, cpu_baseline_sample, measured_peaks
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    T = args.ep_tokens
+    ops_per_row = 2.0 * (HIDDEN * 2 * INTER + INTER * HIDDEN)
+
+    # The same workload on one GPU (all 256 experts local, no exchange), measured by rank 0 before the group forms:
+    # the reference point for the scaling of this line.
+    n1 = None
+    if world > 1 and rank == 0 and not args.ep_skip_n1:
+        n1 = one_gpu_summary(args, dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    d = _make_rank_data(dev, world, rank, T)
+    ffn, how, launches_per_step = _build_ffn(args, d, T, world)
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+        sampler.mark_begin()
+    ms, wall, rows_local = _timed_steps(ffn, d, args.steps, args.warmup, world)
+    if sampler:
+        sampler.mark_end()
+        clocks = sampler.stop()
+    e2e_ms, h2d, d2h = _e2e_steps(ffn, d, 3)
+    dropped = int(ffn.overflow.item()) if hasattr(ffn, "overflow") else 0
+    trace = None
+    if args.ep_phases and hasattr(ffn, "trace"):
+        ffn.trace = []
+        ffn.forward(d["x"], d["xs"], d["topk"])
+        torch.cuda.synchronize()
+        tr = ffn.trace
+        trace = [(b[0], round(a[1].elapsed_time(b[1]), 3)) for a, b in zip(tr[:-1], tr[1:])]
+        ffn.trace = None
+    stats = torch.tensor([ms, float(rows_local), float(dropped), e2e_ms], dtype=torch.float64, device=dev)
     if world > 1:
         allst = [torch.empty_like(stats) for _ in range(world)]
         dist.all_gather(allst, stats)
-        ms_max = max(float(s[0]) for s in allst)
-        rows_total = sum(float(s[1]) for s in allst)
     else:
-        ms_max, rows_total = ms, float(rows_local)
-    ops_total = 2.0 * rows_total * (H * 2 * I + I * H)
-    phases = None
-    if args.ep_phases:
-        ffn.timers = {}
-        for _ in range(3):
-            ffn.forward(x, xs, topk)
-        phases = {k: v / 3 for k, v in ffn.timers.items()}
-        ffn.timers = None
+        allst = [stats]
+    ms_max = max(float(s_[0]) for s_ in allst)
+    rows_total = sum(float(s_[1]) for s_ in allst)
+    dropped = sum(float(s_[2]) for s_ in allst)
+    e2e_max = max(float(s_[3]) for s_ in allst)
     if rank == 0:
-        tops = ops_total / (ms_max * 1e-3) / 1e12
+        tops = rows_total * ops_per_row / (ms_max * 1e-3) / 1e12
+        peaks = measured_peaks()
+        int8_peak = 2.0 * peaks["bf16_tflops_sustained"]   # a multi-millisecond step runs under the power cap
         line = {
             "metric": "int8 GMM+SwiGLU-quant TOPS", "value": tops, "unit": "TOPS", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_max, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-            "config": {"workload": f"c5 expert-parallel FFN: 256 experts over {world} GPU(s), {T} tokens per GPU, top-8, "
-                                   f"swiglu_quant K=7168 N=4096 then down GEMM K=2048 N=7168, {args.ep_chunks} chunk(s)",
-                       "l2": "inputs larger than L2", "tokens_per_s": T * world / (ms_max * 1e-3),
-                       "rows_total": rows_total, "host_ms_per_step": wall, "phase_ms_serialised": phases},
-            "gpu_launches": 3 * args.ep_chunks * args.steps,
+            "config": {"workload": f"c5 expert-parallel FFN: 256 experts over {world} GPU(s), {T} tokens per GPU, top-8, swiglu_quant "
+                                   f"K=7168 N=4096 then down GEMM K=2048 N=7168; {how}",
+                       "l2": "inputs larger than L2", "tokens_per_s": T * world / (ms_max * 1e-3), "rows_total": rows_total,
+                       "host_ms_per_step": wall, "dropped_rows": dropped, "phase_ms": trace},
+            "roofline": {"bound": "tensor", "achieved": tops / world, "peak": int8_peak, "unit": "TFLOP/s", "frac": tops / world / int8_peak,
+                         "traffic": None, "kernel": "whole step per GPU (dispatch, two GEMM kernels, exchange)",
+                         "peak_basis": f"2 x sustained bf16 of {peaks['source']} ({peaks['bf16_tflops_sustained']} TFLOP/s); int8 ops "
+                                       "counted as 2 per multiply-add"},
+            "e2e": {"value": rows_total * ops_per_row / (e2e_max * 1e-3) / 1e12, "unit": "TOPS", "ms_per_step": e2e_max,
+                    "h2d_bytes_per_step": int(h2d) * world, "d2h_bytes_per_step": int(d2h) * world},
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks,
+            "ep": {"tokens_per_s": T * world / (ms_max * 1e-3), "one_gpu_same_workload": n1,
+                   "scaling_vs_one_gpu": (T * world / (ms_max * 1e-3)) / n1["tokens_per_s"] if n1 else None},
         }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline_sample()
         print(json.dumps(line))
+    if hasattr(ffn, "close"):
+        ffn.close()
     if world > 1:
         dist.destroy_process_group()

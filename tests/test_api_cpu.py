@@ -232,7 +232,7 @@ def test_flat_entry_points_validate_on_the_host():
     assert L.gmmB200GroupedMatmulW8A8WorkspaceSize(256, 1024, 2048, 4, _lib.ACL_BF16, C.byref(size)) == OK and size.value == 256
     assert L.gmmB200GroupedMatmulW8A8WorkspaceSize(256, 1024, 2048, 4, _lib.ACL_FLOAT16, C.byref(size)) == INVALID
     one = C.c_void_p(256)
-    assert L.gmmB200GroupedMatmulW8A8(None, one, one, 0, one, None, 0, one, 1, 0, 1, 16, 16, 1, 0, 0, None, one, 27, one, 256, None) == NULLPTR
-    assert L.gmmB200GroupedMatmulW8A8(one, one, one, 0, one, None, 0, one, 2, 0, 1, 16, 16, 1, 0, 0, None, one, 27, one, 256, None) == INVALID
+    assert L.gmmB200GroupedMatmulW8A8(None, one, one, 0, one, None, 0, one, 1, 0, 1, 16, 16, 1, 0, 0, None, None, 0, one, 27, one, 256, None) == NULLPTR
+    assert L.gmmB200GroupedMatmulW8A8(one, one, one, 0, one, None, 0, one, 2, 0, 1, 16, 16, 1, 0, 0, None, None, 0, one, 27, one, 256, None) == INVALID
     assert L.gmmB200GroupedMatmulSwigluQuant(one, one, one, 0, one, one, 1, 4, 16, 32, 1, one, one, one, 16, None) == INVALID  # workspace too small
     assert "workspaceSize" in _lib.last_error()

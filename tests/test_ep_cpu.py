@@ -37,9 +37,14 @@ def _rank_main(rank, world, port, chunks, ret):
         el = N_EXPERTS // world
         lo, hi = rank * el, (rank + 1) * el
 
-        def compute(x, xs, gl):
+        def compute(x, xs, gl, out_row_index):
             y = _oracle_ffn(O, x.numpy(), xs.numpy(), gl.numpy(), w1[lo:hi], s1[lo:hi], w2[lo:hi], s2[lo:hi])
-            return torch.from_numpy(y.view(np.int16)).view(torch.bfloat16)
+            yt = torch.from_numpy(y.view(np.int16)).view(torch.bfloat16)
+            if out_row_index is None:
+                return yt
+            out = torch.empty_like(yt)
+            out[out_row_index] = yt   # row r -> row out_row_index[r], what the GPU down projection does in its epilogue
+            return out
 
         x = synth.int8_tensor((T, H), 60 + rank, 1)
         xs = synth.scale_tensor((T,), 60 + rank, 2)
@@ -88,3 +93,42 @@ def test_dispatch_plan_sorts_rows_by_expert():
     assert topk.reshape(-1)[p.order].tolist() == [0, 1, 1, 3, 5, 5]
     assert p.src_token.tolist() == [1, 0, 2, 2, 0, 1]
     assert p.send_counts.tolist() == [[1, 2, 0, 1], [0, 2, 0, 0]]
+
+
+def test_fused_maps_place_rows_expert_major_and_return_them_home():
+    """Simulate G ranks on CPU: scatter every rank's send rows by send_dest, check the receiver's buffer is expert major
+    with the right owners, then scatter 'results' by ret_dest and check every row comes back to its send position."""
+    G, E, k, T = 4, 3, 2, 40
+    rng = np.random.default_rng(5)
+    topks = [np.stack([rng.choice(G * E, k, replace=False) for _ in range(T)]).astype(np.int64) for _ in range(G)]
+    plans = [ep.dispatch_plan(torch.from_numpy(t), G * E, G) for t in topks]
+    allc = torch.stack([p.send_counts for p in plans])                      # [src, dst, e]
+    n_send, cap = T * k, 2 * T * k
+    maps = [ep.fused_maps(allc, r, n_send, cap) for r in range(G)]
+    act = np.full((G, cap, 3), -1, np.int64)                                # (src rank, send index, global expert)
+    for r in range(G):
+        send_dest = maps[r][0].numpy()
+        experts = topks[r].reshape(-1)[plans[r].order.numpy()]
+        assert (send_dest >= 0).all()
+        for i, d in enumerate(send_dest):
+            gpu, row = int(d >> ep.ROW_BITS), int(d & ((1 << ep.ROW_BITS) - 1))
+            assert gpu == experts[i] // E
+            assert act[gpu, row, 0] == -1, "two rows sent to the same place"
+            act[gpu, row] = (r, i, experts[i])
+    result = np.full((G, n_send, 2), -1, np.int64)
+    for d in range(G):
+        _, ret_dest, gl, n_recv = maps[d]
+        n = int(n_recv)
+        assert n == int(allc[:, d, :].sum()) and gl.tolist() == np.cumsum(allc[:, d, :].sum(0).numpy()).tolist()
+        local_e = act[d, :n, 2] - d * E
+        assert (act[d, :n, 0] >= 0).all() and (np.diff(local_e) >= 0).all(), "buffer is not expert major"
+        starts = np.concatenate([[0], gl.numpy()])
+        for e in range(E):
+            seg = act[d, starts[e]:starts[e + 1]]
+            assert (seg[:, 2] == d * E + e).all() and (np.diff(seg[:, 0]) >= 0).all()   # rank-minor inside an expert
+        assert (ret_dest[n:] == -1).all()
+        for p_, rd in enumerate(ret_dest[:n].numpy()):
+            gpu, row = int(rd >> ep.ROW_BITS), int(rd & ((1 << ep.ROW_BITS) - 1))
+            assert (gpu, row) == (act[d, p_, 0], act[d, p_, 1]), "result row does not go back to where it came from"
+            result[gpu, row] = (d, p_)
+    assert (result[:, :, 0] >= 0).all(), "some sent row got no result"
