@@ -33,6 +33,16 @@ FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
 
 
+# DRAM traffic per launch of the GEMM kernel from the committed ncu captures (profiles/ncu_gmm_kernel_*.md).  The full-size
+# launches are too large to capture, so the reduced cases are scaled by the units processed (rows, or non-empty experts
+# for the weight-streaming decode case); traffic grows in proportion to them.
+NCU_DRAM_BYTES_PER_LAUNCH = {
+    "c2_small": 488.8e6, "c2": 4 * 488.8e6,
+    "c3_small": 218.3e6, "c3": 4 * 218.3e6,
+    "c4_swiglu_small": 859.8e6, "c4_swiglu": 859.8e6 * 165 / 29,
+}
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -303,7 +313,8 @@ def bench_single(args):
         roof = {"bound": "hbm", "achieved": alg_bytes / (kms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "peak_basis": f"copy bandwidth, {peaks['source']}"}
     roof["frac"] = roof["achieved"] / roof["peak"]
-    roof["traffic"] = None
+    roof["traffic"] = NCU_DRAM_BYTES_PER_LAUNCH.get(name)
+    roof["traffic_source"] = "dram__bytes_read.sum + dram__bytes_write.sum of the ncu capture under profiles/, scaled as stated there"
     roof["kernel"] = "gmm_w8a8_sm100_kernel"
     roof["kernel_ms"] = kms
     roof["algorithmic_bytes"] = alg_bytes
