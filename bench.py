@@ -362,6 +362,7 @@ def main():
     ap.add_argument("--ep-reserve-sms", type=int, default=-1, help="SMs left free for the exchange kernels (-1 = automatic)")
     ap.add_argument("--ep-impl", default="fused", choices=["fused", "nccl"],
                     help="fused: rows move by peer stores inside our kernels; nccl: NCCL all-to-all around the operators")
+    ap.add_argument("--ep-graph", type=int, default=1, help="1: replay the fused expert-parallel step as a CUDA graph")
     ap.add_argument("--ep-skip-n1", action="store_true", help="N>1: skip rank 0's one-GPU run of the same workload")
     ap.add_argument("--ep-phases", action="store_true", help="also report serialised per-phase times (diagnostic)")
     args = ap.parse_args()

@@ -74,11 +74,13 @@ ACL_FUNC_VISIBILITY aclnnStatus gmmB200PeerRelease(void *devPtr);
  * replaces gather + all-to-all + re-ordering (reference: MoeDistributeDispatchV2 with quantMode 2 followed by
  * MoeReRouting, mc2/moe_distribute_dispatch_v2/README.md:167-186, moe/moe_re_routing/README.md:12-26).  Rows whose
  * destination is beyond `capacity` are dropped and counted in *overflowCounter (int32 on the device, cleared by the
- * caller).  The caller orders the GPUs (a barrier) before the receivers read. */
+ * caller).  firstRow (optional, int64 on the device): the send row the kernel starts with, wrapping around; giving every
+ * rank the first row of a different destination keeps the ranks from all storing into one GPU at a time.
+ * The caller orders the GPUs (a barrier) before the receivers read. */
 ACL_FUNC_VISIBILITY aclnnStatus gmmB200EpDispatch(const void *x, const void *xScale, const void *srcToken, const void *dest,
                                                  int64_t rows, int64_t hidden, int64_t capacity, void *const *peerX,
                                                  void *const *peerScale, int32_t numPeers, void *overflowCounter,
-                                                 aclrtStream stream);
+                                                 const void *firstRow, aclrtStream stream);
 
 /* Flat form of aclnnGroupedMatmulSwigluQuant. */
 ACL_FUNC_VISIBILITY aclnnStatus gmmB200GroupedMatmulSwigluQuantWorkspaceSize(int64_t m, int64_t k, int64_t n, int64_t e,

@@ -73,7 +73,7 @@ def _load():
     L.gmmB200PeerExport.argtypes = [p, p]
     L.gmmB200PeerImport.argtypes = [p, C.POINTER(p)]
     L.gmmB200PeerRelease.argtypes = [p]
-    L.gmmB200EpDispatch.argtypes = [p, p, p, p, i64, i64, i64, C.POINTER(p), C.POINTER(p), i32, p, p]
+    L.gmmB200EpDispatch.argtypes = [p, p, p, p, i64, i64, i64, C.POINTER(p), C.POINTER(p), i32, p, p, p]
     L.gmmB200NoAllocScratchBytes.restype = u64
     L.gmmB200GroupedMatmulSwigluQuantNoAlloc.argtypes = [p, p, p, i32, p, p, i64, i64, i64, i64, i64, p, p, p]
     return L

@@ -25,12 +25,18 @@ constexpr long long kRowMask = (1ll << 40) - 1;
 __global__ void __launch_bounds__(256) ep_dispatch_kernel(const int8_t *__restrict__ x, const float *__restrict__ xs,
                                                            const long long *__restrict__ src_token,
                                                            const long long *__restrict__ dest, long long rows, int hidden,
-                                                           long long capacity, PeerPtrs pp, int *overflow)
+                                                           long long capacity, PeerPtrs pp, int *overflow,
+                                                           const long long *__restrict__ first_row)
 {
     const int lane = threadIdx.x & 31;
     const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
     const int vecs = hidden >> 4;
-    for (long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows; row += warps) {
+    // Rows are walked starting at *first_row (wrapping around): when every rank starts with a different destination GPU,
+    // the ranks do not all store into the same GPU at the same time.
+    long long rot = first_row ? *first_row : 0;
+    rot = rot > 0 && rot < rows ? rot : 0;
+    for (long long it = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); it < rows; it += warps) {
+        const long long row = it + rot < rows ? it + rot : it + rot - rows;
         const long long d = dest[row];
         if (d < 0) continue;
         const int gpu = (int)(d >> 40) & 7;
@@ -107,7 +113,7 @@ aclnnStatus gmmB200PeerRelease(void *devPtr)
 
 aclnnStatus gmmB200EpDispatch(const void *x, const void *xScale, const void *srcToken, const void *dest, int64_t rows,
                               int64_t hidden, int64_t capacity, void *const *peerX, void *const *peerScale, int32_t numPeers,
-                              void *overflowCounter, aclrtStream stream)
+                              void *overflowCounter, const void *firstRow, aclrtStream stream)
 {
     gmm::clear_error();
     if (!x || !xScale || !srcToken || !dest || !peerX || !peerScale || !overflowCounter)
@@ -128,7 +134,8 @@ aclnnStatus gmmB200EpDispatch(const void *x, const void *xScale, const void *src
     const int grid = (int)std::min<int64_t>((rows + 7) / 8, (int64_t)sms * 8);
     ep_dispatch_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const int8_t *>(x), static_cast<const float *>(xScale), static_cast<const long long *>(srcToken),
-        static_cast<const long long *>(dest), rows, (int)hidden, capacity, pp, static_cast<int *>(overflowCounter));
+        static_cast<const long long *>(dest), rows, (int)hidden, capacity, pp, static_cast<int *>(overflowCounter),
+        static_cast<const long long *>(firstRow));
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return gmm::fail(ACLNN_ERR_INNER, "dispatch kernel launch failed: %s", cudaGetErrorString(e));
     return ACLNN_SUCCESS;

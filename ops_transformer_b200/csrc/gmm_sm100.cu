@@ -787,63 +787,74 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                     }
                 } else {
                     uint16_t *out = reinterpret_cast<uint16_t *>(p.out);
+                    // Two 32-column chunks at a time: 64 bf16 = 128 bytes per row and pass.
 #pragma unroll 1
-                    for (int c = chalf * 4; c < chalf * 4 + 4; ++c) {
+                    for (int c = chalf * 4; c < chalf * 4 + 4; c += 2) {
                         if (n0 + c * 32 >= p.N) break;
-                        uint32_t v[32];
-                        tmem_ld32(taddr + c * 32, v);
-                        tmem_ld_wait();
-                        uint32_t pk[16];
+                        uint32_t pk[32];
 #pragma unroll
-                        for (int j4 = 0; j4 < 8; ++j4) {
-                            const float4 s4 = *reinterpret_cast<const float4 *>(tsc + c * 32 + j4 * 4);
-                            const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
-                            float o[4];
+                        for (int half = 0; half < 2; ++half) {
+                            uint32_t v[32];
+                            tmem_ld32(taddr + (c + half) * 32, v);
+                            tmem_ld_wait();
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                // (acc * w_scale) * x_scale, optional bf16 bias, optional relu, then bf16 RNE
-                                const int cc = c * 32 + j4 * 4 + j;
-                                int acc = (int)v[j4 * 4 + j];
-                                if (PLAIN) {
-                                    o[j] = __fmul_rn(__fmul_rn(__int2float_rn(acc), sv[j]), xs);
-                                } else {
-                                    const bool in_n = n0 + cc < p.N;
-                                    if (p.bias_dtype == kI32 && in_n) acc += __ldg(reinterpret_cast<const int *>(p.bias) + sbase + n0 + cc);
-                                    float tv = __fmul_rn(__int2float_rn(acc), sv[j]);
-                                    if (p.x_scale) tv = __fmul_rn(tv, xs);
-                                    if (p.bias_dtype == kBF16 && in_n)
-                                        tv = __fadd_rn(tv, __uint_as_float((uint32_t)__ldg(reinterpret_cast<const uint16_t *>(p.bias) + sbase + n0 + cc) << 16));
-                                    if (p.act_type == 1) tv = tv > 0.0f ? tv : 0.0f;
-                                    o[j] = tv;
+                            for (int j4 = 0; j4 < 8; ++j4) {
+                                const float4 s4 = *reinterpret_cast<const float4 *>(tsc + (c + half) * 32 + j4 * 4);
+                                const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
+                                float o[4];
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    // (acc * w_scale) * x_scale, optional bf16 bias, optional relu, then bf16 RNE
+                                    const int cc = (c + half) * 32 + j4 * 4 + j;
+                                    int acc = (int)v[j4 * 4 + j];
+                                    if (PLAIN) {
+                                        o[j] = __fmul_rn(__fmul_rn(__int2float_rn(acc), sv[j]), xs);
+                                    } else {
+                                        const bool in_n = n0 + cc < p.N;
+                                        if (p.bias_dtype == kI32 && in_n) acc += __ldg(reinterpret_cast<const int *>(p.bias) + sbase + n0 + cc);
+                                        float tv = __fmul_rn(__int2float_rn(acc), sv[j]);
+                                        if (p.x_scale) tv = __fmul_rn(tv, xs);
+                                        if (p.bias_dtype == kBF16 && in_n)
+                                            tv = __fadd_rn(tv, __uint_as_float((uint32_t)__ldg(reinterpret_cast<const uint16_t *>(p.bias) + sbase + n0 + cc) << 16));
+                                        if (p.act_type == 1) tv = tv > 0.0f ? tv : 0.0f;
+                                        o[j] = tv;
+                                    }
                                 }
+                                pk[half * 16 + j4 * 2] = pack_bf16x2(o[0], o[1]);
+                                pk[half * 16 + j4 * 2 + 1] = pack_bf16x2(o[2], o[3]);
                             }
-                            pk[j4 * 2] = pack_bf16x2(o[0], o[1]);
-                            pk[j4 * 2 + 1] = pack_bf16x2(o[2], o[3]);
                         }
-                        // Transpose through shared memory so that four lanes write 64 contiguous bytes of one row.
-#pragma unroll
-                        for (int pc = 0; pc < 4; ++pc)
-                            *reinterpret_cast<uint4 *>(my_stage + lane * 64 + (((pc ^ (lane >> 1)) & 3) << 4)) =
-                                make_uint4(pk[pc * 4], pk[pc * 4 + 1], pk[pc * 4 + 2], pk[pc * 4 + 3]);
-                        __syncwarp();
-                        const int pc = lane & 3;
+                        // Transpose through shared memory, 16 rows per round, so that eight lanes write 128 contiguous
+                        // bytes of one row (a full line for local memory, a full-size packet for a peer GPU).
+                        const int pc = lane & 7;
                         const int col = n0 + c * 32 + pc * 8;
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const int rr = i * 8 + (lane >> 2);
-                            const uint4 val = *reinterpret_cast<const uint4 *>(my_stage + rr * 64 + (((pc ^ (rr >> 1)) & 3) << 4));
-                            long long orow = my_row0 + quarter * 32 + rr;
-                            uint16_t *obase = out;
-                            if (SCATTER) {
-                                orow = __shfl_sync(0xffffffffu, out_row, rr);
-                                if (p.num_peers > 0) {  // high bits: which GPU's buffer, low 40 bits: row in it
-                                    obase = reinterpret_cast<uint16_t *>(p.out_peers[(int)(orow >> 40) & 7]);
-                                    orow &= (1ll << 40) - 1;
-                                }
+                        for (int round = 0; round < 2; ++round) {
+                            if ((lane >> 4) == round) {
+#pragma unroll
+                                for (int q8 = 0; q8 < 8; ++q8)
+                                    *reinterpret_cast<uint4 *>(my_stage + (lane & 15) * 128 + (((q8 ^ lane) & 7) << 4)) =
+                                        make_uint4(pk[q8 * 4], pk[q8 * 4 + 1], pk[q8 * 4 + 2], pk[q8 * 4 + 3]);
                             }
-                            if (quarter * 32 + rr < my_rows && col < p.N) *reinterpret_cast<uint4 *>(obase + (size_t)orow * p.N + col) = val;
+                            __syncwarp();
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int r16 = i * 4 + (lane >> 3);
+                                const int rr = round * 16 + r16;
+                                const uint4 val = *reinterpret_cast<const uint4 *>(my_stage + r16 * 128 + (((pc ^ r16) & 7) << 4));
+                                long long orow = my_row0 + quarter * 32 + rr;
+                                uint16_t *obase = out;
+                                if (SCATTER) {
+                                    orow = __shfl_sync(0xffffffffu, out_row, rr);
+                                    if (p.num_peers > 0) {  // high bits: which GPU's buffer, low 40 bits: row in it
+                                        obase = reinterpret_cast<uint16_t *>(p.out_peers[(int)(orow >> 40) & 7]);
+                                        orow &= (1ll << 40) - 1;
+                                    }
+                                }
+                                if (quarter * 32 + rr < my_rows && col < p.N) *reinterpret_cast<uint4 *>(obase + (size_t)orow * p.N + col) = val;
+                            }
+                            __syncwarp();
                         }
-                        __syncwarp();
                     }
                 }
             }

@@ -39,7 +39,9 @@ def dispatch_plan(topk_ids: torch.Tensor, n_experts: int, world: int) -> ChunkPl
     T, k = topk_ids.shape
     flat = topk_ids.reshape(-1).to(torch.int64)
     order = torch.sort(flat, stable=True).indices
-    counts = torch.bincount(flat, minlength=n_experts).reshape(world, n_experts // world)
+    # histogram by scatter-add: unlike bincount it needs no look at the values on the host, so it can be graph-captured
+    counts = torch.zeros(n_experts, dtype=torch.int64, device=flat.device).scatter_add_(0, flat, torch.ones_like(flat))
+    counts = counts.reshape(world, n_experts // world)
     return ChunkPlan(order=order, src_token=order // k, send_counts=counts)
 
 
@@ -204,51 +206,55 @@ class ExpertParallelFFN:
 ROW_BITS = 40  # a destination is (gpu << ROW_BITS) | row
 
 
-def fused_maps(all_counts: torch.Tensor, rank: int, n_send: int, capacity: int):
-    """Row maps of the peer-memory pipeline, from the all-gathered count tensor all_counts[src, dst, e] (rows that rank
-    src sends to local expert e of rank dst).  No value is read on the host.
-
-    Returns (send_dest [n_send], ret_dest [capacity], group_list [E], n_recv [1]):
-      send_dest[i]  where send row i of this rank (rows sorted by global expert) lands: (dst << 40) | row in dst's
-                    expert-major activation buffer (MoeReRouting's DstOffset, moe/moe_re_routing/README.md:12-26);
-      ret_dest[p]   where the result of activation row p of this rank goes back: (src << 40) | row in src's result
-                    buffer, i.e. the position the row had in src's send order (-1 for rows beyond n_recv);
-      group_list    running totals of rows per local expert of this rank.
-    """
+def _count_tables(all_counts: torch.Tensor):
     G, _, E = all_counts.shape
-    dev = all_counts.device
     c = all_counts.to(torch.int64)
     tot = c.sum(0)                                                    # [dst, e] rows of expert e on dst
     expert_off = torch.cumsum(tot, 1) - tot                           # [dst, e] start of expert e in dst's buffer
     src_off = torch.cumsum(c, 0) - c                                  # [src, dst, e] rows of lower ranks inside the expert
     send_flat = c.reshape(G, G * E)
     send_start = (torch.cumsum(send_flat, 1) - send_flat).reshape(G, G, E)   # [src, dst, e] start in src's send order
+    return c, tot, expert_off, src_off, send_start
 
-    # sender side: segments of my send order are (dst, e) in this order
-    seg_len = c[rank].reshape(-1)
+
+def fused_send_map(all_counts: torch.Tensor, rank: int, n_send: int):
+    """send_dest[i]: where send row i of this rank (rows sorted by global expert) lands, (dst << 40) | row in dst's
+    expert-major activation buffer (MoeReRouting's DstOffset, moe/moe_re_routing/README.md:12-26).  all_counts[src, dst, e]
+    = rows that rank src sends to local expert e of rank dst.  Nothing is read on the host."""
+    G, _, E = all_counts.shape
+    dev = all_counts.device
+    c, tot, expert_off, src_off, _ = _count_tables(all_counts)
+    seg_len = c[rank].reshape(-1)                                     # my send order is made of (dst, e) segments
     seg_end = torch.cumsum(seg_len, 0)
     i = torch.arange(n_send, device=dev)
     seg = torch.searchsorted(seg_end, i, right=True).clamp_(max=G * E - 1)
     within = i - (seg_end[seg] - seg_len[seg])
     base = (expert_off + src_off[rank]).reshape(-1)                   # [(dst, e)]
-    dst_rank = seg // E
-    send_dest = (dst_rank << ROW_BITS) | (base[seg] + within)
-    send_dest = torch.where(i < seg_end[-1], send_dest, torch.full_like(send_dest, -1))
+    send_dest = ((seg // E) << ROW_BITS) | (base[seg] + within)
+    return torch.where(i < seg_end[-1], send_dest, torch.full_like(send_dest, -1))
 
-    # receiver side: my activation buffer is ordered (e, src)
-    rlen = c[:, rank, :].t().reshape(-1)                              # [(e, src)]
+
+def fused_return_map(all_counts: torch.Tensor, rank: int, capacity: int):
+    """(ret_dest [capacity], group_list [E], n_recv [1]) of this rank as a receiver: ret_dest[p] = (src << 40) | row says
+    where the result of activation row p goes back - the position the row had in src's send order (-1 beyond n_recv);
+    group_list = running totals of rows per local expert."""
+    G, _, E = all_counts.shape
+    dev = all_counts.device
+    c, tot, _, _, send_start = _count_tables(all_counts)
+    rlen = c[:, rank, :].t().reshape(-1)                              # my activation buffer is ordered (e, src)
     rend = torch.cumsum(rlen, 0)
     p = torch.arange(capacity, device=dev)
     rseg = torch.searchsorted(rend, p, right=True).clamp_(max=G * E - 1)
     rwithin = p - (rend[rseg] - rlen[rseg])
-    src = rseg % G
-    e = rseg // G
     back = send_start[:, rank, :].t().reshape(-1)                     # [(e, src)] start of that segment in src's send order
-    ret_dest = (src << ROW_BITS) | (back[rseg] + rwithin)
+    ret_dest = ((rseg % G) << ROW_BITS) | (back[rseg] + rwithin)
     ret_dest = torch.where(p < rend[-1], ret_dest, torch.full_like(ret_dest, -1))
-    del e
-    group_list = torch.cumsum(tot[rank], 0)
-    return send_dest, ret_dest, group_list, rend[-1:].clone()
+    return ret_dest, torch.cumsum(tot[rank], 0), rend[-1:].clone()
+
+
+def fused_maps(all_counts: torch.Tensor, rank: int, n_send: int, capacity: int):
+    """Both row maps of the peer-memory pipeline: (send_dest, ret_dest, group_list, n_recv)."""
+    return (fused_send_map(all_counts, rank, n_send),) + fused_return_map(all_counts, rank, capacity)
 
 
 class FusedExpertParallelFFN:
@@ -285,6 +291,7 @@ class FusedExpertParallelFFN:
         self.result = self.buf_y.view(torch.bfloat16, (self.n_send, hidden_out))
         self.overflow = torch.zeros(1, dtype=torch.int32, device=dev)
         self._token = torch.zeros(1, dtype=torch.float32, device=dev)
+        self._graph = None
         self.trace = None   # set to a list to collect (label, CUDA event) marks without synchronising
 
     def _mark(self, label):
@@ -314,15 +321,20 @@ class FusedExpertParallelFFN:
         else:
             allc = plan.send_counts.reshape(1, 1, E)
         self._mark("counts_gathered")
-        send_dest, ret_dest, group_list, _ = fused_maps(allc, self.rank, self.n_send, self.capacity)
-        self._mark("maps")
+        send_dest = fused_send_map(allc, self.rank, self.n_send)
+        # start with the rows of the next rank (then wrap around), so that the ranks fan out over different destinations
+        per_dst = plan.send_counts.sum(1)
+        first_row = (torch.cumsum(per_dst, 0) - per_dst)[(self.rank + 1) % G].reshape(1).to(torch.int64).contiguous()
+        self._mark("send_map")
         stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
         p = lambda t: C.c_void_p(t.data_ptr())  # noqa: E731
         rc = L.gmmB200EpDispatch(p(x), p(x_scale), p(plan.src_token), p(send_dest), self.n_send, self.hidden, self.capacity,
-                                 self.buf_x.ptr_array(), self.buf_s.ptr_array(), G, p(self.overflow), stream)
+                                 self.buf_x.ptr_array(), self.buf_s.ptr_array(), G, p(self.overflow), p(first_row), stream)
         if rc != 0:
             raise acl.AclnnError(rc, "gmmB200EpDispatch")
         self._mark("dispatch_kernel")
+        ret_dest, group_list, _ = fused_return_map(allc, self.rank, self.capacity)   # while the other ranks' rows arrive
+        self._mark("return_map")
         self._barrier()   # all rows for my experts have landed
         self._mark("barrier1")
         q, qs = acl.grouped_matmul_swiglu_quant(self.act, self.w1, self.w1_scale, self.act_scale, group_list)
@@ -334,7 +346,31 @@ class FusedExpertParallelFFN:
         self._mark("barrier2")
         return {"y": self.result, "plan": plan, "group_list": group_list}
 
+    def capture(self, x: torch.Tensor, x_scale: torch.Tensor, topk_ids: torch.Tensor):
+        """Record one step into a CUDA graph.  Shapes are static (buffers are sized by capacity and nothing is read on
+        the host), so the whole step - routing plan, count exchange, row maps, dispatch, both GEMMs, barriers - replays
+        with one launch and no Python in between.  Inputs are copied into fixed tensors before every replay."""
+        self._gx, self._gs, self._gt = torch.empty_like(x), torch.empty_like(x_scale), torch.empty_like(topk_ids)
+        self._gx.copy_(x); self._gs.copy_(x_scale); self._gt.copy_(topk_ids)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):   # warm-up outside capture: lazy initialisation of kernels, NCCL and the workspace pool
+                self.forward(self._gx, self._gs, self._gt)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self._graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self._graph):
+            self._graph_out = self.forward(self._gx, self._gs, self._gt)
+        return self
+
+    def replay(self, x: torch.Tensor, x_scale: torch.Tensor, topk_ids: torch.Tensor):
+        self._gx.copy_(x, non_blocking=True); self._gs.copy_(x_scale, non_blocking=True); self._gt.copy_(topk_ids, non_blocking=True)
+        self._graph.replay()
+        return self._graph_out
+
     def close(self):
+        self._graph = None
         for b in (self.buf_x, self.buf_s, self.buf_y):
             b.close()
 
@@ -408,10 +444,15 @@ def _rows_of(res):
     return sum(r["rows_computed"] for r in res)
 
 
-def _timed_steps(ffn, d, steps, warmup, world):
+def _timed_steps(ffn, d, steps, warmup, world, use_graph=False):
     import time
+    if use_graph and hasattr(ffn, "capture"):
+        ffn.capture(d["x"], d["xs"], d["topk"])
+        fwd = ffn.replay
+    else:
+        fwd = ffn.forward
     for _ in range(max(warmup, 3)):
-        res = ffn.forward(d["x"], d["xs"], d["topk"])
+        res = fwd(d["x"], d["xs"], d["topk"])
     torch.cuda.synchronize()
     rows = _rows_of(res)
     if world > 1:
@@ -421,7 +462,7 @@ def _timed_steps(ffn, d, steps, warmup, world):
     t0 = time.perf_counter()
     ev0.record()
     for _ in range(steps):
-        ffn.forward(d["x"], d["xs"], d["topk"])
+        fwd(d["x"], d["xs"], d["topk"])
     ev1.record()
     torch.cuda.synchronize()
     wall = (time.perf_counter() - t0) / steps * 1e3
@@ -441,7 +482,7 @@ def _e2e_steps(ffn, d, steps):
     def step():
         nonlocal host_out
         dx.copy_(hx, non_blocking=True); ds.copy_(hs, non_blocking=True); dt.copy_(ht, non_blocking=True)
-        res = ffn.forward(dx, ds, dt)
+        res = ffn.replay(dx, ds, dt) if getattr(ffn, "_graph", None) is not None else ffn.forward(dx, ds, dt)
         ys = [res["y"]] if isinstance(res, dict) else [r["y"] for r in res]
         if host_out is None:
             host_out = [torch.empty_like(y, device="cpu").pin_memory() for y in ys]
@@ -491,7 +532,7 @@ def bench_main(args):
     if sampler:
         sampler.start()
         sampler.mark_begin()
-    ms, wall, rows_local = _timed_steps(ffn, d, args.steps, args.warmup, world)
+    ms, wall, rows_local = _timed_steps(ffn, d, args.steps, args.warmup, world, use_graph=args.ep_graph and world > 1)
     if sampler:
         sampler.mark_end()
         clocks = sampler.stop()
@@ -499,12 +540,23 @@ def bench_main(args):
     dropped = int(ffn.overflow.item()) if hasattr(ffn, "overflow") else 0
     trace = None
     if args.ep_phases and hasattr(ffn, "trace"):
+        for _ in range(2):
+            ffn.forward(d["x"], d["xs"], d["topk"])   # eager warm-up (the timed steps may have been graph replays)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
         ffn.trace = []
         ffn.forward(d["x"], d["xs"], d["topk"])
         torch.cuda.synchronize()
         tr = ffn.trace
-        trace = [(b[0], round(a[1].elapsed_time(b[1]), 3)) for a, b in zip(tr[:-1], tr[1:])]
+        mine = [(b[0], round(a[1].elapsed_time(b[1]), 3)) for a, b in zip(tr[:-1], tr[1:])]
         ffn.trace = None
+        if world > 1:
+            allt = [None] * world
+            dist.all_gather_object(allt, mine)
+            trace = [(mine[i][0], min(t_[i][1] for t_ in allt), max(t_[i][1] for t_ in allt)) for i in range(len(mine))]
+        else:
+            trace = mine
     stats = torch.tensor([ms, float(rows_local), float(dropped), e2e_ms], dtype=torch.float64, device=dev)
     if world > 1:
         allst = [torch.empty_like(stats) for _ in range(world)]
@@ -526,7 +578,8 @@ def bench_main(args):
             "config": {"workload": f"c5 expert-parallel FFN: 256 experts over {world} GPU(s), {T} tokens per GPU, top-8, swiglu_quant "
                                    f"K=7168 N=4096 then down GEMM K=2048 N=7168; {how}",
                        "l2": "inputs larger than L2", "tokens_per_s": T * world / (ms_max * 1e-3), "rows_total": rows_total,
-                       "host_ms_per_step": wall, "dropped_rows": dropped, "phase_ms": trace},
+                       "host_ms_per_step": wall, "dropped_rows": dropped, "phase_ms": trace,
+                       "cuda_graph": bool(args.ep_graph and args.ep_impl == "fused" and world > 1)},
             "roofline": {"bound": "tensor", "achieved": tops / world, "peak": int8_peak, "unit": "TFLOP/s", "frac": tops / world / int8_peak,
                          "traffic": None, "kernel": "whole step per GPU (dispatch, two GEMM kernels, exchange)",
                          "peak_basis": f"2 x sustained bf16 of {peaks['source']} ({peaks['bf16_tflops_sustained']} TFLOP/s); int8 ops "
