@@ -272,7 +272,11 @@ class FusedExpertParallelFFN:
     """
 
     def __init__(self, n_experts: int, hidden: int, hidden_out: int, w1, w1_scale, w2, w2_scale, *, tokens: int, top_k: int,
-                 capacity: int, group=None):
+                 capacity: int, group=None, chunks: int = 1):
+        """capacity: rows this rank can receive per step (all chunks together).  chunks > 1 splits the tokens; the
+        dispatch of chunk c+1 then runs on a second stream beside the GEMMs of chunk c."""
+        import ctypes as C
+
         from .peer import PeerBuffer
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -280,17 +284,26 @@ class FusedExpertParallelFFN:
         self.n_experts, self.e_local = n_experts, n_experts // self.world
         self.hidden, self.hidden_out = hidden, hidden_out
         self.w1, self.w1_scale, self.w2, self.w2_scale = w1, w1_scale, w2, w2_scale
+        self.tokens, self.top_k, self.chunks = tokens, top_k, chunks
+        self.bounds = [tokens * c // chunks for c in range(chunks + 1)]
         self.n_send = tokens * top_k
         self.capacity = capacity
-        self.buf_x = PeerBuffer(capacity * hidden, group)
-        self.buf_s = PeerBuffer(capacity * 4, group)
+        self.cap_c = (capacity + chunks - 1) // chunks          # rows per chunk buffer
+        self.buf_x = PeerBuffer(chunks * self.cap_c * hidden, group)
+        self.buf_s = PeerBuffer(chunks * self.cap_c * 4, group)
         self.buf_y = PeerBuffer(self.n_send * hidden_out * 2, group)
         dev = torch.device("cuda", torch.cuda.current_device())
-        self.act = self.buf_x.view(torch.int8, (capacity, hidden))
-        self.act_scale = self.buf_s.view(torch.float32, (capacity,))
+        self.act = self.buf_x.view(torch.int8, (chunks, self.cap_c, hidden))
+        self.act_scale = self.buf_s.view(torch.float32, (chunks, self.cap_c))
         self.result = self.buf_y.view(torch.bfloat16, (self.n_send, hidden_out))
+        # per chunk: every rank's activation / scale buffer of that chunk
+        self._x_ptrs = [(C.c_void_p * self.world)(*[C.c_void_p(p + c * self.cap_c * hidden) for p in self.buf_x.ptrs])
+                        for c in range(chunks)]
+        self._s_ptrs = [(C.c_void_p * self.world)(*[C.c_void_p(p + c * self.cap_c * 4) for p in self.buf_s.ptrs])
+                        for c in range(chunks)]
         self.overflow = torch.zeros(1, dtype=torch.int32, device=dev)
         self._token = torch.zeros(1, dtype=torch.float32, device=dev)
+        self._side = torch.cuda.Stream() if chunks > 1 else None
         self._graph = None
         self.trace = None   # set to a list to collect (label, CUDA event) marks without synchronising
 
@@ -301,50 +314,80 @@ class FusedExpertParallelFFN:
             self.trace.append((label, ev))
 
     def _barrier(self):
-        """Stream-ordered barrier across the ranks: completes on this rank's stream only after every rank's earlier
-        work on its stream (the kernels that store into peer memory) has finished."""
+        """Stream-ordered barrier across the ranks: completes on the current stream only after every rank's earlier
+        work on the stream it called this from (the kernels that store into peer memory) has finished."""
         if self.world > 1:
             dist.all_reduce(self._token, group=self.group)
 
-    def forward(self, x: torch.Tensor, x_scale: torch.Tensor, topk_ids: torch.Tensor):
+    def _dispatch(self, c, x, x_scale, plan, send_dest, first_row):
         import ctypes as C
 
         from . import _lib, acl
-        L = _lib.lib()
-        G, E = self.world, self.e_local
-        self._mark("start")
-        plan = dispatch_plan(topk_ids, self.n_experts, G)
-        self._mark("plan")
-        if G > 1:
-            allc = torch.empty((G, G, E), dtype=plan.send_counts.dtype, device=x.device)
-            dist.all_gather_into_tensor(allc, plan.send_counts.contiguous(), group=self.group)
-        else:
-            allc = plan.send_counts.reshape(1, 1, E)
-        self._mark("counts_gathered")
-        send_dest = fused_send_map(allc, self.rank, self.n_send)
-        # start with the rows of the next rank (then wrap around), so that the ranks fan out over different destinations
-        per_dst = plan.send_counts.sum(1)
-        first_row = (torch.cumsum(per_dst, 0) - per_dst)[(self.rank + 1) % G].reshape(1).to(torch.int64).contiguous()
-        self._mark("send_map")
-        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
         p = lambda t: C.c_void_p(t.data_ptr())  # noqa: E731
-        rc = L.gmmB200EpDispatch(p(x), p(x_scale), p(plan.src_token), p(send_dest), self.n_send, self.hidden, self.capacity,
-                                 self.buf_x.ptr_array(), self.buf_s.ptr_array(), G, p(self.overflow), p(first_row), stream)
+        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        n = int(plan.src_token.shape[0])
+        rc = _lib.lib().gmmB200EpDispatch(p(x), p(x_scale), p(plan.src_token), p(send_dest), n, self.hidden, self.cap_c,
+                                          self._x_ptrs[c], self._s_ptrs[c], self.world, p(self.overflow), p(first_row), stream)
         if rc != 0:
             raise acl.AclnnError(rc, "gmmB200EpDispatch")
+
+    def forward(self, x: torch.Tensor, x_scale: torch.Tensor, topk_ids: torch.Tensor):
+        from . import acl
+        G, E, C_ = self.world, self.e_local, self.chunks
+        k = self.top_k
+        self._mark("start")
+        # routing plans and row maps of all chunks first (small kernels), one count exchange for all chunks
+        plans = [dispatch_plan(topk_ids[self.bounds[c]:self.bounds[c + 1]], self.n_experts, G) for c in range(C_)]
+        self._mark("plan")
+        mine = torch.stack([pl.send_counts for pl in plans]).contiguous()                 # [C, G(dst), E]
+        if G > 1:
+            allc = torch.empty((G,) + tuple(mine.shape), dtype=mine.dtype, device=x.device)  # [G(src), C, G(dst), E]
+            dist.all_gather_into_tensor(allc, mine, group=self.group)
+        else:
+            allc = mine.reshape(1, C_, 1, E)
+        self._mark("counts_gathered")
+        send_dest, first_row, tok = [], [], []
+        for c, pl in enumerate(plans):
+            n_c = (self.bounds[c + 1] - self.bounds[c]) * k
+            send_dest.append(fused_send_map(allc[:, c], self.rank, n_c))
+            # start with the rows of the next rank (then wrap around), so that the ranks fan out over different destinations
+            per_dst = pl.send_counts.sum(1)
+            first_row.append((torch.cumsum(per_dst, 0) - per_dst)[(self.rank + 1) % G].reshape(1).to(torch.int64).contiguous())
+            pl.src_token = pl.src_token + self.bounds[c]
+        self._mark("send_map")
+
+        self._dispatch(0, x, x_scale, plans[0], send_dest[0], first_row[0])
         self._mark("dispatch_kernel")
-        ret_dest, group_list, _ = fused_return_map(allc, self.rank, self.capacity)   # while the other ranks' rows arrive
-        self._mark("return_map")
-        self._barrier()   # all rows for my experts have landed
-        self._mark("barrier1")
-        q, qs = acl.grouped_matmul_swiglu_quant(self.act, self.w1, self.w1_scale, self.act_scale, group_list)
-        self._mark("swiglu_quant")
-        acl.grouped_matmul_v4(q, self.w2, self.w2_scale, qs, group_list, group_list_type=0, out_row_index=ret_dest,
-                              out_peers=self.buf_y.ptrs, out=None)
-        self._mark("down_gemm")
-        self._barrier()   # every rank's results have landed, and everyone is done reading its activation buffer
+        main = torch.cuda.current_stream()
+        landed = [None] * C_
+        group_lists = []
+        for c in range(C_):
+            ret_dest, group_list, _ = fused_return_map(allc[:, c], self.rank, self.cap_c)   # while rows are still arriving
+            ret_dest = torch.where(ret_dest >= 0, ret_dest + self.bounds[c] * k, ret_dest)  # rows of chunk c in the result buffer
+            if c == 0:
+                self._mark("return_map")
+                self._barrier()   # all rows of chunk 0 for my experts have landed
+                self._mark("barrier1")
+            else:
+                main.wait_event(landed[c])
+            if c + 1 < C_:
+                # the next chunk's dispatch (and the barrier after it) runs beside this chunk's GEMMs
+                self._side.wait_stream(main)
+                with torch.cuda.stream(self._side):
+                    self._dispatch(c + 1, x, x_scale, plans[c + 1], send_dest[c + 1], first_row[c + 1])
+                    self._barrier()
+                    landed[c + 1] = torch.cuda.Event()
+                    landed[c + 1].record()
+            q, qs = acl.grouped_matmul_swiglu_quant(self.act[c], self.w1, self.w1_scale, self.act_scale[c], group_list)
+            self._mark(f"swiglu_quant{c}")
+            acl.grouped_matmul_v4(q, self.w2, self.w2_scale, qs, group_list, group_list_type=0, out_row_index=ret_dest,
+                                  out_peers=self.buf_y.ptrs, out=None)
+            self._mark(f"down_gemm{c}")
+            group_lists.append(group_list)
+        self._barrier()   # every rank's results have landed, and everyone is done reading its activation buffers
         self._mark("barrier2")
-        return {"y": self.result, "plan": plan, "group_list": group_list}
+        chunk_out = [{"y": self.result[self.bounds[c] * k:self.bounds[c + 1] * k], "plan": plans[c]} for c in range(C_)]
+        return {"y": self.result, "plan": plans[0], "group_list": group_lists[0], "group_lists": group_lists, "chunks": chunk_out}
 
     def capture(self, x: torch.Tensor, x_scale: torch.Tensor, topk_ids: torch.Tensor):
         """Record one step into a CUDA graph.  Shapes are static (buffers are sized by capacity and nothing is read on
@@ -424,9 +467,11 @@ def _make_rank_data(dev, world, rank, tokens):
 
 def _build_ffn(args, d, tokens, world):
     if args.ep_impl == "fused":
+        chunks = args.ep_chunks if args.ep_chunks > 0 else (2 if world >= 4 else 1)
         ffn = FusedExpertParallelFFN(N_EXPERTS, HIDDEN, HIDDEN, d["w1"], d["w1s"], d["w2"], d["w2s"], tokens=tokens, top_k=TOP_K,
-                                     capacity=2 * tokens * TOP_K)
-        return ffn, "dispatch by peer stores, results stored into the owners' buffers by the down-GEMM epilogue", 3
+                                     capacity=2 * tokens * TOP_K, chunks=chunks)
+        return ffn, (f"dispatch by peer stores, results stored into the owners' buffers by the down-GEMM epilogue, {chunks} "
+                     "token chunk(s) with the next chunk's dispatch beside the GEMMs"), 3 * chunks
     chunks = args.ep_chunks if args.ep_chunks > 0 else default_chunks(world)
     reserve = args.ep_reserve_sms if args.ep_reserve_sms >= 0 else (16 if world > 1 and chunks > 1 else 0)
     if reserve > 0:
@@ -440,7 +485,7 @@ def _build_ffn(args, d, tokens, world):
 
 def _rows_of(res):
     if isinstance(res, dict):
-        return int(res["group_list"][-1].item())
+        return sum(int(g[-1].item()) for g in res["group_lists"])
     return sum(r["rows_computed"] for r in res)
 
 

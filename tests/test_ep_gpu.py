@@ -64,26 +64,31 @@ def test_single_rank_ffn_matches_oracle(oracle, chunks):
     _check(oracle, res, chunks, x, xs, topk, w1, s1, w2, s2)
 
 
-def _run_fused(O, dev, rank, world, w1, s1, w2, s2, x, xs, topk):
+def _run_fused(O, dev, rank, world, w1, s1, w2, s2, x, xs, topk, chunks=1):
     el = N_EXPERTS // world
     lo, hi = rank * el, (rank + 1) * el
     t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)  # noqa: E731
     ffn = ep.FusedExpertParallelFFN(N_EXPERTS, H, H, t(w1[lo:hi]), t(s1[lo:hi]), t(w2[lo:hi]), t(s2[lo:hi]), tokens=T, top_k=TOP_K,
-                                    capacity=2 * T * TOP_K)
+                                    capacity=2 * T * TOP_K, chunks=chunks)
     for _ in range(2):  # twice: the second step runs over the first one's buffers
         res = ffn.forward(t(x), t(xs), t(topk))
     torch.cuda.synchronize()
     assert int(ffn.overflow.item()) == 0
-    _check(O, [{"y": res["y"], "plan": res["plan"]}], 1, x, xs, topk, w1, s1, w2, s2)
+    outs = []
+    for c, ch in enumerate(res["chunks"]):  # _check expects chunk-local token numbers in the plan
+        pl = ch["plan"]
+        outs.append({"y": ch["y"], "plan": ep.ChunkPlan(order=pl.order, src_token=pl.src_token - ffn.bounds[c], send_counts=pl.send_counts)})
+    _check(O, outs, chunks, x, xs, topk, w1, s1, w2, s2)
     ffn.close()
 
 
-def test_single_rank_fused_ffn_matches_oracle(oracle):
+@pytest.mark.parametrize("chunks", [1, 3])
+def test_single_rank_fused_ffn_matches_oracle(oracle, chunks):
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     w1, w2, s1, s2 = _weights()
     x, xs, topk = _inputs(0)
-    _run_fused(oracle, torch.device("cuda:0"), 0, 1, w1, s1, w2, s2, x, xs, topk)
+    _run_fused(oracle, torch.device("cuda:0"), 0, 1, w1, s1, w2, s2, x, xs, topk, chunks=chunks)
 
 
 def _rank_main():
@@ -104,6 +109,7 @@ def _rank_main():
     torch.cuda.synchronize()
     _check(O, res, 2, x, xs, topk, w1, s1, w2, s2)
     _run_fused(O, dev, rank, world, w1, s1, w2, s2, x, xs, topk)
+    _run_fused(O, dev, rank, world, w1, s1, w2, s2, x, xs, topk, chunks=2)
     dist.barrier()
     dist.destroy_process_group()
     print(f"rank {rank} ok")
