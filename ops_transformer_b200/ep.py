@@ -467,7 +467,7 @@ def _make_rank_data(dev, world, rank, tokens):
 
 def _build_ffn(args, d, tokens, world):
     if args.ep_impl == "fused":
-        chunks = args.ep_chunks if args.ep_chunks > 0 else (2 if world >= 4 else 1)
+        chunks = args.ep_chunks if args.ep_chunks > 0 else 1   # measured on 8 GPUs: 1 chunk 7.1 ms, 2 chunks 7.6 ms, 4 chunks 8.7 ms
         ffn = FusedExpertParallelFFN(N_EXPERTS, HIDDEN, HIDDEN, d["w1"], d["w1s"], d["w2"], d["w2s"], tokens=tokens, top_k=TOP_K,
                                      capacity=2 * tokens * TOP_K, chunks=chunks)
         return ffn, (f"dispatch by peer stores, results stored into the owners' buffers by the down-GEMM epilogue, {chunks} "
