@@ -82,6 +82,26 @@ ACL_FUNC_VISIBILITY aclnnStatus gmmB200EpDispatch(const void *x, const void *xSc
                                                  void *const *peerScale, int32_t numPeers, void *overflowCounter,
                                                  const void *firstRow, aclrtStream stream);
 
+/* Routing for the expert-parallel dispatch, in two launches around the all-gather of the per-expert counts, without any
+ * read on the host.  topk: int64 [nPairs] global expert of every (token, slot) pair (pair i belongs to token i / topK).
+ *   gmmB200EpCount: totals[nExperts] (int64) = pairs per global expert, blockHist [ceil(nPairs/1024)][nExperts] (int32)
+ *                   = the same per block of 1024 pairs.
+ *   gmmB200EpRoute: allCounts int64 [world][world][expertsPerRank] = every rank's totals (all-gathered).  Writes the send
+ *                   order grouped by global expert: srcToken[pos] (= tokenBase + pair / topK), order[pos] (= pair),
+ *                   sendDest[pos] = (gpu << 40) | row in that GPU's expert-major activation buffer; retDest[capacity]:
+ *                   for every activation row of this rank (gpu << 40) | (resultBase + position in that GPU's send order),
+ *                   -1 beyond the rows received; groupList[expertsPerRank] running totals of this rank's experts;
+ *                   firstRow[1] for gmmB200EpDispatch.
+ * They play the part of the index outputs of the reference's MoeInitRouting / MoeDistributeDispatch
+ * (moe/moe_init_routing_v3/README.md:21-62, mc2/moe_distribute_dispatch_v2/README.md:216-250) and of MoeReRouting's
+ * offsets (moe/moe_re_routing/README.md:12-26). */
+ACL_FUNC_VISIBILITY aclnnStatus gmmB200EpCount(const void *topk, int64_t nPairs, int32_t nExperts, void *blockHist, void *totals,
+                                              aclrtStream stream);
+ACL_FUNC_VISIBILITY aclnnStatus gmmB200EpRoute(const void *topk, const void *blockHist, const void *allCounts, int64_t nPairs,
+                                              int32_t topK, int32_t world, int32_t expertsPerRank, int32_t rank, int64_t capacity,
+                                              int64_t tokenBase, int64_t resultBase, void *srcToken, void *order, void *sendDest,
+                                              void *retDest, void *groupList, void *firstRow, aclrtStream stream);
+
 /* Flat form of aclnnGroupedMatmulSwigluQuant. */
 ACL_FUNC_VISIBILITY aclnnStatus gmmB200GroupedMatmulSwigluQuantWorkspaceSize(int64_t m, int64_t k, int64_t n, int64_t e,
                                                                             uint64_t *workspaceSize);

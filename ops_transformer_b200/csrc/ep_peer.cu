@@ -59,6 +59,139 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const int8_t *__restri
     __threadfence_system();
 }
 
+
+// ---------------------------------------------------------------------------------------------------------
+// Routing: the send order of a rank's (token, slot) pairs and the row maps of the peer-memory pipeline, in two
+// launches with the count all-gather between them (the host never reads a value).
+//   ep_count_kernel : per-block histograms of the destination experts (blocks of kRouteBlock pairs) and the totals
+//   ep_route_kernel : from the all-gathered totals all_counts[src][dst][e]:
+//       send order  - pairs grouped by global expert (dst-major); inside an expert by block, inside a block in arrival
+//                     order of a shared-memory counter (any order inside an expert is valid: rows are independent);
+//       src_token[pos], order[pos], send_dest[pos] = (dst << 40) | row in dst's expert-major buffer (MoeReRouting's
+//                     DstOffset, moe/moe_re_routing/README.md:12-26);
+//       ret_dest[p]   = (src << 40) | position of activation row p in src's send order (where its result goes back);
+//       group_list[e] = running totals of this rank's local experts; first_row = first send row for rank+1.
+// ---------------------------------------------------------------------------------------------------------
+
+constexpr int kRouteBlock = 1024;   // pairs per block
+constexpr int kMaxSegments = 1024;  // world * experts_per_rank, also the most groups a GEMM call accepts
+
+__global__ void __launch_bounds__(256) ep_count_kernel(const long long *__restrict__ topk, int n_pairs, int n_experts,
+                                                        int *__restrict__ block_hist, long long *__restrict__ totals)
+{
+    __shared__ int h[kMaxSegments];
+    for (int i = threadIdx.x; i < n_experts; i += blockDim.x) h[i] = 0;
+    __syncthreads();
+    const int base = blockIdx.x * kRouteBlock;
+    for (int i = threadIdx.x; i < kRouteBlock && base + i < n_pairs; i += blockDim.x) {
+        const long long e = topk[base + i];
+        if (e >= 0 && e < n_experts) atomicAdd(&h[(int)e], 1);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_experts; i += blockDim.x) {
+        block_hist[(size_t)blockIdx.x * n_experts + i] = h[i];
+        if (h[i]) atomicAdd(reinterpret_cast<unsigned long long *>(totals + i), (unsigned long long)h[i]);
+    }
+}
+
+struct RouteParams {
+    const long long *topk;        // [n_pairs] global expert of every (token, slot) pair
+    const int *block_hist;        // [n_blocks][world*E]
+    const long long *all_counts;  // [world(src)][world(dst)][E]
+    int n_pairs, top_k, world, experts, rank, n_blocks, capacity, token_base;
+    long long result_base;        // first row of this chunk in the result buffers
+    long long *src_token, *order, *send_dest;  // [n_pairs]
+    long long *ret_dest;          // [capacity]
+    long long *group_list;        // [E]
+    long long *first_row;         // [1]
+};
+
+// grid = n_blocks (send side) + ceil(capacity / kRouteBlock) (return side)
+__global__ void __launch_bounds__(256) ep_route_kernel(const RouteParams p)
+{
+    __shared__ long long s_a[kMaxSegments];   // send side: first send position of this block's pairs per expert
+    __shared__ long long s_b[kMaxSegments];   // send side: destination row of the segment's first pair / return side: ends
+    __shared__ long long s_c[kMaxSegments];   // return side: position in the source's send order of the segment's first row
+    __shared__ int s_cursor[kMaxSegments];
+    const int G = p.world, E = p.experts, S = G * E, tid = threadIdx.x;
+    const long long *C = p.all_counts;
+    if ((int)blockIdx.x < p.n_blocks) {
+        // ---- send side ----
+        for (int seg = tid; seg < S; seg += blockDim.x) {
+            const int dst = seg / E, e = seg % E;
+            long long seg_start = 0;                         // pairs of this rank for segments before (dst, e)
+            for (int s2 = 0; s2 < seg; ++s2) seg_start += C[(size_t)p.rank * S + s2];
+            long long before_blocks = 0;                     // same segment, earlier blocks
+            for (int b = 0; b < (int)blockIdx.x; ++b) before_blocks += p.block_hist[(size_t)b * S + seg];
+            long long expert_off = 0;                        // rows of dst's experts before e
+            for (int e2 = 0; e2 < e; ++e2)
+                for (int s3 = 0; s3 < G; ++s3) expert_off += C[((size_t)s3 * G + dst) * E + e2];
+            long long src_off = 0;                           // rows of lower ranks inside the expert
+            for (int s3 = 0; s3 < p.rank; ++s3) src_off += C[((size_t)s3 * G + dst) * E + e];
+            s_a[seg] = seg_start + before_blocks;
+            s_b[seg] = expert_off + src_off + before_blocks;
+            s_cursor[seg] = 0;
+        }
+        __syncthreads();
+        const int base = blockIdx.x * kRouteBlock;
+        for (int i = tid; i < kRouteBlock && base + i < p.n_pairs; i += blockDim.x) {
+            const long long ge = p.topk[base + i];
+            if (ge < 0 || ge >= S) continue;
+            const int w = atomicAdd(&s_cursor[(int)ge], 1);
+            const long long pos = s_a[(int)ge] + w;
+            p.src_token[pos] = (long long)p.token_base + (base + i) / p.top_k;
+            p.order[pos] = base + i;
+            p.send_dest[pos] = ((long long)(ge / E) << 40) | (s_b[(int)ge] + w);
+        }
+        if (blockIdx.x == 0) {
+            if (tid == 0) {
+                const int nxt = (p.rank + 1) % G;
+                long long fr = 0;
+                for (int s2 = 0; s2 < nxt * E; ++s2) fr += C[(size_t)p.rank * S + s2];
+                *p.first_row = fr;
+            }
+            for (int e = tid; e < E; e += blockDim.x) {
+                long long run = 0;
+                for (int e2 = 0; e2 <= e; ++e2)
+                    for (int s3 = 0; s3 < G; ++s3) run += C[((size_t)s3 * G + p.rank) * E + e2];
+                p.group_list[e] = run;
+            }
+        }
+    } else {
+        // ---- return side: this rank's activation buffer is ordered (e, src) ----
+        for (int seg = tid; seg < S; seg += blockDim.x) {
+            const int e = seg / G, src = seg % G;
+            long long back = 0;                              // start of segment (rank, e) in src's send order
+            for (int s2 = 0; s2 < p.rank * E + e; ++s2) back += C[(size_t)src * S + s2];
+            s_c[seg] = back;
+            s_b[seg] = C[((size_t)src * G + p.rank) * E + e];  // segment length, turned into running ends below
+        }
+        __syncthreads();
+        if (tid == 0) {
+            long long run = 0;
+            for (int seg = 0; seg < S; ++seg) { run += s_b[seg]; s_b[seg] = run; }
+        }
+        __syncthreads();
+        const long long total = s_b[S - 1];
+        const long long pbase = (long long)((int)blockIdx.x - p.n_blocks) * kRouteBlock;
+        for (int i = tid; i < kRouteBlock; i += blockDim.x) {
+            const long long q = pbase + i;
+            if (q >= p.capacity) break;
+            long long out = -1;
+            if (q < total) {
+                int lo = 0, hi = S - 1;                      // first segment whose end is beyond q
+                while (lo < hi) {
+                    const int mid = (lo + hi) >> 1;
+                    if (s_b[mid] > q) hi = mid; else lo = mid + 1;
+                }
+                const long long seg_begin = lo ? s_b[lo - 1] : 0;
+                out = ((long long)(lo % G) << 40) | (p.result_base + s_c[lo] + (q - seg_begin));
+            }
+            p.ret_dest[q] = out;
+        }
+    }
+}
+
 }  // namespace
 
 extern "C" {
@@ -138,6 +271,50 @@ aclnnStatus gmmB200EpDispatch(const void *x, const void *xScale, const void *src
         static_cast<const long long *>(firstRow));
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return gmm::fail(ACLNN_ERR_INNER, "dispatch kernel launch failed: %s", cudaGetErrorString(e));
+    return ACLNN_SUCCESS;
+}
+
+aclnnStatus gmmB200EpCount(const void *topk, int64_t nPairs, int32_t nExperts, void *blockHist, void *totals, aclrtStream stream)
+{
+    gmm::clear_error();
+    if (!topk || !blockHist || !totals) return gmm::fail(ACLNN_ERR_PARAM_NULLPTR, "topk, blockHist and totals must not be nullptr.");
+    if (nPairs <= 0 || nPairs > 0x7fffffff || nExperts <= 0 || nExperts > kMaxSegments)
+        return gmm::fail(ACLNN_ERR_PARAM_INVALID, "need 0 < nPairs < 2^31 and 0 < nExperts <= %d.", kMaxSegments);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemsetAsync(totals, 0, sizeof(long long) * (size_t)nExperts, st);
+    if (e != cudaSuccess) return gmm::fail(ACLNN_ERR_INNER, "memset failed: %s", cudaGetErrorString(e));
+    const int blocks = (int)((nPairs + kRouteBlock - 1) / kRouteBlock);
+    ep_count_kernel<<<blocks, 256, 0, st>>>(static_cast<const long long *>(topk), (int)nPairs, nExperts, static_cast<int *>(blockHist),
+                                            static_cast<long long *>(totals));
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return gmm::fail(ACLNN_ERR_INNER, "count kernel launch failed: %s", cudaGetErrorString(e));
+    return ACLNN_SUCCESS;
+}
+
+aclnnStatus gmmB200EpRoute(const void *topk, const void *blockHist, const void *allCounts, int64_t nPairs, int32_t topK, int32_t world,
+                           int32_t expertsPerRank, int32_t rank, int64_t capacity, int64_t tokenBase, int64_t resultBase, void *srcToken,
+                           void *order, void *sendDest, void *retDest, void *groupList, void *firstRow, aclrtStream stream)
+{
+    gmm::clear_error();
+    if (!topk || !blockHist || !allCounts || !srcToken || !order || !sendDest || !retDest || !groupList || !firstRow)
+        return gmm::fail(ACLNN_ERR_PARAM_NULLPTR, "all buffers must not be nullptr.");
+    if (nPairs <= 0 || nPairs > 0x7fffffff || topK <= 0 || world < 1 || world > 8 || expertsPerRank < 1 ||
+        world * expertsPerRank > kMaxSegments || rank < 0 || rank >= world || capacity <= 0 || capacity > 0x7fffffff)
+        return gmm::fail(ACLNN_ERR_PARAM_INVALID, "bad sizes (world <= 8, world*expertsPerRank <= %d, sizes below 2^31).", kMaxSegments);
+    RouteParams p;
+    p.topk = static_cast<const long long *>(topk);
+    p.block_hist = static_cast<const int *>(blockHist);
+    p.all_counts = static_cast<const long long *>(allCounts);
+    p.n_pairs = (int)nPairs; p.top_k = topK; p.world = world; p.experts = expertsPerRank; p.rank = rank;
+    p.n_blocks = (int)((nPairs + kRouteBlock - 1) / kRouteBlock);
+    p.capacity = (int)capacity; p.token_base = (int)tokenBase; p.result_base = resultBase;
+    p.src_token = static_cast<long long *>(srcToken); p.order = static_cast<long long *>(order);
+    p.send_dest = static_cast<long long *>(sendDest); p.ret_dest = static_cast<long long *>(retDest);
+    p.group_list = static_cast<long long *>(groupList); p.first_row = static_cast<long long *>(firstRow);
+    const int grid = p.n_blocks + (int)((capacity + kRouteBlock - 1) / kRouteBlock);
+    ep_route_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return gmm::fail(ACLNN_ERR_INNER, "route kernel launch failed: %s", cudaGetErrorString(e));
     return ACLNN_SUCCESS;
 }
 

@@ -303,6 +303,18 @@ class FusedExpertParallelFFN:
                         for c in range(chunks)]
         self.overflow = torch.zeros(1, dtype=torch.int32, device=dev)
         self._token = torch.zeros(1, dtype=torch.float32, device=dev)
+        # routing state written by the library's count / route kernels (two launches per chunk instead of a sort and
+        # some sixty small tensor kernels); route_kernels=False keeps the tensor formulation used by the CPU tests
+        self.route_kernels = True
+        i64 = dict(dtype=torch.int64, device=dev)
+        self._r = []
+        for c in range(chunks):
+            n_c = (self.bounds[c + 1] - self.bounds[c]) * top_k
+            self._r.append(dict(n=n_c, hist=torch.empty(((n_c + 1023) // 1024, n_experts), dtype=torch.int32, device=dev),
+                                src_token=torch.empty(n_c, **i64), order=torch.empty(n_c, **i64), send_dest=torch.empty(n_c, **i64),
+                                ret_dest=torch.empty(self.cap_c, **i64), group_list=torch.empty(self.e_local, **i64),
+                                first_row=torch.empty(1, **i64)))
+        self._totals = torch.empty((chunks, self.world, self.e_local), **i64)
         self._side = torch.cuda.Stream() if chunks > 1 else None
         self._graph = None
         self.trace = None   # set to a list to collect (label, CUDA event) marks without synchronising
@@ -336,6 +348,8 @@ class FusedExpertParallelFFN:
         G, E, C_ = self.world, self.e_local, self.chunks
         k = self.top_k
         self._mark("start")
+        if self.route_kernels:
+            return self._forward_kernels(x, x_scale, topk_ids)
         # routing plans and row maps of all chunks first (small kernels), one count exchange for all chunks
         plans = [dispatch_plan(topk_ids[self.bounds[c]:self.bounds[c + 1]], self.n_experts, G) for c in range(C_)]
         self._mark("plan")
@@ -386,6 +400,68 @@ class FusedExpertParallelFFN:
             group_lists.append(group_list)
         self._barrier()   # every rank's results have landed, and everyone is done reading its activation buffers
         self._mark("barrier2")
+        chunk_out = [{"y": self.result[self.bounds[c] * k:self.bounds[c + 1] * k], "plan": plans[c]} for c in range(C_)]
+        return {"y": self.result, "plan": plans[0], "group_list": group_lists[0], "group_lists": group_lists, "chunks": chunk_out}
+
+    def _forward_kernels(self, x, x_scale, topk_ids):
+        """forward() with the routing done by gmmB200EpCount / gmmB200EpRoute."""
+        import ctypes as C
+
+        from . import _lib, acl
+        L = _lib.lib()
+        G, E, C_, k = self.world, self.e_local, self.chunks, self.top_k
+        p = lambda t: C.c_void_p(t.data_ptr())  # noqa: E731
+        st = lambda: C.c_void_p(torch.cuda.current_stream().cuda_stream)  # noqa: E731
+        topk_ids = topk_ids.contiguous()
+        tk = [topk_ids[self.bounds[c]:self.bounds[c + 1]] for c in range(C_)]
+        for c in range(C_):
+            rc = L.gmmB200EpCount(p(tk[c]), self._r[c]["n"], self.n_experts, p(self._r[c]["hist"]), p(self._totals[c]), st())
+            if rc != 0:
+                raise acl.AclnnError(rc, "gmmB200EpCount")
+        self._mark("plan")
+        if G > 1:
+            allc = torch.empty((G, C_, G, E), dtype=torch.int64, device=x.device)
+            dist.all_gather_into_tensor(allc, self._totals, group=self.group)
+        else:
+            allc = self._totals.reshape(1, C_, 1, E)
+        self._mark("counts_gathered")
+        plans = []
+        for c in range(C_):
+            r = self._r[c]
+            ac = allc[:, c].contiguous()
+            rc = L.gmmB200EpRoute(p(tk[c]), p(r["hist"]), p(ac), r["n"], k, G, E, self.rank, self.cap_c, self.bounds[c],
+                                  self.bounds[c] * k, p(r["src_token"]), p(r["order"]), p(r["send_dest"]), p(r["ret_dest"]),
+                                  p(r["group_list"]), p(r["first_row"]), st())
+            if rc != 0:
+                raise acl.AclnnError(rc, "gmmB200EpRoute")
+            plans.append(ChunkPlan(order=r["order"], src_token=r["src_token"], send_counts=self._totals[c]))
+        self._mark("send_map")
+        self._dispatch(0, x, x_scale, plans[0], self._r[0]["send_dest"], self._r[0]["first_row"])
+        self._mark("dispatch_kernel")
+        main = torch.cuda.current_stream()
+        landed = [None] * C_
+        for c in range(C_):
+            r = self._r[c]
+            if c == 0:
+                self._barrier()   # all rows of chunk 0 for my experts have landed
+                self._mark("barrier1")
+            else:
+                main.wait_event(landed[c])
+            if c + 1 < C_:
+                self._side.wait_stream(main)
+                with torch.cuda.stream(self._side):
+                    self._dispatch(c + 1, x, x_scale, plans[c + 1], self._r[c + 1]["send_dest"], self._r[c + 1]["first_row"])
+                    self._barrier()
+                    landed[c + 1] = torch.cuda.Event()
+                    landed[c + 1].record()
+            q, qs = acl.grouped_matmul_swiglu_quant(self.act[c], self.w1, self.w1_scale, self.act_scale[c], r["group_list"])
+            self._mark(f"swiglu_quant{c}")
+            acl.grouped_matmul_v4(q, self.w2, self.w2_scale, qs, r["group_list"], group_list_type=0, out_row_index=r["ret_dest"],
+                                  out_peers=self.buf_y.ptrs, out=None)
+            self._mark(f"down_gemm{c}")
+        self._barrier()   # every rank's results have landed, and everyone is done reading its activation buffers
+        self._mark("barrier2")
+        group_lists = [self._r[c]["group_list"] for c in range(C_)]
         chunk_out = [{"y": self.result[self.bounds[c] * k:self.bounds[c + 1] * k], "plan": plans[c]} for c in range(C_)]
         return {"y": self.result, "plan": plans[0], "group_list": group_lists[0], "group_lists": group_lists, "chunks": chunk_out}
 

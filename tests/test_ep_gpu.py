@@ -64,12 +64,13 @@ def test_single_rank_ffn_matches_oracle(oracle, chunks):
     _check(oracle, res, chunks, x, xs, topk, w1, s1, w2, s2)
 
 
-def _run_fused(O, dev, rank, world, w1, s1, w2, s2, x, xs, topk, chunks=1):
+def _run_fused(O, dev, rank, world, w1, s1, w2, s2, x, xs, topk, chunks=1, route_kernels=True):
     el = N_EXPERTS // world
     lo, hi = rank * el, (rank + 1) * el
     t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)  # noqa: E731
     ffn = ep.FusedExpertParallelFFN(N_EXPERTS, H, H, t(w1[lo:hi]), t(s1[lo:hi]), t(w2[lo:hi]), t(s2[lo:hi]), tokens=T, top_k=TOP_K,
                                     capacity=2 * T * TOP_K, chunks=chunks)
+    ffn.route_kernels = route_kernels
     for _ in range(2):  # twice: the second step runs over the first one's buffers
         res = ffn.forward(t(x), t(xs), t(topk))
     torch.cuda.synchronize()
@@ -79,6 +80,11 @@ def _run_fused(O, dev, rank, world, w1, s1, w2, s2, x, xs, topk, chunks=1):
         pl = ch["plan"]
         outs.append({"y": ch["y"], "plan": ep.ChunkPlan(order=pl.order, src_token=pl.src_token - ffn.bounds[c], send_counts=pl.send_counts)})
     _check(O, outs, chunks, x, xs, topk, w1, s1, w2, s2)
+    for c, ch in enumerate(res["chunks"]):  # the send order is a permutation of the chunk's pairs, grouped by expert
+        order = ch["plan"].order.cpu().numpy()
+        lo, hi = ffn.bounds[c], ffn.bounds[c + 1]
+        assert sorted(order.tolist()) == list(range((hi - lo) * TOP_K))
+        assert (np.diff(topk[lo:hi].reshape(-1)[order]) >= 0).all()
     ffn.close()
 
 
@@ -89,6 +95,7 @@ def test_single_rank_fused_ffn_matches_oracle(oracle, chunks):
     w1, w2, s1, s2 = _weights()
     x, xs, topk = _inputs(0)
     _run_fused(oracle, torch.device("cuda:0"), 0, 1, w1, s1, w2, s2, x, xs, topk, chunks=chunks)
+    _run_fused(oracle, torch.device("cuda:0"), 0, 1, w1, s1, w2, s2, x, xs, topk, chunks=chunks, route_kernels=False)
 
 
 def _rank_main():
@@ -110,6 +117,7 @@ def _rank_main():
     _check(O, res, 2, x, xs, topk, w1, s1, w2, s2)
     _run_fused(O, dev, rank, world, w1, s1, w2, s2, x, xs, topk)
     _run_fused(O, dev, rank, world, w1, s1, w2, s2, x, xs, topk, chunks=2)
+    _run_fused(O, dev, rank, world, w1, s1, w2, s2, x, xs, topk, route_kernels=False)
     dist.barrier()
     dist.destroy_process_group()
     print(f"rank {rank} ok")
