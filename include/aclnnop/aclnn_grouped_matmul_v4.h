@@ -7,14 +7,17 @@
  *
  * Supported on this path (anything else returns ACLNN_ERR_PARAM_INVALID with a message):
  *   x               list of 1 tensor, int8 [M, K]
- *   weight          list of 1 tensor, int8 [E, K, N]; a transposed view (strides (N*K, 1, K)) is accepted
+ *   weight          list of 1 tensor, int8 [E, K, N]; a transposed view (strides (N*K, 1, K)) is accepted; with format
+ *                   ACL_FORMAT_FRACTAL_NZ the storage is [E, N/32, K/16, 16, 32] (view of 3 or 5 dimensions, K % 16 == 0,
+ *                   N % 32 == 0) and is read by the tensor cores as it lies
  *   biasOptional    null, or list of 1 tensor int32 [E, N] (added to the accumulator) or bf16 [E, N] (added in fp32)
  *   scaleOptional   list of 1 tensor [E, N], bf16 or fp32 (per-channel weight scale); null only for an int32 result
  *   perTokenScaleOptional  list of 1 tensor fp32 [M]
  *   groupListOptional      int64 [<=E] device tensor; groupListType 0 = running total, 1 = per-group count
- *   splitItem 2 or 3, groupType 0, actType GMM_ACT_TYPE_NONE or GMM_ACT_TYPE_RELU
- *   out             list of 1 tensor, bf16 [M, N] (y = bf16((acc * scale[n]) * perTokenScale[m] [+ bias]))
- *                   or int32 [M, N] (raw accumulators, no scales)
+ *   splitItem 2 or 3, groupType 0, actType NONE / RELU / GELU_TANH / FAST_GELU / SILU (GELU_ERR_FUNC is rejected, as in
+ *                   the reference); an int32 result ignores the activation
+ *   out             list of 1 tensor, bf16 [M, N] (y = bf16(act((acc * scale[n]) * perTokenScale[m] [+ bias]))),
+ *                   float16 [M, N] (same arithmetic; scale must then be fp32) or int32 [M, N] (raw accumulators, no scales)
  *   offset / antiquant* / activation* / dynQuant*  must be null.
  * Rows of `out` not covered by group_list are left untouched.
  */

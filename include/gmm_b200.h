@@ -37,7 +37,8 @@ ACL_FUNC_VISIBILITY void gmmB200SetTimingEvents(void *startEvent, void *stopEven
 
 /* Flat form of aclnnGroupedMatmulV4 for the W8A8 path (same arithmetic, same validation of sizes).
  * scaleDtype / biasDtype / yDtype use aclDataType codes; bias may be null (biasDtype ignored);
- * weightTransposed != 0 means the weight is stored [E, N, K].
+ * weightTransposed is the weight's layout: 0 = [E, K, N], 1 = [E, N, K], 2 = FRACTAL_NZ [E, N/32, K/16, 16, 32]
+ * (K % 16 == 0, N % 32 == 0).  actType is a GMMActType; yDtype bf16, float16 (scale then fp32) or int32.
  * outRowIndex (optional, int64 [m] on the device, may be null): result row r is written to row outRowIndex[r] of y
  * instead of row r, which lets a caller fold the un-permute that follows the down projection of an MoE layer into the
  * GEMM (the row scatter of the reference's GroupedMatmulFinalizeRouting, gmm/grouped_matmul_finalize_routing/README.md:11-14,
@@ -102,15 +103,15 @@ ACL_FUNC_VISIBILITY aclnnStatus gmmB200EpRoute(const void *topk, const void *blo
                                               int64_t tokenBase, int64_t resultBase, void *srcToken, void *order, void *sendDest,
                                               void *retDest, void *groupList, void *firstRow, aclrtStream stream);
 
-/* Flat form of aclnnGroupedMatmulSwigluQuant. */
+/* Flat form of aclnnGroupedMatmulSwigluQuant.  weightLayout: 0 = [e, k, n], 2 = FRACTAL_NZ [e, n/32, k/16, 16, 32]. */
 ACL_FUNC_VISIBILITY aclnnStatus gmmB200GroupedMatmulSwigluQuantWorkspaceSize(int64_t m, int64_t k, int64_t n, int64_t e,
                                                                             uint64_t *workspaceSize);
 ACL_FUNC_VISIBILITY aclnnStatus gmmB200GroupedMatmulSwigluQuant(const void *x, const void *weight, const void *weightScale,
                                                                int32_t weightScaleDtype, const void *xScale,
                                                                const void *groupList, int64_t groupListLen, int64_t m,
-                                                               int64_t k, int64_t n, int64_t e, void *output,
-                                                               void *outputScale, void *workspace, uint64_t workspaceSize,
-                                                               aclrtStream stream);
+                                                               int64_t k, int64_t n, int64_t e, int32_t weightLayout,
+                                                               void *output, void *outputScale, void *workspace,
+                                                               uint64_t workspaceSize, aclrtStream stream);
 
 /* grouped_matmul_swiglu_quant without any device allocation.  This entry point has no counterpart in the reference.
  *

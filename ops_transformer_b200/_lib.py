@@ -25,7 +25,10 @@ EXPORTED_SYMBOLS = [
     "aclCreateTensor", "aclDestroyTensor", "aclCreateTensorList", "aclDestroyTensorList", "aclCreateIntArray",
     "aclDestroyIntArray", "aclDestroyAclOpExecutor", "aclGetRecentErrMsg",
     "aclnnGroupedMatmulV4GetWorkspaceSize", "aclnnGroupedMatmulV4",
+    "aclnnGroupedMatmulV5GetWorkspaceSize", "aclnnGroupedMatmulV5",
+    "aclnnGroupedMatmulWeightNzGetWorkspaceSize", "aclnnGroupedMatmulWeightNz",
     "aclnnGroupedMatmulSwigluQuantGetWorkspaceSize", "aclnnGroupedMatmulSwigluQuant",
+    "aclnnGroupedMatmulSwigluQuantWeightNZGetWorkspaceSize", "aclnnGroupedMatmulSwigluQuantWeightNZ",
     "gmmB200Version", "gmmB200CheckStatus", "gmmB200SetTimingEvents", "gmmB200SetSmLimit", "gmmB200GroupedMatmulW8A8WorkspaceSize", "gmmB200GroupedMatmulW8A8",
     "gmmB200GroupedMatmulSwigluQuantWorkspaceSize", "gmmB200GroupedMatmulSwigluQuant",
     "gmmB200NoAllocScratchBytes", "gmmB200GroupedMatmulSwigluQuantNoAlloc",
@@ -57,6 +60,12 @@ def _load():
     L.aclGetRecentErrMsg.restype = C.c_char_p
     L.aclnnGroupedMatmulV4GetWorkspaceSize.argtypes = [p] * 12 + [i64] * 4 + [p] * 3 + [C.POINTER(u64), C.POINTER(p)]
     L.aclnnGroupedMatmulV4.argtypes = [p, u64, p, p]
+    L.aclnnGroupedMatmulV5GetWorkspaceSize.argtypes = [p] * 12 + [i64] * 4 + [p] * 4 + [C.POINTER(u64), C.POINTER(p)]
+    L.aclnnGroupedMatmulV5.argtypes = [p, u64, p, p]
+    L.aclnnGroupedMatmulWeightNzGetWorkspaceSize.argtypes = [p] * 12 + [i64] * 4 + [p, i64] + [p] * 3 + [C.POINTER(u64), C.POINTER(p)]
+    L.aclnnGroupedMatmulWeightNz.argtypes = [p, u64, p, p]
+    L.aclnnGroupedMatmulSwigluQuantWeightNZGetWorkspaceSize.argtypes = [p] * 10 + [C.POINTER(u64), C.POINTER(p)]
+    L.aclnnGroupedMatmulSwigluQuantWeightNZ.argtypes = [p, u64, p, p]
     L.aclnnGroupedMatmulSwigluQuantGetWorkspaceSize.argtypes = [p] * 10 + [C.POINTER(u64), C.POINTER(p)]
     L.aclnnGroupedMatmulSwigluQuant.argtypes = [p, u64, p, p]
     L.gmmB200CheckStatus.argtypes = [p, u64, p, C.POINTER(i32)]
@@ -67,7 +76,7 @@ def _load():
     L.gmmB200GroupedMatmulW8A8WorkspaceSize.argtypes = [i64, i64, i64, i64, i32, C.POINTER(u64)]
     L.gmmB200GroupedMatmulW8A8.argtypes = [p, p, p, i32, p, p, i32, p, i64, i32, i64, i64, i64, i64, i32, i32, p, p, i32, p, i32, p, u64, p]
     L.gmmB200GroupedMatmulSwigluQuantWorkspaceSize.argtypes = [i64, i64, i64, i64, C.POINTER(u64)]
-    L.gmmB200GroupedMatmulSwigluQuant.argtypes = [p, p, p, i32, p, p, i64, i64, i64, i64, i64, p, p, p, u64, p]
+    L.gmmB200GroupedMatmulSwigluQuant.argtypes = [p, p, p, i32, p, p, i64, i64, i64, i64, i64, i32, p, p, p, u64, p]
     L.gmmB200PeerAlloc.argtypes = [u64, C.POINTER(p)]
     L.gmmB200PeerFree.argtypes = [p]
     L.gmmB200PeerExport.argtypes = [p, p]

@@ -14,7 +14,8 @@ from typing import Optional, Sequence
 import torch
 
 from . import _lib
-from ._lib import (ACL_BF16, ACL_FLOAT, ACL_FLOAT16, ACL_FORMAT_ND, ACL_INT8, ACL_INT32, ACL_INT64, ACLNN_SUCCESS)
+from ._lib import (ACL_BF16, ACL_FLOAT, ACL_FLOAT16, ACL_FORMAT_FRACTAL_NZ, ACL_FORMAT_ND, ACL_INT8, ACL_INT32, ACL_INT64,
+                   ACLNN_SUCCESS)
 
 _DTYPES = {
     torch.float32: ACL_FLOAT, torch.float16: ACL_FLOAT16, torch.int8: ACL_INT8, torch.int32: ACL_INT32,
@@ -46,9 +47,19 @@ def create_tensor(t: torch.Tensor, fmt: int = ACL_FORMAT_ND, dtype: Optional[int
     return h
 
 
-def create_tensor_list(tensors: Sequence[torch.Tensor]) -> int:
+def format_cast_nz(weight: torch.Tensor) -> torch.Tensor:
+    """int8 [E, K, N] -> the FRACTAL_NZ storage [E, N/32, K/16, 16, 32] (a copy; K % 16 == 0, N % 32 == 0): element
+    (k, n) moves to [n // 32, k // 16, k % 16, n % 32].  What a caller of the reference does once per weight with its
+    framework's format cast before calling the WeightNZ operators; a set-up step, not part of the hot path."""
+    E, K, N = weight.shape
+    if K % 16 or N % 32:
+        raise ValueError("FRACTAL_NZ needs K % 16 == 0 and N % 32 == 0")
+    return weight.reshape(E, K // 16, 16, N // 32, 32).permute(0, 3, 1, 2, 4).contiguous()
+
+
+def create_tensor_list(tensors: Sequence[torch.Tensor], fmt: int = ACL_FORMAT_ND) -> int:
     """aclCreateTensorList; the list owns its tensor handles (aclDestroyTensorList frees them)."""
-    hs = [create_tensor(t) for t in tensors]
+    hs = [create_tensor(t, fmt) for t in tensors]
     arr = (C.c_void_p * len(hs))(*hs)
     h = _lib.lib().aclCreateTensorList(arr, len(hs))
     if not h:
@@ -98,21 +109,28 @@ def grouped_matmul_v4(x: torch.Tensor, weight: torch.Tensor, scale: Optional[tor
                       group_list_type: int = 0, act_type: int = 0, out: Optional[torch.Tensor] = None,
                       out_dtype: torch.dtype = torch.bfloat16, stream=None, workspace: Optional[torch.Tensor] = None,
                       return_workspace: bool = False, out_row_index: Optional[torch.Tensor] = None,
-                      out_peers: Optional[Sequence[int]] = None):
-    """y = bf16((x @ weight[e]) * scale[e] * per_token_scale) per expert row range (W8A8), or the raw int32
-    accumulators when ``out_dtype`` is torch.int32.  Rows not covered by ``group_list`` keep their contents.
-    ``out_row_index`` (int64 [M], an extension of this library) scatters result row r to row out_row_index[r]; it
-    goes through the flat entry point gmmB200GroupedMatmulW8A8."""
+                      out_peers: Optional[Sequence[int]] = None, weight_format: int = ACL_FORMAT_ND,
+                      api: str = "V4", tuning_config: Optional[Sequence[int]] = None, quant_group_size: int = 0):
+    """y = bf16(act((x @ weight[e]) * scale[e] * per_token_scale)) per expert row range (W8A8), a float16 result with
+    ``out_dtype`` torch.float16, or the raw int32 accumulators with torch.int32.  Rows not covered by ``group_list``
+    keep their contents.  ``weight_format`` ACL_FORMAT_FRACTAL_NZ: ``weight`` is the 5-D storage of ``format_cast_nz``.
+    ``api`` picks the entry point: "V4", "V5" (adds ``tuning_config``) or "WeightNz" (adds ``quant_group_size`` and
+    treats the weight as FRACTAL_NZ) - aclnn_grouped_matmul_v5.h:49-58, aclnn_grouped_matmul_weight_nz.h:50-59 of the
+    reference.  ``out_row_index`` (int64 [M], an extension of this library) scatters result row r to row
+    out_row_index[r]; it goes through the flat entry point gmmB200GroupedMatmulW8A8."""
     L = _lib.lib()
+    nz = weight_format == ACL_FORMAT_FRACTAL_NZ or api == "WeightNz"
     if out is None and not out_peers:
-        out = torch.empty((x.shape[0], weight.shape[2]), dtype=out_dtype, device=x.device)
+        n_out = weight.shape[1] * 32 if (nz and weight.dim() == 5) else weight.shape[2]
+        out = torch.empty((x.shape[0], n_out), dtype=out_dtype, device=x.device)
     if out_row_index is not None:
         return _grouped_matmul_flat(x, weight, scale, per_token_scale, group_list, bias, group_list_type, act_type, out,
-                                    out_row_index, stream, workspace, return_workspace, out_peers)
+                                    out_row_index, stream, workspace, return_workspace, out_peers, nz)
     lists = []
+    tuning = None
     try:
         hx = create_tensor_list([x]); lists.append(hx)
-        hw = create_tensor_list([weight]); lists.append(hw)
+        hw = create_tensor_list([weight], ACL_FORMAT_FRACTAL_NZ if nz else ACL_FORMAT_ND); lists.append(hw)
         hb = None
         if bias is not None:
             hb = create_tensor_list([bias]); lists.append(hb)
@@ -127,22 +145,33 @@ def grouped_matmul_v4(x: torch.Tensor, weight: torch.Tensor, scale: Optional[tor
         try:
             ws_size = C.c_uint64(0)
             ex = C.c_void_p(0)
-            rc = L.aclnnGroupedMatmulV4GetWorkspaceSize(hx, hw, hb, hs, None, None, None, hp, hg, None, None, None,
-                                                        split_item, group_type, group_list_type, act_type, hy, None, None,
-                                                        C.byref(ws_size), C.byref(ex))
+            if tuning_config is not None:
+                tuning = L.aclCreateIntArray(_i64(list(tuning_config)), len(tuning_config))
+            head = (hx, hw, hb, hs, None, None, None, hp, hg, None, None, None, split_item, group_type, group_list_type, act_type)
+            tail = (hy, None, None, C.byref(ws_size), C.byref(ex))
+            if api == "V4":
+                rc = L.aclnnGroupedMatmulV4GetWorkspaceSize(*head, *tail)
+            elif api == "V5":
+                rc = L.aclnnGroupedMatmulV5GetWorkspaceSize(*head, tuning, *tail)
+            elif api == "WeightNz":
+                rc = L.aclnnGroupedMatmulWeightNzGetWorkspaceSize(*head, tuning, quant_group_size, *tail)
+            else:
+                raise ValueError(f"unknown api {api!r}")
             if rc != ACLNN_SUCCESS:
-                raise AclnnError(rc, "aclnnGroupedMatmulV4GetWorkspaceSize")
+                raise AclnnError(rc, f"aclnnGroupedMatmul{api}GetWorkspaceSize")
             if workspace is None:
                 workspace = _WS.get(x.device, ws_size.value)
             elif workspace.numel() < ws_size.value:
                 L.aclDestroyAclOpExecutor(ex)
                 raise ValueError(f"workspace of {workspace.numel()} bytes is smaller than the {ws_size.value} required")
             wptr = C.c_void_p(workspace.data_ptr()) if workspace is not None else None
-            rc = L.aclnnGroupedMatmulV4(wptr, ws_size.value, ex, C.c_void_p(_stream_handle(stream)))
+            rc = getattr(L, "aclnnGroupedMatmul" + api)(wptr, ws_size.value, ex, C.c_void_p(_stream_handle(stream)))
             if rc != ACLNN_SUCCESS:
-                raise AclnnError(rc, "aclnnGroupedMatmulV4")
+                raise AclnnError(rc, "aclnnGroupedMatmul" + api)
         finally:
             L.aclDestroyTensor(hg)
+            if tuning:
+                L.aclDestroyIntArray(tuning)
     finally:
         for h in lists:
             L.aclDestroyTensorList(h)
@@ -150,13 +179,16 @@ def grouped_matmul_v4(x: torch.Tensor, weight: torch.Tensor, scale: Optional[tor
 
 
 def _grouped_matmul_flat(x, weight, scale, per_token_scale, group_list, bias, group_list_type, act_type, out, out_row_index,
-                         stream, workspace, return_workspace, out_peers=None):
+                         stream, workspace, return_workspace, out_peers=None, nz=False):
     """Flat entry point.  ``out_peers`` (device addresses, one [rows, N] bf16 buffer per GPU) makes out_row_index hold
     (gpu << 40) | row; ``out`` may then be None."""
     L = _lib.lib()
     M, K = x.shape
-    E, _, N = weight.shape
-    trans = (not weight.is_contiguous()) and weight.transpose(1, 2).is_contiguous()
+    if nz and weight.dim() == 5:
+        E, N = weight.shape[0], weight.shape[1] * 32
+    else:
+        E, _, N = weight.shape
+    trans = 2 if nz else int((not weight.is_contiguous()) and weight.transpose(1, 2).is_contiguous())
     for t in (x, scale, per_token_scale, group_list, bias, out, out_row_index):
         if t is not None and not t.is_contiguous():
             raise ValueError("the flat entry point needs contiguous tensors")
@@ -174,7 +206,7 @@ def _grouped_matmul_flat(x, weight, scale, per_token_scale, group_list, bias, gr
     p = lambda t: C.c_void_p(t.data_ptr()) if t is not None else None  # noqa: E731
     rc = L.gmmB200GroupedMatmulW8A8(p(x), p(weight), p(scale), _DTYPES[scale.dtype] if scale is not None else 0, p(per_token_scale),
                                     p(bias), _DTYPES[bias.dtype] if bias is not None else 0, p(group_list), group_list.numel(),
-                                    group_list_type, M, K, N, E, int(trans), act_type, p(out_row_index), peers if n_peers else None, n_peers, p(out), ydt, p(workspace),
+                                    group_list_type, M, K, N, E, trans, act_type, p(out_row_index), peers if n_peers else None, n_peers, p(out), ydt, p(workspace),
                                     workspace.numel(), C.c_void_p(_stream_handle(stream)))
     if rc != ACLNN_SUCCESS:
         raise AclnnError(rc, "gmmB200GroupedMatmulW8A8")
@@ -185,9 +217,13 @@ def grouped_matmul_swiglu_quant(x: torch.Tensor, weight: torch.Tensor, weight_sc
                                 group_list: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
                                 offset: Optional[torch.Tensor] = None, output: Optional[torch.Tensor] = None,
                                 output_scale: Optional[torch.Tensor] = None, stream=None,
-                                workspace: Optional[torch.Tensor] = None, return_workspace: bool = False):
+                                workspace: Optional[torch.Tensor] = None, return_workspace: bool = False,
+                                weight_format: int = ACL_FORMAT_ND, api: str = ""):
     """(output int8 [M, N/2], output_scale fp32 [M]) = per-token int8 requant of SwiGLU of the dequantised grouped
-    GEMM.  ``group_list`` holds running totals.  Rows at and beyond group_list[-1] keep their contents."""
+    GEMM.  ``group_list`` holds running totals.  Rows at and beyond group_list[-1] keep their contents.
+    ``weight_format`` ACL_FORMAT_FRACTAL_NZ: ``weight`` is the 5-D storage of ``format_cast_nz``; ``api`` "WeightNZ"
+    calls aclnnGroupedMatmulSwigluQuantWeightNZ (aclnn_grouped_matmul_swiglu_quant_weight_nz.h:37-54 of the reference),
+    which takes the storage as FRACTAL_NZ whatever the format says."""
     L = _lib.lib()
     M = x.shape[0]
     N = weight_scale.shape[1] if weight_scale.dim() == 2 else 0
@@ -203,23 +239,25 @@ def grouped_matmul_swiglu_quant(x: torch.Tensor, weight: torch.Tensor, weight_sc
             h = create_tensor(t)
             handles.append(h)
             return h
-        hx, hw, hb, ho = mk(x), mk(weight), mk(bias), mk(offset)
+        hx, hb, ho = mk(x), mk(bias), mk(offset)
+        hw = create_tensor(weight, weight_format)
+        handles.append(hw)
         hws, hxs, hg, hq, hqs = mk(weight_scale), mk(x_scale), mk(group_list), mk(output), mk(output_scale)
         ws_size = C.c_uint64(0)
         ex = C.c_void_p(0)
-        rc = L.aclnnGroupedMatmulSwigluQuantGetWorkspaceSize(hx, hw, hb, ho, hws, hxs, hg, hq, hqs, None, C.byref(ws_size),
-                                                             C.byref(ex))
+        name = "aclnnGroupedMatmulSwigluQuant" + api
+        rc = getattr(L, name + "GetWorkspaceSize")(hx, hw, hb, ho, hws, hxs, hg, hq, hqs, None, C.byref(ws_size), C.byref(ex))
         if rc != ACLNN_SUCCESS:
-            raise AclnnError(rc, "aclnnGroupedMatmulSwigluQuantGetWorkspaceSize")
+            raise AclnnError(rc, name + "GetWorkspaceSize")
         if workspace is None:
             workspace = _WS.get(x.device, ws_size.value)
         elif workspace.numel() < ws_size.value:
             L.aclDestroyAclOpExecutor(ex)
             raise ValueError(f"workspace of {workspace.numel()} bytes is smaller than the {ws_size.value} required")
         wptr = C.c_void_p(workspace.data_ptr()) if workspace is not None else None
-        rc = L.aclnnGroupedMatmulSwigluQuant(wptr, ws_size.value, ex, C.c_void_p(_stream_handle(stream)))
+        rc = getattr(L, name)(wptr, ws_size.value, ex, C.c_void_p(_stream_handle(stream)))
         if rc != ACLNN_SUCCESS:
-            raise AclnnError(rc, "aclnnGroupedMatmulSwigluQuant")
+            raise AclnnError(rc, name)
     finally:
         for h in handles:
             L.aclDestroyTensor(h)

@@ -24,7 +24,7 @@ enum : int { kStatusOk = 0, kStatusWaitTimeout = 1, kStatusBadSchedule = 2 };
 
 struct Problem {
     const int8_t *x = nullptr;          // [M, K]
-    const int8_t *w = nullptr;          // [E, K, N], or [E, N, K] when w_trans
+    const int8_t *w = nullptr;          // [E, K, N]; [E, N, K] (w_layout 1); FRACTAL_NZ [E, N/32, K/16, 16, 32] (w_layout 2)
     const void *w_scale = nullptr;      // [E, N] f32 / bf16 / f16
     int w_scale_dtype = kF32;
     const float *x_scale = nullptr;     // [M] per-token scale (may be null for mode kModeInt32)
@@ -34,8 +34,9 @@ struct Problem {
     int gl_len = 0;
     int gl_type = 0;                    // 0 = running total, 1 = per-group count
     int64_t M = 0, K = 0, N = 0, E = 0;
-    int w_trans = 0;
-    int act_type = 0;                   // 0 none, 1 relu
+    int w_layout = 0;                   // 0 row major, 1 transposed view, 2 FRACTAL_NZ
+    int act_type = 0;                   // GMMActType: 0 none, 1 relu, 2 gelu (tanh form), 4 fast gelu, 5 silu
+    int out_f16 = 0;                    // mode kModeDequantBf16 with a float16 instead of a bfloat16 result
     int mode = kModeDequantBf16;
     void *out0 = nullptr;               // y (bf16 / int32) or q (int8 [M, N/2])
     void *out1 = nullptr;               // q_scale f32 [M] (swiglu only)
@@ -73,5 +74,28 @@ cudaError_t simt_launch(const Problem &p, Plan &plan, void *workspace, cudaStrea
 int device_sm_count();
 // Caps the number of CTAs the persistent kernels launch (0 = one per SM).
 void set_sm_limit(int n);
+
+#ifdef __CUDACC__
+// Activations of the dequantising epilogue (ActivationCompute, gmm/grouped_matmul/op_kernel/grouped_matmul_quant_mixcore.h:390-405).
+// The reference calls its vector library's Relu / Gelu / FasterGelu / Silu; the library's published definitions are
+//   Gelu(x)       = x / (1 + exp(-1.59576912 * (x + 0.044715 * x^3)))      (tanh form)
+//   FasterGelu(x) = x / (1 + exp(-1.702 * x))
+//   Silu(x)       = x / (1 + exp(-x))
+// evaluated here in fp32 with every operation rounded separately.
+__device__ __forceinline__ float apply_activation(int act_type, float v)
+{
+    switch (act_type) {
+        case 1: return v > 0.0f ? v : 0.0f;
+        case 2: {
+            const float v3 = __fmul_rn(__fmul_rn(v, v), v);
+            const float u = __fmul_rn(-1.59576912f, __fadd_rn(v, __fmul_rn(0.044715f, v3)));
+            return __fdiv_rn(v, __fadd_rn(1.0f, expf(u)));
+        }
+        case 4: return __fdiv_rn(v, __fadd_rn(1.0f, expf(__fmul_rn(-1.702f, v))));
+        case 5: return __fdiv_rn(v, __fadd_rn(1.0f, expf(-v)));
+        default: return v;
+    }
+}
+#endif
 
 }  // namespace gmm

@@ -63,12 +63,19 @@ struct SimtParams {
     const int64_t *gl;
     int gl_len, gl_type;
     int M, K, N;
-    long long wsk, wsn;  // weight element (k, n) of a group sits at k*wsk + n*wsn
-    int act_type, mode;
+    long long wsk, wsn;  // weight element (k, n) of a group sits at k*wsk + n*wsn ...
+    int nz;              // ... unless the layout is FRACTAL_NZ: ((n/32 * K/16 + k/16) * 16 + k%16) * 32 + n%32
+    int act_type, mode, out_f16;
     void *out0;
     float *out1;
     const long long *out_row_index;
 };
+
+__device__ __forceinline__ long long w_offset(const SimtParams &p, int k, int n)
+{
+    if (p.nz) return (((long long)(n >> 5) * (p.K >> 4) + (k >> 4)) * 16 + (k & 15)) * 32 + (n & 31);
+    return k * p.wsk + n * p.wsn;
+}
 
 // One CTA per row; threads stride over the output columns.
 __global__ void __launch_bounds__(256) gmm_simt_kernel(const SimtParams p)
@@ -85,7 +92,7 @@ __global__ void __launch_bounds__(256) gmm_simt_kernel(const SimtParams p)
     const size_t orow = p.out_row_index ? (size_t)p.out_row_index[m] : (size_t)m;
     for (int n = threadIdx.x; n < p.N; n += blockDim.x) {
         int acc = 0;
-        for (int k = 0; k < p.K; ++k) acc += (int)xr[k] * (int)wg[k * p.wsk + n * p.wsn];
+        for (int k = 0; k < p.K; ++k) acc += (int)xr[k] * (int)wg[w_offset(p, k, n)];
         if (p.bias_dtype == kI32) acc += reinterpret_cast<const int *>(p.bias)[(size_t)g * p.N + n];
         if (p.mode == kModeInt32) {
             reinterpret_cast<int *>(p.out0)[orow * p.N + n] = acc;
@@ -94,8 +101,9 @@ __global__ void __launch_bounds__(256) gmm_simt_kernel(const SimtParams p)
         float t = __fmul_rn(__int2float_rn(acc), load_scale1(p.w_scale, p.w_scale_dtype, (size_t)g * p.N + n));
         if (p.x_scale) t = __fmul_rn(t, xs);
         if (p.bias_dtype == kBF16) t = __fadd_rn(t, load_scale1(p.bias, kBF16, (size_t)g * p.N + n));
-        if (p.act_type == 1) t = t > 0.0f ? t : 0.0f;
-        reinterpret_cast<__nv_bfloat16 *>(p.out0)[orow * p.N + n] = __float2bfloat16_rn(t);
+        t = apply_activation(p.act_type, t);
+        if (p.out_f16) reinterpret_cast<__half *>(p.out0)[orow * p.N + n] = __float2half_rn(t);
+        else reinterpret_cast<__nv_bfloat16 *>(p.out0)[orow * p.N + n] = __float2bfloat16_rn(t);
     }
 }
 
@@ -118,8 +126,8 @@ __global__ void __launch_bounds__(256) swiglu_simt_kernel(const SimtParams p)
         int a0 = 0, a1 = 0;
         for (int k = 0; k < p.K; ++k) {
             const int xv = xr[k];
-            a0 += xv * (int)wg[k * p.wsk + j * p.wsn];
-            a1 += xv * (int)wg[k * p.wsk + (j + H) * p.wsn];
+            a0 += xv * (int)wg[w_offset(p, k, j)];
+            a1 += xv * (int)wg[w_offset(p, k, j + H)];
         }
         const float a = __fmul_rn(__fmul_rn(__int2float_rn(a0), xs), load_scale1(p.w_scale, p.w_scale_dtype, (size_t)g * p.N + j));
         const float b = __fmul_rn(__fmul_rn(__int2float_rn(a1), xs), load_scale1(p.w_scale, p.w_scale_dtype, (size_t)g * p.N + H + j));
@@ -198,9 +206,10 @@ cudaError_t simt_launch(const Problem &p, Plan &, void *, cudaStream_t stream)
     sp.bias = p.bias; sp.bias_dtype = p.bias ? p.bias_dtype : kNone;
     sp.gl = p.group_list; sp.gl_len = p.gl_len; sp.gl_type = p.gl_type;
     sp.M = (int)p.M; sp.K = (int)p.K; sp.N = (int)p.N;
-    sp.wsk = p.w_trans ? 1 : p.N;
-    sp.wsn = p.w_trans ? p.K : 1;
-    sp.act_type = p.act_type; sp.mode = p.mode; sp.out0 = p.out0; sp.out1 = reinterpret_cast<float *>(p.out1);
+    sp.wsk = p.w_layout == 1 ? 1 : p.N;
+    sp.wsn = p.w_layout == 1 ? p.K : 1;
+    sp.nz = p.w_layout == 2;
+    sp.act_type = p.act_type; sp.mode = p.mode; sp.out_f16 = p.out_f16; sp.out0 = p.out0; sp.out1 = reinterpret_cast<float *>(p.out1);
     sp.out_row_index = reinterpret_cast<const long long *>(p.out_row_index);
     if (p.M <= 0) return cudaSuccess;
     if (p.mode == kModeSwigluQuant) {

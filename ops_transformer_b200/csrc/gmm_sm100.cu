@@ -61,6 +61,8 @@ constexpr long long DRAIN_LIMIT_CYCLES = 1ll << 24;  // a few milliseconds
 
 constexpr int EPI_THREADS = 32 * EPI_WARPS;
 enum : int { kEpiPlain = 0, kEpiScatter = 1, kEpiGeneric = 2 };
+// Weight layouts: [E,K,N]; [E,N,K] (the transposed view); FRACTAL_NZ [E, N/32, K/16, 16, 32] (32-byte runs along N).
+enum : int { kBRowMajor = 0, kBTransposed = 1, kBFractalNz = 2 };
 constexpr int SCALE_BUFS = 3;          // an epilogue thread can run at most two tiles ahead of another one
 constexpr int OUT_STAGE_BYTES = 2048;  // per epilogue warp: 32 rows x 64 bytes of packed bf16
 
@@ -98,7 +100,7 @@ struct KParams {
     const float *x_scale;
     const void *bias;
     int bias_dtype;
-    int act_type;
+    int act_type, out_f16;
     void *out;            // y (bf16 / int32) or the fp32 SwiGLU staging [M, N/2]
     const long long *out_row_index;  // optional: result row r is written to row out_row_index[r] (bf16 / int32 modes)
     void *out_peers[8];              // bf16 mode with num_peers > 0: out_row_index = (gpu << 40) | row, base per gpu here
@@ -186,6 +188,13 @@ __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, i
         ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
         : "memory");
 }
+__device__ __forceinline__ void tma_load_5d(void *dst, const CUtensorMap *map, int c0, int c1, int c2, int c3, int c4, uint64_t *bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+        ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(smem_u32(bar))
+        : "memory");
+}
 // Pair (cta_group::2) forms: the copy lands in the executing CTA's shared memory, the byte count is credited to the
 // mbarrier at `bar_cluster_addr`, a shared::cluster address that may belong to the other CTA of the pair.
 __device__ __forceinline__ void tma_load_2d_pair(void *dst, const CUtensorMap *map, int c0, int c1, uint32_t bar_cluster_addr)
@@ -200,6 +209,14 @@ __device__ __forceinline__ void tma_load_3d_pair(void *dst, const CUtensorMap *m
     asm volatile(
         "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
         ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(c0), "r"(c1), "r"(c2), "r"(bar_cluster_addr)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_5d_pair(void *dst, const CUtensorMap *map, int c0, int c1, int c2, int c3, int c4,
+                                                 uint32_t bar_cluster_addr)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.5d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+        ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(bar_cluster_addr)
         : "memory");
 }
 // shared::cluster address of `p` (a location in this CTA's shared memory) as seen in CTA `rank` of the cluster.
@@ -305,14 +322,14 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 // Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1.
 //   K-major operand : rows of 128 bytes, 8-row groups 1024 bytes apart (SBO); LBO unused.
 //   MN-major operand: 128-byte runs along M/N; the next 8 K-rows are SBO bytes on, the next 128 M/N LBO bytes on.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes)
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint64_t layout_type = 2)
 {
     uint64_t d = 0;
     d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
     d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
     d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
     d |= 1ull << 46;
-    d |= 2ull << 61;
+    d |= layout_type << 61;  // 2 = 128-byte swizzle, 6 = 32-byte swizzle
     return d;
 }
 
@@ -432,6 +449,12 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi)
     return *reinterpret_cast<const uint32_t *>(&v);
 }
 
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi)
+{
+    const __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&v);
+}
+
 __device__ __forceinline__ int ld_acquire_gpu(const int *p)
 {
     int v;
@@ -532,10 +555,11 @@ __device__ bool settle_pending(const KParams &p, Shared *sh, Pending &pd, uint32
 // (the common case, compiled without per-element tests for the options); kEpiScatter = the same arithmetic with the
 // result rows scattered through out_row_index, optionally into other GPUs' memory; kEpiGeneric = every option
 // tested at run time.  CTAS: 1 = one CTA per tile, 2 = a cluster of two CTAs per 256-row tile.
-template <int MODE, bool B_MN_MAJOR, int EPI, int CTAS>
+template <int MODE, int BL, int EPI, int CTAS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const KParams p)
 {
+    constexpr bool B_MN_MAJOR = BL != kBTransposed;  // [E,K,N] and the fractal layout are N-contiguous
     constexpr bool PLAIN = EPI != kEpiGeneric;   // lean arithmetic
     constexpr bool SCATTER = EPI != kEpiPlain;  // rows go where out_row_index says
     using C = Cfg<CTAS>;
@@ -604,7 +628,10 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                     if (CTAS == 1) {
                         mbar_arrive_expect_tx(&sh->full[stage], C::kTxBytes);
                         tma_load_2d(adst, &map_x, kb * BK, my_row0, &sh->full[stage]);
-                        if (B_MN_MAJOR) {  // weight [E, K, N]: map dims {N, K, E}
+                        if (BL == kBFractalNz) {  // map dims {32 n, 16 k, K/16, N/32, E}: a box is 128 k x 128 n in 32-column slabs
+                            tma_load_5d(bdst, &map_w, 0, 0, kb * (BK / 16), n0 >> 5, tl.g, &sh->full[stage]);
+                            tma_load_5d(bdst + B_BOX, &map_w, 0, 0, kb * (BK / 16), n1 >> 5, tl.g, &sh->full[stage]);
+                        } else if (B_MN_MAJOR) {  // weight [E, K, N]: map dims {N, K, E}
                             tma_load_3d(bdst, &map_w, n0, kb * BK, tl.g, &sh->full[stage]);
                             tma_load_3d(bdst + B_BOX, &map_w, n1, kb * BK, tl.g, &sh->full[stage]);
                         } else {           // weight [E, N, K]: map dims {K, N, E}
@@ -614,7 +641,8 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                     } else {
                         if (rank == 0) mbar_arrive_expect_tx(&sh->full[stage], C::kTxBytes);
                         tma_load_2d_pair(adst, &map_x, kb * BK, my_row0, full_rank0 + (uint32_t)stage * 8u);
-                        if (B_MN_MAJOR) tma_load_3d_pair(bdst, &map_w, nb, kb * BK, tl.g, full_rank0 + (uint32_t)stage * 8u);
+                        if (BL == kBFractalNz) tma_load_5d_pair(bdst, &map_w, 0, 0, kb * (BK / 16), nb >> 5, tl.g, full_rank0 + (uint32_t)stage * 8u);
+                        else if (B_MN_MAJOR) tma_load_3d_pair(bdst, &map_w, nb, kb * BK, tl.g, full_rank0 + (uint32_t)stage * 8u);
                         else tma_load_3d_pair(bdst, &map_w, kb * BK, nb, tl.g, full_rank0 + (uint32_t)stage * 8u);
                     }
                     ++issued;
@@ -657,8 +685,11 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
 #pragma unroll
                     for (int j = 0; j < BK / UMMA_K; ++j) {
                         const uint64_t a_desc = make_smem_desc(a_addr + j * UMMA_K, 16, 1024);
-                        const uint64_t b_desc = B_MN_MAJOR ? make_smem_desc(b_addr + j * UMMA_K * 128, B_BOX, 1024)
-                                                           : make_smem_desc(b_addr + j * UMMA_K, 16, 1024);
+                        // [E,K,N]: 128-byte runs along N, 8 K-rows = 1024 B, next 128 columns one box on.
+                        // fractal: 32-byte runs along N, 8 K-rows = 256 B, next 32 columns 128 K-rows (4096 B) on.
+                        const uint64_t b_desc = BL == kBFractalNz ? make_smem_desc(b_addr + j * UMMA_K * 32, 4096, 256, 6)
+                                                : B_MN_MAJOR      ? make_smem_desc(b_addr + j * UMMA_K * 128, B_BOX, 1024)
+                                                                  : make_smem_desc(b_addr + j * UMMA_K, 16, 1024);
                         if (CTAS == 1) umma_i8(d_tmem, a_desc, b_desc, idesc, (kb | j) != 0 ? 1u : 0u);
                         else umma_i8_pair(d_tmem, a_desc, b_desc, idesc, (kb | j) != 0 ? 1u : 0u);
                     }
@@ -816,12 +847,17 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                                         if (p.x_scale) tv = __fmul_rn(tv, xs);
                                         if (p.bias_dtype == kBF16 && in_n)
                                             tv = __fadd_rn(tv, __uint_as_float((uint32_t)__ldg(reinterpret_cast<const uint16_t *>(p.bias) + sbase + n0 + cc) << 16));
-                                        if (p.act_type == 1) tv = tv > 0.0f ? tv : 0.0f;
+                                        tv = apply_activation(p.act_type, tv);
                                         o[j] = tv;
                                     }
                                 }
-                                pk[half * 16 + j4 * 2] = pack_bf16x2(o[0], o[1]);
-                                pk[half * 16 + j4 * 2 + 1] = pack_bf16x2(o[2], o[3]);
+                                if (!PLAIN && p.out_f16) {
+                                    pk[half * 16 + j4 * 2] = pack_f16x2(o[0], o[1]);
+                                    pk[half * 16 + j4 * 2 + 1] = pack_f16x2(o[2], o[3]);
+                                } else {
+                                    pk[half * 16 + j4 * 2] = pack_bf16x2(o[0], o[1]);
+                                    pk[half * 16 + j4 * 2 + 1] = pack_bf16x2(o[2], o[3]);
+                                }
                             }
                         }
                         // Transpose through shared memory, 16 rows per round, so that eight lanes write 128 contiguous
@@ -917,10 +953,10 @@ EncodeTiledFn encode_fn()
     return fn;
 }
 
-template <int MODE, bool B_MN, int EPI, int CTAS>
+template <int MODE, int BL, int EPI, int CTAS>
 cudaError_t launch_variant(const Plan &plan, const KParams &kp, cudaStream_t stream)
 {
-    auto kern = gmm_w8a8_sm100_kernel<MODE, B_MN, EPI, CTAS>;
+    auto kern = gmm_w8a8_sm100_kernel<MODE, BL, EPI, CTAS>;
     // Once per device and instantiation; the attribute is idempotent, so a race only repeats the call.
     static unsigned long long done_mask = 0;
     int dev = 0;
@@ -945,18 +981,26 @@ cudaError_t launch_variant(const Plan &plan, const KParams &kp, cudaStream_t str
     return cudaLaunchKernelEx(&cfg, kern, plan.map_x, plan.map_w, kp);
 }
 
-template <int MODE, bool B_MN, int EPI>
+template <int MODE, int BL, int EPI>
 cudaError_t launch_ctas(const Plan &plan, const KParams &kp, cudaStream_t stream)
 {
-    return plan.ctas == 2 ? launch_variant<MODE, B_MN, EPI, 2>(plan, kp, stream) : launch_variant<MODE, B_MN, EPI, 1>(plan, kp, stream);
+    return plan.ctas == 2 ? launch_variant<MODE, BL, EPI, 2>(plan, kp, stream) : launch_variant<MODE, BL, EPI, 1>(plan, kp, stream);
 }
 
-template <int MODE, bool B_MN>
+template <int MODE, int BL>
 cudaError_t launch_epi(int epi, const Plan &plan, const KParams &kp, cudaStream_t stream)
 {
-    if (epi == kEpiPlain) return launch_ctas<MODE, B_MN, kEpiPlain>(plan, kp, stream);
-    if (epi == kEpiScatter) return launch_ctas<MODE, B_MN, kEpiScatter>(plan, kp, stream);
-    return launch_ctas<MODE, B_MN, kEpiGeneric>(plan, kp, stream);
+    if (MODE == kModeSwigluQuant || epi == kEpiPlain) return launch_ctas<MODE, BL, kEpiPlain>(plan, kp, stream);
+    if (epi == kEpiScatter) return launch_ctas<MODE, BL, kEpiScatter>(plan, kp, stream);
+    return launch_ctas<MODE, BL, kEpiGeneric>(plan, kp, stream);
+}
+
+template <int MODE>
+cudaError_t launch_layout(int layout, int epi, const Plan &plan, const KParams &kp, cudaStream_t stream)
+{
+    if (layout == kBTransposed) return launch_epi<MODE, kBTransposed>(epi, plan, kp, stream);
+    if (layout == kBFractalNz) return launch_epi<MODE, kBFractalNz>(epi, plan, kp, stream);
+    return launch_epi<MODE, kBRowMajor>(epi, plan, kp, stream);
 }
 
 cudaEvent_t g_ev_start = nullptr, g_ev_stop = nullptr;
@@ -975,6 +1019,7 @@ bool sm100_shape_ok(const Problem &p)
 {
     if (p.K % 16 != 0 || p.N % 16 != 0) return false;
     if (p.mode == kModeSwigluQuant && p.N % 32 != 0) return false;
+    if (p.w_layout == kBFractalNz && (p.N % 32 != 0 || (p.mode == kModeSwigluQuant && p.N % 64 != 0))) return false;
     if (p.gl_len > MAX_GROUPS || p.gl_len <= 0) return false;
     if (p.M <= 0 || p.M > 0x7fffffffll / 2 || p.K > 0x7fffffffll || p.N > 0x7fffffffll) return false;
     if ((reinterpret_cast<uintptr_t>(p.x) & 15) || (reinterpret_cast<uintptr_t>(p.w) & 15)) return false;
@@ -999,8 +1044,19 @@ cudaError_t sm100_encode_maps(const Problem &p, Plan &plan)
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
     }
-    {
-        const cuuint64_t inner = p.w_trans ? p.K : p.N, mid = p.w_trans ? p.N : p.K;
+    if (p.w_layout == kBFractalNz) {
+        // FRACTAL_NZ [E, N/32, K/16, 16, 32]: element (k, n) at ((n/32 * K/16 + k/16) * 16 + k%16) * 32 + n%32
+        cuuint64_t dims[5] = {32, 16, (cuuint64_t)(p.K / 16), (cuuint64_t)(p.N / 32), (cuuint64_t)p.E};
+        cuuint64_t strides[4] = {32, 512, (cuuint64_t)p.K * 32, (cuuint64_t)p.K * (cuuint64_t)p.N};
+        cuuint32_t box[5] = {32, 16, BK / 16, 4, 1};
+        cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+        CUresult r = enc(&plan.map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, const_cast<int8_t *>(p.w), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+    } else {
+        const bool tr = p.w_layout == kBTransposed;
+        const cuuint64_t inner = tr ? p.K : p.N, mid = tr ? p.N : p.K;
         cuuint64_t dims[3] = {inner, mid, (cuuint64_t)p.E};
         cuuint64_t strides[2] = {inner, inner * mid};
         cuuint32_t box[3] = {128, 128, 1};
@@ -1040,6 +1096,7 @@ cudaError_t sm100_launch(const Problem &p, Plan &plan, void *workspace, cudaStre
     kp.bias = p.bias;
     kp.bias_dtype = p.bias ? p.bias_dtype : kNone;
     kp.act_type = p.act_type;
+    kp.out_f16 = p.out_f16;
     kp.status = reinterpret_cast<int *>(ws + plan.off_status);
     kp.amax_bits = reinterpret_cast<unsigned *>(ws + plan.off_amax);
     kp.rb_counter = reinterpret_cast<int *>(ws + plan.off_done);
@@ -1049,19 +1106,15 @@ cudaError_t sm100_launch(const Problem &p, Plan &plan, void *workspace, cudaStre
     kp.out = p.mode == kModeSwigluQuant ? static_cast<void *>(ws + plan.off_stage) : p.out0;
 
     cudaError_t e;
-    const bool mn = !p.w_trans;
-    const bool lean = !p.bias && p.act_type == 0 && (p.mode != kModeDequantBf16 || p.x_scale);
+    const bool lean = !p.bias && p.act_type == 0 && !p.out_f16 && (p.mode != kModeDequantBf16 || p.x_scale);
     const int epi = !lean ? kEpiGeneric : (p.out_row_index ? kEpiScatter : kEpiPlain);
     kp.num_peers = p.mode == kModeDequantBf16 ? p.num_peers : 0;
     for (int i = 0; i < 8; ++i) kp.out_peers[i] = i < kp.num_peers ? p.out_peers[i] : nullptr;
     if (kp.num_peers > 0 && epi != kEpiScatter) return cudaErrorInvalidValue;
     if (g_ev_start) cudaEventRecord(g_ev_start, stream);
-    if (p.mode == kModeSwigluQuant)
-        e = mn ? launch_ctas<kModeSwigluQuant, true, kEpiPlain>(plan, kp, stream) : launch_ctas<kModeSwigluQuant, false, kEpiPlain>(plan, kp, stream);
-    else if (p.mode == kModeInt32)
-        e = mn ? launch_epi<kModeInt32, true>(epi, plan, kp, stream) : launch_epi<kModeInt32, false>(epi, plan, kp, stream);
-    else
-        e = mn ? launch_epi<kModeDequantBf16, true>(epi, plan, kp, stream) : launch_epi<kModeDequantBf16, false>(epi, plan, kp, stream);
+    if (p.mode == kModeSwigluQuant) e = launch_layout<kModeSwigluQuant>(p.w_layout, epi, plan, kp, stream);
+    else if (p.mode == kModeInt32) e = launch_layout<kModeInt32>(p.w_layout, epi, plan, kp, stream);
+    else e = launch_layout<kModeDequantBf16>(p.w_layout, epi, plan, kp, stream);
     if (g_ev_stop) cudaEventRecord(g_ev_stop, stream);
     return e;
 }

@@ -14,7 +14,10 @@
 
 #include "acl_shim.h"
 #include "aclnnop/aclnn_grouped_matmul_swiglu_quant.h"
+#include "aclnnop/aclnn_grouped_matmul_swiglu_quant_weight_nz.h"
 #include "aclnnop/aclnn_grouped_matmul_v4.h"
+#include "aclnnop/aclnn_grouped_matmul_v5.h"
+#include "aclnnop/aclnn_grouped_matmul_weight_nz.h"
 #include "gmm_b200.h"
 
 namespace gmm {
@@ -110,7 +113,10 @@ void gmmB200SetTimingEvents(void *startEvent, void *stopEvent)
     set_timing_events(static_cast<cudaEvent_t>(startEvent), static_cast<cudaEvent_t>(stopEvent));
 }
 
-aclnnStatus aclnnGroupedMatmulV4GetWorkspaceSize(
+// Shared first phase of aclnnGroupedMatmulV4 / V5 / WeightNz (aclnnGroupedMatmulGetWorkspaceSizeCommon,
+// gmm/grouped_matmul/op_host/op_api/aclnn_grouped_matmul.cpp:1839-1880).  force_nz: the weight's storage is FRACTAL_NZ
+// whatever its format field says (the WeightNz entry point, :1917-1955).
+static aclnnStatus gmm_phase1(const char *kOp, bool force_nz,
     const aclTensorList *x, const aclTensorList *weight, const aclTensorList *biasOptional,
     const aclTensorList *scaleOptional, const aclTensorList *offsetOptional,
     const aclTensorList *antiquantScaleOptional, const aclTensorList *antiquantOffsetOptional,
@@ -120,11 +126,11 @@ aclnnStatus aclnnGroupedMatmulV4GetWorkspaceSize(
     int64_t actType, aclTensorList *out, aclTensorList *activationFeatureOutOptional,
     aclTensorList *dynQuantScaleOutOptional, uint64_t *workspaceSize, aclOpExecutor **executor)
 {
-    static const char *kOp = "aclnnGroupedMatmulV4";
     clear_error();
     // CheckNotNull
     GMM_REQUIRE(x != nullptr, ACLNN_ERR_PARAM_NULLPTR, "x must not be nullptr.");
     GMM_REQUIRE(!x->items.empty(), ACLNN_ERR_PARAM_INVALID, "x must not be empty tensorlist.");
+    (void)kOp;
     GMM_REQUIRE(weight != nullptr, ACLNN_ERR_PARAM_NULLPTR, "weight must not be nullptr.");
     GMM_REQUIRE(!weight->items.empty(), ACLNN_ERR_PARAM_INVALID, "weight must not be empty tensorlist.");
     GMM_REQUIRE(out != nullptr, ACLNN_ERR_PARAM_NULLPTR, "y must not be nullptr.");
@@ -167,8 +173,8 @@ aclnnStatus aclnnGroupedMatmulV4GetWorkspaceSize(
     // CheckFunctionParams: the int8 x int8 family.
     GMM_REQUIRE(tx->dtype == ACL_INT8 && tw->dtype == ACL_INT8, ACLNN_ERR_PARAM_INVALID,
                 "this build supports int8 x with int8 weight only.");
-    GMM_REQUIRE(ty->dtype == ACL_BF16 || ty->dtype == ACL_INT32, ACLNN_ERR_PARAM_INVALID,
-                "Expect yDtype is int32 or bfloat16 in quant case on this build (int8 and float16 results are not implemented).");
+    GMM_REQUIRE(ty->dtype == ACL_BF16 || ty->dtype == ACL_FLOAT16 || ty->dtype == ACL_INT32, ACLNN_ERR_PARAM_INVALID,
+                "Expect yDtype is int32, float16 or bfloat16 in quant case on this build (the int8 result is not implemented).");
     const aclTensor *tbias = nullptr;
     if (biasOptional != nullptr && !biasOptional->items.empty()) {
         GMM_REQUIRE(biasOptional->items.size() == 1 && biasOptional->items[0], ACLNN_ERR_PARAM_INVALID, "bias must hold one tensor.");
@@ -186,8 +192,12 @@ aclnnStatus aclnnGroupedMatmulV4GetWorkspaceSize(
         tscale = scaleOptional->items[0];
         // Reference pairs (bf16 scale, bf16 y); fp32 scale with a bf16 result is accepted as an extension
         // (the kernel converts every scale to fp32, grouped_matmul_quant_mixcore.h:262).
-        GMM_REQUIRE(tscale->dtype == ACL_BF16 || tscale->dtype == ACL_FLOAT, ACLNN_ERR_PARAM_INVALID,
-                    "quant case supports scale data type bfloat16 or float32 with output data type bfloat16.");
+        if (ty->dtype == ACL_FLOAT16)
+            GMM_REQUIRE(tscale->dtype == ACL_FLOAT, ACLNN_ERR_PARAM_INVALID,
+                        "quant case only supports scale with data type float32 when output is float16.");
+        else
+            GMM_REQUIRE(tscale->dtype == ACL_BF16 || tscale->dtype == ACL_FLOAT, ACLNN_ERR_PARAM_INVALID,
+                        "quant case supports scale data type bfloat16 or float32 with output data type bfloat16.");
         if (perTokenScaleOptional != nullptr) {
             GMM_REQUIRE(perTokenScaleOptional->items.size() == 1, ACLNN_ERR_PARAM_INVALID,
                         "perTokenScaleOptional size[%zu] must be 1 and equal with x size[1].", perTokenScaleOptional->items.size());
@@ -200,17 +210,26 @@ aclnnStatus aclnnGroupedMatmulV4GetWorkspaceSize(
         GMM_REQUIRE(antiquantScaleOptional == nullptr && antiquantOffsetOptional == nullptr, ACLNN_ERR_PARAM_INVALID,
                     "Detected quant, but antiquant inputs is not empty!");
     }
-    GMM_REQUIRE(actType == GMM_ACT_TYPE_NONE || actType == GMM_ACT_TYPE_RELU, ACLNN_ERR_PARAM_INVALID,
-                "this build implements actType NONE and RELU only, got %lld.", (long long)actType);
 
     // SplitMSingleXSingleWeightSingleY: dims and shapes x(m,k), weight(e,k,n), y(m,n).
     GMM_REQUIRE(!is_private_format(tx->format) && !is_private_format(ty->format), ACLNN_ERR_PARAM_INVALID, "Invalid format.");
-    GMM_REQUIRE(!is_private_format(tw->format), ACLNN_ERR_PARAM_INVALID, "weight format FRACTAL_NZ is not supported by this build.");
+    const bool w_nz = force_nz || tw->format == ACL_FORMAT_FRACTAL_NZ;
+    GMM_REQUIRE(w_nz || !is_private_format(tw->format), ACLNN_ERR_PARAM_INVALID, "Invalid weight format.");
     GMM_REQUIRE(tx->rank() == 2, ACLNN_ERR_PARAM_INVALID, "x[0] dim num should be 2 in this case, but now is %zu.", tx->rank());
-    GMM_REQUIRE(tw->rank() == 3, ACLNN_ERR_PARAM_INVALID, "weight[0] dim num should be 3 in this case, but now is %zu.", tw->rank());
     GMM_REQUIRE(ty->rank() == 2, ACLNN_ERR_PARAM_INVALID, "y[0] dim num should be 2 in this case, but now is %zu.", ty->rank());
-    const int64_t M = tx->dim(0), K = tx->dim(1), E = tw->dim(0), N = tw->dim(2);
-    GMM_REQUIRE(tw->dim(1) == K, ACLNN_ERR_PARAM_INVALID, "k dim value of x and weight is not matched.");
+    const int64_t M = tx->dim(0), K = tx->dim(1), E = tw->rank() ? tw->dim(0) : 0;
+    int64_t N = 0;
+    if (w_nz && tw->rank() == 5) {
+        // FRACTAL_NZ view [E, N/32, K/16, 16, 32] (int8 fractal 16 x 32)
+        GMM_REQUIRE(tw->dim(3) == 16 && tw->dim(4) == 32 && tw->dim(2) * 16 == K, ACLNN_ERR_PARAM_INVALID,
+                    "FRACTAL_NZ weight must be [E, N/32, K/16, 16, 32] with K/16 * 16 equal to x's K.");
+        N = tw->dim(1) * 32;
+    } else {
+        GMM_REQUIRE(tw->rank() == 3, ACLNN_ERR_PARAM_INVALID, "weight[0] dim num should be 3 in this case, but now is %zu.", tw->rank());
+        N = tw->dim(2);
+        GMM_REQUIRE(tw->dim(1) == K, ACLNN_ERR_PARAM_INVALID, "k dim value of x and weight is not matched.");
+        if (w_nz) GMM_REQUIRE(K % 16 == 0 && N % 32 == 0, ACLNN_ERR_PARAM_INVALID, "FRACTAL_NZ weight needs K %% 16 == 0 and N %% 32 == 0.");
+    }
     GMM_REQUIRE(ty->dim(0) == M, ACLNN_ERR_PARAM_INVALID, "m dim value of x and y is not matched.");
     GMM_REQUIRE(ty->dim(1) == N, ACLNN_ERR_PARAM_INVALID, "n dim value of weight and y is not matched.");
     GMM_REQUIRE(K <= kMaxInnerAxis && N <= kMaxInnerAxis, ACLNN_ERR_PARAM_INVALID, "inner axis of x / weight must not exceed %lld.", (long long)kMaxInnerAxis);
@@ -237,8 +256,8 @@ aclnnStatus aclnnGroupedMatmulV4GetWorkspaceSize(
     // Empty tensors: nothing to launch (CheckZeroShape, aclnn_grouped_matmul.cpp:1535-1548).
     if (M == 0 || N == 0 || glLen == 0) return finish_phase1(e, workspaceSize, executor);
 
-    const bool w_trans = !tw->contiguous() && is_transposed_last_two(tw);
-    if (!(tx->contiguous() && ty->contiguous() && (tw->contiguous() || w_trans) && groupListOptional->contiguous() &&
+    const bool w_trans = !w_nz && !tw->contiguous() && is_transposed_last_two(tw);
+    if (!(tx->contiguous() && ty->contiguous() && (tw->contiguous() || w_trans || w_nz) && groupListOptional->contiguous() &&
           (!tscale || tscale->contiguous()) && (!tpts || tpts->contiguous()) && (!tbias || tbias->contiguous()))) {
         delete e;
         return fail(ACLNN_ERR_PARAM_INVALID, "this build needs contiguous tensors (a transposed weight view excepted).");
@@ -255,13 +274,32 @@ aclnnStatus aclnnGroupedMatmulV4GetWorkspaceSize(
     p.gl_len = (int)(E == 1 ? 1 : glLen);
     p.gl_type = (int)groupListType;
     p.M = M; p.K = K; p.N = N; p.E = E;
-    p.w_trans = w_trans ? 1 : 0;
-    p.act_type = (int)actType;
+    p.w_layout = w_nz ? 2 : (w_trans ? 1 : 0);
+    // The reference's test for an activation with an int32 result never fires (aclnn_grouped_matmul.cpp:984-985) and its
+    // int32 kernel has no vector stage: the activation is accepted and has no effect.
+    p.act_type = int32_out ? 0 : (int)actType;
     p.mode = int32_out ? kModeInt32 : kModeDequantBf16;
+    p.out_f16 = ty->dtype == ACL_FLOAT16 ? 1 : 0;
     p.out0 = tensor_ptr(ty);
     e->kind = aclOpExecutor::kGmm;
     make_plan(p, &e->plan);
     return finish_phase1(e, workspaceSize, executor);
+}
+
+aclnnStatus aclnnGroupedMatmulV4GetWorkspaceSize(
+    const aclTensorList *x, const aclTensorList *weight, const aclTensorList *biasOptional,
+    const aclTensorList *scaleOptional, const aclTensorList *offsetOptional,
+    const aclTensorList *antiquantScaleOptional, const aclTensorList *antiquantOffsetOptional,
+    const aclTensorList *perTokenScaleOptional, const aclTensor *groupListOptional,
+    const aclTensorList *activationInputOptional, const aclTensorList *activationQuantScaleOptional,
+    const aclTensorList *activationQuantOffsetOptional, int64_t splitItem, int64_t groupType, int64_t groupListType,
+    int64_t actType, aclTensorList *out, aclTensorList *activationFeatureOutOptional,
+    aclTensorList *dynQuantScaleOutOptional, uint64_t *workspaceSize, aclOpExecutor **executor)
+{
+    return gmm_phase1("aclnnGroupedMatmulV4", false, x, weight, biasOptional, scaleOptional, offsetOptional, antiquantScaleOptional,
+                      antiquantOffsetOptional, perTokenScaleOptional, groupListOptional, activationInputOptional,
+                      activationQuantScaleOptional, activationQuantOffsetOptional, splitItem, groupType, groupListType, actType, out,
+                      activationFeatureOutOptional, dynQuantScaleOutOptional, workspaceSize, executor);
 }
 
 aclnnStatus aclnnGroupedMatmulV4(void *workspace, uint64_t workspaceSize, aclOpExecutor *executor, aclrtStream stream)
@@ -269,13 +307,71 @@ aclnnStatus aclnnGroupedMatmulV4(void *workspace, uint64_t workspaceSize, aclOpE
     return run_executor("aclnnGroupedMatmulV4", workspace, workspaceSize, executor, stream);
 }
 
-aclnnStatus aclnnGroupedMatmulSwigluQuantGetWorkspaceSize(const aclTensor *x, const aclTensor *weight, const aclTensor *bias,
-                                                          const aclTensor *offset, const aclTensor *weightScale,
-                                                          const aclTensor *xScale, const aclTensor *groupList,
-                                                          aclTensor *output, aclTensor *outputScale, aclTensor *outputOffset,
-                                                          uint64_t *workspaceSize, aclOpExecutor **executor)
+// tuningConfigOptional is a hint for the reference's host tiling (expected rows per group,
+// aclnn_grouped_matmul.cpp:1336-1360); the device scheduler here reads group_list itself, so the hint is only validated.
+static aclnnStatus check_tuning_config(const aclIntArray *cfg)
 {
-    static const char *kOp = "aclnnGroupedMatmulSwigluQuant";
+    if (cfg)
+        for (int64_t v : cfg->values)
+            if (v < 0) return fail(ACLNN_ERR_PARAM_INVALID, "tuningConfig values must not be negative.");
+    return ACLNN_SUCCESS;
+}
+
+aclnnStatus aclnnGroupedMatmulV5GetWorkspaceSize(
+    const aclTensorList *x, const aclTensorList *weight, const aclTensorList *biasOptional,
+    const aclTensorList *scaleOptional, const aclTensorList *offsetOptional,
+    const aclTensorList *antiquantScaleOptional, const aclTensorList *antiquantOffsetOptional,
+    const aclTensorList *perTokenScaleOptional, const aclTensor *groupListOptional,
+    const aclTensorList *activationInputOptional, const aclTensorList *activationQuantScaleOptional,
+    const aclTensorList *activationQuantOffsetOptional, int64_t splitItem, int64_t groupType, int64_t groupListType,
+    int64_t actType, aclIntArray *tuningConfigOptional, aclTensorList *out, aclTensorList *activationFeatureOutOptional,
+    aclTensorList *dynQuantScaleOutOptional, uint64_t *workspaceSize, aclOpExecutor **executor)
+{
+    clear_error();
+    if (check_tuning_config(tuningConfigOptional) != ACLNN_SUCCESS) return ACLNN_ERR_PARAM_INVALID;
+    return gmm_phase1("aclnnGroupedMatmulV5", false, x, weight, biasOptional, scaleOptional, offsetOptional, antiquantScaleOptional,
+                      antiquantOffsetOptional, perTokenScaleOptional, groupListOptional, activationInputOptional,
+                      activationQuantScaleOptional, activationQuantOffsetOptional, splitItem, groupType, groupListType, actType, out,
+                      activationFeatureOutOptional, dynQuantScaleOutOptional, workspaceSize, executor);
+}
+
+aclnnStatus aclnnGroupedMatmulV5(void *workspace, uint64_t workspaceSize, aclOpExecutor *executor, aclrtStream stream)
+{
+    return run_executor("aclnnGroupedMatmulV5", workspace, workspaceSize, executor, stream);
+}
+
+aclnnStatus aclnnGroupedMatmulWeightNzGetWorkspaceSize(
+    const aclTensorList *x, const aclTensorList *weight, const aclTensorList *biasOptional,
+    const aclTensorList *scaleOptional, const aclTensorList *offsetOptional,
+    const aclTensorList *antiquantScaleOptional, const aclTensorList *antiquantOffsetOptional,
+    const aclTensorList *perTokenScaleOptional, const aclTensor *groupListOptional,
+    const aclTensorList *activationInputOptional, const aclTensorList *activationQuantScaleOptional,
+    const aclTensorList *activationQuantOffsetOptional, int64_t splitItem, int64_t groupType, int64_t groupListType,
+    int64_t actType, aclIntArray *tuningConfigOptional, int64_t quantGroupSize, aclTensorList *out,
+    aclTensorList *activationFeatureOutOptional, aclTensorList *dynQuantScaleOutOptional, uint64_t *workspaceSize,
+    aclOpExecutor **executor)
+{
+    clear_error();
+    if (check_tuning_config(tuningConfigOptional) != ACLNN_SUCCESS) return ACLNN_ERR_PARAM_INVALID;
+    GMM_REQUIRE(quantGroupSize >= 0, ACLNN_ERR_PARAM_INVALID, "quantGroupSize must not be negative.");
+    return gmm_phase1("aclnnGroupedMatmulWeightNz", true, x, weight, biasOptional, scaleOptional, offsetOptional,
+                      antiquantScaleOptional, antiquantOffsetOptional, perTokenScaleOptional, groupListOptional,
+                      activationInputOptional, activationQuantScaleOptional, activationQuantOffsetOptional, splitItem, groupType,
+                      groupListType, actType, out, activationFeatureOutOptional, dynQuantScaleOutOptional, workspaceSize, executor);
+}
+
+aclnnStatus aclnnGroupedMatmulWeightNz(void *workspace, uint64_t workspaceSize, aclOpExecutor *executor, aclrtStream stream)
+{
+    return run_executor("aclnnGroupedMatmulWeightNz", workspace, workspaceSize, executor, stream);
+}
+
+// Shared first phase of aclnnGroupedMatmulSwigluQuant and its WeightNZ twin
+// (aclnnGroupedMatmulSwigluQuantGetWorkspaceSizeCommon, aclnn_grouped_matmul_swiglu_quant.cpp:411-465).
+static aclnnStatus swiglu_phase1(const char *kOp, bool force_nz, const aclTensor *x, const aclTensor *weight, const aclTensor *bias,
+                                 const aclTensor *offset, const aclTensor *weightScale, const aclTensor *xScale,
+                                 const aclTensor *groupList, aclTensor *output, aclTensor *outputScale, aclTensor *outputOffset,
+                                 uint64_t *workspaceSize, aclOpExecutor **executor)
+{
     clear_error();
     (void)bias; (void)offset; (void)outputOffset;  // accepted and ignored, as in the reference (:86-104)
     // OP_CHECK_COMM_INPUT + CheckNotNull
@@ -290,9 +386,13 @@ aclnnStatus aclnnGroupedMatmulSwigluQuantGetWorkspaceSize(const aclTensor *x, co
     GMM_REQUIRE(outputScale != nullptr, ACLNN_ERR_PARAM_NULLPTR, "outputScale must not be nullptr.");
     // CheckInputOutDims_A8W8
     GMM_REQUIRE(x->rank() == 2, ACLNN_ERR_PARAM_INVALID, "x dim num should be 2, but now is %zu.", x->rank());
-    GMM_REQUIRE(!is_private_format(weight->format), ACLNN_ERR_PARAM_INVALID,
-                "weight storage format FRACTAL_NZ is not supported by this build; pass the ND [E, K, N] tensor.");
-    GMM_REQUIRE(weight->rank() == 3, ACLNN_ERR_PARAM_INVALID, "weight dim num should be 3, but now is %zu.", weight->rank());
+    const bool w_nz = force_nz || weight->format == ACL_FORMAT_FRACTAL_NZ;
+    GMM_REQUIRE(w_nz || !is_private_format(weight->format), ACLNN_ERR_PARAM_INVALID, "weight format must be ND or FRACTAL_NZ.");
+    if (force_nz)
+        GMM_REQUIRE(weight->storage_dims.size() == 5, ACLNN_ERR_PARAM_INVALID,
+                    "The dimnum of storageShape for second input (weight) must be 5, but is %zu.", weight->storage_dims.size());
+    const bool nz_view = w_nz && weight->rank() == 5;
+    GMM_REQUIRE(nz_view || weight->rank() == 3, ACLNN_ERR_PARAM_INVALID, "weight dim num should be 3 (ND) or 5 (FRACTAL_NZ), but now is %zu.", weight->rank());
     GMM_REQUIRE(weightScale->rank() == 2, ACLNN_ERR_PARAM_INVALID, "weightScale dim num should be 2, but now is %zu.", weightScale->rank());
     GMM_REQUIRE(xScale->rank() == 1, ACLNN_ERR_PARAM_INVALID, "xScale dim num should be 1, but now is %zu.", xScale->rank());
     GMM_REQUIRE(groupList->rank() == 1, ACLNN_ERR_PARAM_INVALID, "groupList dim num should be 1, but now is %zu.", groupList->rank());
@@ -301,7 +401,13 @@ aclnnStatus aclnnGroupedMatmulSwigluQuantGetWorkspaceSize(const aclTensor *x, co
     // CheckInputOutShape_A8W8
     const int64_t M = x->dim(0), K = x->dim(1), N = weightScale->dim(1), E = weight->dim(0);
     GMM_REQUIRE(N % 2 == 0, ACLNN_ERR_PARAM_INVALID, "aclnnGroupedMatmulSwiGluQuant, N is %lld , not an even number.", (long long)N);
-    GMM_REQUIRE(weight->dim(1) == K && weight->dim(2) == N, ACLNN_ERR_PARAM_INVALID, "weight shape must be [%lld, %lld, %lld].", (long long)E, (long long)K, (long long)N);
+    if (nz_view)
+        GMM_REQUIRE(weight->dim(1) == N / 32 && weight->dim(2) == K / 16 && weight->dim(3) == 16 && weight->dim(4) == 32 && N % 32 == 0 && K % 16 == 0,
+                    ACLNN_ERR_PARAM_INVALID, "weight shape must be [%lld, %lld, %lld, 16, 32].", (long long)E, (long long)(N / 32), (long long)(K / 16));
+    else
+        GMM_REQUIRE(weight->dim(1) == K && weight->dim(2) == N, ACLNN_ERR_PARAM_INVALID, "weight shape must be [%lld, %lld, %lld].", (long long)E, (long long)K, (long long)N);
+    if (w_nz)
+        GMM_REQUIRE(K % 16 == 0 && N % 32 == 0, ACLNN_ERR_PARAM_INVALID, "a FRACTAL_NZ weight needs K %% 16 == 0 and N %% 32 == 0 on this build.");
     GMM_REQUIRE(weightScale->dim(0) == E, ACLNN_ERR_PARAM_INVALID, "weightScale shape must be [%lld, %lld].", (long long)E, (long long)N);
     GMM_REQUIRE(xScale->dim(0) == M, ACLNN_ERR_PARAM_INVALID, "xScale shape must be [%lld].", (long long)M);
     GMM_REQUIRE(output->dim(0) == M && output->dim(1) == N / 2, ACLNN_ERR_PARAM_INVALID, "output shape must be [%lld, %lld].", (long long)M, (long long)(N / 2));
@@ -328,7 +434,7 @@ aclnnStatus aclnnGroupedMatmulSwigluQuantGetWorkspaceSize(const aclTensor *x, co
     GMM_REQUIRE(e != nullptr, ACLNN_ERR_INNER_CREATE_EXECUTOR, "cannot create executor.");
     // Empty tensors (aclnn_grouped_matmul_swiglu_quant.cpp:425-429)
     if (output->empty() || groupList->empty() || outputScale->empty()) return finish_phase1(e, workspaceSize, executor);
-    if (!(x->contiguous() && weight->contiguous() && weightScale->contiguous() && xScale->contiguous() &&
+    if (!(x->contiguous() && (weight->contiguous() || w_nz) && weightScale->contiguous() && xScale->contiguous() &&
           groupList->contiguous() && output->contiguous() && outputScale->contiguous())) {
         delete e;
         return fail(ACLNN_ERR_PARAM_INVALID, "this build needs contiguous tensors.");
@@ -343,6 +449,7 @@ aclnnStatus aclnnGroupedMatmulSwigluQuantGetWorkspaceSize(const aclTensor *x, co
     p.gl_len = (int)glLen;
     p.gl_type = 0;
     p.M = M; p.K = K; p.N = N; p.E = E;
+    p.w_layout = w_nz ? 2 : 0;
     p.mode = kModeSwigluQuant;
     p.out0 = tensor_ptr(output);
     p.out1 = tensor_ptr(outputScale);
@@ -351,9 +458,36 @@ aclnnStatus aclnnGroupedMatmulSwigluQuantGetWorkspaceSize(const aclTensor *x, co
     return finish_phase1(e, workspaceSize, executor);
 }
 
+aclnnStatus aclnnGroupedMatmulSwigluQuantGetWorkspaceSize(const aclTensor *x, const aclTensor *weight, const aclTensor *bias,
+                                                          const aclTensor *offset, const aclTensor *weightScale,
+                                                          const aclTensor *xScale, const aclTensor *groupList,
+                                                          aclTensor *output, aclTensor *outputScale, aclTensor *outputOffset,
+                                                          uint64_t *workspaceSize, aclOpExecutor **executor)
+{
+    return swiglu_phase1("aclnnGroupedMatmulSwigluQuant", false, x, weight, bias, offset, weightScale, xScale, groupList, output,
+                         outputScale, outputOffset, workspaceSize, executor);
+}
+
 aclnnStatus aclnnGroupedMatmulSwigluQuant(void *workspace, uint64_t workspaceSize, aclOpExecutor *executor, aclrtStream stream)
 {
     return run_executor("aclnnGroupedMatmulSwigluQuant", workspace, workspaceSize, executor, stream);
+}
+
+aclnnStatus aclnnGroupedMatmulSwigluQuantWeightNZGetWorkspaceSize(const aclTensor *x, const aclTensor *weight, const aclTensor *bias,
+                                                                  const aclTensor *offset, const aclTensor *weightScale,
+                                                                  const aclTensor *xScale, const aclTensor *groupList,
+                                                                  aclTensor *output, aclTensor *outputScale,
+                                                                  aclTensor *outputOffset, uint64_t *workspaceSize,
+                                                                  aclOpExecutor **executor)
+{
+    return swiglu_phase1("aclnnGroupedMatmulSwigluQuantWeightNZ", true, x, weight, bias, offset, weightScale, xScale, groupList,
+                         output, outputScale, outputOffset, workspaceSize, executor);
+}
+
+aclnnStatus aclnnGroupedMatmulSwigluQuantWeightNZ(void *workspace, uint64_t workspaceSize, aclOpExecutor *executor,
+                                                  aclrtStream stream)
+{
+    return run_executor("aclnnGroupedMatmulSwigluQuantWeightNZ", workspace, workspaceSize, executor, stream);
 }
 
 aclnnStatus gmmB200CheckStatus(const void *workspace, uint64_t workspaceSize, aclrtStream stream, int32_t record[4])
@@ -406,7 +540,7 @@ aclnnStatus gmmB200GroupedMatmulW8A8WorkspaceSize(int64_t m, int64_t k, int64_t 
     GMM_REQUIRE(workspaceSize != nullptr, ACLNN_ERR_PARAM_NULLPTR, "workspaceSize must not be nullptr.");
     aclnnStatus rc = flat_sizes_ok(m, k, n, e);
     if (rc != ACLNN_SUCCESS) return rc;
-    GMM_REQUIRE(yDtype == ACL_BF16 || yDtype == ACL_INT32, ACLNN_ERR_PARAM_INVALID, "yDtype must be bfloat16 or int32.");
+    GMM_REQUIRE(yDtype == ACL_BF16 || yDtype == ACL_FLOAT16 || yDtype == ACL_INT32, ACLNN_ERR_PARAM_INVALID, "yDtype must be bfloat16, float16 or int32.");
     *workspaceSize = flat_ws(m, k, n, e, yDtype == ACL_INT32 ? kModeInt32 : kModeDequantBf16);
     return ACLNN_SUCCESS;
 }
@@ -422,7 +556,7 @@ aclnnStatus gmmB200GroupedMatmulW8A8(const void *x, const void *weight, const vo
     GMM_REQUIRE(x && weight && groupList && (y || numPeers > 0), ACLNN_ERR_PARAM_NULLPTR, "x, weight, groupList and y must not be nullptr.");
     aclnnStatus rc = flat_sizes_ok(m, k, n, e);
     if (rc != ACLNN_SUCCESS) return rc;
-    GMM_REQUIRE(yDtype == ACL_BF16 || yDtype == ACL_INT32, ACLNN_ERR_PARAM_INVALID, "yDtype must be bfloat16 or int32.");
+    GMM_REQUIRE(yDtype == ACL_BF16 || yDtype == ACL_FLOAT16 || yDtype == ACL_INT32, ACLNN_ERR_PARAM_INVALID, "yDtype must be bfloat16, float16 or int32.");
     GMM_REQUIRE(numPeers >= 0 && numPeers <= 8, ACLNN_ERR_PARAM_INVALID, "numPeers must be in [0, 8].");
     if (numPeers > 0) {
         GMM_REQUIRE(outPeers && outRowIndex && yDtype == ACL_BF16 && !bias && actType == 0 && perTokenScale, ACLNN_ERR_PARAM_INVALID,
@@ -430,15 +564,19 @@ aclnnStatus gmmB200GroupedMatmulW8A8(const void *x, const void *weight, const vo
         for (int i = 0; i < numPeers; ++i)
             GMM_REQUIRE(outPeers[i] && !(reinterpret_cast<uintptr_t>(outPeers[i]) & 15), ACLNN_ERR_PARAM_INVALID, "outPeers[%d] is null or unaligned.", i);
     }
-    if (yDtype == ACL_BF16) {
-        GMM_REQUIRE(scale != nullptr, ACLNN_ERR_PARAM_NULLPTR, "scale must not be nullptr for a bfloat16 result.");
+    if (yDtype != ACL_INT32) {
+        GMM_REQUIRE(scale != nullptr, ACLNN_ERR_PARAM_NULLPTR, "scale must not be nullptr for a floating-point result.");
         GMM_REQUIRE(scaleDtype == ACL_BF16 || scaleDtype == ACL_FLOAT, ACLNN_ERR_PARAM_INVALID, "scaleDtype must be bfloat16 or float32.");
     }
     GMM_REQUIRE(!bias || biasDtype == ACL_INT32 || biasDtype == ACL_BF16, ACLNN_ERR_PARAM_INVALID, "biasDtype must be int32 or bfloat16.");
     GMM_REQUIRE(groupListType == 0 || groupListType == 1, ACLNN_ERR_PARAM_INVALID, "groupListType should be 0 or 1.");
     GMM_REQUIRE(groupListLen >= 0 && groupListLen <= e && groupListLen <= kMaxGroupListLen, ACLNN_ERR_PARAM_INVALID,
                 "groupListLen %lld out of range [0, min(e, %lld)].", (long long)groupListLen, (long long)kMaxGroupListLen);
-    GMM_REQUIRE(actType == 0 || actType == 1, ACLNN_ERR_PARAM_INVALID, "actType must be 0 (none) or 1 (relu).");
+    GMM_REQUIRE(actType == 0 || actType == 1 || actType == 2 || actType == 4 || actType == 5, ACLNN_ERR_PARAM_INVALID,
+                "actType must be 0 (none), 1 (relu), 2 (gelu tanh), 4 (fast gelu) or 5 (silu).");
+    GMM_REQUIRE(weightTransposed >= 0 && weightTransposed <= 2, ACLNN_ERR_PARAM_INVALID,
+                "weight layout must be 0 ([e,k,n]), 1 ([e,n,k]) or 2 (FRACTAL_NZ).");
+    GMM_REQUIRE(weightTransposed != 2 || (k % 16 == 0 && n % 32 == 0), ACLNN_ERR_PARAM_INVALID, "FRACTAL_NZ needs k %% 16 == 0 and n %% 32 == 0.");
     if (m == 0 || groupListLen == 0) return ACLNN_SUCCESS;
     Problem p;
     p.x = static_cast<const int8_t *>(x);
@@ -449,9 +587,10 @@ aclnnStatus gmmB200GroupedMatmulW8A8(const void *x, const void *weight, const vo
     p.group_list = static_cast<const int64_t *>(groupList);
     p.gl_len = (int)groupListLen; p.gl_type = groupListType;
     p.M = m; p.K = k; p.N = n; p.E = e;
-    p.w_trans = weightTransposed ? 1 : 0;
-    p.act_type = actType;
+    p.w_layout = weightTransposed;
+    p.act_type = yDtype == ACL_INT32 ? 0 : actType;
     p.mode = yDtype == ACL_INT32 ? kModeInt32 : kModeDequantBf16;
+    p.out_f16 = yDtype == ACL_FLOAT16 ? 1 : 0;
     p.out0 = y ? y : outPeers[0];
     p.out_row_index = static_cast<const int64_t *>(outRowIndex);
     p.num_peers = numPeers;
@@ -480,8 +619,8 @@ aclnnStatus gmmB200GroupedMatmulSwigluQuantWorkspaceSize(int64_t m, int64_t k, i
 
 aclnnStatus gmmB200GroupedMatmulSwigluQuant(const void *x, const void *weight, const void *weightScale, int32_t weightScaleDtype,
                                             const void *xScale, const void *groupList, int64_t groupListLen, int64_t m, int64_t k,
-                                            int64_t n, int64_t e, void *output, void *outputScale, void *workspace,
-                                            uint64_t workspaceSize, aclrtStream stream)
+                                            int64_t n, int64_t e, int32_t weightLayout, void *output, void *outputScale,
+                                            void *workspace, uint64_t workspaceSize, aclrtStream stream)
 {
     clear_error();
     GMM_REQUIRE(x && weight && weightScale && xScale && groupList && output && outputScale, ACLNN_ERR_PARAM_NULLPTR,
@@ -494,6 +633,8 @@ aclnnStatus gmmB200GroupedMatmulSwigluQuant(const void *x, const void *weight, c
                 "weightScaleDtype must be float32, float16 or bfloat16.");
     GMM_REQUIRE(groupListLen >= 0 && groupListLen <= e && groupListLen <= kMaxGroupListLen, ACLNN_ERR_PARAM_INVALID,
                 "groupListLen %lld out of range [0, min(e, %lld)].", (long long)groupListLen, (long long)kMaxGroupListLen);
+    GMM_REQUIRE(weightLayout == 0 || (weightLayout == 2 && k % 16 == 0 && n % 32 == 0), ACLNN_ERR_PARAM_INVALID,
+                "weightLayout must be 0 ([e,k,n]) or 2 (FRACTAL_NZ, which needs k %% 16 == 0 and n %% 32 == 0).");
     if (m == 0 || groupListLen == 0) return ACLNN_SUCCESS;
     Problem p;
     p.x = static_cast<const int8_t *>(x);
@@ -503,6 +644,7 @@ aclnnStatus gmmB200GroupedMatmulSwigluQuant(const void *x, const void *weight, c
     p.group_list = static_cast<const int64_t *>(groupList);
     p.gl_len = (int)groupListLen; p.gl_type = 0;
     p.M = m; p.K = k; p.N = n; p.E = e;
+    p.w_layout = weightLayout;
     p.mode = kModeSwigluQuant;
     p.out0 = output; p.out1 = outputScale;
     Plan plan;

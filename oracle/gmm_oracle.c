@@ -253,13 +253,32 @@ static void gemm_group(const int8_t *x, int64_t rows, int64_t K, int64_t N, cons
  *   t = t * per_token_scale[m]                PerTokenQuant Mul, :300   (order: (acc*w_scale)*x_scale)
  *   t = t + float(bias[e,n])  if bias is bf16 :309-313
  *   act_type 1: t = max(t, 0)                 Relu, :398
- *   y = bf16_rne(t)                           :282
+ *   act_type 2 / 4 / 5: Gelu / FasterGelu / Silu of the vector library, :394-403.  The library is not part of the
+ *             reference's sources; its published definitions are restated in activation() below (parity unpinned).
+ *   y = bf16_rne(t)  (or fp16_rne(t))         :282
  * An int32 bias is added inside the matmul to the accumulator (gmm/grouped_matmul/op_kernel/grouped_matmul.h:451-469).
  *
- * y_dtype: 27 = bf16 output; 3 = raw int32 accumulators (+ int32 bias) written to y.
+ * y_dtype: 27 = bf16 output; 1 = fp16 output; 3 = raw int32 accumulators (+ int32 bias) written to y.
  * w_trans: 0 = weight stored [E,K,N]; 1 = weight stored [E,N,K] (the transposed view the operator accepts).
  * Rows not covered by group_list are left untouched.  acc_out / pre_cast (both [M,N], optional) receive
  * the int32 accumulators and the fp32 values before the final cast. */
+/* Gelu(x) = x / (1 + exp(-1.59576912 (x + 0.044715 x^3))), FasterGelu(x) = x / (1 + exp(-1.702 x)),
+ * Silu(x) = x / (1 + exp(-x)); fp32, every operation rounded on its own (-ffp-contract=off). */
+static inline float activation(int act_type, float t)
+{
+    switch (act_type) {
+        case 1: return t > 0.0f ? t : 0.0f;
+        case 2: {
+            const float t3 = (t * t) * t;
+            const float u = -1.59576912f * (t + 0.044715f * t3);
+            return t / (1.0f + expf(u));
+        }
+        case 4: return t / (1.0f + expf(-1.702f * t));
+        case 5: return t / (1.0f + expf(-t));
+        default: return t;
+    }
+}
+
 ORACLE_API int oracle_gmm_w8a8(const int8_t *x, const int8_t *w, const void *scale, int scale_dtype,
                                const float *per_token_scale, const void *bias, int bias_dtype,
                                const int64_t *group_list, int64_t gl_len, int gl_type, int64_t M, int64_t K,
@@ -291,9 +310,9 @@ ORACLE_API int oracle_gmm_w8a8(const int8_t *x, const int8_t *w, const void *sca
                 t = t * load_scale(scale, scale_dtype, g * N + n);
                 if (per_token_scale) t = t * xs;
                 if (bias && bias_dtype == DT_BF16) t = t + bf16_to_f32(((const uint16_t *)bias)[g * N + n]);
-                if (act_type == 1) t = t > 0.0f ? t : 0.0f;
+                t = activation(act_type, t);
                 if (pre_cast) pre_cast[m * N + n] = t;
-                ((uint16_t *)y)[m * N + n] = f32_to_bf16_rne(t);
+                ((uint16_t *)y)[m * N + n] = y_dtype == DT_F16 ? f32_to_f16_rne(t) : f32_to_bf16_rne(t);
             }
         }
     }

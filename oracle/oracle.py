@@ -99,9 +99,9 @@ def gmm_w8a8(x, w, scale, per_token_scale, group_list, gl_type=0, bias=None, act
     if bias is not None:
         bias = np.ascontiguousarray(bias)
         bias_dt = DT_I32 if bias.dtype == np.int32 else DT_BF16
-    if y_dtype == "bf16":
+    if y_dtype in ("bf16", "f16"):  # both travel as uint16 bit patterns
         y = np.zeros((M, N), np.uint16) if y_init is None else np.array(y_init, np.uint16, copy=True)
-        ydt = DT_BF16
+        ydt = DT_BF16 if y_dtype == "bf16" else DT_F16
     else:
         y = np.zeros((M, N), np.int32) if y_init is None else np.array(y_init, np.int32, copy=True)
         ydt = DT_I32

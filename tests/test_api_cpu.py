@@ -30,17 +30,26 @@ def test_library_exports_every_declared_symbol(gmm_lib):
     assert gmm_lib.gmmB200Version() >= 100
 
 
-def _v4_phase1(x, w, scale, pts, gl, out, bias=None, split_item=3, group_type=0, gl_type=0, act=0, extra=None):
+def _v4_phase1(x, w, scale, pts, gl, out, bias=None, split_item=3, group_type=0, gl_type=0, act=0, extra=None, api="V4",
+               fmt_w=_lib.ACL_FORMAT_ND, tuning=None, quant_group_size=0):
     L = _lib.lib()
     mk = lambda t: acl.create_tensor_list([t]) if t is not None else None  # noqa: E731
-    hx, hw, hb, hs, hp, hy = mk(x), mk(w), mk(bias), mk(scale), mk(pts), mk(out)
+    hx, hb, hs, hp, hy = mk(x), mk(bias), mk(scale), mk(pts), mk(out)
+    hw = acl.create_tensor_list([w], fmt_w) if w is not None else None
     hg = acl.create_tensor(gl) if gl is not None else None
     size, ex = C.c_uint64(123), C.c_void_p(0)
     args = [hx, hw, hb, hs, None, None, None, hp, hg, None, None, None, split_item, group_type, gl_type, act, hy, None, None]
     if extra:
         for k, v in extra.items():
             args[k] = v
-    rc = L.aclnnGroupedMatmulV4GetWorkspaceSize(*args, C.byref(size), C.byref(ex))
+    ht = L.aclCreateIntArray((C.c_int64 * len(tuning))(*tuning), len(tuning)) if tuning is not None else None
+    if api == "V5":
+        args = args[:16] + [ht] + args[16:]
+    elif api == "WeightNz":
+        args = args[:16] + [ht, quant_group_size] + args[16:]
+    rc = getattr(L, f"aclnnGroupedMatmul{api}GetWorkspaceSize")(*args, C.byref(size), C.byref(ex))
+    if ht:
+        L.aclDestroyIntArray(ht)
     if rc == OK:
         assert L.aclDestroyAclOpExecutor(ex) == OK
     for h in (hx, hw, hb, hs, hp, hy):
@@ -138,14 +147,14 @@ def test_v4_transposed_weight_view_and_unaligned_shapes():
     assert "contiguous" in _lib.last_error()
 
 
-def _sw_phase1(x, w, ws, xs, gl, q, qs, fmt_w=_lib.ACL_FORMAT_ND, null=()):
+def _sw_phase1(x, w, ws, xs, gl, q, qs, fmt_w=_lib.ACL_FORMAT_ND, null=(), api=""):
     L = _lib.lib()
     hs = dict(x=x, w=w, ws=ws, xs=xs, gl=gl, q=q, qs=qs)
     h = {k: (acl.create_tensor(v, fmt=fmt_w if k == "w" else _lib.ACL_FORMAT_ND) if (v is not None and k not in null) else None)
          for k, v in hs.items()}
     size, ex = C.c_uint64(7), C.c_void_p(0)
-    rc = L.aclnnGroupedMatmulSwigluQuantGetWorkspaceSize(h["x"], h["w"], None, None, h["ws"], h["xs"], h["gl"], h["q"], h["qs"], None,
-                                                         C.byref(size), C.byref(ex))
+    rc = getattr(L, f"aclnnGroupedMatmulSwigluQuant{api}GetWorkspaceSize")(h["x"], h["w"], None, None, h["ws"], h["xs"], h["gl"],
+                                                                         h["q"], h["qs"], None, C.byref(size), C.byref(ex))
     if rc == OK:
         assert L.aclDestroyAclOpExecutor(ex) == OK
     for v in h.values():
@@ -197,10 +206,55 @@ def test_swiglu_invalid_shapes_dtypes_limits():
     assert _sw_phase1(**odd)[0] == INVALID                                                                  # N odd
     assert _sw_phase1(**_sw_tensors(m=4, k=64, n=10242, e=1))[0] == INVALID                                 # N > 10240
     assert _sw_phase1(**_sw_tensors(m=2, k=65536, n=32, e=1))[0] == INVALID                                 # K >= 65536
-    assert _sw_phase1(**t, fmt_w=_lib.ACL_FORMAT_FRACTAL_NZ)[0] == INVALID                                  # NZ storage not built
     e = _sw_tensors(m=0)
     rc, size = _sw_phase1(**e)
     assert rc == OK and size == 0
+
+
+def test_fractal_nz_weights_and_twin_entry_points():
+    NZ = _lib.ACL_FORMAT_FRACTAL_NZ
+    # swiglu: E=4, K=2048, N=2048 -> storage [4, 64, 128, 16, 32]
+    t = _sw_tensors()
+    w5 = torch.empty((4, 64, 128, 16, 32), dtype=torch.int8)
+    assert _sw_phase1(**{**t, "w": w5}, fmt_w=NZ)[0] == OK
+    assert _sw_phase1(**{**t, "w": w5}, api="WeightNZ")[0] == OK                 # storage counted as NZ whatever the format
+    assert _sw_phase1(**{**t, "w": w5})[0] == INVALID                            # 5-D weight that is not NZ
+    assert _sw_phase1(**t, api="WeightNZ")[0] == INVALID                         # WeightNZ wants a 5-D storage shape
+    assert "storageShape" in _lib.last_error()
+    assert _sw_phase1(**{**t, "w": torch.empty((4, 64, 127, 16, 32), dtype=torch.int8)}, fmt_w=NZ)[0] == INVALID
+    assert _sw_phase1(**{**t, "w": torch.empty((4, 64, 128, 32, 16), dtype=torch.int8)}, fmt_w=NZ)[0] == INVALID
+    assert _sw_phase1(**t, fmt_w=NZ)[0] == OK                                    # 3-D view over NZ storage
+    odd = _sw_tensors(m=8, k=40, n=64, e=1)
+    assert _sw_phase1(**odd, fmt_w=NZ)[0] == INVALID                             # K % 16 != 0
+    assert _sw_phase1(**t, fmt_w=3)[0] == INVALID                                # another private format (NC1HWC0)
+    # grouped_matmul: E=4, K=5120, N=2560 -> [4, 80, 320, 16, 32]
+    v = _v4_tensors()
+    v5d = torch.empty((4, 80, 320, 16, 32), dtype=torch.int8)
+    for api in ("V4", "V5"):
+        assert _v4_phase1(**{**v, "w": v5d}, fmt_w=NZ, api=api)[0] == OK
+        assert _v4_phase1(**v, fmt_w=NZ, api=api)[0] == OK
+        assert _v4_phase1(**{**v, "w": v5d}, api=api)[0] == INVALID
+    assert _v4_phase1(**{**v, "w": v5d}, api="WeightNz")[0] == OK
+    assert _v4_phase1(**v, api="WeightNz")[0] == OK
+    assert _v4_phase1(**{**v, "w": v5d}, api="WeightNz", tuning=[21], quant_group_size=0)[0] == OK
+    assert _v4_phase1(**{**v, "w": v5d}, api="WeightNz", quant_group_size=-1)[0] == INVALID
+    assert _v4_phase1(**{**v, "w": v5d}, api="V5", fmt_w=NZ, tuning=[-3])[0] == INVALID
+    assert _v4_phase1(**{**v, "w": torch.empty((4, 80, 319, 16, 32), dtype=torch.int8)}, api="WeightNz")[0] == INVALID
+    u = dict(x=torch.empty((16, 24), dtype=torch.int8), w=torch.empty((2, 24, 32), dtype=torch.int8),
+             scale=torch.empty((2, 32), dtype=torch.bfloat16), pts=torch.empty((16,), dtype=torch.float32),
+             gl=torch.tensor([8, 16], dtype=torch.int64), out=torch.empty((16, 32), dtype=torch.bfloat16))
+    assert _v4_phase1(**u, api="WeightNz")[0] == INVALID                         # K % 16 != 0
+    assert _v4_phase1(**u)[0] == OK
+
+
+def test_v4_float16_result_and_activations():
+    t = _v4_tensors(scale_dtype=torch.float32, out_dtype=torch.float16)
+    assert _v4_phase1(**t)[0] == OK
+    assert _v4_phase1(**_v4_tensors(out_dtype=torch.float16))[0] == INVALID      # float16 result needs a float32 scale
+    for act in (1, 2, 4, 5):
+        assert _v4_phase1(**_v4_tensors(), act=act)[0] == OK
+    assert _v4_phase1(**_v4_tensors(), act=3)[0] == INVALID
+    assert "GELU_ERR_FUNC" in _lib.last_error()
 
 
 def test_second_phase_host_checks():
@@ -230,9 +284,10 @@ def test_flat_entry_points_validate_on_the_host():
     assert size.value >= 32768 * 2048 * 4
     assert L.gmmB200GroupedMatmulSwigluQuantWorkspaceSize(16, 64, 33, 1, C.byref(size)) == INVALID
     assert L.gmmB200GroupedMatmulW8A8WorkspaceSize(256, 1024, 2048, 4, _lib.ACL_BF16, C.byref(size)) == OK and size.value == 256
-    assert L.gmmB200GroupedMatmulW8A8WorkspaceSize(256, 1024, 2048, 4, _lib.ACL_FLOAT16, C.byref(size)) == INVALID
+    assert L.gmmB200GroupedMatmulW8A8WorkspaceSize(256, 1024, 2048, 4, _lib.ACL_FLOAT16, C.byref(size)) == OK
+    assert L.gmmB200GroupedMatmulW8A8WorkspaceSize(256, 1024, 2048, 4, _lib.ACL_FLOAT, C.byref(size)) == INVALID
     one = C.c_void_p(256)
     assert L.gmmB200GroupedMatmulW8A8(None, one, one, 0, one, None, 0, one, 1, 0, 1, 16, 16, 1, 0, 0, None, None, 0, one, 27, one, 256, None) == NULLPTR
     assert L.gmmB200GroupedMatmulW8A8(one, one, one, 0, one, None, 0, one, 2, 0, 1, 16, 16, 1, 0, 0, None, None, 0, one, 27, one, 256, None) == INVALID
-    assert L.gmmB200GroupedMatmulSwigluQuant(one, one, one, 0, one, one, 1, 4, 16, 32, 1, one, one, one, 16, None) == INVALID  # workspace too small
+    assert L.gmmB200GroupedMatmulSwigluQuant(one, one, one, 0, one, one, 1, 4, 16, 32, 1, 0, one, one, one, 16, None) == INVALID  # workspace too small
     assert "workspaceSize" in _lib.last_error()

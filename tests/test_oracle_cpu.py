@@ -111,6 +111,33 @@ def test_gmm_matches_numpy_formulation(oracle, gl_type):
     assert np.array_equal(rt["y"], r0["y"])
 
 
+def test_gmm_activations_and_float16_result(oracle):
+    # the activations against float64 evaluations of their published definitions; the float16 cast against numpy's
+    M, K, N, E = 40, 64, 48, 2
+    x = synth.int8_tensor((M, K), 5, 1)
+    w = synth.int8_tensor((E, K, N), 5, 2)
+    ws = (synth.scale_tensor((E, N), 5, 3) * 0.5).astype(np.float32)
+    xs = synth.scale_tensor((M,), 5, 4)
+    gl = [15, 40]
+    pre = oracle.gmm_w8a8(x, w, ws, xs, gl, 0, want_pre=True)["pre"].astype(np.float64)
+    want = {
+        1: np.maximum(pre, 0),
+        2: pre / (1 + np.exp(-1.59576912 * (pre + 0.044715 * pre ** 3))),
+        4: pre / (1 + np.exp(-1.702 * pre)),
+        5: pre / (1 + np.exp(-pre)),
+    }
+    assert np.abs(pre).max() > 3 and np.abs(pre).min() < 0.1   # both the flat and the curved parts are visited
+    for act, exp in want.items():
+        r = oracle.gmm_w8a8(x, w, ws, xs, gl, 0, act_type=act, want_pre=True)
+        assert np.allclose(r["pre"], exp, rtol=2e-6, atol=1e-7), act
+        assert np.array_equal(r["y"], oracle.f32_to_bf16_bits(r["pre"]))
+        h = oracle.gmm_w8a8(x, w, ws, xs, gl, 0, act_type=act, y_dtype="f16", want_pre=True)
+        assert np.array_equal(h["y"], h["pre"].astype(np.float16).view(np.uint16))
+    # 2 (tanh form) equals 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))) analytically
+    tanh_form = 0.5 * pre * (1 + np.tanh(np.sqrt(2 / np.pi) * (pre + 0.044715 * pre ** 3)))
+    assert np.allclose(want[2], tanh_form, rtol=1e-6, atol=1e-7)
+
+
 def test_gmm_scale_order_is_weight_then_token(oracle):
     # (acc*w_scale)*x_scale and (acc*x_scale)*w_scale differ in the last bit for some inputs; the two operators
     # use opposite orders (grouped_matmul_quant_mixcore.h:262,300 vs grouped_matmul_swiglu_quant.h:392,450).

@@ -37,8 +37,14 @@ def make_inputs(M, K, N, E, seed=0):
     return x, w, ws, xs
 
 
+def nd_to_nz(w):
+    """[E, K, N] -> FRACTAL_NZ storage [E, N/32, K/16, 16, 32]."""
+    E, K, N = w.shape
+    return np.ascontiguousarray(w.reshape(E, K // 16, 16, N // 32, 32).transpose(0, 3, 1, 2, 4))
+
+
 def check_gmm(oracle, x, w, ws, xs, gl, gl_type=0, bias=None, act_type=0, w_trans=False, out_dtype="bf16",
-              scale_bf16=False, expect_exact=True):
+              scale_bf16=False, expect_exact=True, w_nz=False, api="V4", **api_kw):
     import ops_transformer_b200 as ops
     dev = _dev()
     M, K = x.shape
@@ -67,21 +73,26 @@ def check_gmm(oracle, x, w, ws, xs, gl, gl_type=0, bias=None, act_type=0, w_tran
     xt = torch.from_numpy(x).to(dev)
     if w_trans:
         wt = torch.from_numpy(w_o).to(dev).transpose(1, 2)  # view [E, K, N] with strides (N*K, 1, K)
+    elif w_nz:
+        wt = torch.from_numpy(nd_to_nz(w)).to(dev)
+        if api != "WeightNz":
+            api_kw["weight_format"] = ops.ACL_FORMAT_FRACTAL_NZ
     else:
         wt = torch.from_numpy(w).to(dev)
     xst = torch.from_numpy(xs).to(dev) if xs is not None else None
     glt = torch.from_numpy(gl).to(dev)
-    tdt = torch.bfloat16 if out_dtype == "bf16" else torch.int32
-    sentinel = 0x7fc1 if out_dtype == "bf16" else -123456789
-    if out_dtype == "bf16":
+    tdt = {"bf16": torch.bfloat16, "f16": torch.float16, "int32": torch.int32}[out_dtype]
+    sentinel = 0x7fc1 if out_dtype != "int32" else -123456789
+    floating = out_dtype != "int32"
+    if floating:
         out = torch.full((M, N), 0, dtype=torch.int16, device=dev)
         out.fill_(np.int16(np.uint16(sentinel).view(np.int16)).item())
-        out = out.view(torch.bfloat16)
+        out = out.view(tdt)
     else:
         out = torch.full((M, N), sentinel, dtype=torch.int32, device=dev)
-    y, wsb = ops.grouped_matmul_v4(xt, wt, ws_t if out_dtype == "bf16" else None, xst if out_dtype == "bf16" else None,
+    y, wsb = ops.grouped_matmul_v4(xt, wt, ws_t if floating else None, xst if floating else None,
                                    glt, bias=bias_t, group_list_type=gl_type, act_type=act_type, out=out,
-                                   out_dtype=tdt, return_workspace=True)
+                                   out_dtype=tdt, return_workspace=True, api=api, **api_kw)
     ops.check_status(wsb)
     rs, rc = oracle.group_layout(gl[: E if E > 1 else 1], gl_type, M)
     covered = np.zeros(M, bool)
@@ -93,8 +104,12 @@ def check_gmm(oracle, x, w, ws, xs, gl, gl_type=0, bias=None, act_type=0, w_tran
         assert (got[~covered] == sentinel).all(), "rows outside group_list were written"
         return
     got_bits = _bf16_bits(y)
-    got = oracle.bf16_bits_to_f32(got_bits)
-    exp = oracle.bf16_bits_to_f32(ref["y"])
+    if out_dtype == "f16":
+        got = got_bits.view(np.float16).astype(np.float32)
+        exp = ref["y"].view(np.float16).astype(np.float32)
+    else:
+        got = oracle.bf16_bits_to_f32(got_bits)
+        exp = oracle.bf16_bits_to_f32(ref["y"])
     err = np.abs(got[covered] - exp[covered])
     assert (err <= BF16_ATOL + BF16_RTOL * np.abs(exp[covered])).all(), f"bf16 max err {err.max()}"
     assert (got_bits[~covered] == sentinel).all(), "rows outside group_list were written"
@@ -103,7 +118,7 @@ def check_gmm(oracle, x, w, ws, xs, gl, gl_type=0, bias=None, act_type=0, w_tran
         assert nbad == 0, f"{nbad} bf16 values are not bit-identical to the oracle"
 
 
-def check_swiglu(oracle, x, w, ws, xs, gl, ws_dtype="f32"):
+def check_swiglu(oracle, x, w, ws, xs, gl, ws_dtype="f32", w_nz=False, api=""):
     import ops_transformer_b200 as ops
     dev = _dev()
     M, K = x.shape
@@ -123,9 +138,17 @@ def check_swiglu(oracle, x, w, ws, xs, gl, ws_dtype="f32"):
     ref = oracle.swiglu_quant(x, w, ws_o, xs, gl)
     q0 = torch.full((M, H), -77, dtype=torch.int8, device=dev)
     qs0 = torch.full((M,), -5.0, dtype=torch.float32, device=dev)
-    q, qs, wsb = ops.grouped_matmul_swiglu_quant(torch.from_numpy(x).to(dev), torch.from_numpy(w).to(dev), ws_t,
+    kw = {}
+    if w_nz:
+        wt = torch.from_numpy(nd_to_nz(w)).to(dev)
+        kw["api"] = api
+        if api != "WeightNZ":
+            kw["weight_format"] = ops.ACL_FORMAT_FRACTAL_NZ
+    else:
+        wt = torch.from_numpy(w).to(dev)
+    q, qs, wsb = ops.grouped_matmul_swiglu_quant(torch.from_numpy(x).to(dev), wt, ws_t,
                                                  torch.from_numpy(xs).to(dev), torch.from_numpy(gl).to(dev), output=q0,
-                                                 output_scale=qs0, return_workspace=True)
+                                                 output_scale=qs0, return_workspace=True, **kw)
     ops.check_status(wsb)
     rs, rc = oracle.group_layout(gl, 0, M)
     covered = np.zeros(M, bool)
@@ -323,3 +346,76 @@ def test_gmm_deepseek_down_width_few_rows(oracle):
     counts = [3, 0, 17, 1, 0, 40]
     x, w, ws, xs = make_inputs(sum(counts), 2048, 7168, 6, seed=26)
     check_gmm(oracle, x, w, ws, xs, np.cumsum(counts), 0)
+
+
+# ----------------------------------------------------------------------------------------------------------
+# FRACTAL_NZ weights, the V5 / WeightNz / WeightNZ entry points, float16 results, activations
+# ----------------------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("ctas", ["1", "2"])
+def test_gmm_fractal_nz_weight(oracle, monkeypatch, ctas):
+    monkeypatch.setenv("GMM_B200_CTAS", ctas)
+    counts = [0, 5, 130, 0, 1, 600]
+    x, w, ws, xs = make_inputs(sum(counts) + 9, 144, 288, len(counts), seed=40)  # K and N tails inside the NZ boxes
+    check_gmm(oracle, x, w, ws, xs, np.cumsum(counts), 0, w_nz=True)
+    check_gmm(oracle, x, w, ws, xs, counts, 1, w_nz=True, out_dtype="int32")
+    check_gmm(oracle, x, w, ws, xs, counts, 1, w_nz=True, api="WeightNz", tuning_config=[128], quant_group_size=0)
+
+
+def test_gmm_fractal_nz_deep_k(oracle):
+    counts = [300, 40, 513]
+    x, w, ws, xs = make_inputs(sum(counts), 2048, 1024, 3, seed=41)
+    check_gmm(oracle, x, w, ws, xs, np.cumsum(counts), 0, w_nz=True, scale_bf16=True)
+
+
+def test_gmm_fractal_nz_cuda_core_path(oracle):
+    # the smallest legal FRACTAL_NZ weight: one 16 x 32 fractal per expert
+    x, w, ws, xs = make_inputs(24, 16, 32, 2, seed=42)
+    check_gmm(oracle, x, w, ws, xs, [10, 24], 0, w_nz=True)
+
+
+def test_gmm_v5_tuning_config(oracle):
+    counts = [100, 37, 300]
+    x, w, ws, xs = make_inputs(437, 512, 768, 3, seed=43)
+    check_gmm(oracle, x, w, ws, xs, np.cumsum(counts), 0, api="V5", tuning_config=[146])
+    check_gmm(oracle, x, w, ws, xs, np.cumsum(counts), 0, api="V5")
+
+
+def test_gmm_float16_result(oracle):
+    counts = [70, 0, 200, 3]
+    x, w, ws, xs = make_inputs(sum(counts) + 2, 256, 528, 4, seed=44)
+    check_gmm(oracle, x, w, ws, xs, np.cumsum(counts), 0, out_dtype="f16")
+    bbf = oracle.f32_to_bf16_bits(np.random.default_rng(45).uniform(-5, 5, size=(4, 528)).astype(np.float32))
+    check_gmm(oracle, x, w, ws, xs, np.cumsum(counts), 0, out_dtype="f16", bias=bbf, act_type=1)
+
+
+@pytest.mark.parametrize("act_type", [2, 4, 5])
+def test_gmm_activations(oracle, act_type):
+    # GELU (tanh form), fast GELU, SiLU: expf differs by an ulp between libm and the GPU, so bit identity is not asked
+    counts = [70, 0, 200]
+    x, w, ws, xs = make_inputs(270, 256, 512, 3, seed=46 + act_type)
+    ws = (ws * 0.3).astype(np.float32)  # keeps many values inside the curved part of the activations
+    check_gmm(oracle, x, w, ws, xs, np.cumsum(counts), 0, act_type=act_type, expect_exact=False)
+    x, w, ws, xs = make_inputs(16, 10, 10, 2, seed=50 + act_type)  # CUDA-core path
+    check_gmm(oracle, x, w, ws, xs, [8, 8], 1, act_type=act_type, expect_exact=False)
+
+
+@pytest.mark.parametrize("ctas", ["1", "2"])
+@pytest.mark.parametrize("api", ["", "WeightNZ"])
+def test_swiglu_fractal_nz_weight(oracle, monkeypatch, ctas, api):
+    monkeypatch.setenv("GMM_B200_CTAS", ctas)
+    counts = [0, 3, 0, 131, 600]
+    x, w, ws, xs = make_inputs(sum(counts) + 5, 144, 576, 8, seed=55)  # list shorter than E, K/N tails
+    check_swiglu(oracle, x, w, ws, xs, np.cumsum(counts), w_nz=True, api=api)
+
+
+def test_swiglu_fractal_nz_reference_api_case(oracle):
+    # the reference's WeightNZ example: E=4, M=192 (96 covered), K=2048, N=2048
+    x, w, ws, xs = make_inputs(192, 2048, 2048, 4, seed=56)
+    check_swiglu(oracle, x, w, ws, xs, [24, 48, 72, 96], w_nz=True, api="WeightNZ")
+
+
+def test_swiglu_fractal_nz_n_multiple_of_32_only(oracle):
+    # N = 96: N/2 = 48 is not a multiple of 32, the tensor-core path declines and the CUDA-core kernel runs
+    x, w, ws, xs = make_inputs(20, 32, 96, 2, seed=57)
+    check_swiglu(oracle, x, w, ws, xs, [7, 20], w_nz=True)

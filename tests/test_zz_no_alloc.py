@@ -36,7 +36,7 @@ def _run_pair(L, dev, seed, M, K, N, E, counts):
     wsb = torch.empty(int(size.value), dtype=torch.uint8, device=dev)
     q_ref = torch.full((M, N // 2), 99, dtype=torch.int8, device=dev)
     qs_ref = torch.full((M,), -1.0, dtype=torch.float32, device=dev)
-    rc = L.gmmB200GroupedMatmulSwigluQuant(p(x), p(w), p(ws), _lib.ACL_FLOAT, p(xs), p(gl), len(counts), M, K, N, E, p(q_ref),
+    rc = L.gmmB200GroupedMatmulSwigluQuant(p(x), p(w), p(ws), _lib.ACL_FLOAT, p(xs), p(gl), len(counts), M, K, N, E, 0, p(q_ref),
                                            p(qs_ref), p(wsb), size.value, stream)
     assert rc == 0, _lib.last_error()
     assert L.gmmB200CheckStatus(p(wsb), size.value, stream, None) == 0, _lib.last_error()
