@@ -220,6 +220,10 @@ def bench_single(args):
     x, w, ws, xs = gen_device_inputs(torch, dev, M, K, N, E, 0)
     gl = torch.from_numpy(np.cumsum(counts)).to(dev)
     nonempty = int((counts > 0).sum())
+    wkw = {}
+    if args.weight_format == "nz":  # the layout the reference's A8W8 SwiGLU operator asks for; cast once, outside the timing
+        w = ops.format_cast_nz(w)
+        wkw = {"weight_format": ops.ACL_FORMAT_FRACTAL_NZ}
     if swiglu:
         out0 = torch.empty((M, N // 2), dtype=torch.int8, device=dev)
         out1 = torch.empty((M,), dtype=torch.float32, device=dev)
@@ -233,8 +237,8 @@ def bench_single(args):
 
     def step():
         if swiglu:
-            return ops.grouped_matmul_swiglu_quant(x, w, ws, xs, gl, output=out0, output_scale=out1, return_workspace=True)[-1]
-        return ops.grouped_matmul_v4(x, w, ws, xs, gl, out=out0, return_workspace=True)[-1]
+            return ops.grouped_matmul_swiglu_quant(x, w, ws, xs, gl, output=out0, output_scale=out1, return_workspace=True, **wkw)[-1]
+        return ops.grouped_matmul_v4(x, w, ws, xs, gl, out=out0, return_workspace=True, **wkw)[-1]
 
     # L2 policy: for the prefill workloads one step streams > 1 GB, far more than the 126 MB L2; for the small
     # decode workloads a 256 MB buffer is rewritten between timed steps.
@@ -286,10 +290,10 @@ def bench_single(args):
     def e2e_step():
         dx.copy_(hx, non_blocking=True); dxs.copy_(hxs, non_blocking=True); dgl.copy_(hgl, non_blocking=True)
         if swiglu:
-            ops.grouped_matmul_swiglu_quant(dx, w, ws, dxs, dgl, output=out0, output_scale=out1)
+            ops.grouped_matmul_swiglu_quant(dx, w, ws, dxs, dgl, output=out0, output_scale=out1, **wkw)
             ho0.copy_(out0, non_blocking=True); ho1.copy_(out1, non_blocking=True)
         else:
-            ops.grouped_matmul_v4(dx, w, ws, dxs, dgl, out=out0)
+            ops.grouped_matmul_v4(dx, w, ws, dxs, dgl, out=out0, **wkw)
             ho0.copy_(out0, non_blocking=True)
         torch.cuda.synchronize()
 
@@ -327,6 +331,7 @@ def bench_single(args):
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
         "data": "synthetic",
         "config": {"workload": f"{name}: E={E} K={K} N={N} rows={M} non-empty experts={nonempty}",
+                   "weight_format": "FRACTAL_NZ" if args.weight_format == "nz" else "ND",
                    "l2": "inputs larger than L2" if flush is None else "256 MB flush write between steps",
                    "tokens_per_s": (cfg.get("tokens", 0) / (ms * 1e-3)) if cfg.get("tokens") else None},
         "roofline": roof,
@@ -355,6 +360,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, help="c2 (default at N=1), c3, c4_swiglu, c4_down")
+    ap.add_argument("--weight-format", default="nd", choices=["nd", "nz"], help="N=1: weight layout [E,K,N] or FRACTAL_NZ")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-ep", action="store_true", help="N=1: skip the one-GPU run of the expert-parallel workload")
     ap.add_argument("--ep-tokens", type=int, default=16384, help="tokens per GPU of the expert-parallel workload")
