@@ -212,8 +212,9 @@ def bench_single(args):
     torch.cuda.set_device(dev)
     L = _lib.lib()
     name = args.workload or "c2"
-    cfg = synth.CONFIGS[name]
-    counts = synth.config_counts(name, 0)
+    finalize = name == "c3_finalize"  # the down projection of c3 fused with the weighted combine (finalize routing)
+    cfg = synth.CONFIGS["c3" if finalize else name]
+    counts = synth.config_counts("c3" if finalize else name, 0)
     E, K, N = cfg["E"], cfg["K"], cfg["N"]
     M = int(counts.sum())
     swiglu = name in ("c2", "c4_swiglu", "c2_small", "c4_swiglu_small")
@@ -224,7 +225,18 @@ def bench_single(args):
     if args.weight_format == "nz":  # the layout the reference's A8W8 SwiGLU operator asks for; cast once, outside the timing
         w = ops.format_cast_nz(w)
         wkw = {"weight_format": ops.ACL_FORMAT_FRACTAL_NZ}
-    if swiglu:
+    if finalize:
+        topk = 8
+        batch = M // topk
+        g = torch.Generator(device="cpu").manual_seed(5)
+        row_index = (torch.randperm(M, generator=g) % batch).to(dev)
+        logit = torch.rand(M, generator=g).mul_(0.5).add_(0.05).to(dev)
+        shared = torch.randn(batch, N, generator=g).to(torch.bfloat16).to(dev)
+        out0 = torch.empty((batch, N), dtype=torch.float32, device=dev)
+        out1 = None
+        out_bytes = batch * N * 4 + batch * N * 2 + M * 12   # fp32 result, bf16 shared rows, logits and row indices
+        wflat = (2 if args.weight_format == "nz" else 0)
+    elif swiglu:
         out0 = torch.empty((M, N // 2), dtype=torch.int8, device=dev)
         out1 = torch.empty((M,), dtype=torch.float32, device=dev)
         out_bytes = M * (N // 2) + M * 4
@@ -236,9 +248,17 @@ def bench_single(args):
     alg_bytes = M * K + nonempty * K * N + nonempty * N * 4 + M * 4 + out_bytes + E * 8
 
     def step():
+        if finalize:
+            ops.grouped_matmul_finalize_routing_flat(x, w, wflat, ws, gl_counts, row_index, out0, pertoken_scale=xs,
+                                                     shared_input=shared, logit=logit, workspace=fin_ws)
+            return fin_ws
         if swiglu:
             return ops.grouped_matmul_swiglu_quant(x, w, ws, xs, gl, output=out0, output_scale=out1, return_workspace=True, **wkw)[-1]
         return ops.grouped_matmul_v4(x, w, ws, xs, gl, out=out0, return_workspace=True, **wkw)[-1]
+
+    if finalize:
+        gl_counts = torch.from_numpy(np.asarray(counts, np.int64)).to(dev)
+        fin_ws = torch.zeros(256, dtype=torch.uint8, device=dev)
 
     # L2 policy: for the prefill workloads one step streams > 1 GB, far more than the 126 MB L2; for the small
     # decode workloads a 256 MB buffer is rewritten between timed steps.
@@ -289,7 +309,11 @@ def bench_single(args):
 
     def e2e_step():
         dx.copy_(hx, non_blocking=True); dxs.copy_(hxs, non_blocking=True); dgl.copy_(hgl, non_blocking=True)
-        if swiglu:
+        if finalize:
+            ops.grouped_matmul_finalize_routing_flat(dx, w, wflat, ws, gl_counts, row_index, out0, pertoken_scale=dxs,
+                                                     shared_input=shared, logit=logit, workspace=fin_ws)
+            ho0.copy_(out0, non_blocking=True)
+        elif swiglu:
             ops.grouped_matmul_swiglu_quant(dx, w, ws, dxs, dgl, output=out0, output_scale=out1, **wkw)
             ho0.copy_(out0, non_blocking=True); ho1.copy_(out1, non_blocking=True)
         else:
@@ -326,7 +350,7 @@ def bench_single(args):
 
     tops = ops_per_step / (ms * 1e-3) / 1e12
     line = {
-        "metric": "int8 GMM+SwiGLU-quant TOPS" if swiglu else "int8 GMM W8A8 TOPS",
+        "metric": "int8 GMM+SwiGLU-quant TOPS" if swiglu else ("int8 GMM+finalize-routing TOPS" if finalize else "int8 GMM W8A8 TOPS"),
         "value": tops, "unit": "TOPS", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
         "data": "synthetic",
@@ -337,7 +361,9 @@ def bench_single(args):
         "roofline": roof,
         "e2e": {"value": ops_per_step / (e2e_ms * 1e-3) / 1e12, "unit": "TOPS", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
-        "gpu_launches": args.steps,  # one kernel per operator call (the int8 requant is fused into the GEMM kernel)
+        # one kernel per operator call (the int8 requant is fused into the GEMM kernel); finalize routing adds the kernel
+        # that initialises the fp32 result
+        "gpu_launches": args.steps * (2 if finalize else 1),
         "clocks": clocks,
         "pct_of_nominal_int8_peak": tops / 4500.0 * 100.0,
     }
@@ -359,7 +385,7 @@ def main():
     ap.add_argument("--steps", type=int, default=400)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=None, help="c2 (default at N=1), c3, c4_swiglu, c4_down")
+    ap.add_argument("--workload", default=None, help="c2 (default at N=1), c3, c4_swiglu, c4_down, c3_finalize")
     ap.add_argument("--weight-format", default="nd", choices=["nd", "nz"], help="N=1: weight layout [E,K,N] or FRACTAL_NZ")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-ep", action="store_true", help="N=1: skip the one-GPU run of the expert-parallel workload")

@@ -103,6 +103,18 @@ ACL_FUNC_VISIBILITY aclnnStatus gmmB200EpRoute(const void *topk, const void *blo
                                               int64_t tokenBase, int64_t resultBase, void *srcToken, void *order, void *sendDest,
                                               void *retDest, void *groupList, void *firstRow, aclrtStream stream);
 
+/* Flat form of aclnnGroupedMatmulFinalizeRoutingWeightNz (include/aclnnop/aclnn_grouped_matmul_finalize_routing_weight_nz.h),
+ * with two freedoms the aclnn form lacks: weightLayout 0 ([e, k, n], the faster layout on B200) besides 2 (FRACTAL_NZ), and
+ * groupListType 0 (running totals) besides 1.  sharedInput and logit are given together (rows are added to y, which the
+ * call first fills with the weighted shared rows and zeros) or both null (rows are stored, y is not initialised).
+ * y is fp32 [yRows, n]; rowIndexDtype is ACL_INT64 or ACL_INT32; the workspace needs 256 bytes. */
+ACL_FUNC_VISIBILITY aclnnStatus gmmB200GroupedMatmulFinalizeRouting(
+    const void *x, const void *weight, int32_t weightLayout, const void *scale, int32_t scaleDtype, const void *bias,
+    const void *perTokenScale, const void *groupList, int64_t groupListLen, int32_t groupListType, const void *sharedInput,
+    int64_t sharedRows, int64_t sharedOffset, float sharedWeight, const void *logit, const void *rowIndex, int32_t rowIndexDtype,
+    int64_t m, int64_t k, int64_t n, int64_t e, void *y, int64_t yRows, void *workspace, uint64_t workspaceSize,
+    aclrtStream stream);
+
 /* Flat form of aclnnGroupedMatmulSwigluQuant.  weightLayout: 0 = [e, k, n], 2 = FRACTAL_NZ [e, n/32, k/16, 16, 32]. */
 ACL_FUNC_VISIBILITY aclnnStatus gmmB200GroupedMatmulSwigluQuantWorkspaceSize(int64_t m, int64_t k, int64_t n, int64_t e,
                                                                             uint64_t *workspaceSize);

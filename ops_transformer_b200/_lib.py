@@ -27,6 +27,9 @@ EXPORTED_SYMBOLS = [
     "aclnnGroupedMatmulV4GetWorkspaceSize", "aclnnGroupedMatmulV4",
     "aclnnGroupedMatmulV5GetWorkspaceSize", "aclnnGroupedMatmulV5",
     "aclnnGroupedMatmulWeightNzGetWorkspaceSize", "aclnnGroupedMatmulWeightNz",
+    "aclnnGroupedMatmulFinalizeRoutingWeightNzGetWorkspaceSize", "aclnnGroupedMatmulFinalizeRoutingWeightNz",
+    "aclnnGroupedMatmulFinalizeRoutingWeightNzV2GetWorkspaceSize", "aclnnGroupedMatmulFinalizeRoutingWeightNzV2",
+    "gmmB200GroupedMatmulFinalizeRouting",
     "aclnnGroupedMatmulSwigluQuantGetWorkspaceSize", "aclnnGroupedMatmulSwigluQuant",
     "aclnnGroupedMatmulSwigluQuantWeightNZGetWorkspaceSize", "aclnnGroupedMatmulSwigluQuantWeightNZ",
     "gmmB200Version", "gmmB200CheckStatus", "gmmB200SetTimingEvents", "gmmB200SetSmLimit", "gmmB200GroupedMatmulW8A8WorkspaceSize", "gmmB200GroupedMatmulW8A8",
@@ -64,6 +67,12 @@ def _load():
     L.aclnnGroupedMatmulV5.argtypes = [p, u64, p, p]
     L.aclnnGroupedMatmulWeightNzGetWorkspaceSize.argtypes = [p] * 12 + [i64] * 4 + [p, i64] + [p] * 3 + [C.POINTER(u64), C.POINTER(p)]
     L.aclnnGroupedMatmulWeightNz.argtypes = [p, u64, p, p]
+    f32, b8 = C.c_float, C.c_bool
+    L.aclnnGroupedMatmulFinalizeRoutingWeightNzGetWorkspaceSize.argtypes = [p] * 9 + [i64, f32, i64, b8, b8, i64, p, C.POINTER(u64), C.POINTER(p)]
+    L.aclnnGroupedMatmulFinalizeRoutingWeightNz.argtypes = [p, u64, p, p]
+    L.aclnnGroupedMatmulFinalizeRoutingWeightNzV2GetWorkspaceSize.argtypes = [p] * 12 + [i64, f32, i64, b8, b8, i64, p, p, C.POINTER(u64), C.POINTER(p)]
+    L.aclnnGroupedMatmulFinalizeRoutingWeightNzV2.argtypes = [p, u64, p, p]
+    L.gmmB200GroupedMatmulFinalizeRouting.argtypes = [p, p, i32, p, i32, p, p, p, i64, i32, p, i64, i64, f32, p, p, i32, i64, i64, i64, i64, p, i64, p, u64, p]
     L.aclnnGroupedMatmulSwigluQuantWeightNZGetWorkspaceSize.argtypes = [p] * 10 + [C.POINTER(u64), C.POINTER(p)]
     L.aclnnGroupedMatmulSwigluQuantWeightNZ.argtypes = [p, u64, p, p]
     L.aclnnGroupedMatmulSwigluQuantGetWorkspaceSize.argtypes = [p] * 10 + [C.POINTER(u64), C.POINTER(p)]

@@ -35,12 +35,21 @@ def _i64(values: Sequence[int]):
     return (C.c_int64 * len(values))(*values)
 
 
-def create_tensor(t: torch.Tensor, fmt: int = ACL_FORMAT_ND, dtype: Optional[int] = None) -> int:
-    """aclCreateTensor over a torch tensor's view (dims, strides, device address).  The caller destroys it."""
-    dims = list(t.shape)
-    strides = list(t.stride())
+def create_tensor(t: torch.Tensor, fmt: int = ACL_FORMAT_ND, dtype: Optional[int] = None,
+                  view_dims: Optional[Sequence[int]] = None) -> int:
+    """aclCreateTensor over a torch tensor's view (dims, strides, device address).  The caller destroys it.
+    ``view_dims``: the tensor is the storage (its shape becomes the storage shape) and is viewed with these dimensions,
+    as a FRACTAL_NZ weight is: storage [E, N/32, K/16, 16, 32], view [E, K, N]."""
+    storage = list(t.shape)
+    if view_dims is None:
+        dims, strides = storage, list(t.stride())
+    else:
+        dims = list(view_dims)
+        strides = [1] * len(dims)
+        for i in range(len(dims) - 2, -1, -1):
+            strides[i] = strides[i + 1] * dims[i + 1]
     code = _DTYPES[t.dtype] if dtype is None else dtype
-    h = _lib.lib().aclCreateTensor(_i64(dims), len(dims), code, _i64(strides), 0, fmt, _i64(dims), len(dims),
+    h = _lib.lib().aclCreateTensor(_i64(dims), len(dims), code, _i64(strides), 0, fmt, _i64(storage), len(storage),
                                    C.c_void_p(t.data_ptr()))
     if not h:
         raise MemoryError("aclCreateTensor returned null")
@@ -262,3 +271,89 @@ def grouped_matmul_swiglu_quant(x: torch.Tensor, weight: torch.Tensor, weight_sc
         for h in handles:
             L.aclDestroyTensor(h)
     return (output, output_scale, workspace) if return_workspace else (output, output_scale)
+
+
+def grouped_matmul_finalize_routing(x: torch.Tensor, weight_nz: torch.Tensor, scale: torch.Tensor, group_list: torch.Tensor,
+                                    row_index: torch.Tensor, batch: int, *, bias: Optional[torch.Tensor] = None,
+                                    pertoken_scale: Optional[torch.Tensor] = None, shared_input: Optional[torch.Tensor] = None,
+                                    logit: Optional[torch.Tensor] = None, shared_input_weight: float = 1.0,
+                                    shared_input_offset: int = 0, group_list_type: int = 1, out: Optional[torch.Tensor] = None,
+                                    view_3d: bool = True, api: str = "", tuning_config: Optional[Sequence[int]] = None,
+                                    stream=None, workspace: Optional[torch.Tensor] = None, return_workspace: bool = False):
+    """aclnnGroupedMatmulFinalizeRoutingWeightNz (``api`` "") or ...WeightNzV2 (``api`` "V2"): W8A8 grouped GEMM whose fp32
+    result rows, weighted by ``logit``, are added into row ``row_index[i]`` of ``out`` [batch, N] on top of the weighted
+    ``shared_input`` rows (gmm/grouped_matmul_finalize_routing/op_host/op_api/aclnn_grouped_matmul_finalize_routing_weight_nz.h:48-64
+    of the reference).  ``weight_nz`` is the FRACTAL_NZ storage [E, N/32, K/16, 16, 32] (``format_cast_nz``); with
+    ``view_3d`` it is described to the operator as the reference's callers do, a view [E, K, N] over that storage."""
+    L = _lib.lib()
+    E, n1, k1 = weight_nz.shape[0], weight_nz.shape[1], weight_nz.shape[2]
+    N, K = n1 * 32, k1 * 16
+    if out is None:
+        out = torch.empty((batch, N), dtype=torch.float32, device=x.device)
+    handles = []
+    tuning = None
+    try:
+        def mk(t, **kw):
+            if t is None:
+                return None
+            h = create_tensor(t, **kw)
+            handles.append(h)
+            return h
+        hx = mk(x)
+        hw = mk(weight_nz, fmt=ACL_FORMAT_FRACTAL_NZ, view_dims=[E, K, N] if view_3d else None)
+        hs, hb, hp, hg = mk(scale), mk(bias), mk(pertoken_scale), mk(group_list)
+        hsh, hl, hr, hy = mk(shared_input), mk(logit), mk(row_index), mk(out)
+        ws_size = C.c_uint64(0)
+        ex = C.c_void_p(0)
+        name = "aclnnGroupedMatmulFinalizeRoutingWeightNz" + api
+        if api == "V2":
+            if tuning_config is not None:
+                tuning = L.aclCreateIntArray(_i64(list(tuning_config)), len(tuning_config))
+            rc = L.aclnnGroupedMatmulFinalizeRoutingWeightNzV2GetWorkspaceSize(
+                hx, hw, hs, hb, None, None, None, hp, hg, hsh, hl, hr, 0, shared_input_weight, shared_input_offset, False, False,
+                group_list_type, tuning, hy, C.byref(ws_size), C.byref(ex))
+        else:
+            rc = L.aclnnGroupedMatmulFinalizeRoutingWeightNzGetWorkspaceSize(
+                hx, hw, hs, hb, hp, hg, hsh, hl, hr, 0, shared_input_weight, shared_input_offset, False, False, group_list_type,
+                hy, C.byref(ws_size), C.byref(ex))
+        if rc != ACLNN_SUCCESS:
+            raise AclnnError(rc, name + "GetWorkspaceSize")
+        if workspace is None:
+            workspace = _WS.get(x.device, ws_size.value)
+        elif workspace.numel() < ws_size.value:
+            L.aclDestroyAclOpExecutor(ex)
+            raise ValueError(f"workspace of {workspace.numel()} bytes is smaller than the {ws_size.value} required")
+        wptr = C.c_void_p(workspace.data_ptr()) if workspace is not None else None
+        rc = getattr(L, name)(wptr, ws_size.value, ex, C.c_void_p(_stream_handle(stream)))
+        if rc != ACLNN_SUCCESS:
+            raise AclnnError(rc, name)
+    finally:
+        for h in handles:
+            L.aclDestroyTensor(h)
+        if tuning:
+            L.aclDestroyIntArray(tuning)
+    return (out, workspace) if return_workspace else out
+
+
+def grouped_matmul_finalize_routing_flat(x, weight, weight_layout, scale, group_list, row_index, out, *, bias=None,
+                                         pertoken_scale=None, shared_input=None, logit=None, shared_input_weight=1.0,
+                                         shared_input_offset=0, group_list_type=1, stream=None, workspace=None):
+    """gmmB200GroupedMatmulFinalizeRouting: the same operator without handles; ``weight_layout`` 0 takes the ND [E, K, N]
+    weight (the faster layout here), 2 the FRACTAL_NZ storage."""
+    L = _lib.lib()
+    M, K = x.shape
+    if weight_layout == 2:
+        E, N = weight.shape[0], weight.shape[1] * 32
+    else:
+        E, _, N = weight.shape
+    if workspace is None:
+        workspace = _WS.get(x.device, 256)
+    p = lambda t: C.c_void_p(t.data_ptr()) if t is not None else None  # noqa: E731
+    rc = L.gmmB200GroupedMatmulFinalizeRouting(
+        p(x), p(weight), weight_layout, p(scale), _DTYPES[scale.dtype], p(bias), p(pertoken_scale), p(group_list),
+        group_list.numel(), group_list_type, p(shared_input), 0 if shared_input is None else shared_input.shape[0],
+        shared_input_offset, shared_input_weight, p(logit), p(row_index), _DTYPES[row_index.dtype], M, K, N, E, p(out),
+        out.shape[0], p(workspace), workspace.numel(), C.c_void_p(_stream_handle(stream)))
+    if rc != ACLNN_SUCCESS:
+        raise AclnnError(rc, "gmmB200GroupedMatmulFinalizeRouting")
+    return out

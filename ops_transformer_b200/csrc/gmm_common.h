@@ -43,6 +43,18 @@ struct Problem {
     const int64_t *out_row_index = nullptr;  // optional [M]: result row r goes to row out_row_index[r] (grouped_matmul only)
     void *out_peers[8] = {nullptr};          // with num_peers > 0: out_row_index = (gpu << 40) | row, one result buffer per gpu
     int num_peers = 0;
+    // grouped_matmul_finalize_routing (mode kModeDequantBf16 with combine = 1): out0 is fp32 [out_rows, N]; row r of the
+    // GEMM, weighted by logit[r], is added to (scatter_add = 1) or stored at (0) row row_index[r].
+    int combine = 0;
+    const float *logit = nullptr;       // [M], optional
+    const void *row_index = nullptr;    // [M] int64 or int32
+    int row_index_i32 = 0;
+    int scatter_add = 0;
+    int64_t out_rows = 0;
+    const void *shared_input = nullptr; // bf16 [shared_rows, N], optional: rows [shared_offset, +shared_rows) start as
+    int64_t shared_rows = 0;            // float(shared_input) * shared_weight, every other row as 0 (scatter_add only)
+    int64_t shared_offset = 0;
+    float shared_weight = 1.0f;
 };
 
 struct Plan {
@@ -69,6 +81,8 @@ cudaError_t sm100_launch(const Problem &p, Plan &plan, void *workspace, cudaStre
 // Optional pair of events recorded right before / after the tensor-core kernel (nullptr = off).
 void set_timing_events(cudaEvent_t start, cudaEvent_t stop);
 // gmm_simt.cu
+// Initial contents of the combined result (PreProcess of grouped_matmul_finalize_routing.h:208-258).
+cudaError_t combine_init_launch(const Problem &p, cudaStream_t stream);
 cudaError_t simt_launch(const Problem &p, Plan &plan, void *workspace, cudaStream_t stream);
 
 int device_sm_count();

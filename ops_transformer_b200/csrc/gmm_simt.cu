@@ -69,6 +69,10 @@ struct SimtParams {
     void *out0;
     float *out1;
     const long long *out_row_index;
+    int combine, row_index_i32, scatter_add;
+    const float *logit;
+    const void *row_index;
+    long long out_rows;
 };
 
 __device__ __forceinline__ long long w_offset(const SimtParams &p, int k, int n)
@@ -99,6 +103,19 @@ __global__ void __launch_bounds__(256) gmm_simt_kernel(const SimtParams p)
             continue;
         }
         float t = __fmul_rn(__int2float_rn(acc), load_scale1(p.w_scale, p.w_scale_dtype, (size_t)g * p.N + n));
+        if (p.combine) {  // grouped_matmul_finalize_routing: weighted row added to / stored at row row_index[m]
+            const long long dst = p.row_index_i32 ? (long long)reinterpret_cast<const int *>(p.row_index)[m]
+                                                  : reinterpret_cast<const long long *>(p.row_index)[m];
+            const float lg = p.logit ? p.logit[m] : 1.0f;
+            t = __fmul_rn(t, p.logit ? (p.x_scale ? __fmul_rn(xs, lg) : lg) : xs);
+            if (p.bias_dtype == kBF16) t = __fadd_rn(t, __fmul_rn(lg, load_scale1(p.bias, kBF16, (size_t)g * p.N + n)));
+            if (dst >= 0 && dst < p.out_rows) {
+                float *o = reinterpret_cast<float *>(p.out0) + (size_t)dst * p.N + n;
+                if (p.scatter_add) atomicAdd(o, t);
+                else *o = t;
+            }
+            continue;
+        }
         if (p.x_scale) t = __fmul_rn(t, xs);
         if (p.bias_dtype == kBF16) t = __fadd_rn(t, load_scale1(p.bias, kBF16, (size_t)g * p.N + n));
         t = apply_activation(p.act_type, t);
@@ -148,7 +165,41 @@ __global__ void __launch_bounds__(256) swiglu_simt_kernel(const SimtParams p)
     for (int j = threadIdx.x; j < H; j += blockDim.x) qrow[j] = (int8_t)quant1(s_row[j], rcp);
 }
 
+// Rows [shared_offset, shared_offset + shared_rows) of y start as float(shared_input) * weight, all other rows as 0.
+__global__ void __launch_bounds__(256) combine_init_kernel(float4 *y, const uint2 *shared, long long n4, long long rows,
+                                                           long long shared_offset, long long shared_rows, float weight)
+{
+    const long long total = rows * n4;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / n4;
+        float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (r >= shared_offset && r < shared_offset + shared_rows) {
+            const uint2 b = __ldg(shared + (i - shared_offset * n4));  // four bf16
+            v.x = __fmul_rn(__uint_as_float(b.x << 16), weight);
+            v.y = __fmul_rn(__uint_as_float(b.x & 0xffff0000u), weight);
+            v.z = __fmul_rn(__uint_as_float(b.y << 16), weight);
+            v.w = __fmul_rn(__uint_as_float(b.y & 0xffff0000u), weight);
+        }
+        y[i] = v;
+    }
+}
+
 }  // namespace
+
+cudaError_t combine_init_launch(const Problem &p, cudaStream_t stream)
+{
+    if (p.out_rows <= 0 || p.N <= 0) return cudaSuccess;
+    if (p.N % 4 != 0) return cudaErrorInvalidValue;
+    const long long n4 = p.N / 4, total = p.out_rows * n4;
+    const int sms = device_sm_count();
+    long long blocks = (total + 255) / 256;
+    const long long cap = (long long)(sms > 0 ? sms : 1) * 8;
+    if (blocks > cap) blocks = cap;
+    combine_init_kernel<<<(unsigned)blocks, 256, 0, stream>>>(reinterpret_cast<float4 *>(p.out0), reinterpret_cast<const uint2 *>(p.shared_input),
+                                                             n4, p.out_rows, p.shared_offset, p.shared_input ? p.shared_rows : 0,
+                                                             p.shared_weight);
+    return cudaGetLastError();
+}
 
 static int g_sm_limit = 0;
 
@@ -211,6 +262,8 @@ cudaError_t simt_launch(const Problem &p, Plan &, void *, cudaStream_t stream)
     sp.nz = p.w_layout == 2;
     sp.act_type = p.act_type; sp.mode = p.mode; sp.out_f16 = p.out_f16; sp.out0 = p.out0; sp.out1 = reinterpret_cast<float *>(p.out1);
     sp.out_row_index = reinterpret_cast<const long long *>(p.out_row_index);
+    sp.combine = p.combine; sp.row_index_i32 = p.row_index_i32; sp.scatter_add = p.scatter_add;
+    sp.logit = p.logit; sp.row_index = p.row_index; sp.out_rows = p.out_rows;
     if (p.M <= 0) return cudaSuccess;
     if (p.mode == kModeSwigluQuant) {
         const size_t smem = (size_t)(p.N / 2) * sizeof(float);
@@ -226,6 +279,10 @@ cudaError_t launch(const Problem &p, Plan &plan, void *workspace, size_t workspa
     if (workspace_bytes < plan.ws_bytes || (plan.ws_bytes && !workspace)) return cudaErrorInvalidValue;
     if (plan.zero_bytes) {
         cudaError_t e = cudaMemsetAsync(workspace, 0, plan.zero_bytes, stream);
+        if (e != cudaSuccess) return e;
+    }
+    if (p.combine && p.scatter_add) {
+        cudaError_t e = combine_init_launch(p, stream);
         if (e != cudaSuccess) return e;
     }
     if (plan.path == kPathSm100) return sm100_launch(p, plan, workspace, stream);

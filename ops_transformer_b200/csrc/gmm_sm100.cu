@@ -60,7 +60,7 @@ constexpr long long WAIT_LIMIT_CYCLES = 1ll << 31;   // about a second
 constexpr long long DRAIN_LIMIT_CYCLES = 1ll << 24;  // a few milliseconds
 
 constexpr int EPI_THREADS = 32 * EPI_WARPS;
-enum : int { kEpiPlain = 0, kEpiScatter = 1, kEpiGeneric = 2 };
+enum : int { kEpiPlain = 0, kEpiScatter = 1, kEpiGeneric = 2, kEpiCombine = 3 };
 // Weight layouts: [E,K,N]; [E,N,K] (the transposed view); FRACTAL_NZ [E, N/32, K/16, 16, 32] (32-byte runs along N).
 enum : int { kBRowMajor = 0, kBTransposed = 1, kBFractalNz = 2 };
 constexpr int SCALE_BUFS = 3;          // an epilogue thread can run at most two tiles ahead of another one
@@ -105,6 +105,12 @@ struct KParams {
     const long long *out_row_index;  // optional: result row r is written to row out_row_index[r] (bf16 / int32 modes)
     void *out_peers[8];              // bf16 mode with num_peers > 0: out_row_index = (gpu << 40) | row, base per gpu here
     int num_peers;
+    // combine epilogue (grouped_matmul_finalize_routing): fp32 result rows added to / stored at row row_index[r] of out
+    const float *logit;        // [M] routing weight per row, may be null
+    const void *row_index;     // [M] int64 or int32
+    int row_index_i32;
+    int scatter_add;           // 1: atomic adds (shared-expert rows and logits given), 0: plain stores
+    long long out_rows;        // rows of the fp32 result; indices outside [0, out_rows) are skipped
     unsigned *amax_bits;  // [M] row max of |S| as float bits (swiglu)
     int *rb_counter;      // per 128-row block: number of N tiles that have stored their part (swiglu)
     int8_t *q_out;        // int8 [M, N/2] (swiglu)
@@ -455,6 +461,12 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi)
     return *reinterpret_cast<const uint32_t *>(&v);
 }
 
+// Four fp32 additions to 16 aligned bytes of global memory in one request, no value returned.
+__device__ __forceinline__ void red_add_v4(float *p, const float4 v)
+{
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+
 __device__ __forceinline__ int ld_acquire_gpu(const int *p)
 {
     int v;
@@ -562,6 +574,7 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     constexpr bool B_MN_MAJOR = BL != kBTransposed;  // [E,K,N] and the fractal layout are N-contiguous
     constexpr bool PLAIN = EPI != kEpiGeneric;   // lean arithmetic
     constexpr bool SCATTER = EPI != kEpiPlain;  // rows go where out_row_index says
+    constexpr bool COMBINE = EPI == kEpiCombine;  // fp32 rows combined into row_index[r] of a [out_rows, N] result
     using C = Cfg<CTAS>;
     constexpr int STAGES = C::kStages;
     constexpr int STAGE_BYTES = C::kStageBytes;
@@ -752,7 +765,15 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             }
             const float xs = (valid && p.x_scale) ? __ldg(p.x_scale + grow) : 1.0f;
             long long out_row = grow;
-            if (MODE != kModeSwigluQuant && SCATTER && p.out_row_index && valid) out_row = __ldg(p.out_row_index + grow);
+            float lg = 1.0f;
+            if (COMBINE) {
+                out_row = -1;
+                if (valid) {
+                    out_row = p.row_index_i32 ? (long long)__ldg(reinterpret_cast<const int *>(p.row_index) + grow)
+                                              : __ldg(reinterpret_cast<const long long *>(p.row_index) + grow);
+                    if (p.logit) lg = __ldg(p.logit + grow);
+                }
+            } else if (MODE != kModeSwigluQuant && SCATTER && p.out_row_index && valid) out_row = __ldg(p.out_row_index + grow);
             if (MODE != kModeInt32 && !mbar_wait(&sh->scale_ready[sb], (uint32_t)(it / SCALE_BUFS) & 1u, sh, p.status, 500 + sb)) break;
             if (!mbar_wait(&sh->acc_full[buf], acc_phase, sh, p.status, 400 + buf)) break;
             tc_fence_after();
@@ -814,6 +835,63 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                                 *reinterpret_cast<int4 *>(reinterpret_cast<int *>(p.out) + (size_t)out_row * p.N + col) =
                                     make_int4(acc[0], acc[1], acc[2], acc[3]);
                             }
+                        }
+                    }
+                } else if (COMBINE) {
+                    // grouped_matmul_finalize_routing: t = float(acc) * scale[n]; t *= (per_token[m] * logit[m]);
+                    // t += logit[m] * float(bias[n]); y[row_index[m], n] += t  (ComputeDequantAndActivate,
+                    // DataCopyPerTokenScaleAndBrcb, VectorAtomicProcess of
+                    // gmm/grouped_matmul_finalize_routing/op_kernel/grouped_matmul_finalize_routing.h:418-448, 497-545, 343-366).
+                    float *out = reinterpret_cast<float *>(p.out);
+                    const float rs = p.logit ? (p.x_scale ? __fmul_rn(xs, lg) : lg) : xs;
+                    // One 32-column chunk at a time: 32 fp32 = 128 bytes per row and pass.
+#pragma unroll 1
+                    for (int c = chalf * 4; c < chalf * 4 + 4; ++c) {
+                        if (n0 + c * 32 >= p.N) break;
+                        uint32_t v[32], pk[32];
+                        tmem_ld32(taddr + c * 32, v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j4 = 0; j4 < 8; ++j4) {
+                            const float4 s4 = *reinterpret_cast<const float4 *>(tsc + c * 32 + j4 * 4);
+                            const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const int cc = c * 32 + j4 * 4 + j;
+                                float tv = __fmul_rn(__fmul_rn(__int2float_rn((int)v[j4 * 4 + j]), sv[j]), rs);
+                                if (p.bias_dtype == kBF16 && n0 + cc < p.N) {
+                                    const float b = __uint_as_float((uint32_t)__ldg(reinterpret_cast<const uint16_t *>(p.bias) + sbase + n0 + cc) << 16);
+                                    tv = __fadd_rn(tv, __fmul_rn(lg, b));
+                                }
+                                pk[j4 * 4 + j] = __float_as_uint(tv);
+                            }
+                        }
+                        // Same transposition as the bf16 path: eight lanes then hold 128 contiguous bytes of one row, so a
+                        // vector reduction covers whole 32-byte sectors of the fp32 result.
+                        const int pc = lane & 7;
+                        const int col = n0 + c * 32 + pc * 4;
+#pragma unroll
+                        for (int round = 0; round < 2; ++round) {
+                            if ((lane >> 4) == round) {
+#pragma unroll
+                                for (int q8 = 0; q8 < 8; ++q8)
+                                    *reinterpret_cast<uint4 *>(my_stage + (lane & 15) * 128 + (((q8 ^ lane) & 7) << 4)) =
+                                        make_uint4(pk[q8 * 4], pk[q8 * 4 + 1], pk[q8 * 4 + 2], pk[q8 * 4 + 3]);
+                            }
+                            __syncwarp();
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int r16 = i * 4 + (lane >> 3);
+                                const int rr = round * 16 + r16;
+                                const float4 val = *reinterpret_cast<const float4 *>(my_stage + r16 * 128 + (((pc ^ r16) & 7) << 4));
+                                const long long orow = __shfl_sync(0xffffffffu, out_row, rr);
+                                if (quarter * 32 + rr < my_rows && col < p.N && orow >= 0 && orow < p.out_rows) {
+                                    float *dst = out + (size_t)orow * p.N + col;
+                                    if (p.scatter_add) red_add_v4(dst, val);
+                                    else *reinterpret_cast<float4 *>(dst) = val;
+                                }
+                            }
+                            __syncwarp();
                         }
                     }
                 } else {
@@ -992,6 +1070,7 @@ cudaError_t launch_epi(int epi, const Plan &plan, const KParams &kp, cudaStream_
 {
     if (MODE == kModeSwigluQuant || epi == kEpiPlain) return launch_ctas<MODE, BL, kEpiPlain>(plan, kp, stream);
     if (epi == kEpiScatter) return launch_ctas<MODE, BL, kEpiScatter>(plan, kp, stream);
+    if (MODE == kModeDequantBf16 && epi == kEpiCombine) return launch_ctas<MODE, BL, MODE == kModeDequantBf16 ? kEpiCombine : kEpiPlain>(plan, kp, stream);
     return launch_ctas<MODE, BL, kEpiGeneric>(plan, kp, stream);
 }
 
@@ -1107,7 +1186,13 @@ cudaError_t sm100_launch(const Problem &p, Plan &plan, void *workspace, cudaStre
 
     cudaError_t e;
     const bool lean = !p.bias && p.act_type == 0 && !p.out_f16 && (p.mode != kModeDequantBf16 || p.x_scale);
-    const int epi = !lean ? kEpiGeneric : (p.out_row_index ? kEpiScatter : kEpiPlain);
+    const int epi = p.combine ? kEpiCombine : !lean ? kEpiGeneric : (p.out_row_index ? kEpiScatter : kEpiPlain);
+    kp.logit = p.logit;
+    kp.row_index = p.row_index;
+    kp.row_index_i32 = p.row_index_i32;
+    kp.scatter_add = p.scatter_add;
+    kp.out_rows = p.out_rows;
+    if (p.combine && (p.mode != kModeDequantBf16 || !p.row_index)) return cudaErrorInvalidValue;
     kp.num_peers = p.mode == kModeDequantBf16 ? p.num_peers : 0;
     for (int i = 0; i < 8; ++i) kp.out_peers[i] = i < kp.num_peers ? p.out_peers[i] : nullptr;
     if (kp.num_peers > 0 && epi != kEpiScatter) return cudaErrorInvalidValue;

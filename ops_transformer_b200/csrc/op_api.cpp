@@ -13,6 +13,7 @@
 #include <cstring>
 
 #include "acl_shim.h"
+#include "aclnnop/aclnn_grouped_matmul_finalize_routing_weight_nz.h"
 #include "aclnnop/aclnn_grouped_matmul_swiglu_quant.h"
 #include "aclnnop/aclnn_grouped_matmul_swiglu_quant_weight_nz.h"
 #include "aclnnop/aclnn_grouped_matmul_v4.h"
@@ -365,6 +366,185 @@ aclnnStatus aclnnGroupedMatmulWeightNz(void *workspace, uint64_t workspaceSize, 
     return run_executor("aclnnGroupedMatmulWeightNz", workspace, workspaceSize, executor, stream);
 }
 
+// ------------------------------------------------------------------------------------------------------------
+// grouped_matmul_finalize_routing, W8A8 with a FRACTAL_NZ weight
+// ------------------------------------------------------------------------------------------------------------
+
+// Shared first phase of aclnnGroupedMatmulFinalizeRoutingWeightNz and its V2 twin.  Checks in the reference's order:
+// CheckSupportScene (aclnn_grouped_matmul_finalize_routing.cpp:913-946), PreMatmulCalcProcess (:775-789), CheckParams
+// (:617-636: CheckDtypeValid :252-307, CheckShape :531-588, CheckFormat :319-339, CheckEmptyTensor, CheckTuningConfig).
+static aclnnStatus finalize_routing_phase1(const char *kOp, const aclTensor *x1, const aclTensor *x2, const aclTensor *scale,
+                                           const aclTensor *bias, const aclTensor *offset, const aclTensor *pertokenScale,
+                                           const aclTensor *groupList, const aclTensor *sharedInput, const aclTensor *logit,
+                                           const aclTensor *rowIndex, int64_t dtype, float sharedInputWeight,
+                                           int64_t sharedInputOffset, bool transposeX1, bool transposeX2, int64_t groupListType,
+                                           const aclIntArray *tuningConfig, aclTensor *out, uint64_t *workspaceSize,
+                                           aclOpExecutor **executor)
+{
+    clear_error();
+    GMM_REQUIRE(workspaceSize != nullptr, ACLNN_ERR_PARAM_NULLPTR, "workspaceSize must not be nullptr.");
+    GMM_REQUIRE(executor != nullptr, ACLNN_ERR_PARAM_NULLPTR, "executor must not be nullptr.");
+    // Two supported scenes: shared input, logit and row index all given (rows are added), or row index alone (rows are stored).
+    const bool base = x1 && x2 && scale && groupList && rowIndex;
+    GMM_REQUIRE(base && ((sharedInput && logit) || (!sharedInput && !logit)), ACLNN_ERR_PARAM_NULLPTR,
+                "GroupedMatmulFinalizeRoutingWeightNz do not support input nullptr.");
+    GMM_REQUIRE(dtype == 0, ACLNN_ERR_PARAM_INVALID, "GroupedMatmulFinalizeRoutingWeightNz dtype must be 0, but is %lld.", (long long)dtype);
+    GMM_REQUIRE(x2->rank() >= 2, ACLNN_ERR_PARAM_INVALID, "w's view dimNum should greater than 1, but is %zu.", x2->rank());
+    GMM_REQUIRE(!transposeX1 && !transposeX2, ACLNN_ERR_PARAM_INVALID, "GroupedMatmulFinalizeRoutingWeightNz transpose should be false");
+    GMM_REQUIRE(x1->format == ACL_FORMAT_ND && x2->format == ACL_FORMAT_FRACTAL_NZ, ACLNN_ERR_PARAM_INVALID,
+                "Only support x1: ND, x2: NZ.");
+    GMM_REQUIRE(out != nullptr, ACLNN_ERR_PARAM_NULLPTR, "out must not be nullptr.");
+    GMM_REQUIRE(offset == nullptr, ACLNN_ERR_PARAM_INVALID, "offset belongs to the int4 weight path, which is not part of this build.");
+    // dtypes
+    GMM_REQUIRE(x1->dtype == ACL_INT8 && x2->dtype == ACL_INT8, ACLNN_ERR_PARAM_INVALID,
+                "x1 and x2 must be int8 (the int4 weight path is not part of this build).");
+    GMM_REQUIRE(scale->dtype == ACL_FLOAT || scale->dtype == ACL_BF16, ACLNN_ERR_PARAM_INVALID,
+                "scale dtype must be float32 or bfloat16 (the int64 packed scale is not part of this build).");
+    GMM_REQUIRE(rowIndex->dtype == ACL_INT64 || rowIndex->dtype == ACL_INT32, ACLNN_ERR_PARAM_INVALID, "rowIndex dtype must be int64 or int32.");
+    GMM_REQUIRE(!bias || bias->dtype == ACL_BF16, ACLNN_ERR_PARAM_INVALID, "bias dtype must be bfloat16.");
+    GMM_REQUIRE(!pertokenScale || pertokenScale->dtype == ACL_FLOAT, ACLNN_ERR_PARAM_INVALID, "pertokenScale dtype must be float32.");
+    GMM_REQUIRE(groupList->dtype == ACL_INT64, ACLNN_ERR_PARAM_INVALID, "groupList dtype must be int64.");
+    GMM_REQUIRE(!sharedInput || sharedInput->dtype == ACL_BF16, ACLNN_ERR_PARAM_INVALID, "sharedInput dtype must be bfloat16.");
+    GMM_REQUIRE(!logit || logit->dtype == ACL_FLOAT, ACLNN_ERR_PARAM_INVALID, "logit dtype must be float32.");
+    GMM_REQUIRE(out->dtype == ACL_FLOAT, ACLNN_ERR_PARAM_INVALID, "y's dtype should be [DT_FLOAT].");
+    // dimension counts (CheckDimRange, :341-377)
+    GMM_REQUIRE(x1->rank() == 2, ACLNN_ERR_PARAM_INVALID, "x dim num should be 2, but is %zu.", x1->rank());
+    GMM_REQUIRE(x2->rank() == 3 || x2->rank() == 5, ACLNN_ERR_PARAM_INVALID, "w must be viewed as [e, k, n] or as [e, n/32, k/16, 16, 32].");
+    GMM_REQUIRE(scale->rank() == 2, ACLNN_ERR_PARAM_INVALID, "scale dim num should be 2.");
+    GMM_REQUIRE(!pertokenScale || pertokenScale->rank() == 1, ACLNN_ERR_PARAM_INVALID, "pertokenScale dim num should be 1.");
+    GMM_REQUIRE(groupList->rank() == 1, ACLNN_ERR_PARAM_INVALID, "groupList dim num should be 1.");
+    GMM_REQUIRE(!sharedInput || sharedInput->rank() == 2, ACLNN_ERR_PARAM_INVALID, "sharedInput dim num should be 2.");
+    GMM_REQUIRE(!logit || logit->rank() == 1, ACLNN_ERR_PARAM_INVALID, "logit dim num should be 1.");
+    GMM_REQUIRE(rowIndex->rank() == 1, ACLNN_ERR_PARAM_INVALID, "rowIndex dim num should be 1.");
+    GMM_REQUIRE(!bias || bias->rank() == 2, ACLNN_ERR_PARAM_INVALID, "bias dim num should be 2.");
+    // shapes
+    const int64_t M = x1->dim(0), K = x1->dim(1), E = x2->dim(0);
+    int64_t wK, N;
+    if (x2->rank() == 5) {
+        GMM_REQUIRE(x2->dim(3) == 16 && x2->dim(4) == 32, ACLNN_ERR_PARAM_INVALID, "a 5-dimensional w must be [e, n/32, k/16, 16, 32].");
+        wK = x2->dim(2) * 16; N = x2->dim(1) * 32;
+    } else {
+        wK = x2->dim(1); N = x2->dim(2);
+        // the storage must hold the fractal form of the view (CheckWeightNzFormat :891-911, CheckShapeForWeightNz :499-518)
+        GMM_REQUIRE(x2->storage_dims.size() >= 5, ACLNN_ERR_PARAM_INVALID,
+                    "x2's storage shape must be the FRACTAL_NZ form [e, n/32, k/16, 16, 32] of its view.");
+        int64_t prod = 1;
+        for (int64_t d : x2->storage_dims) prod *= d;
+        GMM_REQUIRE(prod == E * ((N + 31) / 32) * ((wK + 15) / 16) * 16 * 32, ACLNN_ERR_PARAM_INVALID,
+                    "x2's format only support NZ, but x2's storage shape is not the fractal form of its view.");
+        GMM_REQUIRE(x2->storage_dims[x2->storage_dims.size() - 3] * 16 == (K + 15) / 16 * 16, ACLNN_ERR_PARAM_INVALID,
+                    "AlignedK1 value is not matched with k1 value times 16.");
+    }
+    GMM_REQUIRE(K == wK, ACLNN_ERR_PARAM_INVALID, "x1 k dim and x2 k dim should be same, but x1 is %lld, x2 is %lld.", (long long)K, (long long)wK);
+    GMM_REQUIRE(K % 16 == 0 && N % 32 == 0 && N >= 256, ACLNN_ERR_PARAM_INVALID,
+                "k dim %lld and n dim %lld do not support. only support k mod 16 equal 0, n mod 32 equal 0 and n bigger or equal 256",
+                (long long)K, (long long)N);
+    GMM_REQUIRE(out->rank() == 2, ACLNN_ERR_PARAM_INVALID, "Out dim num should be equal to 2, but is %zu.", out->rank());
+    const int64_t BS = out->dim(0);
+    GMM_REQUIRE(BS <= M && BS >= 0, ACLNN_ERR_PARAM_INVALID, "Out 1st dim should be less than or equal to x MDim , but out 1st dim is %lld", (long long)BS);
+    GMM_REQUIRE(out->dim(1) == N, ACLNN_ERR_PARAM_INVALID, "Out 2nd dim should be equal to weight NDim.");
+    GMM_REQUIRE(sharedInputOffset >= 0, ACLNN_ERR_PARAM_INVALID, "sharedInputOffset should bigger than or equal to 0");
+    GMM_REQUIRE(groupListType == 1, ACLNN_ERR_PARAM_INVALID, "groupListType is 1, but is %lld", (long long)groupListType);
+    GMM_REQUIRE(scale->dim(0) == E && scale->dim(1) == N, ACLNN_ERR_PARAM_INVALID, "Scale must be [%lld, %lld].", (long long)E, (long long)N);
+    GMM_REQUIRE(!bias || (bias->dim(0) == E && bias->dim(1) == N), ACLNN_ERR_PARAM_INVALID, "bias must be [%lld, %lld].", (long long)E, (long long)N);
+    GMM_REQUIRE(!pertokenScale || pertokenScale->dim(0) == M, ACLNN_ERR_PARAM_INVALID, "pertokenScale fisrt dim should equal to x MDim %lld.", (long long)M);
+    GMM_REQUIRE(groupList->dim(0) == E, ACLNN_ERR_PARAM_INVALID, "groupList fisrt dim should equal to weight EDim %lld.", (long long)E);
+    const int64_t sharedRows = sharedInput ? sharedInput->dim(0) : 0;
+    GMM_REQUIRE(!sharedInput || (sharedRows <= BS && sharedInput->dim(1) == N), ACLNN_ERR_PARAM_INVALID,
+                "shareInput fisrt dim should less than or equal to outputBS %lld, last dim should equal to weight NDim %lld.", (long long)BS, (long long)N);
+    GMM_REQUIRE(!logit || logit->dim(0) == M, ACLNN_ERR_PARAM_INVALID, "logit fisrt dim should equal to x MDim %lld.", (long long)M);
+    GMM_REQUIRE(rowIndex->dim(0) == M, ACLNN_ERR_PARAM_INVALID, "rowIndex fisrt dim should equal to x MDim %lld.", (long long)M);
+    GMM_REQUIRE(sharedInputOffset + sharedRows <= BS, ACLNN_ERR_PARAM_INVALID,
+                "shareInputOffset add shareInputDim should be less than or equal to outputBS.");
+    GMM_REQUIRE(!x1->empty() && !x2->empty() && !scale->empty() && !groupList->empty() && !rowIndex->empty() &&
+                    !(pertokenScale && pertokenScale->empty()) && !(sharedInput && sharedInput->empty()) && !(logit && logit->empty()),
+                ACLNN_ERR_PARAM_INVALID, "GroupedMatmulFinalizeRouting WeightNz do not support input tensor size is 0.");
+    // formats
+    for (const aclTensor *t : {scale, bias, pertokenScale, groupList, sharedInput, logit, rowIndex, (const aclTensor *)out})
+        GMM_REQUIRE(!t || t->format == ACL_FORMAT_ND, ACLNN_ERR_PARAM_INVALID, "every tensor but x2 must have format ND.");
+    if (tuningConfig && !tuningConfig->values.empty())
+        GMM_REQUIRE(tuningConfig->values[0] >= 0 && tuningConfig->values[0] <= M, ACLNN_ERR_PARAM_INVALID,
+                    "Invalid tuningConfigOptional (%lld)! It should be a non-negative num and smaller than (%lld)",
+                    (long long)tuningConfig->values[0], (long long)M);
+    GMM_REQUIRE(E <= kMaxGroupListLen, ACLNN_ERR_PARAM_INVALID, "more than %lld experts.", (long long)kMaxGroupListLen);
+    GMM_REQUIRE(K <= kMaxInnerAxis && N <= kMaxInnerAxis, ACLNN_ERR_PARAM_INVALID, "k and n must not exceed %lld.", (long long)kMaxInnerAxis);
+
+    aclOpExecutor *e = new_executor(kOp);
+    GMM_REQUIRE(e != nullptr, ACLNN_ERR_INNER_CREATE_EXECUTOR, "cannot create executor.");
+    if (out->empty()) return finish_phase1(e, workspaceSize, executor);
+    for (const aclTensor *t : {x1, scale, bias, pertokenScale, groupList, sharedInput, logit, rowIndex, (const aclTensor *)out}) {
+        if (t && !t->contiguous()) {
+            delete e;
+            return fail(ACLNN_ERR_PARAM_INVALID, "this build needs contiguous tensors.");
+        }
+    }
+    Problem &p = e->problem;
+    p.x = static_cast<const int8_t *>(tensor_ptr(x1));
+    p.w = static_cast<const int8_t *>(tensor_ptr(x2));
+    p.w_scale = tensor_ptr(scale);
+    p.w_scale_dtype = (int)scale->dtype;
+    p.x_scale = pertokenScale ? static_cast<const float *>(tensor_ptr(pertokenScale)) : nullptr;
+    p.bias = bias ? tensor_ptr(bias) : nullptr;
+    p.bias_dtype = bias ? kBF16 : kNone;
+    p.group_list = static_cast<const int64_t *>(tensor_ptr(groupList));
+    p.gl_len = (int)E;
+    p.gl_type = 1;
+    p.M = M; p.K = K; p.N = N; p.E = E;
+    p.w_layout = 2;
+    p.mode = kModeDequantBf16;
+    p.out0 = tensor_ptr(out);
+    p.combine = 1;
+    p.logit = logit ? static_cast<const float *>(tensor_ptr(logit)) : nullptr;
+    p.row_index = tensor_ptr(rowIndex);
+    p.row_index_i32 = rowIndex->dtype == ACL_INT32;
+    p.scatter_add = (sharedInput || logit) ? 1 : 0;   // grouped_matmul_finalize_routing_base_tiling.cpp:296-300
+    p.out_rows = BS;
+    p.shared_input = sharedInput ? tensor_ptr(sharedInput) : nullptr;
+    p.shared_rows = sharedRows;
+    p.shared_offset = sharedInputOffset;
+    p.shared_weight = sharedInputWeight;
+    e->kind = aclOpExecutor::kGmm;
+    make_plan(p, &e->plan);
+    return finish_phase1(e, workspaceSize, executor);
+}
+
+aclnnStatus aclnnGroupedMatmulFinalizeRoutingWeightNzGetWorkspaceSize(
+    const aclTensor *x1, const aclTensor *x2, const aclTensor *scale, const aclTensor *bias, const aclTensor *pertokenScaleOptional,
+    const aclTensor *groupList, const aclTensor *sharedInput, const aclTensor *logit, const aclTensor *rowIndex, int64_t dtype,
+    float sharedInputWeight, int64_t sharedInputOffset, bool transposeX1, bool transposeX2, int64_t groupListType, aclTensor *out,
+    uint64_t *workspaceSize, aclOpExecutor **executor)
+{
+    return finalize_routing_phase1("aclnnGroupedMatmulFinalizeRoutingWeightNz", x1, x2, scale, bias, nullptr, pertokenScaleOptional,
+                                   groupList, sharedInput, logit, rowIndex, dtype, sharedInputWeight, sharedInputOffset, transposeX1,
+                                   transposeX2, groupListType, nullptr, out, workspaceSize, executor);
+}
+
+aclnnStatus aclnnGroupedMatmulFinalizeRoutingWeightNz(void *workspace, uint64_t workspaceSize, aclOpExecutor *executor,
+                                                      aclrtStream stream)
+{
+    return run_executor("aclnnGroupedMatmulFinalizeRoutingWeightNz", workspace, workspaceSize, executor, stream);
+}
+
+aclnnStatus aclnnGroupedMatmulFinalizeRoutingWeightNzV2GetWorkspaceSize(
+    const aclTensor *x1, aclTensor *x2, const aclTensor *scale, const aclTensor *bias, const aclTensor *offsetOptional,
+    const aclTensor *antiquantScaleOptional, const aclTensor *antiquantOffsetOptional, const aclTensor *pertokenScaleOptional,
+    const aclTensor *groupList, const aclTensor *sharedInput, const aclTensor *logit, const aclTensor *rowIndex, int64_t dtype,
+    float sharedInputWeight, int64_t sharedInputOffset, bool transposeX1, bool transposeX2, int64_t groupListType,
+    const aclIntArray *tuningConfigOptional, aclTensor *out, uint64_t *workspaceSize, aclOpExecutor **executor)
+{
+    (void)antiquantScaleOptional; (void)antiquantOffsetOptional;  // unused in the reference too (:1007-1008)
+    return finalize_routing_phase1("aclnnGroupedMatmulFinalizeRoutingWeightNzV2", x1, x2, scale, bias, offsetOptional,
+                                   pertokenScaleOptional, groupList, sharedInput, logit, rowIndex, dtype, sharedInputWeight,
+                                   sharedInputOffset, transposeX1, transposeX2, groupListType, tuningConfigOptional, out, workspaceSize,
+                                   executor);
+}
+
+aclnnStatus aclnnGroupedMatmulFinalizeRoutingWeightNzV2(void *workspace, uint64_t workspaceSize, aclOpExecutor *executor,
+                                                        aclrtStream stream)
+{
+    return run_executor("aclnnGroupedMatmulFinalizeRoutingWeightNzV2", workspace, workspaceSize, executor, stream);
+}
+
 // Shared first phase of aclnnGroupedMatmulSwigluQuant and its WeightNZ twin
 // (aclnnGroupedMatmulSwigluQuantGetWorkspaceSizeCommon, aclnn_grouped_matmul_swiglu_quant.cpp:411-465).
 static aclnnStatus swiglu_phase1(const char *kOp, bool force_nz, const aclTensor *x, const aclTensor *weight, const aclTensor *bias,
@@ -654,6 +834,52 @@ aclnnStatus gmmB200GroupedMatmulSwigluQuant(const void *x, const void *weight, c
     GMM_REQUIRE(workspace != nullptr, ACLNN_ERR_PARAM_NULLPTR, "workspace must not be nullptr.");
     cudaError_t ce = launch(p, plan, workspace, workspaceSize, static_cast<cudaStream_t>(stream));
     if (ce != cudaSuccess) return fail(ACLNN_ERR_INNER, "kernel launch failed: %s", cudaGetErrorString(ce));
+    return ACLNN_SUCCESS;
+}
+
+aclnnStatus gmmB200GroupedMatmulFinalizeRouting(const void *x, const void *weight, int32_t weightLayout, const void *scale,
+                                                int32_t scaleDtype, const void *bias, const void *perTokenScale, const void *groupList,
+                                                int64_t groupListLen, int32_t groupListType, const void *sharedInput,
+                                                int64_t sharedRows, int64_t sharedOffset, float sharedWeight, const void *logit,
+                                                const void *rowIndex, int32_t rowIndexDtype, int64_t m, int64_t k, int64_t n, int64_t e,
+                                                void *y, int64_t yRows, void *workspace, uint64_t workspaceSize, aclrtStream stream)
+{
+    clear_error();
+    GMM_REQUIRE(x && weight && scale && groupList && rowIndex && y, ACLNN_ERR_PARAM_NULLPTR, "x, weight, scale, groupList, rowIndex and y must not be nullptr.");
+    GMM_REQUIRE((sharedInput != nullptr) == (logit != nullptr), ACLNN_ERR_PARAM_NULLPTR, "sharedInput and logit come together or not at all.");
+    GMM_REQUIRE(m > 0 && k > 0 && n > 0 && e > 0 && yRows >= 0 && k <= kMaxInnerAxis && n <= kMaxInnerAxis, ACLNN_ERR_PARAM_INVALID, "bad sizes.");
+    GMM_REQUIRE(n % 4 == 0, ACLNN_ERR_PARAM_INVALID, "n must be a multiple of 4.");
+    GMM_REQUIRE(weightLayout == 0 || (weightLayout == 2 && k % 16 == 0 && n % 32 == 0), ACLNN_ERR_PARAM_INVALID,
+                "weightLayout must be 0 ([e,k,n]) or 2 (FRACTAL_NZ, k %% 16 == 0, n %% 32 == 0).");
+    GMM_REQUIRE(scaleDtype == ACL_FLOAT || scaleDtype == ACL_BF16, ACLNN_ERR_PARAM_INVALID, "scaleDtype must be float32 or bfloat16.");
+    GMM_REQUIRE(rowIndexDtype == ACL_INT64 || rowIndexDtype == ACL_INT32, ACLNN_ERR_PARAM_INVALID, "rowIndexDtype must be int64 or int32.");
+    GMM_REQUIRE(groupListType == 0 || groupListType == 1, ACLNN_ERR_PARAM_INVALID, "groupListType must be 0 or 1.");
+    GMM_REQUIRE(groupListLen > 0 && groupListLen <= e && groupListLen <= kMaxGroupListLen, ACLNN_ERR_PARAM_INVALID, "bad groupListLen.");
+    GMM_REQUIRE(sharedRows >= 0 && sharedOffset >= 0 && sharedOffset + sharedRows <= yRows, ACLNN_ERR_PARAM_INVALID, "shared rows exceed y.");
+    Problem p;
+    p.x = static_cast<const int8_t *>(x);
+    p.w = static_cast<const int8_t *>(weight);
+    p.w_scale = scale; p.w_scale_dtype = scaleDtype;
+    p.x_scale = static_cast<const float *>(perTokenScale);
+    p.bias = bias; p.bias_dtype = bias ? kBF16 : kNone;
+    p.group_list = static_cast<const int64_t *>(groupList);
+    p.gl_len = (int)groupListLen; p.gl_type = groupListType;
+    p.M = m; p.K = k; p.N = n; p.E = e;
+    p.w_layout = weightLayout;
+    p.mode = kModeDequantBf16;
+    p.out0 = y;
+    p.combine = 1;
+    p.logit = static_cast<const float *>(logit);
+    p.row_index = rowIndex;
+    p.row_index_i32 = rowIndexDtype == ACL_INT32;
+    p.scatter_add = sharedInput ? 1 : 0;
+    p.out_rows = yRows;
+    p.shared_input = sharedInput; p.shared_rows = sharedRows; p.shared_offset = sharedOffset; p.shared_weight = sharedWeight;
+    Plan plan;
+    make_plan(p, &plan);
+    GMM_REQUIRE(workspaceSize >= plan.ws_bytes && workspace, ACLNN_ERR_PARAM_INVALID, "workspace of %llu bytes needed.", (unsigned long long)plan.ws_bytes);
+    cudaError_t ce = launch(p, plan, workspace, workspaceSize, static_cast<cudaStream_t>(stream));
+    if (ce != cudaSuccess) return fail(ACLNN_ERR_INNER, "gmmB200GroupedMatmulFinalizeRouting: launch failed: %s", cudaGetErrorString(ce));
     return ACLNN_SUCCESS;
 }
 

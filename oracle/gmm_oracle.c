@@ -322,6 +322,81 @@ ORACLE_API int oracle_gmm_w8a8(const int8_t *x, const int8_t *w, const void *sca
 }
 
 /* ------------------------------------------------------------------------------------------- */
+/* grouped_matmul_finalize_routing, W8A8                                                        */
+/* ------------------------------------------------------------------------------------------- */
+
+/* QuantGroupMatmul<combine = true> of gmm/grouped_matmul_finalize_routing/op_kernel/grouped_matmul_finalize_routing.h:
+ *   PreProcess (:208-258), only when shared_input / logit are given ("scatterAdd", base_tiling.cpp:296-300):
+ *     y[r, :] = 0 for r outside [shared_offset, shared_offset + shared_rows)
+ *     y[shared_offset + r, :] = float(shared_input[r, :]) * shared_weight        Cast CAST_NONE + Muls, :245-249
+ *   per row m of group g (groups with no rows skipped, :272-275):
+ *     t = float(acc[m, n]) * float(scale[g, n])                                   AscendDequant, :432
+ *     s = per_token[m] * logit[m]  (logit[m] alone without per_token)             Mul, :524
+ *     t = t * s                                                                   Mul, :441-446
+ *     t = t + logit[m] * float(bias[g, n])    if bias (bf16)                      :535-540, :443
+ *     y[row_index[m], n] += t   (atomic add, :347-360)   -- or  = t  without shared_input / logit
+ * The reference's additions are atomic and unordered; this restatement adds in row order, so a comparison needs a
+ * tolerance of a few fp32 ulps of the sum of magnitudes (abs_sum, optional [y_rows, N], receives that sum).
+ * Without logits the reference multiplies the bias by a buffer it never filled (:535); here the bias is then added as is.
+ * group_list: gl_type 1 (counts, the only value the reference's API admits) or 0.  row_index is int64 (idx_i32 = 0) or int32. */
+ORACLE_API int oracle_gmm_finalize_routing(const int8_t *x, const int8_t *w, const void *scale, int scale_dtype,
+                                           const uint16_t *bias_bf16, const float *per_token, const int64_t *group_list,
+                                           int64_t gl_len, int gl_type, const uint16_t *shared_bf16, int64_t shared_rows,
+                                           int64_t shared_offset, float shared_weight, const float *logit,
+                                           const void *row_index, int idx_i32, int64_t M, int64_t K, int64_t N, int64_t E,
+                                           float *y, int64_t y_rows, double *abs_sum)
+{
+    if (gl_len > E) return -1;
+    const int add = shared_bf16 != NULL || logit != NULL;
+    if (add) {
+        for (int64_t r = 0; r < y_rows; ++r) {
+            const int in_shared = shared_bf16 && r >= shared_offset && r < shared_offset + shared_rows;
+            for (int64_t n = 0; n < N; ++n) {
+                float v = 0.0f;
+                if (in_shared) v = bf16_to_f32(shared_bf16[(r - shared_offset) * N + n]) * shared_weight;
+                y[r * N + n] = v;
+                if (abs_sum) abs_sum[r * N + n] = fabs((double)v);
+            }
+        }
+    }
+    int64_t *rs = (int64_t *)malloc(sizeof(int64_t) * (size_t)(2 * gl_len + 2));
+    int64_t *rc = rs + gl_len + 1;
+    oracle_group_layout(group_list, gl_len, gl_type, M, rs, rc);
+    int64_t maxrows = 0;
+    for (int64_t g = 0; g < gl_len; ++g) if (rc[g] > maxrows) maxrows = rc[g];
+    int32_t *acc = (int32_t *)malloc(sizeof(int32_t) * (size_t)(maxrows > 0 ? maxrows : 1) * (size_t)N);
+    for (int64_t g = 0; g < gl_len; ++g) {
+        const int64_t r0 = rs[g], rows = rc[g];
+        if (rows <= 0) continue;
+        gemm_group(x + r0 * K, rows, K, N, w + g * K * N, N, 1, acc);
+        for (int64_t r = 0; r < rows; ++r) {   /* sequential: rows may share a destination */
+            const int64_t m = r0 + r;
+            const int64_t dst = idx_i32 ? (int64_t)((const int32_t *)row_index)[m] : ((const int64_t *)row_index)[m];
+            if (dst < 0 || dst >= y_rows) continue;
+            const float lg = logit ? logit[m] : 1.0f;
+            float s;
+            if (logit) s = per_token ? per_token[m] * lg : lg;
+            else s = per_token ? per_token[m] : 1.0f;
+            for (int64_t n = 0; n < N; ++n) {
+                float t = (float)acc[r * N + n] * load_scale(scale, scale_dtype, g * N + n);
+                t = t * s;
+                if (bias_bf16) t = t + lg * bf16_to_f32(bias_bf16[g * N + n]);
+                if (add) {
+                    y[dst * N + n] = y[dst * N + n] + t;
+                    if (abs_sum) abs_sum[dst * N + n] += fabs((double)t);
+                } else {
+                    y[dst * N + n] = t;
+                    if (abs_sum) abs_sum[dst * N + n] = fabs((double)t);
+                }
+            }
+        }
+    }
+    free(acc);
+    free(rs);
+    return 0;
+}
+
+/* ------------------------------------------------------------------------------------------- */
 /* grouped_matmul_swiglu_quant, A8W8                                                            */
 /* ------------------------------------------------------------------------------------------- */
 

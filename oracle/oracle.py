@@ -115,6 +115,68 @@ def gmm_w8a8(x, w, scale, per_token_scale, group_list, gl_type=0, bias=None, act
     return {"y": y, "acc": acc, "pre": pre}
 
 
+def gmm_finalize_routing(x, w, scale, per_token, group_list, row_index, y_rows, gl_type=1, bias=None, shared_input=None,
+                         shared_offset=0, shared_weight=1.0, logit=None, y_init=None):
+    """grouped_matmul_finalize_routing W8A8.  ``w`` int8 [E,K,N]; bf16 tensors (scale if uint16, bias, shared_input) are
+    uint16 bit patterns.  Returns dict(y fp32 [y_rows, N], abs_sum float64: sum of the magnitudes of the terms of every
+    element, the scale of the rounding differences an unordered summation may show)."""
+    x = np.ascontiguousarray(x, np.int8)
+    w = np.ascontiguousarray(w, np.int8)
+    M, K = x.shape
+    E, _, N = w.shape
+    gl = np.ascontiguousarray(group_list, np.int64)
+    scale = np.ascontiguousarray(scale)
+    pts = None if per_token is None else np.ascontiguousarray(per_token, np.float32)
+    bias = None if bias is None else np.ascontiguousarray(bias, np.uint16)
+    sh = None if shared_input is None else np.ascontiguousarray(shared_input, np.uint16)
+    lg = None if logit is None else np.ascontiguousarray(logit, np.float32)
+    ri = np.ascontiguousarray(row_index)
+    if ri.dtype not in (np.int64, np.int32):
+        raise TypeError("row_index must be int64 or int32")
+    y = np.zeros((y_rows, N), np.float32) if y_init is None else np.array(y_init, np.float32, copy=True)
+    abs_sum = np.zeros((y_rows, N), np.float64)
+    fn = lib().oracle_gmm_finalize_routing
+    fn.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int,
+                   C.c_void_p, C.c_int64, C.c_int64, C.c_float, C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64,
+                   C.c_int64, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p]
+    fn.restype = C.c_int
+    rc = fn(_ptr(x), _ptr(w), _ptr(scale), _scale_dtype(scale), _ptr(bias), _ptr(pts), _ptr(gl), len(gl), gl_type, _ptr(sh),
+            0 if sh is None else sh.shape[0], shared_offset, float(shared_weight), _ptr(lg), _ptr(ri), int(ri.dtype == np.int32),
+            M, K, N, E, _ptr(y), y_rows, _ptr(abs_sum))
+    if rc != 0:
+        raise ValueError("oracle_gmm_finalize_routing rejected the arguments")
+    return {"y": y, "abs_sum": abs_sum}
+
+
+def np_gmm_finalize_routing(x, w, scale_f32, per_token, group_list, row_index, y_rows, gl_type=1, bias_f32=None,
+                            shared_f32=None, shared_offset=0, shared_weight=1.0, logit=None):
+    """Independent float64 formulation of the same operator (for tolerance checks of the C restatement)."""
+    M, K = x.shape
+    N = w.shape[2]
+    add = shared_f32 is not None or logit is not None
+    y = np.zeros((y_rows, N), np.float64)
+    if shared_f32 is not None:
+        y[shared_offset:shared_offset + shared_f32.shape[0]] = shared_f32.astype(np.float64) * float(np.float32(shared_weight))
+    for g, (s, r) in enumerate(np_group_ranges(group_list, gl_type, M)):
+        if r <= 0:
+            continue
+        a = (x[s:s + r].astype(np.int64) @ w[g].astype(np.int64)).astype(np.float64)
+        t = a * np.asarray(scale_f32[g], np.float64)[None, :]
+        rowscale = np.ones(r) if per_token is None else np.asarray(per_token[s:s + r], np.float64)
+        lg = np.ones(r) if logit is None else np.asarray(logit[s:s + r], np.float64)
+        t = t * (rowscale * lg)[:, None]
+        if bias_f32 is not None:
+            t = t + lg[:, None] * np.asarray(bias_f32[g], np.float64)[None, :]
+        for i in range(r):
+            d = int(row_index[s + i])
+            if 0 <= d < y_rows:
+                if add:
+                    y[d] += t[i]
+                else:
+                    y[d] = t[i]
+    return y
+
+
 def swiglu_quant(x, w, w_scale, x_scale, group_list, w_trans=False, q_init=None, qs_init=None, want_acc=False,
                  want_s=False):
     """grouped_matmul_swiglu_quant A8W8.  Returns dict(q int8 [M,N/2], q_scale f32 [M], acc, s)."""

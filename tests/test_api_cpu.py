@@ -257,6 +257,98 @@ def test_v4_float16_result_and_activations():
     assert "GELU_ERR_FUNC" in _lib.last_error()
 
 
+def _fr_tensors(m=192, k=2048, n=7168, e=4, batch=24, shared=8):
+    return dict(x=torch.empty((m, k), dtype=torch.int8), w=torch.empty((e, n // 32, k // 16, 16, 32), dtype=torch.int8),
+                scale=torch.empty((e, n), dtype=torch.float32), bias=None, pts=torch.empty((m,), dtype=torch.float32),
+                gl=torch.empty((e,), dtype=torch.int64), shared=torch.empty((shared, n), dtype=torch.bfloat16),
+                logit=torch.empty((m,), dtype=torch.float32), ri=torch.empty((m,), dtype=torch.int64),
+                out=torch.empty((batch, n), dtype=torch.float32))
+
+
+def _fr_phase1(x, w, scale, bias, pts, gl, shared, logit, ri, out, dtype=0, weight=1.0, offset=0, tx=False, tw=False, gl_type=1,
+               fmt_w=_lib.ACL_FORMAT_FRACTAL_NZ, view_3d=True, api="", tuning=None, v2_offset=None):
+    L = _lib.lib()
+    hs = []
+
+    def mk(t, **kw):
+        if t is None:
+            return None
+        h = acl.create_tensor(t, **kw)
+        hs.append(h)
+        return h
+    view = None
+    if w is not None and view_3d and w.dim() == 5:
+        view = [w.shape[0], w.shape[2] * 16, w.shape[1] * 32]
+    hw = mk(w, fmt=fmt_w, view_dims=view)
+    hx, hsc, hb, hp, hg, hsh, hl, hr, hy = (mk(t) for t in (x, scale, bias, pts, gl, shared, logit, ri, out))
+    size, ex = C.c_uint64(9), C.c_void_p(0)
+    if api == "V2":
+        ht = L.aclCreateIntArray((C.c_int64 * len(tuning))(*tuning), len(tuning)) if tuning is not None else None
+        rc = L.aclnnGroupedMatmulFinalizeRoutingWeightNzV2GetWorkspaceSize(hx, hw, hsc, hb, mk(v2_offset), None, None, hp, hg, hsh, hl, hr,
+                                                                           dtype, weight, offset, tx, tw, gl_type, ht, hy,
+                                                                           C.byref(size), C.byref(ex))
+        if ht:
+            L.aclDestroyIntArray(ht)
+    else:
+        rc = L.aclnnGroupedMatmulFinalizeRoutingWeightNzGetWorkspaceSize(hx, hw, hsc, hb, hp, hg, hsh, hl, hr, dtype, weight, offset, tx,
+                                                                         tw, gl_type, hy, C.byref(size), C.byref(ex))
+    if rc == OK:
+        assert L.aclDestroyAclOpExecutor(ex) == OK
+    for h in hs:
+        L.aclDestroyTensor(h)
+    return rc, size.value
+
+
+def test_finalize_routing_phase1_status_codes():
+    NZ = _lib.ACL_FORMAT_FRACTAL_NZ
+    t = _fr_tensors()   # the reference's example: m=192, k=2048, n=7168, e=4, batch=24, 8 shared rows
+    rc, size = _fr_phase1(**t)
+    assert rc == OK and size >= 256
+    assert _fr_phase1(**t, view_3d=False)[0] == OK                                   # 5-dimensional view
+    assert _fr_phase1(**t, api="V2", tuning=[48])[0] == OK
+    assert _fr_phase1(**{**t, "scale": torch.empty((4, 7168), dtype=torch.bfloat16)})[0] == OK
+    assert _fr_phase1(**{**t, "ri": torch.empty((192,), dtype=torch.int32)})[0] == OK
+    assert _fr_phase1(**{**t, "bias": torch.empty((4, 7168), dtype=torch.bfloat16)})[0] == OK
+    assert _fr_phase1(**{**t, "pts": None})[0] == OK
+    assert _fr_phase1(**{**t, "shared": None, "logit": None})[0] == OK               # scene 2: plain stores
+    # the two scenes are the only legal combinations of null arguments
+    assert _fr_phase1(**{**t, "shared": None})[0] == NULLPTR
+    assert _fr_phase1(**{**t, "logit": None})[0] == NULLPTR
+    for name in ("x", "w", "scale", "gl", "ri"):
+        assert _fr_phase1(**{**t, name: None})[0] == NULLPTR
+    assert _fr_phase1(**{**t, "out": None})[0] == NULLPTR
+    # attributes
+    assert _fr_phase1(**t, dtype=1)[0] == INVALID
+    assert _fr_phase1(**t, tx=True)[0] == INVALID
+    assert _fr_phase1(**t, tw=True)[0] == INVALID
+    assert _fr_phase1(**t, gl_type=0)[0] == INVALID
+    assert "groupListType" in _lib.last_error()
+    assert _fr_phase1(**t, offset=-1)[0] == INVALID
+    assert _fr_phase1(**t, offset=17)[0] == INVALID                                  # 17 + 8 shared rows > batch 24
+    assert _fr_phase1(**t, offset=16)[0] == OK
+    assert _fr_phase1(**t, api="V2", tuning=[193])[0] == INVALID
+    assert _fr_phase1(**t, api="V2", tuning=[-1])[0] == INVALID
+    assert _fr_phase1(**t, api="V2", v2_offset=torch.empty((4, 1, 7168), dtype=torch.float32))[0] == INVALID
+    # formats, dtypes, shapes
+    assert _fr_phase1(**t, fmt_w=_lib.ACL_FORMAT_ND)[0] == INVALID                   # this entry point wants the NZ weight
+    assert _fr_phase1(**{**t, "w": torch.empty((4, 2048, 7168), dtype=torch.int8)})[0] == INVALID   # NZ format over an ND storage shape
+    assert _fr_phase1(**{**t, "out": torch.empty((24, 7168), dtype=torch.bfloat16)})[0] == INVALID
+    assert _fr_phase1(**{**t, "scale": torch.empty((4, 7168), dtype=torch.int64)})[0] == INVALID
+    assert _fr_phase1(**{**t, "bias": torch.empty((4, 7168), dtype=torch.float32)})[0] == INVALID
+    assert _fr_phase1(**{**t, "ri": torch.empty((192,), dtype=torch.float32)})[0] == INVALID
+    assert _fr_phase1(**{**t, "ri": torch.empty((100,), dtype=torch.int64)})[0] == INVALID
+    assert _fr_phase1(**{**t, "logit": torch.empty((100,), dtype=torch.float32)})[0] == INVALID
+    assert _fr_phase1(**{**t, "gl": torch.empty((3,), dtype=torch.int64)})[0] == INVALID
+    assert _fr_phase1(**{**t, "shared": torch.empty((25, 7168), dtype=torch.bfloat16)})[0] == INVALID  # more shared rows than batch
+    assert _fr_phase1(**{**t, "shared": torch.empty((8, 7000), dtype=torch.bfloat16)})[0] == INVALID
+    assert _fr_phase1(**{**t, "out": torch.empty((193, 7168), dtype=torch.float32)})[0] == INVALID     # batch > m
+    assert _fr_phase1(**{**t, "x": torch.empty((192, 2032), dtype=torch.int8)})[0] == INVALID          # k mismatch
+    small = _fr_tensors(m=16, k=64, n=128, e=2, batch=4, shared=2)
+    assert _fr_phase1(**small)[0] == INVALID                                                            # n < 256
+    assert _fr_phase1(**_fr_tensors(m=16, k=64, n=256, e=2, batch=4, shared=2))[0] == OK
+    assert _fr_phase1(**{**t, "shared": torch.empty((0, 7168), dtype=torch.bfloat16)})[0] == INVALID   # empty tensors are refused
+
+
 def test_second_phase_host_checks():
     L = _lib.lib()
     assert L.aclnnGroupedMatmulV4(None, 0, None, None) == NULLPTR

@@ -138,6 +138,54 @@ def test_gmm_activations_and_float16_result(oracle):
     assert np.allclose(want[2], tanh_form, rtol=1e-6, atol=1e-7)
 
 
+def _finalize_inputs(seed, M, K, N, E, counts, topk, shared_rows):
+    rng = np.random.default_rng(seed)
+    x = synth.int8_tensor((M, K), seed, 1)
+    w = synth.int8_tensor((E, K, N), seed, 2)
+    ws = synth.scale_tensor((E, N), seed, 3)
+    xs = synth.scale_tensor((M,), seed, 4)
+    batch = M // topk
+    row_index = rng.permutation(M).astype(np.int64) % batch      # every destination row receives topk rows
+    logit = rng.uniform(0.05, 0.6, size=M).astype(np.float32)
+    shared = rng.uniform(-40, 40, size=(shared_rows, N)).astype(np.float32)
+    bias = rng.uniform(-20, 20, size=(E, N)).astype(np.float32)
+    return x, w, ws, xs, np.asarray(counts, np.int64), row_index, logit, shared, bias, batch
+
+
+def test_finalize_routing_matches_float64_formulation(oracle):
+    M, K, N, E, topk = 96, 80, 64, 4, 4
+    counts = [30, 0, 50, 10]                       # 6 trailing rows belong to no group
+    x, w, ws, xs, gl, ri, logit, shared, bias, batch = _finalize_inputs(7, M, K, N, E, counts, topk, 10)
+    sh_bits, b_bits = oracle.f32_to_bf16_bits(shared), oracle.f32_to_bf16_bits(bias)
+    # scene 1: shared rows, logits, per-token scale, bias; shared rows sit at an offset
+    r = oracle.gmm_finalize_routing(x, w, ws, xs, gl, ri, batch, bias=b_bits, shared_input=sh_bits, shared_offset=5,
+                                    shared_weight=0.5, logit=logit, y_init=np.full((batch, N), 7.0, np.float32))
+    want = oracle.np_gmm_finalize_routing(x, w, ws, xs, gl, ri, batch, bias_f32=oracle.bf16_bits_to_f32(b_bits),
+                                          shared_f32=oracle.bf16_bits_to_f32(sh_bits), shared_offset=5, shared_weight=0.5,
+                                          logit=logit)
+    assert np.all(np.abs(r["y"] - want) <= 4e-7 * r["abs_sum"] + 1e-30)
+    assert np.abs(want).max() > 1.0
+    # rows that receive nothing and lie outside the shared range are zero, not the previous contents
+    touched = np.zeros(batch, bool)
+    touched[ri[:90]] = True
+    touched[5:15] = True
+    assert (r["y"][~touched] == 0).all()
+    # int32 row index, count versus running-total group list, bf16 scale: same numbers
+    r32 = oracle.gmm_finalize_routing(x, w, ws, xs, np.cumsum(gl), ri.astype(np.int32), batch, gl_type=0, bias=b_bits,
+                                      shared_input=sh_bits, shared_offset=5, shared_weight=0.5, logit=logit)
+    assert np.array_equal(r32["y"], r["y"])
+    # scene 2: neither shared input nor logits: plain stores of (acc * scale) * per_token, other rows keep their contents
+    perm = np.random.default_rng(8).permutation(M).astype(np.int64)
+    r2 = oracle.gmm_finalize_routing(x, w, ws, xs, gl, perm, M, y_init=np.full((M, N), 7.0, np.float32))
+    g = oracle.gmm_w8a8(x, w, ws, xs, gl, 1, want_pre=True)["pre"]
+    assert np.array_equal(r2["y"][perm[:90]], g[:90])
+    assert (r2["y"][perm[90:]] == 7.0).all()
+    # out-of-range destinations are skipped
+    bad = ri.copy(); bad[3] = batch + 5; bad[4] = -1
+    rb = oracle.gmm_finalize_routing(x, w, ws, xs, gl, bad, batch, shared_input=sh_bits, logit=logit)
+    assert np.isfinite(rb["y"]).all()
+
+
 def test_gmm_scale_order_is_weight_then_token(oracle):
     # (acc*w_scale)*x_scale and (acc*x_scale)*w_scale differ in the last bit for some inputs; the two operators
     # use opposite orders (grouped_matmul_quant_mixcore.h:262,300 vs grouped_matmul_swiglu_quant.h:392,450).

@@ -419,3 +419,90 @@ def test_swiglu_fractal_nz_n_multiple_of_32_only(oracle):
     # N = 96: N/2 = 48 is not a multiple of 32, the tensor-core path declines and the CUDA-core kernel runs
     x, w, ws, xs = make_inputs(20, 32, 96, 2, seed=57)
     check_swiglu(oracle, x, w, ws, xs, [7, 20], w_nz=True)
+
+
+# ----------------------------------------------------------------------------------------------------------
+# grouped_matmul_finalize_routing (down GEMM + weighted combine)
+# ----------------------------------------------------------------------------------------------------------
+
+def check_finalize(oracle, M, K, N, E, counts, topk, seed, *, shared_rows=0, shared_offset=0, shared_weight=1.0, use_logit=True,
+                   use_bias=False, use_pts=True, idx32=False, scale_bf16=False, api="", flat_layout=None, view_3d=True,
+                   batch=None):
+    """fp32 sums of up to topk + 1 terms in an order that differs from the oracle's: every element must lie within
+    4 ulp-sized steps of the sum of magnitudes (4 * 2^-23 * abs_sum) of the oracle's value."""
+    import ops_transformer_b200 as ops
+    dev = _dev()
+    rng = np.random.default_rng(seed)
+    x, w, ws, xs = make_inputs(M, K, N, E, seed=seed)
+    if batch is None:
+        batch = M // topk
+    scatter = use_logit
+    ri = (rng.permutation(M) % batch).astype(np.int64) if scatter else rng.permutation(M)[:M].astype(np.int64)
+    logit = rng.uniform(0.05, 0.6, size=M).astype(np.float32) if use_logit else None
+    shared = oracle.f32_to_bf16_bits(rng.uniform(-40, 40, size=(shared_rows, N)).astype(np.float32)) if scatter else None
+    bias = oracle.f32_to_bf16_bits(rng.uniform(-20, 20, size=(E, N)).astype(np.float32)) if use_bias else None
+    gl = np.asarray(counts, np.int64)
+    ws_o = oracle.f32_to_bf16_bits(ws) if scale_bf16 else ws
+    y_rows = batch if scatter else M
+    y0 = np.full((y_rows, N), 3.5, np.float32)
+    ref = oracle.gmm_finalize_routing(x, w, ws_o, xs if use_pts else None, gl, ri.astype(np.int32) if idx32 else ri, y_rows, bias=bias,
+                                      shared_input=shared, shared_offset=shared_offset, shared_weight=shared_weight, logit=logit,
+                                      y_init=y0)
+    t = lambda a: None if a is None else torch.from_numpy(a).to(dev)  # noqa: E731
+    bf = lambda a: None if a is None else torch.from_numpy(a.view(np.int16)).to(dev).view(torch.bfloat16)  # noqa: E731
+    ws_t = bf(ws_o) if scale_bf16 else t(ws)
+    out = torch.from_numpy(y0).to(dev)
+    ri_t = t(ri.astype(np.int32)) if idx32 else t(ri)
+    kw = dict(bias=bf(bias), pertoken_scale=t(xs) if use_pts else None, shared_input=bf(shared), logit=t(logit),
+              shared_input_weight=shared_weight, shared_input_offset=shared_offset)
+    if flat_layout is None:
+        y, wsb = ops.grouped_matmul_finalize_routing(t(x), t(nd_to_nz(w)), ws_t, t(gl), ri_t, y_rows, out=out, api=api, view_3d=view_3d,
+                                                     return_workspace=True, **kw)
+        ops.check_status(wsb)
+    else:
+        wt = t(nd_to_nz(w)) if flat_layout == 2 else t(w)
+        y = ops.grouped_matmul_finalize_routing_flat(t(x), wt, flat_layout, ws_t, t(gl), ri_t, out, **kw)
+        torch.cuda.synchronize()
+    got = y.cpu().numpy()
+    tol = 4 * 2.0 ** -23 * ref["abs_sum"] + 1e-30
+    err = np.abs(got.astype(np.float64) - ref["y"].astype(np.float64))
+    assert (err <= tol).all(), f"max excess {float((err - tol).max())}"
+    if not scatter:  # rows nobody wrote keep their contents
+        covered = np.zeros(M, bool)
+        covered[ri[: int(gl.sum())]] = True
+        assert (got[~covered] == 3.5).all()
+
+
+@pytest.mark.parametrize("ctas", ["1", "2"])
+def test_finalize_routing_reference_example_shape(oracle, monkeypatch, ctas):
+    # the reference's example: m=192, k=2048, n=7168, e=4, batch=24 (top-8), 8 shared rows
+    monkeypatch.setenv("GMM_B200_CTAS", ctas)
+    check_finalize(oracle, 192, 2048, 7168, 4, [48, 40, 64, 40], 8, 60, shared_rows=8, shared_offset=4, shared_weight=0.5)
+
+
+@pytest.mark.parametrize("ctas", ["1", "2"])
+def test_finalize_routing_ragged_groups_bias_int32_index(oracle, monkeypatch, ctas):
+    monkeypatch.setenv("GMM_B200_CTAS", ctas)
+    counts = [0, 5, 530, 0, 1, 260]          # 4 trailing rows in no group; tails in both tile sizes
+    check_finalize(oracle, sum(counts) + 4, 144, 288, 6, counts, 4, 61, shared_rows=50, shared_offset=10, use_bias=True, idx32=True,
+                   scale_bf16=True, api="V2")
+
+
+def test_finalize_routing_without_per_token_scale_and_5d_view(oracle):
+    check_finalize(oracle, 256, 256, 512, 3, [100, 56, 100], 2, 62, shared_rows=128, use_pts=False, view_3d=False)
+
+
+def test_finalize_routing_plain_store_scene(oracle):
+    # neither shared input nor logits: rows are stored at row_index, nothing is initialised
+    check_finalize(oracle, 300, 256, 512, 3, [100, 37, 150], 1, 63, use_logit=False)
+    check_finalize(oracle, 300, 256, 512, 3, [100, 37, 150], 1, 64, use_logit=False, use_bias=True, idx32=True)
+
+
+@pytest.mark.parametrize("layout", [0, 2])
+def test_finalize_routing_flat_entry_point(oracle, layout):
+    check_finalize(oracle, 512, 512, 1024, 4, [128, 200, 0, 184], 8, 65, shared_rows=64, flat_layout=layout, use_bias=True)
+
+
+def test_finalize_routing_batch_smaller_than_rows_per_token(oracle):
+    # many rows per destination: 64 destinations for 1024 rows (16 atomics per element)
+    check_finalize(oracle, 1024, 128, 256, 2, [500, 524], 16, 66, shared_rows=64, shared_weight=2.0)
