@@ -379,13 +379,65 @@ def bench_single(args):
     print(json.dumps(line))
 
 
+def bench_init_routing(args):
+    """The producer of c2's inputs: 4096 bf16 tokens x top-8 over 32 experts, hidden 7168, dynamic per-row int8 quantisation
+    (MoeInitRoutingV3).  HBM-bound byte work: every token row is read from DRAM once (its 8 uses hit the L2), every
+    output row written once."""
+    import torch
+
+    import ops_transformer_b200 as ops
+
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    n, k, h, E = 4096, 8, 7168, 32
+    g = torch.Generator(device="cpu").manual_seed(0)
+    x = torch.randn(n, h, generator=g).to(torch.bfloat16).to(dev)
+    idx = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(n)]).to(torch.int32).to(dev)
+    outs = (torch.empty((n * k, h), dtype=torch.int8, device=dev), torch.empty((n * k,), dtype=torch.int32, device=dev),
+            torch.empty((E,), dtype=torch.int64, device=dev), torch.empty((n * k,), dtype=torch.float32, device=dev))
+    alg_bytes = n * h * 2 + n * k * h + n * k * (4 + 4 + 4) + E * 8
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+
+    def step():
+        ops.moe_init_routing_v3(x, idx, expert_num=E, active_expert_range=(0, E), quant_mode=1, outputs=outs)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    sampler = ClockSampler(0)
+    sampler.start()
+    time.sleep(0.3)
+    sampler.mark_begin()
+    for i in range(args.steps):
+        flush.fill_(i & 0xff)
+        ev[i][0].record()
+        step()
+        ev[i][1].record()
+    torch.cuda.synchronize()
+    sampler.mark_end()
+    clocks = sampler.stop()
+    ms = float(np.mean([a.elapsed_time(b) for a, b in ev]))
+    peaks = measured_peaks()
+    gbs = alg_bytes / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "MoeInitRoutingV3 dynamic-quant GB/s", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16->int8", "data": "synthetic",
+        "config": {"workload": f"init_routing: {n} tokens x top-{k}, {E} experts, hidden {h}", "l2": "256 MB flush write between steps"},
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
+                     "traffic": None, "algorithmic_bytes": alg_bytes, "kernel": "routing_quant_kernel (+ count, scan, scatter)",
+                     "peak_basis": f"copy bandwidth, {peaks['source']}"},
+        "gpu_launches": args.steps * 4, "clocks": clocks, "rows_per_s": n * k / (ms * 1e-3)}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=400)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=None, help="c2 (default at N=1), c3, c4_swiglu, c4_down, c3_finalize")
+    ap.add_argument("--workload", default=None, help="c2 (default at N=1), c3, c4_swiglu, c4_down, c3_finalize, init_routing")
     ap.add_argument("--weight-format", default="nd", choices=["nd", "nz"], help="N=1: weight layout [E,K,N] or FRACTAL_NZ")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-ep", action="store_true", help="N=1: skip the one-GPU run of the expert-parallel workload")
@@ -406,6 +458,9 @@ def main():
     if args.gpus > 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1 or args.workload == "c5":
         from ops_transformer_b200 import ep
         ep.bench_main(args)
+        return
+    if args.workload == "init_routing":
+        bench_init_routing(args)
         return
     bench_single(args)
 

@@ -30,6 +30,7 @@ EXPORTED_SYMBOLS = [
     "aclnnGroupedMatmulFinalizeRoutingWeightNzGetWorkspaceSize", "aclnnGroupedMatmulFinalizeRoutingWeightNz",
     "aclnnGroupedMatmulFinalizeRoutingWeightNzV2GetWorkspaceSize", "aclnnGroupedMatmulFinalizeRoutingWeightNzV2",
     "gmmB200GroupedMatmulFinalizeRouting",
+    "aclnnMoeInitRoutingV3GetWorkspaceSize", "aclnnMoeInitRoutingV3",
     "aclnnGroupedMatmulSwigluQuantGetWorkspaceSize", "aclnnGroupedMatmulSwigluQuant",
     "aclnnGroupedMatmulSwigluQuantWeightNZGetWorkspaceSize", "aclnnGroupedMatmulSwigluQuantWeightNZ",
     "gmmB200Version", "gmmB200CheckStatus", "gmmB200SetTimingEvents", "gmmB200SetSmLimit", "gmmB200GroupedMatmulW8A8WorkspaceSize", "gmmB200GroupedMatmulW8A8",
@@ -72,6 +73,8 @@ def _load():
     L.aclnnGroupedMatmulFinalizeRoutingWeightNz.argtypes = [p, u64, p, p]
     L.aclnnGroupedMatmulFinalizeRoutingWeightNzV2GetWorkspaceSize.argtypes = [p] * 12 + [i64, f32, i64, b8, b8, i64, p, p, C.POINTER(u64), C.POINTER(p)]
     L.aclnnGroupedMatmulFinalizeRoutingWeightNzV2.argtypes = [p, u64, p, p]
+    L.aclnnMoeInitRoutingV3GetWorkspaceSize.argtypes = [p] * 4 + [i64] * 5 + [b8, i64, p, i64] + [p] * 4 + [C.POINTER(u64), C.POINTER(p)]
+    L.aclnnMoeInitRoutingV3.argtypes = [p, u64, p, p]
     L.gmmB200GroupedMatmulFinalizeRouting.argtypes = [p, p, i32, p, i32, p, p, p, i64, i32, p, i64, i64, f32, p, p, i32, i64, i64, i64, i64, p, i64, p, u64, p]
     L.aclnnGroupedMatmulSwigluQuantWeightNZGetWorkspaceSize.argtypes = [p] * 10 + [C.POINTER(u64), C.POINTER(p)]
     L.aclnnGroupedMatmulSwigluQuantWeightNZ.argtypes = [p, u64, p, p]

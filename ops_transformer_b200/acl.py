@@ -357,3 +357,52 @@ def grouped_matmul_finalize_routing_flat(x, weight, weight_layout, scale, group_
     if rc != ACLNN_SUCCESS:
         raise AclnnError(rc, "gmmB200GroupedMatmulFinalizeRouting")
     return out
+
+
+def moe_init_routing_v3(x: torch.Tensor, expert_idx: torch.Tensor, *, expert_num: int, active_expert_range: Sequence[int],
+                        quant_mode: int = 1, scale: Optional[torch.Tensor] = None, offset: Optional[torch.Tensor] = None,
+                        active_num: Optional[int] = None, expert_capacity: int = 0, drop_pad_mode: int = 0,
+                        expert_tokens_num_type: int = 1, expert_tokens_num_flag: bool = True, row_idx_type: int = 1,
+                        outputs=None, stream=None, workspace: Optional[torch.Tensor] = None):
+    """aclnnMoeInitRoutingV3 (moe/moe_init_routing_v3/op_host/op_api/aclnn_moe_init_routing_v3.h:24-47 of the reference):
+    returns (expandedX, expandedRowIdx, expertTokensCountOrCumsum, expandedScale).  With ``quant_mode`` 1 expandedX is int8
+    and expandedScale the per-row scale, i.e. the x / per-token scale of the grouped GEMM operators."""
+    L = _lib.lib()
+    n, h = x.shape
+    k = expert_idx.shape[1]
+    start, end = active_expert_range
+    if outputs is None:
+        ex = torch.empty((n * k, h), dtype=torch.int8 if quant_mode == 1 else x.dtype, device=x.device)
+        ri = torch.empty((n * k,), dtype=torch.int32, device=x.device)
+        cnt = torch.empty((end - start,) if expert_tokens_num_type == 1 else (expert_num, 2), dtype=torch.int64, device=x.device)
+        es = torch.empty((n * k,), dtype=torch.float32, device=x.device)
+    else:
+        ex, ri, cnt, es = outputs
+    handles = []
+    rng = L.aclCreateIntArray(_i64(list(active_expert_range)), len(active_expert_range))
+    try:
+        def mk(t):
+            if t is None:
+                return None
+            hh = create_tensor(t)
+            handles.append(hh)
+            return hh
+        hx, hi, hs, ho, hex_, hri, hc, hes = (mk(t) for t in (x, expert_idx, scale, offset, ex, ri, cnt, es))
+        ws_size = C.c_uint64(0)
+        exr = C.c_void_p(0)
+        rc = L.aclnnMoeInitRoutingV3GetWorkspaceSize(hx, hi, hs, ho, n * k if active_num is None else active_num, expert_capacity,
+                                                     expert_num, drop_pad_mode, expert_tokens_num_type, expert_tokens_num_flag,
+                                                     quant_mode, rng, row_idx_type, hex_, hri, hc, hes, C.byref(ws_size), C.byref(exr))
+        if rc != ACLNN_SUCCESS:
+            raise AclnnError(rc, "aclnnMoeInitRoutingV3GetWorkspaceSize")
+        if workspace is None:
+            workspace = _WS.get(x.device, ws_size.value)
+        wptr = C.c_void_p(workspace.data_ptr()) if workspace is not None else None
+        rc = L.aclnnMoeInitRoutingV3(wptr, ws_size.value, exr, C.c_void_p(_stream_handle(stream)))
+        if rc != ACLNN_SUCCESS:
+            raise AclnnError(rc, "aclnnMoeInitRoutingV3")
+    finally:
+        for hh in handles:
+            L.aclDestroyTensor(hh)
+        L.aclDestroyIntArray(rng)
+    return ex, ri, cnt, es

@@ -46,12 +46,13 @@ struct aclIntArray {
 };
 
 struct aclOpExecutor {
-    enum Kind { kNoop = 0, kGmm = 1 } kind = kNoop;
+    enum Kind { kNoop = 0, kGmm = 1, kInitRouting = 2 } kind = kNoop;
     uint32_t magic = 0xac10e8ecu;
     bool consumed = false;
     const char *op_name = "";
     gmm::Problem problem;
     gmm::Plan plan;
+    gmm::InitRoutingProblem routing;
 };
 
 namespace gmm {

@@ -69,6 +69,25 @@ struct Plan {
     alignas(64) CUtensorMap map_w;
 };
 
+// MoeInitRoutingV3 (moe_init_routing.cu): rows of x grouped by expert, optionally quantised per row.
+struct InitRoutingProblem {
+    const void *x = nullptr;            // [n, h] f32 / f16 / bf16 (int8 only without quantisation)
+    int x_dtype = kBF16;
+    const int *expert_idx = nullptr;    // [n, k] int32
+    const float *scale = nullptr;       // quant: [expert_end - expert_start, h] smooth scale; else [n]; optional
+    int64_t n = 0, k = 0, h = 0;
+    int64_t expert_num = 0, expert_start = 0, expert_end = 0;
+    int quant = 0;                      // 1: dynamic per-row int8 quantisation, 0: rows copied as they are
+    int row_idx_type = 0;               // 0: expanded_row_idx[pair] = output row (-1 if filtered out), 1: [output row] = pair
+    int count_type = 1;                 // 1: counts per active expert, 2: (expert, count) pairs of the non-empty ones
+    void *expanded_x = nullptr;         // [n*k, h]
+    int *expanded_row_idx = nullptr;    // [n*k]
+    long long *counts_out = nullptr;    // [range] or [expert_num, 2]
+    float *expanded_scale = nullptr;    // [n*k]
+};
+size_t init_routing_workspace_bytes(const InitRoutingProblem &r);
+cudaError_t init_routing_launch(const InitRoutingProblem &r, void *workspace, size_t workspace_bytes, cudaStream_t stream);
+
 // Host only: choose the kernel path and the workspace layout.  Never touches the device.
 void make_plan(const Problem &p, Plan *plan);
 // Enqueue the operator on `stream`.  Returns cudaSuccess or the first CUDA error.

@@ -1,0 +1,304 @@
+// MoeInitRoutingV3 on the GPU: the producer of the grouped GEMM path's inputs.  From token rows x [n, h] and the top-k
+// expert ids [n, k] it writes the rows grouped by expert (stable in pair order), optionally quantised per row to int8
+// with a dynamic scale, the row map and the per-expert counts - exactly the x / per-token scale / group list that
+// grouped_matmul_swiglu_quant and grouped_matmul consume.
+//
+// Follows moe/moe_init_routing_v3/op_kernel of the reference: the key-value sort of (expert id, pair index)
+// (moe_v3_sort_*.h; equal keys keep their pair order), ExpertTokensCount (moe_v3_expert_tokens_count.h:246-282),
+// RowIdxGather (moe_v3_row_idx_gather.h:141-156), MoeGatherOut (moe_v3_gather_out.h:197-233) and
+// MoeGatherOutDynamicQuant::Compute (moe_v3_gather_dynamic_quant.h:103-143).
+//
+// Four launches, no host read in between:
+//   count   - one histogram of the active experts per block of 1024 pairs
+//   scan    - per expert: exclusive prefix over the blocks; over experts: start of every expert's rows, the counts output
+//   scatter - every pair finds its place: expert start + earlier blocks + earlier pairs of its block (warps take turns,
+//             __match_any_sync orders the lanes), which keeps the order of equal keys
+//   gather  - one CTA per output row: read the token row, (quantise,) store
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "gmm_common.h"
+
+namespace gmm {
+namespace {
+
+constexpr int kPairsPerBlock = 1024;
+
+struct RoutingParams {
+    const void *x;
+    int x_dtype;               // kF32 / kF16 / kBF16 / kI8
+    const int *expert_idx;     // [n, k]
+    const float *scale;        // quant: smooth scale [range, h]; no quant: per-token scale [n]; may be null
+    long long pairs;           // n * k
+    int k, h;
+    int e_start, range, expert_num;
+    int quant, row_idx_type, count_type, vec_ok;
+    void *expanded_x;
+    int *expanded_row_idx;
+    long long *counts_out;
+    float *expanded_scale;
+    int *block_hist;           // [nb, range]: counts, then exclusive offsets over the blocks
+    int *expert_first;         // [range]: first output row of every active expert
+    int *sorted_row;           // [pairs]: pair index of every output row
+    int *total;                // number of output rows
+    int nb;
+};
+
+__global__ void __launch_bounds__(kPairsPerBlock) routing_count_kernel(const RoutingParams p)
+{
+    extern __shared__ int hist[];
+    for (int e = threadIdx.x; e < p.range; e += blockDim.x) hist[e] = 0;
+    __syncthreads();
+    const long long j = (long long)blockIdx.x * kPairsPerBlock + threadIdx.x;
+    if (j < p.pairs) {
+        const int e = __ldg(p.expert_idx + j) - p.e_start;
+        if (e >= 0 && e < p.range) atomicAdd(&hist[e], 1);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < p.range; e += blockDim.x) p.block_hist[(size_t)blockIdx.x * p.range + e] = hist[e];
+}
+
+// Inclusive scan of one int per thread over a 1024-thread block; returns the inclusive value, *block_sum the total.
+__device__ int block_scan_1024(int v, int *warp_sums, int *block_sum)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += t;
+    }
+    if (lane == 31) warp_sums[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        int s = warp_sums[lane];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, s, o);
+            if (lane >= o) s += t;
+        }
+        warp_sums[lane] = s;
+    }
+    __syncthreads();
+    if (warp > 0) v += warp_sums[warp - 1];
+    *block_sum = warp_sums[31];
+    __syncthreads();
+    return v;
+}
+
+__global__ void __launch_bounds__(1024) routing_scan_kernel(const RoutingParams p)
+{
+    __shared__ int warp_sums[32];
+    // per expert: exclusive prefix over the blocks, total into expert_first (as a count for now)
+    for (int e = threadIdx.x; e < p.range; e += blockDim.x) {
+        int run = 0;
+        for (int b = 0; b < p.nb; ++b) {
+            const size_t i = (size_t)b * p.range + e;
+            const int t = p.block_hist[i];
+            p.block_hist[i] = run;
+            run += t;
+        }
+        p.expert_first[e] = run;
+    }
+    __syncthreads();
+    // over the experts, 1024 at a time: first row of every expert, the counts output (count or key-value form)
+    int row_carry = 0, nz_carry = 0;
+    const int written_pairs = min(p.range + 1, p.expert_num);  // key-value form: entries the operator writes
+    for (int base = 0; base < p.range; base += 1024) {
+        const int e = base + threadIdx.x;
+        const int c = e < p.range ? p.expert_first[e] : 0;
+        int sum_c, sum_nz;
+        const int inc_c = block_scan_1024(c, warp_sums, &sum_c);
+        const int inc_nz = block_scan_1024(c != 0 ? 1 : 0, warp_sums, &sum_nz);
+        if (e < p.range) {
+            p.expert_first[e] = row_carry + inc_c - c;
+            if (p.count_type == 1) {
+                p.counts_out[e] = c;
+            } else if (c != 0) {
+                const int slot = nz_carry + inc_nz - 1;
+                p.counts_out[2 * (size_t)slot] = e + p.e_start;
+                p.counts_out[2 * (size_t)slot + 1] = c;
+            }
+        }
+        row_carry += sum_c;
+        nz_carry += sum_nz;
+    }
+    if (p.count_type == 2)  // the compact list ends in zero entries (moe_v3_expert_tokens_count.h:126-128, 255-257)
+        for (int i = nz_carry + threadIdx.x; i < written_pairs; i += blockDim.x) {
+            p.counts_out[2 * (size_t)i] = 0;
+            p.counts_out[2 * (size_t)i + 1] = 0;
+        }
+    if (threadIdx.x == 0) *p.total = row_carry;
+}
+
+__global__ void __launch_bounds__(kPairsPerBlock) routing_scatter_kernel(const RoutingParams p)
+{
+    extern __shared__ int running[];
+    for (int e = threadIdx.x; e < p.range; e += blockDim.x) running[e] = 0;
+    const long long j = (long long)blockIdx.x * kPairsPerBlock + threadIdx.x;
+    int e = -1;
+    if (j < p.pairs) {
+        e = __ldg(p.expert_idx + j) - p.e_start;
+        if (e < 0 || e >= p.range) e = -1;
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int before = 0;  // pairs of this block with the same expert that come earlier
+    __syncthreads();
+    for (int w = 0; w < kPairsPerBlock / 32; ++w) {
+        if (warp == w) {
+            const unsigned peers = __match_any_sync(0xffffffffu, e);
+            const int rank = __popc(peers & ((1u << lane) - 1u));
+            int base = 0;
+            if (e >= 0 && rank == 0) {
+                base = running[e];
+                running[e] = base + __popc(peers);
+            }
+            base = __shfl_sync(0xffffffffu, base, __ffs(peers) - 1);
+            before = base + rank;
+        }
+        __syncthreads();
+    }
+    if (j >= p.pairs) return;
+    if (e < 0) {
+        if (p.row_idx_type == 0) p.expanded_row_idx[j] = -1;
+        return;
+    }
+    const int pos = p.expert_first[e] + p.block_hist[(size_t)blockIdx.x * p.range + e] + before;
+    p.sorted_row[pos] = (int)j;
+    if (p.row_idx_type == 1) p.expanded_row_idx[pos] = (int)j;
+    else p.expanded_row_idx[j] = pos;
+}
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+// fp32 -> fp16 towards zero, fp16 -> int8 to nearest with ties away from zero (CAST_TRUNC then CAST_ROUND,
+// moe_v3_gather_dynamic_quant.h:134-137).  0 / 0 (an all-zero row) maps to 0.
+__device__ __forceinline__ int8_t quant_trunc_round(float v, float scale)
+{
+    const float f = __half2float(__float2half_rz(__fdiv_rn(v, scale)));
+    if (!(f == f)) return 0;
+    const int q = (int)(f + (f < 0.0f ? -0.5f : 0.5f));
+    return (int8_t)max(-128, min(127, q));
+}
+
+// One CTA per output row.  Dynamic quantisation: v = float(x) [* smooth[expert]], scale = max|v| / 127, q = v / scale.
+template <typename T>
+__global__ void __launch_bounds__(128) routing_quant_kernel(const RoutingParams p)
+{
+    __shared__ float red[4];
+    const int pos = blockIdx.x;
+    if (pos >= *p.total) return;
+    const int j = p.sorted_row[pos];
+    const T *row = reinterpret_cast<const T *>(p.x) + (size_t)(j / p.k) * p.h;
+    const float *smooth = p.scale ? p.scale + (size_t)(__ldg(p.expert_idx + j) - p.e_start) * p.h : nullptr;
+    float amax = 0.0f;
+    for (int c = threadIdx.x; c < p.h; c += blockDim.x) {
+        float v = to_f32(row[c]);
+        if (smooth) v = __fmul_rn(v, __ldg(smooth + c));
+        amax = fmaxf(amax, fabsf(v));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    const float scale = __fdiv_rn(amax, 127.0f);
+    if (threadIdx.x == 0) p.expanded_scale[pos] = scale;
+    int8_t *out = reinterpret_cast<int8_t *>(p.expanded_x) + (size_t)pos * p.h;
+    if (p.vec_ok) {  // four outputs per store; the second read of the row comes from L1 / L2
+        for (int c = threadIdx.x * 4; c < p.h; c += blockDim.x * 4) {
+            char4 q;
+            float v0 = to_f32(row[c]), v1 = to_f32(row[c + 1]), v2 = to_f32(row[c + 2]), v3 = to_f32(row[c + 3]);
+            if (smooth) {
+                const float4 s = __ldg(reinterpret_cast<const float4 *>(smooth + c));
+                v0 = __fmul_rn(v0, s.x); v1 = __fmul_rn(v1, s.y); v2 = __fmul_rn(v2, s.z); v3 = __fmul_rn(v3, s.w);
+            }
+            q.x = quant_trunc_round(v0, scale); q.y = quant_trunc_round(v1, scale);
+            q.z = quant_trunc_round(v2, scale); q.w = quant_trunc_round(v3, scale);
+            *reinterpret_cast<char4 *>(out + c) = q;
+        }
+    } else {
+        for (int c = threadIdx.x; c < p.h; c += blockDim.x) {
+            float v = to_f32(row[c]);
+            if (smooth) v = __fmul_rn(v, __ldg(smooth + c));
+            out[c] = quant_trunc_round(v, scale);
+        }
+    }
+}
+
+// One CTA per output row: plain copy of the token row (any element size), and of the token's scale if one is given.
+__global__ void __launch_bounds__(128) routing_copy_kernel(const RoutingParams p, int elem_bytes)
+{
+    const int pos = blockIdx.x;
+    if (pos >= *p.total) return;
+    const int j = p.sorted_row[pos];
+    const size_t row_bytes = (size_t)p.h * elem_bytes;
+    const char *src = reinterpret_cast<const char *>(p.x) + (size_t)(j / p.k) * row_bytes;
+    char *dst = reinterpret_cast<char *>(p.expanded_x) + (size_t)pos * row_bytes;
+    if ((row_bytes & 15) == 0 && ((reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.expanded_x)) & 15) == 0) {
+        for (size_t c = threadIdx.x * 16; c < row_bytes; c += blockDim.x * 16)
+            *reinterpret_cast<uint4 *>(dst + c) = __ldg(reinterpret_cast<const uint4 *>(src + c));
+    } else {
+        for (size_t c = threadIdx.x; c < row_bytes; c += blockDim.x) dst[c] = src[c];
+    }
+    if (p.scale && p.expanded_scale && threadIdx.x == 0) p.expanded_scale[pos] = __ldg(p.scale + j / p.k);
+}
+
+size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+
+}  // namespace
+
+size_t init_routing_workspace_bytes(const InitRoutingProblem &r)
+{
+    const long long pairs = r.n * r.k;
+    const long long nb = (pairs + kPairsPerBlock - 1) / kPairsPerBlock;
+    const long long range = r.expert_end - r.expert_start;
+    return 256 + align256((size_t)nb * range * 4) + align256((size_t)range * 4) + align256((size_t)pairs * 4);
+}
+
+cudaError_t init_routing_launch(const InitRoutingProblem &r, void *workspace, size_t workspace_bytes, cudaStream_t stream)
+{
+    const long long pairs = r.n * r.k;
+    if (pairs <= 0) return cudaSuccess;
+    if (workspace_bytes < init_routing_workspace_bytes(r) || !workspace) return cudaErrorInvalidValue;
+    const long long nb = (pairs + kPairsPerBlock - 1) / kPairsPerBlock;
+    const int range = (int)(r.expert_end - r.expert_start);
+    if (pairs > 0x7fffffffll || nb > 0x7fffffffll || range <= 0 || (size_t)range * 4 > 48 * 1024) return cudaErrorInvalidValue;
+    uint8_t *ws = static_cast<uint8_t *>(workspace);
+    RoutingParams p;
+    p.x = r.x; p.x_dtype = r.x_dtype; p.expert_idx = r.expert_idx; p.scale = r.scale;
+    p.pairs = pairs; p.k = (int)r.k; p.h = (int)r.h;
+    p.e_start = (int)r.expert_start; p.range = range; p.expert_num = (int)r.expert_num;
+    p.quant = r.quant; p.row_idx_type = r.row_idx_type; p.count_type = r.count_type;
+    p.vec_ok = (r.h % 4 == 0) && ((reinterpret_cast<uintptr_t>(r.scale) | reinterpret_cast<uintptr_t>(r.expanded_x)) & 15) == 0;
+    p.expanded_x = r.expanded_x; p.expanded_row_idx = r.expanded_row_idx; p.counts_out = r.counts_out;
+    p.expanded_scale = r.expanded_scale;
+    p.total = reinterpret_cast<int *>(ws);
+    size_t off = 256;
+    p.block_hist = reinterpret_cast<int *>(ws + off); off += align256((size_t)nb * range * 4);
+    p.expert_first = reinterpret_cast<int *>(ws + off); off += align256((size_t)range * 4);
+    p.sorted_row = reinterpret_cast<int *>(ws + off);
+    p.nb = (int)nb;
+    const size_t smem = (size_t)range * 4;
+    routing_count_kernel<<<(unsigned)nb, kPairsPerBlock, smem, stream>>>(p);
+    routing_scan_kernel<<<1, 1024, 0, stream>>>(p);
+    routing_scatter_kernel<<<(unsigned)nb, kPairsPerBlock, smem, stream>>>(p);
+    if (r.quant) {
+        if (r.x_dtype == kF32) routing_quant_kernel<float><<<(unsigned)pairs, 128, 0, stream>>>(p);
+        else if (r.x_dtype == kF16) routing_quant_kernel<__half><<<(unsigned)pairs, 128, 0, stream>>>(p);
+        else if (r.x_dtype == kBF16) routing_quant_kernel<__nv_bfloat16><<<(unsigned)pairs, 128, 0, stream>>>(p);
+        else return cudaErrorInvalidValue;
+    } else {
+        const int eb = r.x_dtype == kF32 ? 4 : (r.x_dtype == kI8 ? 1 : 2);
+        routing_copy_kernel<<<(unsigned)pairs, 128, 0, stream>>>(p, eb);
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace gmm

@@ -19,6 +19,7 @@
 #include "aclnnop/aclnn_grouped_matmul_v4.h"
 #include "aclnnop/aclnn_grouped_matmul_v5.h"
 #include "aclnnop/aclnn_grouped_matmul_weight_nz.h"
+#include "aclnnop/aclnn_moe_init_routing_v3.h"
 #include "gmm_b200.h"
 
 namespace gmm {
@@ -65,7 +66,7 @@ aclOpExecutor *new_executor(const char *name)
 
 aclnnStatus finish_phase1(aclOpExecutor *e, uint64_t *workspaceSize, aclOpExecutor **executor)
 {
-    *workspaceSize = e->kind == aclOpExecutor::kNoop ? 0 : e->plan.ws_bytes;
+    *workspaceSize = e->kind == aclOpExecutor::kNoop ? 0 : e->plan.ws_bytes;   // kInitRouting stores its size in plan.ws_bytes too
     register_executor(e);
     *executor = e;
     return ACLNN_SUCCESS;
@@ -83,14 +84,16 @@ aclnnStatus run_executor(const char *op_name, void *workspace, uint64_t workspac
     aclnnStatus rc = ACLNN_SUCCESS;
     if (std::strcmp(executor->op_name, op_name) != 0) {
         rc = fail(ACLNN_ERR_PARAM_INVALID, "%s: executor was built by %s.", op_name, executor->op_name);
-    } else if (executor->kind == aclOpExecutor::kGmm) {
+    } else if (executor->kind != aclOpExecutor::kNoop) {
         if (workspace_size < executor->plan.ws_bytes) {
             rc = fail(ACLNN_ERR_PARAM_INVALID, "%s: workspaceSize %llu is smaller than the %llu bytes required.", op_name,
                       (unsigned long long)workspace_size, (unsigned long long)executor->plan.ws_bytes);
         } else if (executor->plan.ws_bytes && !workspace) {
             rc = fail(ACLNN_ERR_PARAM_NULLPTR, "%s: workspace must not be nullptr.", op_name);
         } else {
-            cudaError_t ce = launch(executor->problem, executor->plan, workspace, workspace_size, static_cast<cudaStream_t>(stream));
+            cudaError_t ce = executor->kind == aclOpExecutor::kInitRouting
+                                 ? init_routing_launch(executor->routing, workspace, workspace_size, static_cast<cudaStream_t>(stream))
+                                 : launch(executor->problem, executor->plan, workspace, workspace_size, static_cast<cudaStream_t>(stream));
             if (ce != cudaSuccess)
                 rc = fail(ACLNN_ERR_INNER, "%s: kernel launch failed: %s", op_name, cudaGetErrorString(ce));
         }
@@ -364,6 +367,113 @@ aclnnStatus aclnnGroupedMatmulWeightNzGetWorkspaceSize(
 aclnnStatus aclnnGroupedMatmulWeightNz(void *workspace, uint64_t workspaceSize, aclOpExecutor *executor, aclrtStream stream)
 {
     return run_executor("aclnnGroupedMatmulWeightNz", workspace, workspaceSize, executor, stream);
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// MoeInitRoutingV3
+// ------------------------------------------------------------------------------------------------------------
+
+// Checks of CheckParams (moe/moe_init_routing_v3/op_host/op_api/aclnn_moe_init_routing_v3.cpp:52-181) in their order, then the
+// attribute rules the reference enforces in its tiling (README.md "constraints"): dropPadMode 0, expertTokensNumType 1 or 2,
+// expertTokensNumFlag true, quantMode 1 or -1, rowIdxType 0 or 1, activeNum = n*k (or 0), 0 <= start < end <= expertNum.
+aclnnStatus aclnnMoeInitRoutingV3GetWorkspaceSize(const aclTensor *x, const aclTensor *expertIdx, const aclTensor *scaleOptional,
+                                                  const aclTensor *offsetOptional, int64_t activeNum, int64_t expertCapacity,
+                                                  int64_t expertNum, int64_t dropPadMode, int64_t expertTokensNumType,
+                                                  bool expertTokensNumFlag, int64_t quantMode,
+                                                  const aclIntArray *activeExpertRangeOptional, int64_t rowIdxType,
+                                                  const aclTensor *expandedXOut, const aclTensor *expandedRowIdxOut,
+                                                  const aclTensor *expertTokensCountOrCumsumOut, const aclTensor *expandedScaleOut,
+                                                  uint64_t *workspaceSize, aclOpExecutor **executor)
+{
+    static const char *kOp = "aclnnMoeInitRoutingV3";
+    clear_error();
+    GMM_REQUIRE(workspaceSize != nullptr, ACLNN_ERR_PARAM_NULLPTR, "workspaceSize must not be nullptr.");
+    GMM_REQUIRE(executor != nullptr, ACLNN_ERR_PARAM_NULLPTR, "executor must not be nullptr.");
+    GMM_REQUIRE(x && expertIdx && expandedXOut && expandedRowIdxOut && expertTokensCountOrCumsumOut && expandedScaleOut,
+                ACLNN_ERR_PARAM_NULLPTR, "x, expertIdx and the four outputs must not be nullptr.");
+    GMM_REQUIRE(x->dtype == ACL_FLOAT16 || x->dtype == ACL_BF16 || x->dtype == ACL_FLOAT || x->dtype == ACL_INT8, ACLNN_ERR_PARAM_INVALID,
+                "x dtype must be float16, bfloat16, float32 or int8.");
+    GMM_REQUIRE(expertIdx->dtype == ACL_INT32, ACLNN_ERR_PARAM_INVALID, "expertIdx dtype must be int32.");
+    GMM_REQUIRE(!scaleOptional || scaleOptional->dtype == ACL_FLOAT, ACLNN_ERR_PARAM_INVALID, "scale dtype must be float32.");
+    GMM_REQUIRE(!offsetOptional || offsetOptional->dtype == ACL_FLOAT, ACLNN_ERR_PARAM_INVALID, "offset dtype must be float32.");
+    GMM_REQUIRE(expandedXOut->dtype == ACL_FLOAT16 || expandedXOut->dtype == ACL_BF16 || expandedXOut->dtype == ACL_FLOAT ||
+                    expandedXOut->dtype == ACL_INT8, ACLNN_ERR_PARAM_INVALID, "expandedXOut dtype must be float16, bfloat16, float32 or int8.");
+    GMM_REQUIRE(expandedRowIdxOut->dtype == ACL_INT32, ACLNN_ERR_PARAM_INVALID, "expandedRowIdxOut dtype must be int32.");
+    GMM_REQUIRE(expertTokensCountOrCumsumOut->dtype == ACL_INT64, ACLNN_ERR_PARAM_INVALID, "expertTokensCountOrCumsumOut dtype must be int64.");
+    GMM_REQUIRE(expandedScaleOut->dtype == ACL_FLOAT, ACLNN_ERR_PARAM_INVALID, "expandedScaleOut dtype must be float32.");
+    // the reference dereferences the range without a test (:100); a missing range is refused here
+    GMM_REQUIRE(activeExpertRangeOptional && activeExpertRangeOptional->values.size() == 2, ACLNN_ERR_PARAM_INVALID,
+                "activeExpertRange must hold [expertStart, expertEnd].");
+    const int64_t eStart = activeExpertRangeOptional->values[0], eEnd = activeExpertRangeOptional->values[1];
+    const int64_t range = eEnd - eStart;
+    GMM_REQUIRE(x->rank() == 2 && expertIdx->rank() == 2, ACLNN_ERR_PARAM_INVALID, "x and expertIdx must have 2 dimensions.");
+    const int64_t n = x->dim(0), h = x->dim(1), k = expertIdx->dim(1);
+    GMM_REQUIRE(expertIdx->dim(0) == n, ACLNN_ERR_PARAM_INVALID, "expertIdx shape error");
+    if (scaleOptional && quantMode != 0) {
+        if (quantMode == -1)
+            GMM_REQUIRE(scaleOptional->rank() == 1 && scaleOptional->dim(0) == n, ACLNN_ERR_PARAM_INVALID, "scale shape error");
+        else if (quantMode == 1)
+            GMM_REQUIRE(scaleOptional->rank() == 2 && scaleOptional->dim(0) == range && scaleOptional->dim(1) == h, ACLNN_ERR_PARAM_INVALID,
+                        "scale shape error");
+        GMM_REQUIRE(expandedScaleOut->rank() == 1 && expandedScaleOut->dim(0) == n * k, ACLNN_ERR_PARAM_INVALID, "expandedScaleOut shape error");
+    }
+    GMM_REQUIRE(expandedXOut->rank() == 2 && expandedXOut->dim(0) == n * k && expandedXOut->dim(1) == h, ACLNN_ERR_PARAM_INVALID,
+                "expandedXOut shape error");
+    GMM_REQUIRE(expandedRowIdxOut->rank() == 1 && expandedRowIdxOut->dim(0) == n * k, ACLNN_ERR_PARAM_INVALID, "expandedRowIdxOut shape error");
+    if (expertTokensNumType == 1)
+        GMM_REQUIRE(expertTokensCountOrCumsumOut->rank() == 1 && expertTokensCountOrCumsumOut->dim(0) == range, ACLNN_ERR_PARAM_INVALID,
+                    "expertTokensCountOrCumsumOut shape error");
+    else if (expertTokensNumType == 2)
+        GMM_REQUIRE(expertTokensCountOrCumsumOut->rank() == 2 && expertTokensCountOrCumsumOut->dim(0) == expertNum &&
+                        expertTokensCountOrCumsumOut->dim(1) == 2, ACLNN_ERR_PARAM_INVALID, "expertTokensCountOrCumsumOut shape error");
+    // attributes
+    GMM_REQUIRE(dropPadMode == 0, ACLNN_ERR_PARAM_INVALID, "dropPadMode only supports 0 (dropless).");
+    GMM_REQUIRE(expertTokensNumType == 1 || expertTokensNumType == 2, ACLNN_ERR_PARAM_INVALID, "expertTokensNumType only supports 1 (count) and 2 (key_value).");
+    GMM_REQUIRE(expertTokensNumFlag, ACLNN_ERR_PARAM_INVALID, "expertTokensNumFlag only supports true.");
+    GMM_REQUIRE(quantMode == 1 || quantMode == -1, ACLNN_ERR_PARAM_INVALID, "quantMode only supports 1 (dynamic quant) and -1 (no quant).");
+    GMM_REQUIRE(rowIdxType == 0 || rowIdxType == 1, ACLNN_ERR_PARAM_INVALID, "rowIdxType only supports 0 (gather) and 1 (scatter).");
+    GMM_REQUIRE(expertCapacity >= 0, ACLNN_ERR_PARAM_INVALID, "expertCapacity must not be negative.");
+    GMM_REQUIRE(activeNum == 0 || activeNum == n * k, ACLNN_ERR_PARAM_INVALID, "activeNum must equal NUM_ROWS * K.");
+    GMM_REQUIRE(expertNum > 0 && expertNum <= (expertTokensNumType == 2 ? 5120 : 10240), ACLNN_ERR_PARAM_INVALID, "expertNum out of range.");
+    GMM_REQUIRE(eStart >= 0 && eStart < eEnd && eEnd <= expertNum, ACLNN_ERR_PARAM_INVALID, "activeExpertRange must satisfy 0 <= start < end <= expertNum.");
+    GMM_REQUIRE(n * k <= 0x7fffffffll && h <= 0x7fffffffll, ACLNN_ERR_PARAM_INVALID, "too many rows.");
+    if (quantMode == 1) {
+        GMM_REQUIRE(x->dtype != ACL_INT8, ACLNN_ERR_PARAM_INVALID, "dynamic quant needs a floating-point x.");
+        GMM_REQUIRE(expandedXOut->dtype == ACL_INT8, ACLNN_ERR_PARAM_INVALID, "dynamic quant writes an int8 expandedXOut.");
+    } else {
+        GMM_REQUIRE(expandedXOut->dtype == x->dtype, ACLNN_ERR_PARAM_INVALID, "without quantisation expandedXOut has x's dtype.");
+    }
+    aclOpExecutor *e = new_executor(kOp);
+    GMM_REQUIRE(e != nullptr, ACLNN_ERR_INNER_CREATE_EXECUTOR, "cannot create executor.");
+    if (n * k == 0 || h == 0) return finish_phase1(e, workspaceSize, executor);
+    for (const aclTensor *t : {x, expertIdx, scaleOptional, expandedXOut, expandedRowIdxOut, expertTokensCountOrCumsumOut, expandedScaleOut}) {
+        if (t && !t->contiguous()) {
+            delete e;
+            return fail(ACLNN_ERR_PARAM_INVALID, "this build needs contiguous tensors.");
+        }
+    }
+    InitRoutingProblem &r = e->routing;
+    r.x = tensor_ptr(x);
+    r.x_dtype = (int)x->dtype;
+    r.expert_idx = static_cast<const int *>(tensor_ptr(expertIdx));
+    r.scale = scaleOptional ? static_cast<const float *>(tensor_ptr(scaleOptional)) : nullptr;
+    r.n = n; r.k = k; r.h = h;
+    r.expert_num = expertNum; r.expert_start = eStart; r.expert_end = eEnd;
+    r.quant = quantMode == 1;
+    r.row_idx_type = (int)rowIdxType;
+    r.count_type = (int)expertTokensNumType;
+    r.expanded_x = tensor_ptr(expandedXOut);
+    r.expanded_row_idx = static_cast<int *>(tensor_ptr(expandedRowIdxOut));
+    r.counts_out = static_cast<long long *>(tensor_ptr(expertTokensCountOrCumsumOut));
+    r.expanded_scale = static_cast<float *>(tensor_ptr(expandedScaleOut));
+    e->kind = aclOpExecutor::kInitRouting;
+    e->plan.ws_bytes = init_routing_workspace_bytes(r);
+    return finish_phase1(e, workspaceSize, executor);
+}
+
+aclnnStatus aclnnMoeInitRoutingV3(void *workspace, uint64_t workspaceSize, aclOpExecutor *executor, aclrtStream stream)
+{
+    return run_executor("aclnnMoeInitRoutingV3", workspace, workspaceSize, executor, stream);
 }
 
 // ------------------------------------------------------------------------------------------------------------

@@ -397,6 +397,98 @@ ORACLE_API int oracle_gmm_finalize_routing(const int8_t *x, const int8_t *w, con
 }
 
 /* ------------------------------------------------------------------------------------------- */
+/* moe_init_routing_v3 (the producer of the path's inputs)                                      */
+/* ------------------------------------------------------------------------------------------- */
+
+/* fp32 -> fp16 towards zero (CAST_TRUNC). */
+static inline uint16_t f32_to_f16_rz(float f)
+{
+    uint16_t h = f32_to_f16_rne(f);
+    if ((h & 0x7fffu) > 0x7c00u) return h;                        /* NaN */
+    const float back = f16_to_f32(h);
+    if (fabsf(back) > fabsf(f)) h = (uint16_t)(h - 1);            /* rounded away from zero: step one value back */
+    return h;
+}
+
+/* Restatement of moe/moe_init_routing_v3/op_kernel:
+ *   pair j = token * k + slot; pairs with start <= expert < end are sorted by expert, equal experts by j (key-value sort of
+ *   moe_v3_sort_*.h); ExpertTokensCount (moe_v3_expert_tokens_count.h:246-282) gives the counts;
+ *   row_idx_type 1: expanded_row_idx[i] = j; 0: expanded_row_idx[j] = i, -1 for filtered pairs (moe_v3_row_idx_gather.h:141-156).
+ *   quant = 1 (MoeGatherOutDynamicQuant::Compute, moe_v3_gather_dynamic_quant.h:103-143):
+ *     v = float(x) [* smooth[expert - start]]; s = max|v| / 127; q = int8(round_half_away(fp16_towards_zero(v / s)))
+ *   quant = 0 (MoeGatherOut, moe_v3_gather_out.h:197-233): row copied, expanded_scale[i] = scale[token] if given.
+ * x_dtype: DT_F32 / DT_F16 / DT_BF16 (16-bit types as bit patterns); int8 rows (x_dtype 2) only with quant = 0.
+ * Returns the number of output rows. */
+ORACLE_API int64_t oracle_moe_init_routing_v3(const void *x, int x_dtype, const int32_t *expert_idx, const float *scale, int64_t n,
+                                              int64_t k, int64_t h, int64_t expert_num, int64_t start, int64_t end, int quant,
+                                              int row_idx_type, int count_type, void *expanded_x, int32_t *expanded_row_idx,
+                                              int64_t *counts_out, float *expanded_scale)
+{
+    const int64_t pairs = n * k, range = end - start;
+    int64_t *count = (int64_t *)calloc((size_t)range + 1, sizeof(int64_t));
+    int64_t *first = (int64_t *)calloc((size_t)range + 1, sizeof(int64_t));
+    for (int64_t j = 0; j < pairs; ++j) {
+        const int64_t e = (int64_t)expert_idx[j] - start;
+        if (e >= 0 && e < range) count[e]++;
+    }
+    int64_t total = 0, nz = 0;
+    for (int64_t e = 0; e < range; ++e) {
+        first[e] = total;
+        total += count[e];
+        if (count_type == 1) counts_out[e] = count[e];
+        else if (count[e] != 0) { counts_out[2 * nz] = e + start; counts_out[2 * nz + 1] = count[e]; ++nz; }
+    }
+    if (count_type == 2) {
+        const int64_t written = range + 1 < expert_num ? range + 1 : expert_num;
+        for (int64_t i = nz; i < written; ++i) { counts_out[2 * i] = 0; counts_out[2 * i + 1] = 0; }
+    }
+    const size_t eb = x_dtype == DT_F32 ? 4 : (x_dtype == 2 ? 1 : 2);
+    float *v = (float *)malloc(sizeof(float) * (size_t)(h > 0 ? h : 1));
+    for (int64_t j = 0; j < pairs; ++j) {          /* ascending j inside every expert: the stable order */
+        const int64_t e = (int64_t)expert_idx[j] - start;
+        if (e < 0 || e >= range) {
+            if (row_idx_type == 0) expanded_row_idx[j] = -1;
+            continue;
+        }
+        const int64_t i = first[e]++;
+        if (row_idx_type == 1) expanded_row_idx[i] = (int32_t)j;
+        else expanded_row_idx[j] = (int32_t)i;
+        const int64_t token = j / k;
+        const char *src = (const char *)x + (size_t)token * (size_t)h * eb;
+        if (!quant) {
+            memcpy((char *)expanded_x + (size_t)i * (size_t)h * eb, src, (size_t)h * eb);
+            if (scale && expanded_scale) expanded_scale[i] = scale[token];
+            continue;
+        }
+        float amax = 0.0f;
+        for (int64_t c = 0; c < h; ++c) {
+            float t;
+            if (x_dtype == DT_F32) t = ((const float *)src)[c];
+            else if (x_dtype == DT_F16) t = f16_to_f32(((const uint16_t *)src)[c]);
+            else t = bf16_to_f32(((const uint16_t *)src)[c]);
+            if (scale) t = t * scale[e * h + c];
+            v[c] = t;
+            if (fabsf(t) > amax) amax = fabsf(t);
+        }
+        const float s = amax / 127.0f;
+        expanded_scale[i] = s;
+        int8_t *q = (int8_t *)expanded_x + (size_t)i * (size_t)h;
+        for (int64_t c = 0; c < h; ++c) {
+            const float f = f16_to_f32(f32_to_f16_rz(v[c] / s));
+            if (!(f == f)) { q[c] = 0; continue; }
+            int r = (int)(f + (f < 0.0f ? -0.5f : 0.5f));
+            if (r > 127) r = 127;
+            if (r < -128) r = -128;
+            q[c] = (int8_t)r;
+        }
+    }
+    free(v);
+    free(count);
+    free(first);
+    return total;
+}
+
+/* ------------------------------------------------------------------------------------------- */
 /* grouped_matmul_swiglu_quant, A8W8                                                            */
 /* ------------------------------------------------------------------------------------------- */
 

@@ -177,6 +177,28 @@ def np_gmm_finalize_routing(x, w, scale_f32, per_token, group_list, row_index, y
     return y
 
 
+def moe_init_routing_v3(x, expert_idx, expert_num, active_range, quant, row_idx_type=1, count_type=1, scale=None):
+    """moe_init_routing_v3.  ``x`` [n,h] float32, float16, uint16 (bf16 bits) or int8; returns dict(expanded_x, expanded_row_idx,
+    counts, expanded_scale, rows).  Rows beyond ``rows`` keep the fill values (-77 / -5.0 / -9)."""
+    x = np.ascontiguousarray(x)
+    idx = np.ascontiguousarray(expert_idx, np.int32)
+    n, h = x.shape
+    k = idx.shape[1]
+    dt = {np.dtype(np.float32): DT_F32, np.dtype(np.float16): DT_F16, np.dtype(np.uint16): DT_BF16, np.dtype(np.int8): 2}[x.dtype]
+    start, end = active_range
+    sc = None if scale is None else np.ascontiguousarray(scale, np.float32)
+    ex = np.full((n * k, h), -77, np.int8) if quant else np.zeros((n * k, h), x.dtype)
+    ri = np.full((n * k,), -9, np.int32)
+    counts = np.full((end - start,) if count_type == 1 else (expert_num, 2), -9, np.int64)
+    es = np.full((n * k,), -5.0, np.float32)
+    fn = lib().oracle_moe_init_routing_v3
+    fn.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p] + [C.c_int64] * 6 + [C.c_int] * 3 + [C.c_void_p] * 4
+    fn.restype = C.c_int64
+    rows = fn(_ptr(x), dt, _ptr(idx), _ptr(sc), n, k, h, expert_num, start, end, int(quant), row_idx_type, count_type, _ptr(ex),
+              _ptr(ri), _ptr(counts), _ptr(es))
+    return {"expanded_x": ex, "expanded_row_idx": ri, "counts": counts, "expanded_scale": es, "rows": int(rows)}
+
+
 def swiglu_quant(x, w, w_scale, x_scale, group_list, w_trans=False, q_init=None, qs_init=None, want_acc=False,
                  want_s=False):
     """grouped_matmul_swiglu_quant A8W8.  Returns dict(q int8 [M,N/2], q_scale f32 [M], acc, s)."""

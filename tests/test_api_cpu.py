@@ -349,6 +349,63 @@ def test_finalize_routing_phase1_status_codes():
     assert _fr_phase1(**{**t, "shared": torch.empty((0, 7168), dtype=torch.bfloat16)})[0] == INVALID   # empty tensors are refused
 
 
+def _ir_phase1(n=8, k=2, h=64, E=16, rng_=(0, 16), quant=1, x_dtype=torch.bfloat16, out_dtype=None, count_type=1, row_idx_type=1,
+               drop=0, flag=True, active_num=None, scale=None, null=(), counts_shape=None, idx_dtype=torch.int32, **over):
+    L = _lib.lib()
+    if out_dtype is None:
+        out_dtype = torch.int8 if quant == 1 else x_dtype
+    t = dict(x=torch.empty((n, h), dtype=x_dtype), idx=torch.empty((n, k), dtype=idx_dtype), scale=scale,
+             ex=torch.empty((n * k, h), dtype=out_dtype), ri=torch.empty((n * k,), dtype=torch.int32),
+             cnt=torch.empty(counts_shape or (((rng_[1] - rng_[0]) if rng_ else 1,) if count_type == 1 else (E, 2)), dtype=torch.int64),
+             es=torch.empty((n * k,), dtype=torch.float32))
+    t.update(over)
+    h_ = {name: (acl.create_tensor(v) if (v is not None and name not in null) else None) for name, v in t.items()}
+    ra = L.aclCreateIntArray((C.c_int64 * len(rng_))(*rng_), len(rng_)) if rng_ is not None else None
+    size, ex = C.c_uint64(5), C.c_void_p(0)
+    rc = L.aclnnMoeInitRoutingV3GetWorkspaceSize(h_["x"], h_["idx"], h_["scale"], None, n * k if active_num is None else active_num, 0, E,
+                                                 drop, count_type, flag, quant, ra, row_idx_type, h_["ex"], h_["ri"], h_["cnt"], h_["es"],
+                                                 C.byref(size), C.byref(ex))
+    if rc == OK:
+        assert L.aclDestroyAclOpExecutor(ex) == OK
+    for v in h_.values():
+        if v:
+            L.aclDestroyTensor(v)
+    if ra:
+        L.aclDestroyIntArray(ra)
+    return rc, size.value
+
+
+def test_moe_init_routing_v3_phase1_status_codes():
+    rc, size = _ir_phase1()
+    assert rc == OK and size >= 256
+    assert _ir_phase1(quant=-1)[0] == OK
+    assert _ir_phase1(quant=-1, x_dtype=torch.int8)[0] == OK
+    assert _ir_phase1(x_dtype=torch.float32)[0] == OK and _ir_phase1(x_dtype=torch.float16)[0] == OK
+    assert _ir_phase1(count_type=2)[0] == OK and _ir_phase1(row_idx_type=0)[0] == OK
+    assert _ir_phase1(rng_=(4, 12), scale=torch.empty((8, 64), dtype=torch.float32))[0] == OK      # smooth scale [range, h]
+    assert _ir_phase1(quant=-1, scale=torch.empty((8,), dtype=torch.float32))[0] == OK             # per-token scale [n]
+    assert _ir_phase1(n=0)[0] == OK and _ir_phase1(n=0)[1] == 0
+    for name in ("x", "idx", "ex", "ri", "cnt", "es"):
+        assert _ir_phase1(null=(name,))[0] == NULLPTR
+    assert _ir_phase1(idx_dtype=torch.int64)[0] == INVALID
+    assert _ir_phase1(x_dtype=torch.int8)[0] == INVALID                                            # dynamic quant of int8 rows
+    assert _ir_phase1(out_dtype=torch.bfloat16)[0] == INVALID                                      # quant output must be int8
+    assert _ir_phase1(quant=-1, out_dtype=torch.float32)[0] == INVALID
+    assert _ir_phase1(quant=0)[0] == INVALID and _ir_phase1(quant=2)[0] == INVALID                 # static quant is not supported
+    assert _ir_phase1(drop=1)[0] == INVALID and _ir_phase1(flag=False)[0] == INVALID
+    assert _ir_phase1(count_type=0)[0] == INVALID and _ir_phase1(row_idx_type=2)[0] == INVALID
+    assert _ir_phase1(active_num=5)[0] == INVALID
+    assert _ir_phase1(rng_=(4, 4))[0] == INVALID and _ir_phase1(rng_=(0, 17))[0] == INVALID and _ir_phase1(rng_=None)[0] == INVALID
+    assert _ir_phase1(E=10241, rng_=(0, 16))[0] == INVALID
+    assert _ir_phase1(count_type=2, E=5121, rng_=(0, 16))[0] == INVALID
+    assert _ir_phase1(counts_shape=(15,))[0] == INVALID
+    assert _ir_phase1(scale=torch.empty((16, 32), dtype=torch.float32))[0] == INVALID
+    assert _ir_phase1(scale=torch.empty((16, 64), dtype=torch.float16))[0] == INVALID
+    assert _ir_phase1(ex=torch.empty((15, 64), dtype=torch.int8))[0] == INVALID
+    assert _ir_phase1(ri=torch.empty((16,), dtype=torch.int64))[0] == INVALID
+    assert _ir_phase1(idx=torch.empty((7, 2), dtype=torch.int32))[0] == INVALID
+
+
 def test_second_phase_host_checks():
     L = _lib.lib()
     assert L.aclnnGroupedMatmulV4(None, 0, None, None) == NULLPTR

@@ -186,6 +186,58 @@ def test_finalize_routing_matches_float64_formulation(oracle):
     assert np.isfinite(rb["y"]).all()
 
 
+def test_moe_init_routing_matches_numpy_formulation(oracle):
+    rng = np.random.default_rng(11)
+    n, k, h, E = 37, 4, 48, 16
+    x = rng.standard_normal((n, h)).astype(np.float32)
+    x[5] = 0.0                                           # an all-zero row: scale 0, zeros
+    idx = np.stack([rng.permutation(E)[:k] for _ in range(n)]).astype(np.int32)
+    start, end = 3, 12
+    flat = idx.ravel()
+    keep = np.nonzero((flat >= start) & (flat < end))[0]
+    order = keep[np.argsort(flat[keep], kind="stable")]   # stable sort of the active pairs by expert
+    smooth = rng.uniform(0.5, 2.0, size=(end - start, h)).astype(np.float32)
+    for sc in (None, smooth):
+        r = oracle.moe_init_routing_v3(x, idx, E, (start, end), True, row_idx_type=1, count_type=1, scale=sc)
+        assert r["rows"] == len(order)
+        assert np.array_equal(r["expanded_row_idx"][:len(order)], order)
+        assert (r["expanded_row_idx"][len(order):] == -9).all()
+        assert np.array_equal(r["counts"], np.bincount(flat[keep] - start, minlength=end - start))
+        for i, j in enumerate(order):
+            v = x[j // k] if sc is None else (x[j // k] * sc[flat[j] - start]).astype(np.float32)
+            s = np.float32(np.abs(v).max()) / np.float32(127.0)
+            assert r["expanded_scale"][i] == s
+            if s == 0:
+                assert (r["expanded_x"][i] == 0).all()
+                continue
+            u = (v / s).astype(np.float32)
+            hz = np.where(np.abs(u.astype(np.float16).astype(np.float32)) > np.abs(u),              # fp16 towards zero
+                          np.nextafter(u.astype(np.float16), np.float16(0)), u.astype(np.float16)).astype(np.float32)
+            q = np.trunc(hz + np.copysign(np.float32(0.5), hz))                                       # ties away from zero
+            assert np.array_equal(r["expanded_x"][i], q.astype(np.int8)), i
+        assert (r["expanded_x"][len(order):] == -77).all() and (r["expanded_scale"][len(order):] == -5.0).all()
+    # gather-type row index and key-value counts
+    r0 = oracle.moe_init_routing_v3(x, idx, E, (start, end), True, row_idx_type=0, count_type=2)
+    inv = np.full(n * k, -1, np.int32)
+    inv[order] = np.arange(len(order))
+    assert np.array_equal(r0["expanded_row_idx"], inv)
+    cnt = np.bincount(flat[keep] - start, minlength=end - start)
+    nzp = [(e + start, c) for e, c in enumerate(cnt) if c]
+    assert [tuple(p) for p in r0["counts"][:len(nzp)]] == nzp
+    written = min(end - start + 1, E)
+    assert (r0["counts"][len(nzp):written] == 0).all() and (r0["counts"][written:] == -9).all()
+    # no quantisation: rows and per-token scales are copied; bf16 / int8 rows pass through untouched
+    ps = rng.uniform(1, 2, size=n).astype(np.float32)
+    xb = oracle.f32_to_bf16_bits(x)
+    rc = oracle.moe_init_routing_v3(xb, idx, E, (0, E), False, scale=ps)
+    full = np.argsort(flat, kind="stable")
+    assert np.array_equal(rc["expanded_x"], xb[full // k]) and np.array_equal(rc["expanded_scale"], ps[full // k])
+    # bf16 and fp16 inputs quantise like their float32 values
+    rb = oracle.moe_init_routing_v3(xb, idx, E, (0, E), True)
+    rf = oracle.moe_init_routing_v3(oracle.bf16_bits_to_f32(xb), idx, E, (0, E), True)
+    assert np.array_equal(rb["expanded_x"], rf["expanded_x"]) and np.array_equal(rb["expanded_scale"], rf["expanded_scale"])
+
+
 def test_gmm_scale_order_is_weight_then_token(oracle):
     # (acc*w_scale)*x_scale and (acc*x_scale)*w_scale differ in the last bit for some inputs; the two operators
     # use opposite orders (grouped_matmul_quant_mixcore.h:262,300 vs grouped_matmul_swiglu_quant.h:392,450).

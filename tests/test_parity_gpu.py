@@ -506,3 +506,114 @@ def test_finalize_routing_flat_entry_point(oracle, layout):
 def test_finalize_routing_batch_smaller_than_rows_per_token(oracle):
     # many rows per destination: 64 destinations for 1024 rows (16 atomics per element)
     check_finalize(oracle, 1024, 128, 256, 2, [500, 524], 16, 66, shared_rows=64, shared_weight=2.0)
+
+
+# ----------------------------------------------------------------------------------------------------------
+# moe_init_routing_v3 (producer of the path's inputs): every output is integer or exactly rounded, so bit-exact
+# ----------------------------------------------------------------------------------------------------------
+
+def check_init_routing(oracle, n, k, h, E, rng_, seed, *, quant=True, x_kind="bf16", smooth=False, row_idx_type=1, count_type=1,
+                       per_token_scale=False, zero_row=True):
+    import ops_transformer_b200 as ops
+    dev = _dev()
+    rng = np.random.default_rng(seed)
+    xf = (rng.standard_normal((n, h)) * rng.uniform(0.1, 4.0, size=(n, 1))).astype(np.float32)
+    if zero_row and n > 2:
+        xf[2] = 0.0
+    idx = np.stack([rng.permutation(E)[:k] for _ in range(n)]).astype(np.int32)
+    if x_kind == "bf16":
+        x_o = oracle.f32_to_bf16_bits(xf)
+        x_t = torch.from_numpy(x_o.view(np.int16)).to(dev).view(torch.bfloat16)
+    elif x_kind == "f16":
+        x_o = xf.astype(np.float16)
+        x_t = torch.from_numpy(x_o).to(dev)
+    elif x_kind == "int8":
+        x_o = rng.integers(-127, 128, size=(n, h)).astype(np.int8)
+        x_t = torch.from_numpy(x_o).to(dev)
+    else:
+        x_o = xf
+        x_t = torch.from_numpy(xf).to(dev)
+    sc = None
+    if smooth:
+        sc = rng.uniform(0.5, 2.0, size=(rng_[1] - rng_[0], h)).astype(np.float32)
+    elif per_token_scale:
+        sc = rng.uniform(0.5, 2.0, size=(n,)).astype(np.float32)
+    ref = oracle.moe_init_routing_v3(x_o, idx, E, rng_, quant, row_idx_type=row_idx_type, count_type=count_type, scale=sc)
+    rows = ref["rows"]
+    ex = torch.full((n * k, h), -77, dtype=torch.int8, device=dev) if quant else torch.zeros((n * k, h), dtype=x_t.dtype, device=dev)
+    ri = torch.full((n * k,), -9, dtype=torch.int32, device=dev)
+    cnt = torch.full(ref["counts"].shape, -9, dtype=torch.int64, device=dev)
+    es = torch.full((n * k,), -5.0, dtype=torch.float32, device=dev)
+    ops.moe_init_routing_v3(x_t, torch.from_numpy(idx).to(dev), expert_num=E, active_expert_range=rng_, quant_mode=1 if quant else -1,
+                            scale=None if sc is None else torch.from_numpy(sc).to(dev), expert_tokens_num_type=count_type,
+                            row_idx_type=row_idx_type, outputs=(ex, ri, cnt, es))
+    torch.cuda.synchronize()
+    assert np.array_equal(cnt.cpu().numpy(), ref["counts"])
+    assert np.array_equal(ri.cpu().numpy(), ref["expanded_row_idx"])
+    got = ex.view(torch.int16).cpu().numpy().view(np.uint16) if x_kind == "bf16" and not quant else ex.cpu().numpy()
+    assert np.array_equal(got, ref["expanded_x"]), "expanded rows differ"
+    if quant or sc is not None:
+        assert np.array_equal(es.cpu().numpy(), ref["expanded_scale"])
+    return rows
+
+
+def test_init_routing_dynamic_quant_deepseek_width(oracle):
+    rows = check_init_routing(oracle, 96, 8, 7168, 256, (0, 256), 70)
+    assert rows == 96 * 8
+
+
+def test_init_routing_active_range_smooth_scale_and_gather_index(oracle):
+    check_init_routing(oracle, 300, 4, 512, 64, (16, 48), 71, smooth=True, row_idx_type=0, count_type=2)
+    check_init_routing(oracle, 300, 4, 512, 64, (16, 48), 72, smooth=True, x_kind="f32")
+    check_init_routing(oracle, 5, 2, 20, 8, (1, 8), 73, x_kind="f16", row_idx_type=0)      # h not a multiple of 4
+
+
+def test_init_routing_many_blocks_keep_pair_order(oracle):
+    # 40000 pairs = 40 blocks of 1024: the order of equal experts must hold across warps and blocks
+    check_init_routing(oracle, 5000, 8, 64, 32, (0, 32), 74)
+    check_init_routing(oracle, 5000, 8, 64, 2048, (100, 1900), 75, count_type=2)
+
+
+def test_init_routing_without_quantisation(oracle):
+    check_init_routing(oracle, 200, 4, 256, 32, (0, 32), 76, quant=False, per_token_scale=True)
+    check_init_routing(oracle, 200, 4, 256, 32, (4, 20), 77, quant=False, x_kind="int8", row_idx_type=0)
+    check_init_routing(oracle, 64, 2, 100, 16, (0, 16), 78, quant=False, x_kind="f32")
+
+
+def test_init_routing_feeds_the_grouped_gemms(oracle):
+    # bf16 tokens -> init routing (int8 rows, scales, counts) -> swiglu_quant -> finalize routing back to token order
+    import ops_transformer_b200 as ops
+    dev = _dev()
+    rng = np.random.default_rng(79)
+    n, k, h, inter, E = 64, 4, 512, 256, 8
+    xf = rng.standard_normal((n, h)).astype(np.float32)
+    xb = oracle.f32_to_bf16_bits(xf)
+    idx = np.stack([rng.permutation(E)[:k] for _ in range(n)]).astype(np.int32)
+    w1 = synth.int8_tensor((E, h, 2 * inter), 79, 2)
+    s1 = synth.scale_tensor((E, 2 * inter), 79, 3)
+    w2 = synth.int8_tensor((E, inter, h), 79, 5)
+    s2 = synth.scale_tensor((E, h), 79, 6)
+    logit = rng.uniform(0.1, 0.4, size=(n, k)).astype(np.float32)
+    # oracle chain
+    r = oracle.moe_init_routing_v3(xb, idx, E, (0, E), True, row_idx_type=1)
+    gl = np.cumsum(r["counts"])
+    a = oracle.swiglu_quant(r["expanded_x"], w1, s1, r["expanded_scale"], gl)
+    pair = r["expanded_row_idx"]
+    fin = oracle.gmm_finalize_routing(a["q"], w2, s2, a["q_scale"], r["counts"], (pair // k).astype(np.int64), n,
+                                      shared_input=oracle.f32_to_bf16_bits(np.zeros((n, h), np.float32)), logit=logit.ravel()[pair])
+    # GPU chain
+    t = lambda v: torch.from_numpy(v).to(dev)  # noqa: E731
+    ex, ri, cnt, es = ops.moe_init_routing_v3(torch.from_numpy(xb.view(np.int16)).to(dev).view(torch.bfloat16), t(idx), expert_num=E,
+                                              active_expert_range=(0, E), quant_mode=1)
+    q, qs = ops.grouped_matmul_swiglu_quant(ex, t(w1), t(s1), es, torch.cumsum(cnt, 0))
+    tok = torch.div(ri, k, rounding_mode="floor").to(torch.int64)
+    y = ops.grouped_matmul_finalize_routing(q, t(nd_to_nz(w2)), t(s2), cnt, tok, n, pertoken_scale=qs,
+                                            shared_input=torch.zeros((n, h), dtype=torch.bfloat16, device=dev),
+                                            logit=t(logit.ravel())[ri.to(torch.int64)])
+    torch.cuda.synchronize()
+    assert np.array_equal(ex.cpu().numpy(), r["expanded_x"]) and np.array_equal(cnt.cpu().numpy(), r["counts"])
+    d = np.abs(q.cpu().numpy().astype(np.int32) - a["q"].astype(np.int32))
+    assert d.max() <= 1 and np.count_nonzero(d) <= max(1, int(1e-4 * d.size))
+    err = np.abs(y.cpu().numpy().astype(np.float64) - fin["y"])
+    # a 1-LSB difference of the int8 intermediate moves an output by about one part in 127 of a term
+    assert (err <= 4 * 2.0 ** -23 * fin["abs_sum"] + (np.count_nonzero(d) > 0) * 2e-2 * fin["abs_sum"]).all()
