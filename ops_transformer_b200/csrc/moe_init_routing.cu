@@ -37,9 +37,11 @@ struct RoutingParams {
     int *expanded_row_idx;
     long long *counts_out;
     float *expanded_scale;
-    int *block_hist;           // [nb, range]: counts, then exclusive offsets over the blocks
+    int *block_hist;           // [nb, range]: pairs per block and active expert
+    int *block_off;            // [nb, range]: the same, summed over the earlier blocks
     int *expert_first;         // [range]: first output row of every active expert
     int *sorted_row;           // [pairs]: pair index of every output row
+    int *pair_pos;             // [pairs]: output row of every pair, -1 if its expert is not active
     int *total;                // number of output rows
     int nb;
 };
@@ -88,16 +90,26 @@ __device__ int block_scan_1024(int v, int *warp_sums, int *block_sum)
 __global__ void __launch_bounds__(1024) routing_scan_kernel(const RoutingParams p)
 {
     __shared__ int warp_sums[32];
-    // per expert: exclusive prefix over the blocks, total into expert_first (as a count for now)
-    for (int e = threadIdx.x; e < p.range; e += blockDim.x) {
-        int run = 0;
-        for (int b = 0; b < p.nb; ++b) {
-            const size_t i = (size_t)b * p.range + e;
-            const int t = p.block_hist[i];
-            p.block_hist[i] = run;
-            run += t;
+    // per expert: exclusive prefix over the blocks, total into expert_first (as a count for now).  One warp per expert,
+    // its lanes over 32 blocks at a time.
+    {
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        for (int e = warp; e < p.range; e += 32) {
+            int carry = 0;
+            for (int b0 = 0; b0 < p.nb; b0 += 32) {
+                const int b = b0 + lane;
+                const int t = b < p.nb ? p.block_hist[(size_t)b * p.range + e] : 0;
+                int inc = t;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int u = __shfl_up_sync(0xffffffffu, inc, o);
+                    if (lane >= o) inc += u;
+                }
+                if (b < p.nb) p.block_off[(size_t)b * p.range + e] = carry + inc - t;
+                carry += __shfl_sync(0xffffffffu, inc, 31);
+            }
+            if (lane == 0) p.expert_first[e] = carry;
         }
-        p.expert_first[e] = run;
     }
     __syncthreads();
     // over the experts, 1024 at a time: first row of every expert, the counts output (count or key-value form)
@@ -130,10 +142,16 @@ __global__ void __launch_bounds__(1024) routing_scan_kernel(const RoutingParams 
     if (threadIdx.x == 0) *p.total = row_carry;
 }
 
+constexpr int kWarpTableRange = 256;  // up to this many active experts the scatter keeps one counter per warp and expert
+
+// PER_WARP: shared memory holds [32 warps][range] counters, all warps count at once and a scan over the warps gives every
+// warp its start; otherwise one counter per expert and the warps take turns.
+template <bool PER_WARP>
 __global__ void __launch_bounds__(kPairsPerBlock) routing_scatter_kernel(const RoutingParams p)
 {
     extern __shared__ int running[];
-    for (int e = threadIdx.x; e < p.range; e += blockDim.x) running[e] = 0;
+    const int slots = PER_WARP ? p.range * (kPairsPerBlock / 32) : p.range;
+    for (int e = threadIdx.x; e < slots; e += blockDim.x) running[e] = 0;
     const long long j = (long long)blockIdx.x * kPairsPerBlock + threadIdx.x;
     int e = -1;
     if (j < p.pairs) {
@@ -143,27 +161,47 @@ __global__ void __launch_bounds__(kPairsPerBlock) routing_scatter_kernel(const R
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     int before = 0;  // pairs of this block with the same expert that come earlier
     __syncthreads();
-    for (int w = 0; w < kPairsPerBlock / 32; ++w) {
-        if (warp == w) {
-            const unsigned peers = __match_any_sync(0xffffffffu, e);
-            const int rank = __popc(peers & ((1u << lane) - 1u));
-            int base = 0;
-            if (e >= 0 && rank == 0) {
-                base = running[e];
-                running[e] = base + __popc(peers);
+    if (PER_WARP) {
+        const unsigned peers = __match_any_sync(0xffffffffu, e);
+        const int rank = __popc(peers & ((1u << lane) - 1u));
+        if (e >= 0 && rank == 0) running[warp * p.range + e] = __popc(peers);
+        __syncthreads();
+        for (int x = threadIdx.x; x < p.range; x += blockDim.x) {  // exclusive scan over the warps, one expert per thread
+            int run = 0;
+#pragma unroll
+            for (int w = 0; w < kPairsPerBlock / 32; ++w) {
+                const int t = running[w * p.range + x];
+                running[w * p.range + x] = run;
+                run += t;
             }
-            base = __shfl_sync(0xffffffffu, base, __ffs(peers) - 1);
-            before = base + rank;
         }
         __syncthreads();
+        if (e >= 0) before = running[warp * p.range + e] + rank;
+    } else {
+        for (int w = 0; w < kPairsPerBlock / 32; ++w) {
+            if (warp == w) {
+                const unsigned peers = __match_any_sync(0xffffffffu, e);
+                const int rank = __popc(peers & ((1u << lane) - 1u));
+                int base = 0;
+                if (e >= 0 && rank == 0) {
+                    base = running[e];
+                    running[e] = base + __popc(peers);
+                }
+                base = __shfl_sync(0xffffffffu, base, __ffs(peers) - 1);
+                before = base + rank;
+            }
+            __syncthreads();
+        }
     }
     if (j >= p.pairs) return;
     if (e < 0) {
+        p.pair_pos[j] = -1;
         if (p.row_idx_type == 0) p.expanded_row_idx[j] = -1;
         return;
     }
-    const int pos = p.expert_first[e] + p.block_hist[(size_t)blockIdx.x * p.range + e] + before;
+    const int pos = p.expert_first[e] + p.block_off[(size_t)blockIdx.x * p.range + e] + before;
     p.sorted_row[pos] = (int)j;
+    p.pair_pos[j] = pos;
     if (p.row_idx_type == 1) p.expanded_row_idx[pos] = (int)j;
     else p.expanded_row_idx[j] = pos;
 }
@@ -232,6 +270,163 @@ __global__ void __launch_bounds__(128) routing_quant_kernel(const RoutingParams 
     }
 }
 
+__device__ __forceinline__ uint32_t pack4(int8_t a, int8_t b, int8_t c, int8_t d)
+{
+    return (uint32_t)(uint8_t)a | ((uint32_t)(uint8_t)b << 8) | ((uint32_t)(uint8_t)c << 16) | ((uint32_t)(uint8_t)d << 24);
+}
+
+__device__ __forceinline__ float block_max_128(float v, float *red)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    __syncthreads();  // red may still be read from the previous use
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    return fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+}
+
+template <typename T>
+__device__ __forceinline__ void unpack16(const uint4 &u, float *f);
+template <>
+__device__ __forceinline__ void unpack16<float>(const uint4 &u, float *f)
+{
+    f[0] = __uint_as_float(u.x); f[1] = __uint_as_float(u.y); f[2] = __uint_as_float(u.z); f[3] = __uint_as_float(u.w);
+}
+template <>
+__device__ __forceinline__ void unpack16<__nv_bfloat16>(const uint4 &u, float *f)
+{
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { f[2 * i] = __uint_as_float(w[i] << 16); f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+}
+template <>
+__device__ __forceinline__ void unpack16<__half>(const uint4 &u, float *f)
+{
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 t = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+        f[2 * i] = t.x; f[2 * i + 1] = t.y;
+    }
+}
+
+// The fast form of the quantising gather: one CTA per TOKEN.  The row is read once, 16 bytes per thread and step, and
+// stays in registers; without a smooth scale it is quantised once and the int8 row is stored at the output row of each
+// of the token's k pairs; with one, every pair is scaled, reduced and quantised from the registers.  DRAM traffic is the
+// algorithmic minimum: x once, every output row once.  Needs h a multiple of the 16-byte vector, h <= 128 * NCH * VEC
+// and 16-byte aligned pointers; other shapes take routing_quant_kernel.
+template <typename T, int NCH>
+__global__ void __launch_bounds__(128) routing_quant_token_kernel(const RoutingParams p)
+{
+    constexpr int VEC = 16 / (int)sizeof(T);
+    __shared__ float red[4];
+    const int token = blockIdx.x;
+    const int chunks = p.h / VEC;
+    const uint4 *row = reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(p.x) + (size_t)token * p.h);
+    float v[NCH][VEC];
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) {
+        const int c = threadIdx.x + i * 128;
+        if (c < chunks) {
+            unpack16<T>(__ldg(row + c), v[i]);
+        } else {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) v[i][e] = 0.0f;
+        }
+    }
+    const bool smooth = p.scale != nullptr;
+    float scale = 0.0f;
+    uint32_t w[NCH][VEC / 4];  // the quantised row, four int8 per word
+    if (!smooth) {             // one quantisation serves all k pairs of the token
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < NCH; ++i)
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) amax = fmaxf(amax, fabsf(v[i][e]));
+        scale = __fdiv_rn(block_max_128(amax, red), 127.0f);
+#pragma unroll
+        for (int i = 0; i < NCH; ++i)
+#pragma unroll
+            for (int e4 = 0; e4 < VEC; e4 += 4)
+                w[i][e4 / 4] = pack4(quant_trunc_round(v[i][e4], scale), quant_trunc_round(v[i][e4 + 1], scale),
+                                     quant_trunc_round(v[i][e4 + 2], scale), quant_trunc_round(v[i][e4 + 3], scale));
+    }
+    for (int s = 0; s < p.k; ++s) {
+        const long long j = (long long)token * p.k + s;
+        const int pos = p.pair_pos[j];
+        if (pos < 0) continue;  // uniform over the CTA
+        if (smooth) {
+            const float *sm = p.scale + (size_t)(__ldg(p.expert_idx + j) - p.e_start) * p.h;
+            float amax = 0.0f;
+#pragma unroll
+            for (int i = 0; i < NCH; ++i) {
+                const int c = threadIdx.x + i * 128;
+                if (c < chunks) {
+#pragma unroll
+                    for (int e4 = 0; e4 < VEC; e4 += 4) {
+                        const float4 m = __ldg(reinterpret_cast<const float4 *>(sm + (size_t)c * VEC + e4));
+                        amax = fmaxf(fmaxf(amax, fabsf(__fmul_rn(v[i][e4], m.x))), fabsf(__fmul_rn(v[i][e4 + 1], m.y)));
+                        amax = fmaxf(fmaxf(amax, fabsf(__fmul_rn(v[i][e4 + 2], m.z))), fabsf(__fmul_rn(v[i][e4 + 3], m.w)));
+                    }
+                }
+            }
+            scale = __fdiv_rn(block_max_128(amax, red), 127.0f);
+#pragma unroll
+            for (int i = 0; i < NCH; ++i) {  // the products are formed again: keeping them would cost 64 registers
+                const int c = threadIdx.x + i * 128;
+                if (c < chunks) {
+#pragma unroll
+                    for (int e4 = 0; e4 < VEC; e4 += 4) {
+                        const float4 m = __ldg(reinterpret_cast<const float4 *>(sm + (size_t)c * VEC + e4));
+                        w[i][e4 / 4] = pack4(quant_trunc_round(__fmul_rn(v[i][e4], m.x), scale), quant_trunc_round(__fmul_rn(v[i][e4 + 1], m.y), scale),
+                                             quant_trunc_round(__fmul_rn(v[i][e4 + 2], m.z), scale), quant_trunc_round(__fmul_rn(v[i][e4 + 3], m.w), scale));
+                    }
+                }
+            }
+        }
+        if (threadIdx.x == 0) p.expanded_scale[pos] = scale;
+        int8_t *out = reinterpret_cast<int8_t *>(p.expanded_x) + (size_t)pos * p.h;
+#pragma unroll
+        for (int i = 0; i < NCH; ++i) {
+            const int c = threadIdx.x + i * 128;
+            if (c < chunks) {
+                if (VEC == 8) *reinterpret_cast<uint2 *>(out + (size_t)c * VEC) = make_uint2(w[i][0], w[i][VEC / 4 - 1]);
+                else *reinterpret_cast<uint32_t *>(out + (size_t)c * VEC) = w[i][0];
+            }
+        }
+    }
+}
+
+// One CTA per token: the row is read once, 16 bytes per thread and step, and stored at the output row of each pair.
+__global__ void __launch_bounds__(128) routing_copy_token_kernel(const RoutingParams p, int row_bytes)
+{
+    const int token = blockIdx.x;
+    const uint4 *src = reinterpret_cast<const uint4 *>(reinterpret_cast<const char *>(p.x) + (size_t)token * row_bytes);
+    const int chunks = row_bytes / 16;
+    for (int c0 = 0; c0 < chunks; c0 += 128 * 4) {
+        uint4 buf[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int c = c0 + i * 128 + threadIdx.x;
+            if (c < chunks) buf[i] = __ldg(src + c);
+        }
+        for (int s = 0; s < p.k; ++s) {
+            const int pos = p.pair_pos[(long long)token * p.k + s];
+            if (pos < 0) continue;
+            uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<char *>(p.expanded_x) + (size_t)pos * row_bytes);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int c = c0 + i * 128 + threadIdx.x;
+                if (c < chunks) dst[c] = buf[i];
+            }
+        }
+    }
+    if (p.scale && p.expanded_scale && threadIdx.x < p.k) {
+        const int pos = p.pair_pos[(long long)token * p.k + threadIdx.x];
+        if (pos >= 0) p.expanded_scale[pos] = __ldg(p.scale + token);
+    }
+}
+
 // One CTA per output row: plain copy of the token row (any element size), and of the token's scale if one is given.
 __global__ void __launch_bounds__(128) routing_copy_kernel(const RoutingParams p, int elem_bytes)
 {
@@ -259,7 +454,7 @@ size_t init_routing_workspace_bytes(const InitRoutingProblem &r)
     const long long pairs = r.n * r.k;
     const long long nb = (pairs + kPairsPerBlock - 1) / kPairsPerBlock;
     const long long range = r.expert_end - r.expert_start;
-    return 256 + align256((size_t)nb * range * 4) + align256((size_t)range * 4) + align256((size_t)pairs * 4);
+    return 256 + 2 * align256((size_t)nb * range * 4) + align256((size_t)range * 4) + 2 * align256((size_t)pairs * 4);
 }
 
 cudaError_t init_routing_launch(const InitRoutingProblem &r, void *workspace, size_t workspace_bytes, cudaStream_t stream)
@@ -282,21 +477,41 @@ cudaError_t init_routing_launch(const InitRoutingProblem &r, void *workspace, si
     p.total = reinterpret_cast<int *>(ws);
     size_t off = 256;
     p.block_hist = reinterpret_cast<int *>(ws + off); off += align256((size_t)nb * range * 4);
+    p.block_off = reinterpret_cast<int *>(ws + off); off += align256((size_t)nb * range * 4);
     p.expert_first = reinterpret_cast<int *>(ws + off); off += align256((size_t)range * 4);
-    p.sorted_row = reinterpret_cast<int *>(ws + off);
+    p.sorted_row = reinterpret_cast<int *>(ws + off); off += align256((size_t)pairs * 4);
+    p.pair_pos = reinterpret_cast<int *>(ws + off);
     p.nb = (int)nb;
     const size_t smem = (size_t)range * 4;
     routing_count_kernel<<<(unsigned)nb, kPairsPerBlock, smem, stream>>>(p);
     routing_scan_kernel<<<1, 1024, 0, stream>>>(p);
-    routing_scatter_kernel<<<(unsigned)nb, kPairsPerBlock, smem, stream>>>(p);
+    if (range <= kWarpTableRange) routing_scatter_kernel<true><<<(unsigned)nb, kPairsPerBlock, smem * (kPairsPerBlock / 32), stream>>>(p);
+    else routing_scatter_kernel<false><<<(unsigned)nb, kPairsPerBlock, smem, stream>>>(p);
+    const int eb = r.x_dtype == kF32 ? 4 : (r.x_dtype == kI8 ? 1 : 2);
+    const bool aligned = ((reinterpret_cast<uintptr_t>(r.x) | reinterpret_cast<uintptr_t>(r.expanded_x) | reinterpret_cast<uintptr_t>(r.scale)) & 15) == 0;
     if (r.quant) {
-        if (r.x_dtype == kF32) routing_quant_kernel<float><<<(unsigned)pairs, 128, 0, stream>>>(p);
-        else if (r.x_dtype == kF16) routing_quant_kernel<__half><<<(unsigned)pairs, 128, 0, stream>>>(p);
-        else if (r.x_dtype == kBF16) routing_quant_kernel<__nv_bfloat16><<<(unsigned)pairs, 128, 0, stream>>>(p);
-        else return cudaErrorInvalidValue;
+        // token-major kernels hold up to 64 values per thread: h <= 8192; h must be a whole number of 16-byte vectors and,
+        // for the 8-byte stores of a row, a multiple of 8
+        const int vec = 16 / eb;
+        const bool fast = aligned && r.h % vec == 0 && r.h % 8 == 0 && r.h / vec <= 128 * (eb == 4 ? 16 : 8) && r.n <= 0x7fffffffll;
+        if (r.x_dtype == kF32) {
+            if (fast) routing_quant_token_kernel<float, 16><<<(unsigned)r.n, 128, 0, stream>>>(p);
+            else routing_quant_kernel<float><<<(unsigned)pairs, 128, 0, stream>>>(p);
+        } else if (r.x_dtype == kF16) {
+            if (fast) routing_quant_token_kernel<__half, 8><<<(unsigned)r.n, 128, 0, stream>>>(p);
+            else routing_quant_kernel<__half><<<(unsigned)pairs, 128, 0, stream>>>(p);
+        } else if (r.x_dtype == kBF16) {
+            if (fast) routing_quant_token_kernel<__nv_bfloat16, 8><<<(unsigned)r.n, 128, 0, stream>>>(p);
+            else routing_quant_kernel<__nv_bfloat16><<<(unsigned)pairs, 128, 0, stream>>>(p);
+        } else {
+            return cudaErrorInvalidValue;
+        }
     } else {
-        const int eb = r.x_dtype == kF32 ? 4 : (r.x_dtype == kI8 ? 1 : 2);
-        routing_copy_kernel<<<(unsigned)pairs, 128, 0, stream>>>(p, eb);
+        const long long row_bytes = r.h * eb;
+        if (aligned && row_bytes % 16 == 0 && row_bytes <= 0x7fffffffll && r.k <= 128)
+            routing_copy_token_kernel<<<(unsigned)r.n, 128, 0, stream>>>(p, (int)row_bytes);
+        else
+            routing_copy_kernel<<<(unsigned)pairs, 128, 0, stream>>>(p, eb);
     }
     return cudaGetLastError();
 }
