@@ -14,7 +14,7 @@ ROOT = os.path.dirname(PKG_DIR)
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libgmm_b200.so")
 
-SOURCES = ["gmm_sm100.cu", "gmm_simt.cu", "gmm_noalloc.cu", "ep_peer.cu", "moe_init_routing.cu", "acl_shim.cpp", "op_api.cpp"]
+SOURCES = ["gmm_sm100.cu", "gmm_simt.cu", "gmm_noalloc.cu", "ep_peer.cu", "moe_init_routing.cu", "view_copy.cu", "acl_shim.cpp", "op_api.cpp"]
 HEADERS = ["gmm_common.h", "acl_shim.h"]
 
 # -fmad=false: the epilogues reproduce the reference's separately rounded fp32 steps, so the compiler must not

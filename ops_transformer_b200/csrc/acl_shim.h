@@ -53,6 +53,8 @@ struct aclOpExecutor {
     gmm::Problem problem;
     gmm::Plan plan;
     gmm::InitRoutingProblem routing;
+    std::vector<gmm::StagedView> staged;   // non-contiguous views with a contiguous copy in the workspace tail
+    size_t staged_bytes = 0;
 };
 
 namespace gmm {

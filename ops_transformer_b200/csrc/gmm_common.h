@@ -6,6 +6,8 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#include <vector>
+
 namespace gmm {
 
 // Data-type codes follow aclDataType (include/aclnn/aclnn_base.h).
@@ -87,6 +89,17 @@ struct InitRoutingProblem {
 };
 size_t init_routing_workspace_bytes(const InitRoutingProblem &r);
 cudaError_t init_routing_launch(const InitRoutingProblem &r, void *workspace, size_t workspace_bytes, cudaStream_t stream);
+
+// A non-contiguous tensor view whose contiguous copy lives in the workspace (view_copy.cu).
+struct StagedView {
+    std::vector<int64_t> dims, strides;  // strides in elements
+    int elem = 1;                        // bytes per element
+    void *data = nullptr;                // address of the view's first element
+    size_t ws_off = 0;                   // offset of the contiguous copy behind the operator's own workspace
+    bool is_output = false;              // outputs are copied in before and back after the operator
+    void **field = nullptr;              // the pointer of the problem description that must name the copy
+};
+cudaError_t view_copy_launch(const StagedView &v, void *contiguous, bool to_contiguous, cudaStream_t stream);
 
 // Host only: choose the kernel path and the workspace layout.  Never touches the device.
 void make_plan(const Problem &p, Plan *plan);

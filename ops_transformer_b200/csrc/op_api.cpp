@@ -11,6 +11,7 @@
 // restricted to the int8 x int8 path.  The first phase is host only and never reads group_list; the second
 // phase enqueues on the caller's CUDA stream and returns.
 #include <cstring>
+#include <type_traits>
 
 #include "acl_shim.h"
 #include "aclnnop/aclnn_grouped_matmul_finalize_routing_weight_nz.h"
@@ -64,9 +65,31 @@ aclOpExecutor *new_executor(const char *name)
     return e;
 }
 
+// Address the operator will use for tensor `t`: the tensor's own memory when it is contiguous; otherwise a contiguous
+// copy in the workspace tail, filled before the launch (and, for an output, copied back afterwards).  The address of a
+// copy is only known in the second phase: until then `*field` holds an aligned stand-in.
+template <typename P>
+void bind_tensor(aclOpExecutor *e, const aclTensor *t, P *field, bool is_output, bool contiguous_enough = false)
+{
+    if (!t) { *field = nullptr; return; }
+    if (t->contiguous() || contiguous_enough) { *field = (P)tensor_ptr(t); return; }
+    StagedView v;
+    v.dims = t->view_dims;
+    v.strides = t->strides;
+    v.elem = (int)dtype_size(t->dtype);
+    v.data = tensor_ptr(t);
+    v.ws_off = e->staged_bytes;
+    v.is_output = is_output;
+    v.field = (void **)field;  // the field is a pointer of some type; only its value is replaced
+    e->staged_bytes += ((size_t)t->numel() * v.elem + 255) / 256 * 256;
+    e->staged.push_back(v);
+    *field = (P)(uintptr_t)4096;
+}
+
 aclnnStatus finish_phase1(aclOpExecutor *e, uint64_t *workspaceSize, aclOpExecutor **executor)
 {
-    *workspaceSize = e->kind == aclOpExecutor::kNoop ? 0 : e->plan.ws_bytes;   // kInitRouting stores its size in plan.ws_bytes too
+    // kInitRouting stores its size in plan.ws_bytes too
+    *workspaceSize = e->kind == aclOpExecutor::kNoop ? 0 : e->plan.ws_bytes + e->staged_bytes;
     register_executor(e);
     *executor = e;
     return ACLNN_SUCCESS;
@@ -85,15 +108,28 @@ aclnnStatus run_executor(const char *op_name, void *workspace, uint64_t workspac
     if (std::strcmp(executor->op_name, op_name) != 0) {
         rc = fail(ACLNN_ERR_PARAM_INVALID, "%s: executor was built by %s.", op_name, executor->op_name);
     } else if (executor->kind != aclOpExecutor::kNoop) {
-        if (workspace_size < executor->plan.ws_bytes) {
+        const size_t need = executor->plan.ws_bytes + executor->staged_bytes;
+        if (workspace_size < need) {
             rc = fail(ACLNN_ERR_PARAM_INVALID, "%s: workspaceSize %llu is smaller than the %llu bytes required.", op_name,
-                      (unsigned long long)workspace_size, (unsigned long long)executor->plan.ws_bytes);
-        } else if (executor->plan.ws_bytes && !workspace) {
+                      (unsigned long long)workspace_size, (unsigned long long)need);
+        } else if (need && !workspace) {
             rc = fail(ACLNN_ERR_PARAM_NULLPTR, "%s: workspace must not be nullptr.", op_name);
         } else {
-            cudaError_t ce = executor->kind == aclOpExecutor::kInitRouting
-                                 ? init_routing_launch(executor->routing, workspace, workspace_size, static_cast<cudaStream_t>(stream))
-                                 : launch(executor->problem, executor->plan, workspace, workspace_size, static_cast<cudaStream_t>(stream));
+            cudaStream_t cs = static_cast<cudaStream_t>(stream);
+            char *tail = static_cast<char *>(workspace) + executor->plan.ws_bytes;
+            cudaError_t ce = cudaSuccess;
+            for (StagedView &v : executor->staged) {  // contiguous copies of the strided views (outputs too: rows the
+                *v.field = tail + v.ws_off;           // operator leaves alone must keep their contents)
+                if (ce == cudaSuccess) ce = view_copy_launch(v, tail + v.ws_off, true, cs);
+            }
+            if (executor->kind == aclOpExecutor::kGmm && executor->plan.path == kPathSm100 && !sm100_shape_ok(executor->problem))
+                executor->plan.path = kPathSimt;      // a workspace that is not 16-byte aligned cannot feed TMA
+            if (ce == cudaSuccess)
+                ce = executor->kind == aclOpExecutor::kInitRouting
+                         ? init_routing_launch(executor->routing, workspace, executor->plan.ws_bytes, cs)
+                         : launch(executor->problem, executor->plan, workspace, executor->plan.ws_bytes, cs);
+            for (StagedView &v : executor->staged)
+                if (v.is_output && ce == cudaSuccess) ce = view_copy_launch(v, tail + v.ws_off, false, cs);
             if (ce != cudaSuccess)
                 rc = fail(ACLNN_ERR_INNER, "%s: kernel launch failed: %s", op_name, cudaGetErrorString(ce));
         }
@@ -261,20 +297,17 @@ static aclnnStatus gmm_phase1(const char *kOp, bool force_nz,
     if (M == 0 || N == 0 || glLen == 0) return finish_phase1(e, workspaceSize, executor);
 
     const bool w_trans = !w_nz && !tw->contiguous() && is_transposed_last_two(tw);
-    if (!(tx->contiguous() && ty->contiguous() && (tw->contiguous() || w_trans || w_nz) && groupListOptional->contiguous() &&
-          (!tscale || tscale->contiguous()) && (!tpts || tpts->contiguous()) && (!tbias || tbias->contiguous()))) {
-        delete e;
-        return fail(ACLNN_ERR_PARAM_INVALID, "this build needs contiguous tensors (a transposed weight view excepted).");
-    }
+    // Strided views are served through contiguous copies in the workspace (Contiguous / ViewCopy of the reference,
+    // aclnn_grouped_matmul.cpp:1640-1667, 1802-1805); the transposed weight view and the fractal storage are read as they lie.
     Problem &p = e->problem;
-    p.x = static_cast<const int8_t *>(tensor_ptr(tx));
-    p.w = static_cast<const int8_t *>(tensor_ptr(tw));
-    p.w_scale = tscale ? tensor_ptr(tscale) : nullptr;
+    bind_tensor(e, tx, &p.x, false);
+    bind_tensor(e, tw, &p.w, false, w_trans || w_nz);
+    bind_tensor(e, tscale, &p.w_scale, false);
     p.w_scale_dtype = tscale ? (int)tscale->dtype : kF32;
-    p.x_scale = tpts ? static_cast<const float *>(tensor_ptr(tpts)) : nullptr;
-    p.bias = tbias ? tensor_ptr(tbias) : nullptr;
+    bind_tensor(e, tpts, &p.x_scale, false);
+    bind_tensor(e, tbias, &p.bias, false);
     p.bias_dtype = tbias ? (int)tbias->dtype : kNone;
-    p.group_list = static_cast<const int64_t *>(tensor_ptr(groupListOptional));
+    bind_tensor(e, groupListOptional, &p.group_list, false);
     p.gl_len = (int)(E == 1 ? 1 : glLen);
     p.gl_type = (int)groupListType;
     p.M = M; p.K = K; p.N = N; p.E = E;
@@ -284,7 +317,7 @@ static aclnnStatus gmm_phase1(const char *kOp, bool force_nz,
     p.act_type = int32_out ? 0 : (int)actType;
     p.mode = int32_out ? kModeInt32 : kModeDequantBf16;
     p.out_f16 = ty->dtype == ACL_FLOAT16 ? 1 : 0;
-    p.out0 = tensor_ptr(ty);
+    bind_tensor(e, ty, &p.out0, true);
     e->kind = aclOpExecutor::kGmm;
     make_plan(p, &e->plan);
     return finish_phase1(e, workspaceSize, executor);
@@ -446,26 +479,20 @@ aclnnStatus aclnnMoeInitRoutingV3GetWorkspaceSize(const aclTensor *x, const aclT
     aclOpExecutor *e = new_executor(kOp);
     GMM_REQUIRE(e != nullptr, ACLNN_ERR_INNER_CREATE_EXECUTOR, "cannot create executor.");
     if (n * k == 0 || h == 0) return finish_phase1(e, workspaceSize, executor);
-    for (const aclTensor *t : {x, expertIdx, scaleOptional, expandedXOut, expandedRowIdxOut, expertTokensCountOrCumsumOut, expandedScaleOut}) {
-        if (t && !t->contiguous()) {
-            delete e;
-            return fail(ACLNN_ERR_PARAM_INVALID, "this build needs contiguous tensors.");
-        }
-    }
     InitRoutingProblem &r = e->routing;
-    r.x = tensor_ptr(x);
+    bind_tensor(e, x, &r.x, false);
     r.x_dtype = (int)x->dtype;
-    r.expert_idx = static_cast<const int *>(tensor_ptr(expertIdx));
-    r.scale = scaleOptional ? static_cast<const float *>(tensor_ptr(scaleOptional)) : nullptr;
+    bind_tensor(e, expertIdx, &r.expert_idx, false);
+    bind_tensor(e, scaleOptional, &r.scale, false);
     r.n = n; r.k = k; r.h = h;
     r.expert_num = expertNum; r.expert_start = eStart; r.expert_end = eEnd;
     r.quant = quantMode == 1;
     r.row_idx_type = (int)rowIdxType;
     r.count_type = (int)expertTokensNumType;
-    r.expanded_x = tensor_ptr(expandedXOut);
-    r.expanded_row_idx = static_cast<int *>(tensor_ptr(expandedRowIdxOut));
-    r.counts_out = static_cast<long long *>(tensor_ptr(expertTokensCountOrCumsumOut));
-    r.expanded_scale = static_cast<float *>(tensor_ptr(expandedScaleOut));
+    bind_tensor(e, expandedXOut, &r.expanded_x, true);
+    bind_tensor(e, expandedRowIdxOut, &r.expanded_row_idx, true);
+    bind_tensor(e, expertTokensCountOrCumsumOut, &r.counts_out, true);
+    bind_tensor(e, expandedScaleOut, &r.expanded_scale, true);
     e->kind = aclOpExecutor::kInitRouting;
     e->plan.ws_bytes = init_routing_workspace_bytes(r);
     return finish_phase1(e, workspaceSize, executor);
@@ -582,34 +609,28 @@ static aclnnStatus finalize_routing_phase1(const char *kOp, const aclTensor *x1,
     aclOpExecutor *e = new_executor(kOp);
     GMM_REQUIRE(e != nullptr, ACLNN_ERR_INNER_CREATE_EXECUTOR, "cannot create executor.");
     if (out->empty()) return finish_phase1(e, workspaceSize, executor);
-    for (const aclTensor *t : {x1, scale, bias, pertokenScale, groupList, sharedInput, logit, rowIndex, (const aclTensor *)out}) {
-        if (t && !t->contiguous()) {
-            delete e;
-            return fail(ACLNN_ERR_PARAM_INVALID, "this build needs contiguous tensors.");
-        }
-    }
     Problem &p = e->problem;
-    p.x = static_cast<const int8_t *>(tensor_ptr(x1));
-    p.w = static_cast<const int8_t *>(tensor_ptr(x2));
-    p.w_scale = tensor_ptr(scale);
+    bind_tensor(e, x1, &p.x, false);
+    bind_tensor(e, x2, &p.w, false, true);   // the fractal storage is read as it lies
+    bind_tensor(e, scale, &p.w_scale, false);
     p.w_scale_dtype = (int)scale->dtype;
-    p.x_scale = pertokenScale ? static_cast<const float *>(tensor_ptr(pertokenScale)) : nullptr;
-    p.bias = bias ? tensor_ptr(bias) : nullptr;
+    bind_tensor(e, pertokenScale, &p.x_scale, false);
+    bind_tensor(e, bias, &p.bias, false);
     p.bias_dtype = bias ? kBF16 : kNone;
-    p.group_list = static_cast<const int64_t *>(tensor_ptr(groupList));
+    bind_tensor(e, groupList, &p.group_list, false);
     p.gl_len = (int)E;
     p.gl_type = 1;
     p.M = M; p.K = K; p.N = N; p.E = E;
     p.w_layout = 2;
     p.mode = kModeDequantBf16;
-    p.out0 = tensor_ptr(out);
+    bind_tensor(e, out, &p.out0, true);
     p.combine = 1;
-    p.logit = logit ? static_cast<const float *>(tensor_ptr(logit)) : nullptr;
-    p.row_index = tensor_ptr(rowIndex);
+    bind_tensor(e, logit, &p.logit, false);
+    bind_tensor(e, rowIndex, &p.row_index, false);
     p.row_index_i32 = rowIndex->dtype == ACL_INT32;
     p.scatter_add = (sharedInput || logit) ? 1 : 0;   // grouped_matmul_finalize_routing_base_tiling.cpp:296-300
     p.out_rows = BS;
-    p.shared_input = sharedInput ? tensor_ptr(sharedInput) : nullptr;
+    bind_tensor(e, sharedInput, &p.shared_input, false);
     p.shared_rows = sharedRows;
     p.shared_offset = sharedInputOffset;
     p.shared_weight = sharedInputWeight;
@@ -724,25 +745,20 @@ static aclnnStatus swiglu_phase1(const char *kOp, bool force_nz, const aclTensor
     GMM_REQUIRE(e != nullptr, ACLNN_ERR_INNER_CREATE_EXECUTOR, "cannot create executor.");
     // Empty tensors (aclnn_grouped_matmul_swiglu_quant.cpp:425-429)
     if (output->empty() || groupList->empty() || outputScale->empty()) return finish_phase1(e, workspaceSize, executor);
-    if (!(x->contiguous() && (weight->contiguous() || w_nz) && weightScale->contiguous() && xScale->contiguous() &&
-          groupList->contiguous() && output->contiguous() && outputScale->contiguous())) {
-        delete e;
-        return fail(ACLNN_ERR_PARAM_INVALID, "this build needs contiguous tensors.");
-    }
     Problem &p = e->problem;
-    p.x = static_cast<const int8_t *>(tensor_ptr(x));
-    p.w = static_cast<const int8_t *>(tensor_ptr(weight));
-    p.w_scale = tensor_ptr(weightScale);
+    bind_tensor(e, x, &p.x, false);
+    bind_tensor(e, weight, &p.w, false, w_nz);
+    bind_tensor(e, weightScale, &p.w_scale, false);
     p.w_scale_dtype = (int)weightScale->dtype;
-    p.x_scale = static_cast<const float *>(tensor_ptr(xScale));
-    p.group_list = static_cast<const int64_t *>(tensor_ptr(groupList));
+    bind_tensor(e, xScale, &p.x_scale, false);
+    bind_tensor(e, groupList, &p.group_list, false);
     p.gl_len = (int)glLen;
     p.gl_type = 0;
     p.M = M; p.K = K; p.N = N; p.E = E;
     p.w_layout = w_nz ? 2 : 0;
     p.mode = kModeSwigluQuant;
-    p.out0 = tensor_ptr(output);
-    p.out1 = tensor_ptr(outputScale);
+    bind_tensor(e, output, &p.out0, true);
+    bind_tensor(e, outputScale, &p.out1, true);
     e->kind = aclOpExecutor::kGmm;
     make_plan(p, &e->plan);
     return finish_phase1(e, workspaceSize, executor);

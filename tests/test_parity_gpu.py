@@ -617,3 +617,78 @@ def test_init_routing_feeds_the_grouped_gemms(oracle):
     err = np.abs(y.cpu().numpy().astype(np.float64) - fin["y"])
     # a 1-LSB difference of the int8 intermediate moves an output by about one part in 127 of a term
     assert (err <= 4 * 2.0 ** -23 * fin["abs_sum"] + (np.count_nonzero(d) > 0) * 2e-2 * fin["abs_sum"]).all()
+
+
+# ----------------------------------------------------------------------------------------------------------
+# non-contiguous views: inputs are made contiguous inside the executor, results are copied back into strided outputs
+# ----------------------------------------------------------------------------------------------------------
+
+def _strided(tensor_2d):
+    """The same values as a view over every second column of a wider buffer."""
+    wide = torch.empty((tensor_2d.shape[0], 2 * tensor_2d.shape[1]), dtype=tensor_2d.dtype, device=tensor_2d.device)
+    view = wide[:, ::2]
+    view.copy_(tensor_2d)
+    assert not view.is_contiguous()
+    return view
+
+
+def test_strided_views_grouped_matmul(oracle):
+    import ops_transformer_b200 as ops
+    dev = _dev()
+    counts = [70, 0, 200]
+    M = sum(counts) + 6
+    x, w, ws, xs = make_inputs(M, 256, 512, 3, seed=80)
+    gl = np.cumsum(counts)
+    ref = oracle.gmm_w8a8(x, w, ws, xs, gl, 0)["y"]
+    t = lambda a: torch.from_numpy(a).to(dev)  # noqa: E731
+    out_wide = torch.full((M, 1024), 0x7fc1, dtype=torch.int16, device=dev)
+    out = out_wide.view(torch.bfloat16)[:, ::2]
+    xs_wide = torch.zeros((M, 3), dtype=torch.float32, device=dev)
+    xs_wide[:, 1] = t(xs)
+    y, wsb = ops.grouped_matmul_v4(_strided(t(x)), t(w), _strided(t(ws)), xs_wide[:, 1], t(gl), out=out, return_workspace=True)
+    ops.check_status(wsb)
+    bits = out_wide.cpu().numpy().view(np.uint16)
+    rows = sum(counts)
+    assert np.array_equal(bits[:rows, ::2], ref[:rows])
+    assert (bits[rows:, ::2] == 0x7fc1).all(), "rows outside group_list must keep their contents"
+    assert (bits[:, 1::2] == 0x7fc1).all(), "the gaps of the strided output must not be written"
+
+
+def test_strided_views_swiglu_quant(oracle):
+    import ops_transformer_b200 as ops
+    dev = _dev()
+    x, w, ws, xs = make_inputs(200, 256, 1024, 2, seed=81)
+    gl = np.array([120, 190], np.int64)
+    ref = oracle.swiglu_quant(x, w, ws, xs, gl)
+    t = lambda a: torch.from_numpy(a).to(dev)  # noqa: E731
+    q_wide = torch.full((200, 1024), -77, dtype=torch.int8, device=dev)
+    qs_wide = torch.full((200, 2), -5.0, dtype=torch.float32, device=dev)
+    _, _, wsb = ops.grouped_matmul_swiglu_quant(_strided(t(x)), t(w), t(ws), t(xs), t(gl), output=q_wide[:, ::2], output_scale=qs_wide[:, 0],
+                                                return_workspace=True)
+    ops.check_status(wsb)
+    qg, qsg = q_wide.cpu().numpy(), qs_wide.cpu().numpy()
+    rel = np.abs(qsg[:190, 0] - ref["q_scale"][:190]) / ref["q_scale"][:190]
+    d = np.abs(qg[:190, ::2].astype(np.int32) - ref["q"][:190].astype(np.int32))
+    assert rel.max() <= QSCALE_RTOL and d.max() <= 1 and np.count_nonzero(d) / d.size <= Q_LSB_FRACTION
+    assert (qg[190:] == -77).all() and (qg[:, 1::2] == -77).all() and (qsg[190:] == -5.0).all() and (qsg[:, 1] == -5.0).all()
+
+
+def test_strided_views_init_routing(oracle):
+    import ops_transformer_b200 as ops
+    dev = _dev()
+    rng = np.random.default_rng(82)
+    n, k, h, E = 50, 2, 64, 8
+    xb = oracle.f32_to_bf16_bits(rng.standard_normal((n, h)).astype(np.float32))
+    idx = np.stack([rng.permutation(E)[:k] for _ in range(n)]).astype(np.int32)
+    ref = oracle.moe_init_routing_v3(xb, idx, E, (0, E), True)
+    x_t = _strided(torch.from_numpy(xb.view(np.int16)).to(dev).view(torch.bfloat16))
+    idx_t = _strided(torch.from_numpy(idx).to(dev))
+    ex_wide = torch.full((n * k, 2 * h), -77, dtype=torch.int8, device=dev)
+    ri = torch.empty((n * k,), dtype=torch.int32, device=dev)
+    cnt = torch.empty((E,), dtype=torch.int64, device=dev)
+    es = torch.empty((n * k,), dtype=torch.float32, device=dev)
+    ops.moe_init_routing_v3(x_t, idx_t, expert_num=E, active_expert_range=(0, E), quant_mode=1, outputs=(ex_wide[:, ::2], ri, cnt, es))
+    torch.cuda.synchronize()
+    got = ex_wide.cpu().numpy()
+    assert np.array_equal(got[:, ::2], ref["expanded_x"]) and (got[:, 1::2] == -77).all()
+    assert np.array_equal(ri.cpu().numpy(), ref["expanded_row_idx"]) and np.array_equal(es.cpu().numpy(), ref["expanded_scale"])
