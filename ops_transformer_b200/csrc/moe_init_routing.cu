@@ -270,9 +270,39 @@ __global__ void __launch_bounds__(128) routing_quant_kernel(const RoutingParams 
     }
 }
 
-__device__ __forceinline__ uint32_t pack4(int8_t a, int8_t b, int8_t c, int8_t d)
+// The same value as quant_trunc_round in five instructions after the division, for the register-tiled kernel.  With
+// |v / scale| <= 127 (scale is the row maximum over 127): fp16 towards zero keeps 11 significant bits, i.e. clears the low
+// 13 mantissa bits of the fp32 quotient (below 2^-14, where fp16 is subnormal, both forms end as 0); adding 0.5 with the
+// quotient's sign is exact and truncation then rounds ties away from zero; 0 / 0 stays NaN and converts to 0.
+// `rcp` is the correctly rounded reciprocal of `scale` (or 0 to ask for the plain division): the quotient is then formed
+// with fused multiply-adds, q0 = v * rcp, twice q = q + (v - q * scale) * rcp.  After the first correction q is a faithful
+// rounding of v / scale, and with an exact residual and a correctly rounded reciprocal the second correction yields the
+// correctly rounded quotient (Markstein's division theorem), i.e. the value __fdiv_rn returns, in five instructions.
+__device__ __forceinline__ float exact_div(float v, float scale, float rcp)
 {
-    return (uint32_t)(uint8_t)a | ((uint32_t)(uint8_t)b << 8) | ((uint32_t)(uint8_t)c << 16) | ((uint32_t)(uint8_t)d << 24);
+    if (rcp == 0.0f) return __fdiv_rn(v, scale);
+    float q = __fmul_rn(v, rcp);
+    q = __fmaf_rn(__fmaf_rn(-q, scale, v), rcp, q);
+    q = __fmaf_rn(__fmaf_rn(-q, scale, v), rcp, q);
+    return q;
+}
+
+// 1 / scale for exact_div, or 0 where the shortcut is not safe (zero, denormal-range or huge scales).
+__device__ __forceinline__ float exact_div_rcp(float scale)
+{
+    return (scale > 1e-30f && scale < 1e30f) ? __frcp_rn(scale) : 0.0f;
+}
+
+__device__ __forceinline__ int quant_fast(float v, float scale, float rcp)
+{
+    const uint32_t b = __float_as_uint(exact_div(v, scale, rcp)) & 0xffffe000u;
+    const float r = __fadd_rn(__uint_as_float(b), __uint_as_float(0x3f000000u | (b & 0x80000000u)));
+    return max(-128, min(127, __float2int_rz(r)));  // the clamp only matters for rows of denormals, whose scale underflows
+}
+
+__device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d)
+{
+    return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
 }
 
 __device__ __forceinline__ float block_max_128(float v, float *red)
@@ -344,12 +374,13 @@ __global__ void __launch_bounds__(128) routing_quant_token_kernel(const RoutingP
 #pragma unroll
             for (int e = 0; e < VEC; ++e) amax = fmaxf(amax, fabsf(v[i][e]));
         scale = __fdiv_rn(block_max_128(amax, red), 127.0f);
+        const float rcp = exact_div_rcp(scale);
 #pragma unroll
         for (int i = 0; i < NCH; ++i)
 #pragma unroll
             for (int e4 = 0; e4 < VEC; e4 += 4)
-                w[i][e4 / 4] = pack4(quant_trunc_round(v[i][e4], scale), quant_trunc_round(v[i][e4 + 1], scale),
-                                     quant_trunc_round(v[i][e4 + 2], scale), quant_trunc_round(v[i][e4 + 3], scale));
+                w[i][e4 / 4] = pack4(quant_fast(v[i][e4], scale, rcp), quant_fast(v[i][e4 + 1], scale, rcp),
+                                     quant_fast(v[i][e4 + 2], scale, rcp), quant_fast(v[i][e4 + 3], scale, rcp));
     }
     for (int s = 0; s < p.k; ++s) {
         const long long j = (long long)token * p.k + s;
@@ -371,6 +402,7 @@ __global__ void __launch_bounds__(128) routing_quant_token_kernel(const RoutingP
                 }
             }
             scale = __fdiv_rn(block_max_128(amax, red), 127.0f);
+            const float rcp = exact_div_rcp(scale);
 #pragma unroll
             for (int i = 0; i < NCH; ++i) {  // the products are formed again: keeping them would cost 64 registers
                 const int c = threadIdx.x + i * 128;
@@ -378,8 +410,8 @@ __global__ void __launch_bounds__(128) routing_quant_token_kernel(const RoutingP
 #pragma unroll
                     for (int e4 = 0; e4 < VEC; e4 += 4) {
                         const float4 m = __ldg(reinterpret_cast<const float4 *>(sm + (size_t)c * VEC + e4));
-                        w[i][e4 / 4] = pack4(quant_trunc_round(__fmul_rn(v[i][e4], m.x), scale), quant_trunc_round(__fmul_rn(v[i][e4 + 1], m.y), scale),
-                                             quant_trunc_round(__fmul_rn(v[i][e4 + 2], m.z), scale), quant_trunc_round(__fmul_rn(v[i][e4 + 3], m.w), scale));
+                        w[i][e4 / 4] = pack4(quant_fast(__fmul_rn(v[i][e4], m.x), scale, rcp), quant_fast(__fmul_rn(v[i][e4 + 1], m.y), scale, rcp),
+                                             quant_fast(__fmul_rn(v[i][e4 + 2], m.z), scale, rcp), quant_fast(__fmul_rn(v[i][e4 + 3], m.w), scale, rcp));
                     }
                 }
             }
