@@ -44,6 +44,35 @@ def main():
         fn = name + ".npz"
         np.savez_compressed(os.path.join(HERE, fn), **out)
         cases.append(dict(file=fn, op=op, group_list_type=gl_type, M=M, K=K, N=N, E=E, seed=seed))
+    # the producer and the consumer either side of the two operators
+    rng = np.random.default_rng(7)
+    n, k, h, E = 24, 2, 64, 6
+    xb = O.f32_to_bf16_bits(rng.standard_normal((n, h)).astype(np.float32))
+    idx = np.stack([rng.permutation(E)[:k] for _ in range(n)]).astype(np.int32)
+    smooth = rng.uniform(0.5, 2.0, size=(4, h)).astype(np.float32)
+    r = O.moe_init_routing_v3(xb, idx, E, (1, 5), True, row_idx_type=0, count_type=2, scale=smooth)
+    np.savez_compressed(os.path.join(HERE, "init_routing_quant_small.npz"), x_bf16_bits=xb, expert_idx=idx, scale=smooth,
+                        expanded_x=r["expanded_x"], expanded_row_idx=r["expanded_row_idx"], counts=r["counts"],
+                        expanded_scale=r["expanded_scale"], rows=np.int64(r["rows"]))
+    cases.append(dict(file="init_routing_quant_small.npz", op="moe_init_routing_v3", n=n, k=k, h=h, E=E, active_range=[1, 5],
+                      quant=1, row_idx_type=0, count_type=2, fill=dict(expanded_x=-77, expanded_row_idx=-9, counts=-9, expanded_scale=-5.0)))
+    M, K, N, E, topk = 64, 64, 256, 3, 4
+    x = synth.int8_tensor((M, K), 120, 1)
+    w = synth.int8_tensor((E, K, N), 120, 2)
+    ws = synth.scale_tensor((E, N), 120, 3)
+    xs = synth.scale_tensor((M,), 120, 4)
+    counts = np.array([20, 0, 40], np.int64)
+    ri = (rng.permutation(M) % (M // topk)).astype(np.int64)
+    logit = rng.uniform(0.05, 0.6, size=M).astype(np.float32)
+    shared = O.f32_to_bf16_bits(rng.uniform(-40, 40, size=(8, N)).astype(np.float32))
+    bias = O.f32_to_bf16_bits(rng.uniform(-20, 20, size=(E, N)).astype(np.float32))
+    f = O.gmm_finalize_routing(x, w, ws, xs, counts, ri, M // topk, bias=bias, shared_input=shared, shared_offset=4, shared_weight=0.5,
+                               logit=logit)
+    np.savez_compressed(os.path.join(HERE, "finalize_routing_small.npz"), x=x, w=w, w_scale=ws, x_scale=xs, group_list=counts,
+                        row_index=ri, logit=logit, shared_bf16_bits=shared, bias_bf16_bits=bias, y=f["y"], abs_sum=f["abs_sum"])
+    cases.append(dict(file="finalize_routing_small.npz", op="grouped_matmul_finalize_routing", M=M, K=K, N=N, E=E, batch=M // topk,
+                      shared_offset=4, shared_weight=0.5, group_list_type=1,
+                      note="y is the sum in row order; an unordered fp32 sum may differ by 4 * 2^-23 * abs_sum"))
     with open(os.path.join(HERE, "manifest.json"), "w") as f:
         json.dump(dict(source="oracle/gmm_oracle.c (the reference has no golden vectors for these operators)",
                        cases=cases), f, indent=1)

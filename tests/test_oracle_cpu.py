@@ -295,7 +295,20 @@ def test_golden_fixtures(oracle):
     assert manifest["cases"], "no golden cases"
     for case in manifest["cases"]:
         d = np.load(os.path.join(GOLDEN, case["file"]))
+        if case["op"] == "moe_init_routing_v3":
+            r = oracle.moe_init_routing_v3(d["x_bf16_bits"], d["expert_idx"], case["E"], tuple(case["active_range"]), bool(case["quant"]),
+                                           row_idx_type=case["row_idx_type"], count_type=case["count_type"], scale=d["scale"])
+            for key in ("expanded_x", "expanded_row_idx", "counts", "expanded_scale"):
+                assert np.array_equal(r[key], d[key]), key
+            assert r["rows"] == int(d["rows"])
+            continue
         x, w, ws, xs, gl = d["x"], d["w"], d["w_scale"], d["x_scale"], d["group_list"]
+        if case["op"] == "grouped_matmul_finalize_routing":
+            r = oracle.gmm_finalize_routing(x, w, ws, xs, gl, d["row_index"], case["batch"], bias=d["bias_bf16_bits"],
+                                            shared_input=d["shared_bf16_bits"], shared_offset=case["shared_offset"],
+                                            shared_weight=case["shared_weight"], logit=d["logit"])
+            assert np.array_equal(r["y"], d["y"])
+            continue
         if case["op"] == "grouped_matmul":
             r = oracle.gmm_w8a8(x, w, ws, xs, gl, int(case["group_list_type"]), want_acc=True)
             assert np.array_equal(r["acc"], d["acc"]) and np.array_equal(r["y"], d["y_bf16_bits"])

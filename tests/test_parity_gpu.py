@@ -692,3 +692,63 @@ def test_strided_views_init_routing(oracle):
     got = ex_wide.cpu().numpy()
     assert np.array_equal(got[:, ::2], ref["expanded_x"]) and (got[:, 1::2] == -77).all()
     assert np.array_equal(ri.cpu().numpy(), ref["expanded_row_idx"]) and np.array_equal(es.cpu().numpy(), ref["expanded_scale"])
+
+
+# ----------------------------------------------------------------------------------------------------------
+# the committed golden fixtures, straight through the C ABI (no oracle involved)
+# ----------------------------------------------------------------------------------------------------------
+
+def test_golden_fixtures_on_the_gpu():
+    import json
+    import os
+
+    import ops_transformer_b200 as ops
+    dev = _dev()
+    golden = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    with open(os.path.join(golden, "manifest.json")) as f:
+        manifest = json.load(f)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)  # noqa: E731
+    bf = lambda a: torch.from_numpy(np.ascontiguousarray(a).view(np.int16)).to(dev).view(torch.bfloat16)  # noqa: E731
+    seen = set()
+    for case in manifest["cases"]:
+        d = np.load(os.path.join(golden, case["file"]))
+        seen.add(case["op"])
+        if case["op"] == "moe_init_routing_v3":
+            n, k, h, E = case["n"], case["k"], case["h"], case["E"]
+            fill = case["fill"]
+            outs = (torch.full((n * k, h), fill["expanded_x"], dtype=torch.int8, device=dev),
+                    torch.full((n * k,), fill["expanded_row_idx"], dtype=torch.int32, device=dev),
+                    torch.full(d["counts"].shape, fill["counts"], dtype=torch.int64, device=dev),
+                    torch.full((n * k,), fill["expanded_scale"], dtype=torch.float32, device=dev))
+            ops.moe_init_routing_v3(bf(d["x_bf16_bits"]), t(d["expert_idx"]), expert_num=E, active_expert_range=tuple(case["active_range"]),
+                                    quant_mode=1, scale=t(d["scale"]), expert_tokens_num_type=case["count_type"],
+                                    row_idx_type=case["row_idx_type"], outputs=outs)
+            torch.cuda.synchronize()
+            for got, key in zip(outs, ("expanded_x", "expanded_row_idx", "counts", "expanded_scale")):
+                assert np.array_equal(got.cpu().numpy(), d[key]), (case["file"], key)
+            continue
+        x, w, ws, xs, gl = d["x"], d["w"], d["w_scale"], d["x_scale"], d["group_list"]
+        if case["op"] == "grouped_matmul_finalize_routing":
+            y = ops.grouped_matmul_finalize_routing(t(x), t(nd_to_nz(w)), t(ws), t(gl), t(d["row_index"]), case["batch"],
+                                                    bias=bf(d["bias_bf16_bits"]), pertoken_scale=t(xs), shared_input=bf(d["shared_bf16_bits"]),
+                                                    logit=t(d["logit"]), shared_input_weight=case["shared_weight"],
+                                                    shared_input_offset=case["shared_offset"])
+            torch.cuda.synchronize()
+            err = np.abs(y.cpu().numpy().astype(np.float64) - d["y"])
+            assert (err <= 4 * 2.0 ** -23 * d["abs_sum"] + 1e-30).all(), case["file"]
+        elif case["op"] == "grouped_matmul":
+            glt = int(case["group_list_type"])
+            y = ops.grouped_matmul_v4(t(x), t(w), t(ws), t(xs), t(gl), group_list_type=glt)
+            acc = ops.grouped_matmul_v4(t(x), t(w), None, None, t(gl), group_list_type=glt, out_dtype=torch.int32)
+            torch.cuda.synchronize()
+            rows = int(gl[-1]) if glt == 0 else int(gl.sum())
+            assert np.array_equal(acc.cpu().numpy()[:rows], d["acc"][:rows]), case["file"]
+            assert np.array_equal(_bf16_bits(y)[:rows], d["y_bf16_bits"][:rows]), case["file"]
+        else:
+            q, qs = ops.grouped_matmul_swiglu_quant(t(x), t(w), t(ws), t(xs), t(gl))
+            torch.cuda.synchronize()
+            rows = int(gl[-1])
+            rel = np.abs(qs.cpu().numpy()[:rows] - d["q_scale"][:rows]) / d["q_scale"][:rows]
+            dd = np.abs(q.cpu().numpy()[:rows].astype(np.int32) - d["q"][:rows].astype(np.int32))
+            assert rel.max() <= QSCALE_RTOL and dd.max() <= 1 and np.count_nonzero(dd) <= max(1, int(Q_LSB_FRACTION * dd.size)), case["file"]
+    assert seen == {"grouped_matmul", "grouped_matmul_swiglu_quant", "moe_init_routing_v3", "grouped_matmul_finalize_routing"}
