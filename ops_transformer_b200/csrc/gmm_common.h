@@ -63,6 +63,7 @@ struct Plan {
     int path = kPathSimt;
     int num_sms = 0;
     int ctas = 1;                       // 1 = one CTA per 128-row tile, 2 = CTA pairs on 256-row tiles
+    bool hybrid = false;                // with ctas == 2: a second launch with 128-row tiles takes trailing blocks of <= 128 rows
     size_t ws_bytes = 0;
     size_t off_status = 0, off_amax = 0, off_stage = 0, off_done = 0;
     size_t zero_bytes = 0;              // leading bytes of the workspace cleared at launch

@@ -232,13 +232,22 @@ void make_plan(const Problem &p, Plan *plan)
         if (e[0] == '1') plan->ctas = 1;
         if (e[0] == '2') plan->ctas = 2;
     }
+    // A second launch with 128-row tiles for the trailing blocks pays only when there are many of them: about half of the
+    // groups end in such a block, and their tiles should fill the GPU several times over (measured: with 32 groups it loses
+    // 5-8 %).  GMM_B200_HYBRID=0|1 overrides.
+    {
+        const long long n_tiles = p.mode == kModeSwigluQuant ? (p.N / 2 + 127) / 128 : (p.N + 255) / 256;
+        const int sms = device_sm_count();
+        plan->hybrid = plan->ctas == 2 && (long long)p.gl_len * n_tiles >= 16ll * (sms > 0 ? sms : 148);
+    }
+    if (const char *e = getenv("GMM_B200_HYBRID")) plan->hybrid = plan->ctas == 2 && e[0] != '0';
     plan->off_status = 0;
     size_t off = 256;
     plan->off_amax = off;
     if (p.mode == kModeSwigluQuant && plan->path == kPathSm100) {
         off += align_up((size_t)p.M * 4, 256);
-        plan->off_done = off;  // one counter per 128-row block; every group can add one partial block
-        off += align_up(((size_t)(p.M + 127) / 128 + (size_t)p.gl_len + 1) * 4, 256);
+        plan->off_done = off;  // one counter per row block of a tile; every group can add a partial block in each of two launches
+        off += align_up(((size_t)(p.M + 127) / 128 + 2 * (size_t)p.gl_len + 2) * 4, 256);
         plan->zero_bytes = off;
         plan->off_stage = off;
         off += align_up((size_t)p.M * (size_t)(p.N / 2) * 4, 256);

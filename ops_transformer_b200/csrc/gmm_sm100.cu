@@ -112,7 +112,9 @@ struct KParams {
     int scatter_add;           // 1: atomic adds (shared-expert rows and logits given), 0: plain stores
     long long out_rows;        // rows of the fp32 result; indices outside [0, out_rows) are skipped
     unsigned *amax_bits;  // [M] row max of |S| as float bits (swiglu)
-    int *rb_counter;      // per 128-row block: number of N tiles that have stored their part (swiglu)
+    int *rb_counter;      // per row block of a tile: number of N tiles that have stored their part (swiglu)
+    int rb_base;          // first counter of this launch (two launches share the array)
+    int part;             // 0: all rows; 1: every group without its trailing rows if those are at most 128; 2: only those
     int8_t *q_out;        // int8 [M, N/2] (swiglu)
     float *q_scale_out;   // fp32 [M] (swiglu)
     int *status;
@@ -394,6 +396,15 @@ __device__ void build_schedule(Shared *sh, const KParams &p, int tile_m)
             if (start < 0) { rows += start; start = 0; if (rows < 0) rows = 0; }
             if (start > p.M) { start = p.M; rows = 0; }
             if (start + rows > p.M) rows = p.M - start;
+            if (p.part != 0) {
+                // A 256-row tile on a trailing block of at most 128 rows would leave the second CTA of the pair idle:
+                // the pair launch (part 1) stops short of such a block and a launch with 128-row tiles (part 2) takes it.
+                const long long r = rows % (2 * BM);
+                const bool small_tail = r > 0 && r <= BM;
+                if (p.part == 1) { if (small_tail) rows -= r; }
+                else if (small_tail) { start += rows - r; rows = r; }
+                else rows = 0;
+            }
             sh->row_start[g] = (int)start;
             sh->rows[g] = (int)rows;
             tsum += (int)((rows + tile_m - 1) / tile_m) * p.n_tiles;
@@ -986,12 +997,12 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                 __threadfence();
                 mbar_arrive(&sh->tile_sync[0]);
                 if (!mbar_wait(&sh->tile_sync[0], (uint32_t)it & 1u, sh, p.status, 600)) break;
-                if (te == 0) atomicAdd(p.rb_counter + t / p.n_tiles, 1);
+                if (te == 0) atomicAdd(p.rb_counter + p.rb_base + t / p.n_tiles, 1);
                 const int shares = p.n_tiles * CTAS;  // every CTA that worked on the row block requantises one share of its rows
                 ok = settle_pending(p, sh, pend, settle_it, te, shares);
                 const int share = tl.n_idx * CTAS + (int)rank;
                 pend.valid = 1;
-                pend.rb = t / p.n_tiles;
+                pend.rb = p.rb_base + t / p.n_tiles;
                 pend.r_begin = tl.row0 + (int)((long long)tl.rows * share / shares);
                 pend.r_end = tl.row0 + (int)((long long)tl.rows * (share + 1) / shares);
             }
@@ -1197,9 +1208,19 @@ cudaError_t sm100_launch(const Problem &p, Plan &plan, void *workspace, cudaStre
     for (int i = 0; i < 8; ++i) kp.out_peers[i] = i < kp.num_peers ? p.out_peers[i] : nullptr;
     if (kp.num_peers > 0 && epi != kEpiScatter) return cudaErrorInvalidValue;
     if (g_ev_start) cudaEventRecord(g_ev_start, stream);
-    if (p.mode == kModeSwigluQuant) e = launch_layout<kModeSwigluQuant>(p.w_layout, epi, plan, kp, stream);
-    else if (p.mode == kModeInt32) e = launch_layout<kModeInt32>(p.w_layout, epi, plan, kp, stream);
-    else e = launch_layout<kModeDequantBf16>(p.w_layout, epi, plan, kp, stream);
+    // Pair tiles for the bulk of every group, then (plan.hybrid) 128-row tiles for the trailing blocks a pair would half waste.
+    const int launches = plan.ctas == 2 && plan.hybrid ? 2 : 1;
+    Plan one = plan;
+    for (int i = 0; i < launches; ++i) {
+        kp.part = launches == 2 ? i + 1 : 0;
+        kp.rb_base = i == 0 ? 0 : (int)((p.M + 2 * BM - 1) / (2 * BM)) + p.gl_len + 1;
+        const Plan &pl = i == 0 ? plan : one;
+        if (i == 1) one.ctas = 1;
+        if (p.mode == kModeSwigluQuant) e = launch_layout<kModeSwigluQuant>(p.w_layout, epi, pl, kp, stream);
+        else if (p.mode == kModeInt32) e = launch_layout<kModeInt32>(p.w_layout, epi, pl, kp, stream);
+        else e = launch_layout<kModeDequantBf16>(p.w_layout, epi, pl, kp, stream);
+        if (e != cudaSuccess) break;
+    }
     if (g_ev_stop) cudaEventRecord(g_ev_stop, stream);
     return e;
 }
