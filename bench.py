@@ -212,9 +212,10 @@ def bench_single(args):
     torch.cuda.set_device(dev)
     L = _lib.lib()
     name = args.workload or "c2"
-    finalize = name == "c3_finalize"  # the down projection of c3 fused with the weighted combine (finalize routing)
-    cfg = synth.CONFIGS["c3" if finalize else name]
-    counts = synth.config_counts("c3" if finalize else name, 0)
+    finalize = name in ("c3_finalize", "c3_finalize_small")  # the down projection of c3 fused with the weighted combine
+    base = name.replace("_finalize", "")
+    cfg = synth.CONFIGS[base]
+    counts = synth.config_counts(base, 0)
     E, K, N = cfg["E"], cfg["K"], cfg["N"]
     M = int(counts.sum())
     swiglu = name in ("c2", "c4_swiglu", "c2_small", "c4_swiglu_small")
