@@ -308,7 +308,17 @@ def bench_single(args):
     ho1 = torch.empty_like(out1, device="cpu").pin_memory() if out1 is not None else None
     dx, dxs, dgl = torch.empty_like(x), torch.empty_like(xs), torch.empty_like(gl)
 
+    pipe = None
+    if not finalize and args.e2e_pieces > 1:
+        # the call a user with host-resident rows makes: the operator split by experts into a copy-in / operator / copy-out
+        # pipeline (ops_transformer_b200/hostio.py); every piece goes through the aclnn entry points
+        from ops_transformer_b200.hostio import HostPipelinedGroupedOp
+        pipe = HostPipelinedGroupedOp("swiglu_quant" if swiglu else "gmm", w, ws, M, pieces=args.e2e_pieces)
+
     def e2e_step():
+        if pipe is not None:
+            pipe.run(hx, hxs, counts, ho0, ho1)
+            return
         dx.copy_(hx, non_blocking=True); dxs.copy_(hxs, non_blocking=True); dgl.copy_(hgl, non_blocking=True)
         if finalize:
             ops.grouped_matmul_finalize_routing_flat(dx, w, wflat, ws, gl_counts, row_index, out0, pertoken_scale=dxs,
@@ -361,6 +371,7 @@ def bench_single(args):
                    "tokens_per_s": (cfg.get("tokens", 0) / (ms * 1e-3)) if cfg.get("tokens") else None},
         "roofline": roof,
         "e2e": {"value": ops_per_step / (e2e_ms * 1e-3) / 1e12, "unit": "TOPS", "ms_per_step": e2e_ms,
+                "pieces": args.e2e_pieces if pipe is not None else 1,
                 "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
         # one kernel per operator call (the int8 requant is fused into the GEMM kernel); finalize routing adds the kernel
         # that initialises the fp32 result
@@ -453,6 +464,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, help="c2 (default at N=1), c3, c4_swiglu, c4_down, c3_finalize, init_routing")
     ap.add_argument("--weight-format", default="nd", choices=["nd", "nz"], help="N=1: weight layout [E,K,N] or FRACTAL_NZ")
+    ap.add_argument("--e2e-pieces", type=int, default=8,
+                    help="N=1 end-to-end leg: expert ranges pipelined as copy-in / operator / copy-out (1 = one whole call)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-ep", action="store_true", help="N=1: skip the one-GPU run of the expert-parallel workload")
     ap.add_argument("--ep-tokens", type=int, default=16384, help="tokens per GPU of the expert-parallel workload")

@@ -752,3 +752,33 @@ def test_golden_fixtures_on_the_gpu():
             dd = np.abs(q.cpu().numpy()[:rows].astype(np.int32) - d["q"][:rows].astype(np.int32))
             assert rel.max() <= QSCALE_RTOL and dd.max() <= 1 and np.count_nonzero(dd) <= max(1, int(Q_LSB_FRACTION * dd.size)), case["file"]
     assert seen == {"grouped_matmul", "grouped_matmul_swiglu_quant", "moe_init_routing_v3", "grouped_matmul_finalize_routing"}
+
+
+def test_host_pipelined_pieces_equal_the_whole_call(oracle):
+    # rows in pinned host memory, the call split by experts into a copy-in / operator / copy-out pipeline
+    import ops_transformer_b200 as ops
+    from ops_transformer_b200.hostio import HostPipelinedGroupedOp
+    dev = _dev()
+    counts = np.array([100, 0, 37, 300, 5, 64, 0, 129])
+    M = int(counts.sum())
+    x, w, ws, xs = make_inputs(M, 256, 512, len(counts), seed=90)
+    t = lambda a: torch.from_numpy(a).to(dev)  # noqa: E731
+    hx, hxs = torch.from_numpy(x).pin_memory(), torch.from_numpy(xs).pin_memory()
+    for op in ("swiglu_quant", "gmm"):
+        pipe = HostPipelinedGroupedOp(op, t(w), t(ws), M, pieces=3)
+        if op == "swiglu_quant":
+            h0 = torch.zeros((M, 256), dtype=torch.int8).pin_memory()
+            h1 = torch.zeros((M,), dtype=torch.float32).pin_memory()
+            pipe.run(hx, hxs, counts, h0, h1)
+            q, qs = ops.grouped_matmul_swiglu_quant(t(x), t(w), t(ws), t(xs), t(np.cumsum(counts)))
+            torch.cuda.synchronize()
+            assert np.array_equal(h1.numpy(), qs.cpu().numpy())
+            d = np.abs(h0.numpy().astype(np.int32) - q.cpu().numpy().astype(np.int32))
+            assert d.max() <= 1 and np.count_nonzero(d) <= max(1, int(Q_LSB_FRACTION * d.size))
+            ref = oracle.swiglu_quant(x, w, ws, xs, np.cumsum(counts))
+            assert np.abs(h1.numpy() - ref["q_scale"]).max() <= QSCALE_RTOL * ref["q_scale"].max()
+        else:
+            h0 = torch.zeros((M, 512), dtype=torch.bfloat16).pin_memory()
+            pipe.run(hx, hxs, counts, h0)
+            ref = oracle.gmm_w8a8(x, w, ws, xs, np.cumsum(counts), 0)["y"]
+            assert np.array_equal(h0.view(torch.int16).numpy().view(np.uint16), ref)
