@@ -179,25 +179,45 @@ def run_reference_arm(args):
     print(json.dumps(line))
 
 
-def cpu_baseline_sample(seconds_budget=15.0):
+def cpu_baseline_sample(name="c2", seconds_budget=15.0):
+    """The oracle (CPU restatement of the reference kernels) timed on a bounded sample of workload `name`."""
     from oracle import oracle as O
     from ops_transformer_b200 import synth
     O.build()
-    cfg = synth.CONFIGS["c2"]
-    counts = synth.config_counts("c2", 0)
+    finalize = name.startswith("c3_finalize")
+    base = name.replace("_finalize", "")
+    cfg = synth.CONFIGS[base]
+    counts = synth.config_counts(base, 0)
+    swiglu = base in ("c2", "c4_swiglu", "c2_small", "c4_swiglu_small")
     rows_per_expert = 64
     x, w, ws, xs, gl = cpu_sample_swiglu(counts, cfg["K"], cfg["N"], rows_per_expert, 0)
     M = x.shape[0]
+    if finalize:
+        rng = np.random.default_rng(5)
+        batch = max(1, M // 8)
+        ri = (rng.permutation(M) % batch).astype(np.int64)
+        lg = rng.uniform(0.05, 0.55, size=M).astype(np.float32)
+        sh = O.f32_to_bf16_bits(rng.standard_normal((batch, cfg["N"])).astype(np.float32))
+        cnt = np.diff(np.concatenate([[0], gl]))
+        fn = lambda: O.gmm_finalize_routing(x, w, ws, xs, cnt, ri, batch, shared_input=sh, logit=lg)  # noqa: E731
+        cores = O.num_threads()  # the GEMM part; the combine loop of the restatement is sequential (rows may share a destination)
+    elif swiglu:
+        fn = lambda: O.swiglu_quant(x, w, ws, xs, gl)  # noqa: E731
+        cores = O.num_threads()
+    else:
+        fn = lambda: O.gmm_w8a8(x, w, ws, xs, gl, 0)  # noqa: E731
+        cores = O.num_threads()
     t0 = time.perf_counter()
     reps = 0
     while True:
-        O.swiglu_quant(x, w, ws, xs, gl)
+        fn()
         reps += 1
         if time.perf_counter() - t0 > seconds_budget or reps >= 5:
             break
     dt = (time.perf_counter() - t0) / reps
-    return {"value": 2.0 * M * cfg["K"] * cfg["N"] / dt / 1e12, "unit": "TOPS", "cores": O.num_threads(), "kind": "port",
-            "sample": f"first {rows_per_expert} rows of each expert ({M} of 32768 rows), full K/N, {reps} repetitions"}
+    total = int(np.asarray(counts).sum())
+    return {"value": 2.0 * M * cfg["K"] * cfg["N"] / dt / 1e12, "unit": "TOPS", "cores": cores, "kind": "port",
+            "sample": f"{name}: first {rows_per_expert} rows of each expert ({M} of {total} rows), full K/N, {reps} repetitions"}
 
 
 def bench_single(args):
@@ -387,8 +407,31 @@ def bench_single(args):
         line["ep"] = {"workload": "c5 on one GPU: 256 local experts, 16384 tokens, top-8, swiglu_quant then down GEMM",
                       **ep.one_gpu_summary(args, dev)}
     if not args.no_cpu_baseline:
-        line["cpu_baseline"] = cpu_baseline_sample()
+        line["cpu_baseline"] = cpu_baseline_sample(name)
     print(json.dumps(line))
+
+
+def cpu_baseline_init_routing(n, k, h, E, alg_bytes):
+    """The oracle's MoeInitRoutingV3 on the first 512 tokens of the workload (same seed), single thread."""
+    from oracle import oracle as O
+    O.build()
+    import torch
+    g = torch.Generator(device="cpu").manual_seed(0)
+    x = torch.randn(n, h, generator=g).to(torch.bfloat16)
+    idx = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(n)]).to(torch.int32)
+    m = 512
+    xb = x[:m].view(torch.int16).numpy().view(np.uint16)
+    ib = idx[:m].numpy()
+    t0 = time.perf_counter()
+    reps = 0
+    while True:
+        O.moe_init_routing_v3(xb, ib, E, (0, E), True)
+        reps += 1
+        if time.perf_counter() - t0 > 10.0 or reps >= 5:
+            break
+    dt = (time.perf_counter() - t0) / reps
+    return {"value": alg_bytes * (m / n) / dt / 1e9, "unit": "GB/s", "cores": 1, "kind": "port",
+            "sample": f"first {m} of {n} tokens, {reps} repetitions"}
 
 
 def bench_init_routing(args):
@@ -453,7 +496,8 @@ def bench_init_routing(args):
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
                      "traffic": None, "algorithmic_bytes": alg_bytes, "kernel": "routing_quant_kernel (+ count, scan, scatter)",
                      "peak_basis": f"copy bandwidth, {peaks['source']}"},
-        "gpu_launches": args.steps * 4, "clocks": clocks, "rows_per_s": n * k / (ms * 1e-3)}))
+        "gpu_launches": args.steps * 4, "clocks": clocks, "rows_per_s": n * k / (ms * 1e-3),
+        "cpu_baseline": None if args.no_cpu_baseline else cpu_baseline_init_routing(n, k, h, E, alg_bytes)}))
 
 
 def main():
