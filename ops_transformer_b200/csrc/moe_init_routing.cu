@@ -305,14 +305,18 @@ __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d)
     return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
 }
 
-__device__ __forceinline__ float block_max_128(float v, float *red)
+template <int THREADS>
+__device__ __forceinline__ float block_max(float v, float *red)
 {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
     __syncthreads();  // red may still be read from the previous use
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
     __syncthreads();
-    return fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    float m = red[0];
+#pragma unroll
+    for (int i = 1; i < THREADS / 32; ++i) m = fmaxf(m, red[i]);
+    return m;
 }
 
 template <typename T>
@@ -343,20 +347,20 @@ __device__ __forceinline__ void unpack16<__half>(const uint4 &u, float *f)
 // The fast form of the quantising gather: one CTA per TOKEN.  The row is read once, 16 bytes per thread and step, and
 // stays in registers; without a smooth scale it is quantised once and the int8 row is stored at the output row of each
 // of the token's k pairs; with one, every pair is scaled, reduced and quantised from the registers.  DRAM traffic is the
-// algorithmic minimum: x once, every output row once.  Needs h a multiple of the 16-byte vector, h <= 128 * NCH * VEC
+// algorithmic minimum: x once, every output row once.  Needs h a multiple of the 16-byte vector, h <= THREADS * NCH * VEC
 // and 16-byte aligned pointers; other shapes take routing_quant_kernel.
-template <typename T, int NCH>
-__global__ void __launch_bounds__(128) routing_quant_token_kernel(const RoutingParams p)
+template <typename T, int NCH, int THREADS>
+__global__ void __launch_bounds__(THREADS, 3) routing_quant_token_kernel(const RoutingParams p)
 {
     constexpr int VEC = 16 / (int)sizeof(T);
-    __shared__ float red[4];
+    __shared__ float red[THREADS / 32];
     const int token = blockIdx.x;
     const int chunks = p.h / VEC;
     const uint4 *row = reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(p.x) + (size_t)token * p.h);
     float v[NCH][VEC];
 #pragma unroll
     for (int i = 0; i < NCH; ++i) {
-        const int c = threadIdx.x + i * 128;
+        const int c = threadIdx.x + i * THREADS;
         if (c < chunks) {
             unpack16<T>(__ldg(row + c), v[i]);
         } else {
@@ -373,7 +377,7 @@ __global__ void __launch_bounds__(128) routing_quant_token_kernel(const RoutingP
         for (int i = 0; i < NCH; ++i)
 #pragma unroll
             for (int e = 0; e < VEC; ++e) amax = fmaxf(amax, fabsf(v[i][e]));
-        scale = __fdiv_rn(block_max_128(amax, red), 127.0f);
+        scale = __fdiv_rn(block_max<THREADS>(amax, red), 127.0f);
         const float rcp = exact_div_rcp(scale);
 #pragma unroll
         for (int i = 0; i < NCH; ++i)
@@ -391,7 +395,7 @@ __global__ void __launch_bounds__(128) routing_quant_token_kernel(const RoutingP
             float amax = 0.0f;
 #pragma unroll
             for (int i = 0; i < NCH; ++i) {
-                const int c = threadIdx.x + i * 128;
+                const int c = threadIdx.x + i * THREADS;
                 if (c < chunks) {
 #pragma unroll
                     for (int e4 = 0; e4 < VEC; e4 += 4) {
@@ -401,11 +405,11 @@ __global__ void __launch_bounds__(128) routing_quant_token_kernel(const RoutingP
                     }
                 }
             }
-            scale = __fdiv_rn(block_max_128(amax, red), 127.0f);
+            scale = __fdiv_rn(block_max<THREADS>(amax, red), 127.0f);
             const float rcp = exact_div_rcp(scale);
 #pragma unroll
             for (int i = 0; i < NCH; ++i) {  // the products are formed again: keeping them would cost 64 registers
-                const int c = threadIdx.x + i * 128;
+                const int c = threadIdx.x + i * THREADS;
                 if (c < chunks) {
 #pragma unroll
                     for (int e4 = 0; e4 < VEC; e4 += 4) {
@@ -420,7 +424,7 @@ __global__ void __launch_bounds__(128) routing_quant_token_kernel(const RoutingP
         int8_t *out = reinterpret_cast<int8_t *>(p.expanded_x) + (size_t)pos * p.h;
 #pragma unroll
         for (int i = 0; i < NCH; ++i) {
-            const int c = threadIdx.x + i * 128;
+            const int c = threadIdx.x + i * THREADS;
             if (c < chunks) {
                 if (VEC == 8) *reinterpret_cast<uint2 *>(out + (size_t)c * VEC) = make_uint2(w[i][0], w[i][VEC / 4 - 1]);
                 else *reinterpret_cast<uint32_t *>(out + (size_t)c * VEC) = w[i][0];
@@ -527,13 +531,13 @@ cudaError_t init_routing_launch(const InitRoutingProblem &r, void *workspace, si
         const int vec = 16 / eb;
         const bool fast = aligned && r.h % vec == 0 && r.h % 8 == 0 && r.h / vec <= 128 * (eb == 4 ? 16 : 8) && r.n <= 0x7fffffffll;
         if (r.x_dtype == kF32) {
-            if (fast) routing_quant_token_kernel<float, 16><<<(unsigned)r.n, 128, 0, stream>>>(p);
+            if (fast) routing_quant_token_kernel<float, 8, 256><<<(unsigned)r.n, 256, 0, stream>>>(p);
             else routing_quant_kernel<float><<<(unsigned)pairs, 128, 0, stream>>>(p);
         } else if (r.x_dtype == kF16) {
-            if (fast) routing_quant_token_kernel<__half, 8><<<(unsigned)r.n, 128, 0, stream>>>(p);
+            if (fast) routing_quant_token_kernel<__half, 4, 256><<<(unsigned)r.n, 256, 0, stream>>>(p);
             else routing_quant_kernel<__half><<<(unsigned)pairs, 128, 0, stream>>>(p);
         } else if (r.x_dtype == kBF16) {
-            if (fast) routing_quant_token_kernel<__nv_bfloat16, 8><<<(unsigned)r.n, 128, 0, stream>>>(p);
+            if (fast) routing_quant_token_kernel<__nv_bfloat16, 4, 256><<<(unsigned)r.n, 256, 0, stream>>>(p);
             else routing_quant_kernel<__nv_bfloat16><<<(unsigned)pairs, 128, 0, stream>>>(p);
         } else {
             return cudaErrorInvalidValue;
