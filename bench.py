@@ -147,10 +147,13 @@ def cpu_sample_swiglu(counts, K, N, rows_per_expert, seed):
 
 
 def run_reference_arm(args):
-    """The reference's CPU golden path (CPU restatement of its kernels) on a bounded sample of the N=1 workload."""
+    """The reference's CPU golden path (CPU restatement of its kernels) on a bounded sample of this arm's workload: the
+    gate/up operator of c2 at N=1; at N>1 the expert FFN of c5 (gate/up with SwiGLU and requantisation, then the down GEMM
+    on its int8 result), as the GPU arm runs it."""
     from oracle import oracle as O
     from ops_transformer_b200 import synth
     O.build()
+    multi = args.gpus > 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1
     cfg = synth.CONFIGS["c2"]
     counts = synth.config_counts("c2", 0)
     K, N = cfg["K"], cfg["N"]
@@ -158,20 +161,35 @@ def run_reference_arm(args):
     x, w, ws, xs, gl = cpu_sample_swiglu(counts, K, N, rows_per_expert, 0)
     M = x.shape[0]
     ops_per_step = 2.0 * M * K * N
+    if multi:
+        w2 = synth.int8_tensor((len(counts), N // 2, K), 0, 5)
+        ws2 = synth.scale_tensor((len(counts), K), 0, 6)
+        ops_per_step += 2.0 * M * (N // 2) * K
+
+    def step():
+        r = O.swiglu_quant(x, w, ws, xs, gl)
+        if multi:
+            O.gmm_w8a8(r["q"], w2, ws2, r["q_scale"], gl, 0)
+
     for _ in range(args.warmup if args.warmup < 2 else 1):
-        O.swiglu_quant(x, w, ws, xs, gl)
+        step()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        O.swiglu_quant(x, w, ws, xs, gl)
+        step()
     dt = (time.perf_counter() - t0) / args.steps
     tops = ops_per_step / dt / 1e12
-    sample = f"first {rows_per_expert} rows of each of the 32 experts ({M} of 32768 rows), full K and N, per step"
+    if multi:
+        workload = ("c5 expert-parallel FFN: 256 experts, 16384 tokens per GPU, top-8, swiglu_quant K=7168 N=4096 then down GEMM "
+                    "K=2048 N=7168")
+        sample = f"32 of the 256 experts, first {rows_per_expert} rows of each ({M} rows), both operators at full K and N, per step"
+    else:
+        workload = "c2: DeepSeek-V3 prefill gate/up, grouped_matmul_swiglu_quant, 32768 rows, 32 experts, K=7168, N=4096"
+        sample = f"first {rows_per_expert} rows of each of the 32 experts ({M} of 32768 rows), full K and N, per step"
     line = {
         "impl": "reference", "metric": "int8 GMM+SwiGLU-quant TOPS", "value": tops, "unit": "TOPS", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-        "config": {"workload": "c2: DeepSeek-V3 prefill gate/up, grouped_matmul_swiglu_quant, 32768 rows, 32 experts, K=7168, N=4096",
-                   "sample": sample},
+        "config": {"workload": workload, "sample": sample},
         "cpu_baseline": {"value": tops, "unit": "TOPS", "cores": O.num_threads(), "kind": "port", "sample": sample},
         "e2e": {"value": tops, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
