@@ -153,6 +153,7 @@ def run_reference_arm(args):
     from oracle import oracle as O
     from ops_transformer_b200 import synth
     O.build()
+    O.use_all_cores()
     multi = args.gpus > 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1
     cfg = synth.CONFIGS["c2"]
     counts = synth.config_counts("c2", 0)
@@ -202,6 +203,7 @@ def cpu_baseline_sample(name="c2", seconds_budget=15.0):
     from oracle import oracle as O
     from ops_transformer_b200 import synth
     O.build()
+    O.use_all_cores()
     finalize = name.startswith("c3_finalize")
     base = name.replace("_finalize", "")
     cfg = synth.CONFIGS[base]

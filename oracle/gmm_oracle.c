@@ -591,6 +591,17 @@ ORACLE_API int oracle_ref_swiglu_tiling_key(int64_t m, int64_t n)
 ORACLE_API uint16_t oracle_f32_to_bf16(float f) { return f32_to_bf16_rne(f); }
 ORACLE_API uint16_t oracle_f32_to_f16(float f) { return f32_to_f16_rne(f); }
 ORACLE_API int8_t oracle_f16_to_i8(uint16_t h) { return f16_to_i8_rne(h); }
+/* A launcher may have exported OMP_NUM_THREADS=1 to every worker (torch.distributed.run does); the timed CPU legs ask
+ * for the host's cores explicitly. */
+ORACLE_API void oracle_set_num_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 ORACLE_API int oracle_num_threads(void)
 {
 #ifdef _OPENMP

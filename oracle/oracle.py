@@ -75,6 +75,14 @@ def num_threads() -> int:
     return int(lib().oracle_num_threads())
 
 
+def use_all_cores() -> int:
+    """Make the OpenMP loops use every core this process may run on, whatever OMP_NUM_THREADS said; returns the count."""
+    import os
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().oracle_set_num_threads(int(n))
+    return num_threads()
+
+
 def group_layout(group_list, gl_type: int, M: int):
     gl = np.ascontiguousarray(group_list, dtype=np.int64)
     rs = np.zeros(len(gl), np.int64)
