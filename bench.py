@@ -408,6 +408,7 @@ def bench_single(args):
     roof["traffic_source"] = "dram__bytes_read.sum + dram__bytes_write.sum of the ncu capture under profiles/, scaled as stated there"
     roof["kernel"] = "gmm_w8a8_sm100_kernel"
     roof["kernel_ms"] = kms
+    roof["kernel_ms_p10_p50_p90"] = [float(np.percentile(kern_ms, q)) for q in (10, 50, 90)]
     roof["algorithmic_bytes"] = alg_bytes
     roof["algorithmic_ops"] = ops_per_step
 
