@@ -353,6 +353,8 @@ template <typename T, int NCH, int THREADS>
 __global__ void __launch_bounds__(THREADS, 3) routing_quant_token_kernel(const RoutingParams p)
 {
     constexpr int VEC = 16 / (int)sizeof(T);
+    constexpr int G = 16 / VEC;  // 16-byte loads that make one 16-byte store of int8: a thread owns G adjacent ones
+    static_assert(NCH % G == 0, "whole stores per thread");
     __shared__ float red[THREADS / 32];
     const int token = blockIdx.x;
     const int chunks = p.h / VEC;
@@ -360,7 +362,7 @@ __global__ void __launch_bounds__(THREADS, 3) routing_quant_token_kernel(const R
     float v[NCH][VEC];
 #pragma unroll
     for (int i = 0; i < NCH; ++i) {
-        const int c = threadIdx.x + i * THREADS;
+        const int c = (threadIdx.x + (i / G) * THREADS) * G + (i % G);
         if (c < chunks) {
             unpack16<T>(__ldg(row + c), v[i]);
         } else {
@@ -395,7 +397,7 @@ __global__ void __launch_bounds__(THREADS, 3) routing_quant_token_kernel(const R
             float amax = 0.0f;
 #pragma unroll
             for (int i = 0; i < NCH; ++i) {
-                const int c = threadIdx.x + i * THREADS;
+                const int c = (threadIdx.x + (i / G) * THREADS) * G + (i % G);
                 if (c < chunks) {
 #pragma unroll
                     for (int e4 = 0; e4 < VEC; e4 += 4) {
@@ -409,7 +411,7 @@ __global__ void __launch_bounds__(THREADS, 3) routing_quant_token_kernel(const R
             const float rcp = exact_div_rcp(scale);
 #pragma unroll
             for (int i = 0; i < NCH; ++i) {  // the products are formed again: keeping them would cost 64 registers
-                const int c = threadIdx.x + i * THREADS;
+                const int c = (threadIdx.x + (i / G) * THREADS) * G + (i % G);
                 if (c < chunks) {
 #pragma unroll
                     for (int e4 = 0; e4 < VEC; e4 += 4) {
@@ -423,11 +425,13 @@ __global__ void __launch_bounds__(THREADS, 3) routing_quant_token_kernel(const R
         if (threadIdx.x == 0) p.expanded_scale[pos] = scale;
         int8_t *out = reinterpret_cast<int8_t *>(p.expanded_x) + (size_t)pos * p.h;
 #pragma unroll
-        for (int i = 0; i < NCH; ++i) {
-            const int c = threadIdx.x + i * THREADS;
+        for (int i = 0; i < NCH; i += G) {
+            const int c = (threadIdx.x + (i / G) * THREADS) * G;
             if (c < chunks) {
-                if (VEC == 8) *reinterpret_cast<uint2 *>(out + (size_t)c * VEC) = make_uint2(w[i][0], w[i][VEC / 4 - 1]);
-                else *reinterpret_cast<uint32_t *>(out + (size_t)c * VEC) = w[i][0];
+                uint4 o;
+                if (VEC == 8) o = make_uint4(w[i][0], w[i][VEC / 4 - 1], w[i + G - 1][0], w[i + G - 1][VEC / 4 - 1]);
+                else o = make_uint4(w[i][0], w[i + 1 < NCH ? i + 1 : i][0], w[i + 2 < NCH ? i + 2 : i][0], w[i + G - 1][0]);
+                *reinterpret_cast<uint4 *>(out + (size_t)c * VEC) = o;
             }
         }
     }
@@ -526,10 +530,9 @@ cudaError_t init_routing_launch(const InitRoutingProblem &r, void *workspace, si
     const int eb = r.x_dtype == kF32 ? 4 : (r.x_dtype == kI8 ? 1 : 2);
     const bool aligned = ((reinterpret_cast<uintptr_t>(r.x) | reinterpret_cast<uintptr_t>(r.expanded_x) | reinterpret_cast<uintptr_t>(r.scale)) & 15) == 0;
     if (r.quant) {
-        // token-major kernels hold up to 64 values per thread: h <= 8192; h must be a whole number of 16-byte vectors and,
-        // for the 8-byte stores of a row, a multiple of 8
+        // token-major kernels hold 32 values per thread (256 threads): h <= 8192, and h a multiple of 16 for the 16-byte stores
         const int vec = 16 / eb;
-        const bool fast = aligned && r.h % vec == 0 && r.h % 8 == 0 && r.h / vec <= 128 * (eb == 4 ? 16 : 8) && r.n <= 0x7fffffffll;
+        const bool fast = aligned && r.h % 16 == 0 && r.h <= 8192 && r.n <= 0x7fffffffll;
         if (r.x_dtype == kF32) {
             if (fast) routing_quant_token_kernel<float, 8, 256><<<(unsigned)r.n, 256, 0, stream>>>(p);
             else routing_quant_kernel<float><<<(unsigned)pairs, 128, 0, stream>>>(p);
