@@ -23,7 +23,9 @@
  * Accepted attribute values, as in the reference: dropPadMode 0, expertTokensNumFlag true, quantMode 1 or -1,
  * activeNum = n * k (or 0), expertCapacity >= 0 (unused), expertNum <= 10240 (5120 for key-value counts),
  * offsetOptional unused.  A violation returns ACLNN_ERR_PARAM_INVALID from the first phase (the reference reports
- * some of them from its tiling step).
+ * some of them from its tiling step).  Without quantisation expandedXOut must have x's dtype: the example in the
+ * reference's documentation (docs/aclnnMoeInitRoutingV3.md:521-586) declares an int8 expandedXOut of 24 bytes for float32
+ * rows with quantMode -1, which cannot hold them; that combination is refused here instead of writing past the buffer.
  */
 #ifndef B200_ACLNN_MOE_INIT_ROUTING_V3_H
 #define B200_ACLNN_MOE_INIT_ROUTING_V3_H

@@ -395,6 +395,11 @@ def test_moe_init_routing_v3_phase1_status_codes():
     assert _ir_phase1(x_dtype=torch.int8)[0] == INVALID                                            # dynamic quant of int8 rows
     assert _ir_phase1(out_dtype=torch.bfloat16)[0] == INVALID                                      # quant output must be int8
     assert _ir_phase1(quant=-1, out_dtype=torch.float32)[0] == INVALID
+    # the example of the reference's documentation (x float32 [3,2], top-4, quantMode -1, per-token scale [3], expertNum 256, range
+    # [0,4) ...) declares an int8 expandedXOut: refused, float32 rows do not fit it; with a float32 output the call is accepted
+    doc = dict(n=3, k=4, h=2, E=256, rng_=(0, 4), quant=-1, x_dtype=torch.float32, scale=torch.empty((3,), dtype=torch.float32))
+    assert _ir_phase1(**doc, out_dtype=torch.int8)[0] == INVALID
+    assert _ir_phase1(**doc)[0] == OK
     assert _ir_phase1(quant=0)[0] == INVALID and _ir_phase1(quant=2)[0] == INVALID                 # static quant is not supported
     assert _ir_phase1(drop=1)[0] == INVALID and _ir_phase1(flag=False)[0] == INVALID
     assert _ir_phase1(count_type=0)[0] == INVALID and _ir_phase1(row_idx_type=2)[0] == INVALID
