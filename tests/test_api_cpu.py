@@ -415,6 +415,34 @@ def test_moe_init_routing_v3_phase1_status_codes():
     assert _ir_phase1(idx=torch.empty((7, 2), dtype=torch.int32))[0] == INVALID
 
 
+def test_finalize_routing_reference_unit_test_cases():
+    """The status codes the reference's own op_api unit tests pin for aclnnGroupedMatmulFinalizeRoutingWeightNz
+    (gmm/grouped_matmul_finalize_routing/tests/ut/op_host/op_api/test_aclnn_grouped_matmul_finalize_routing_weight_nz_l2.cpp:41-621):
+    m=192, k=2048, n=7168, e=4, bs=24, bsdp=8, weight viewed [e,k,n] over storage [e, n/32, k/16, 16, 32]."""
+    i8, f32, bf = torch.int8, torch.float32, torch.bfloat16
+    m, k, n, e, bs, bsdp = 192, 2048, 7168, 4, 24, 8
+    t = _fr_tensors(m, k, n, e, bs, bsdp)
+    assert _fr_phase1(**t)[0] == OK                                                              # normal_case_add_value (:41)
+    assert _fr_phase1(**{**t, "logit": None, "ri": None})[0] == NULLPTR                          # shared_input_null (:68)
+    assert _fr_phase1(**{**t, "bias": torch.empty((e, n), dtype=bf)})[0] == OK                   # bias_not_null (:94)
+    assert _fr_phase1(**{**t, "w": torch.empty((e, k, n), dtype=i8)}, fmt_w=_lib.ACL_FORMAT_ND)[0] == INVALID   # x2_not_nz (:121)
+    assert _fr_phase1(**{**t, "w": None})[0] == NULLPTR                                          # x2_null (:147)
+    assert _fr_phase1(**t, dtype=1)[0] == INVALID                                                # dtype_not_0 (:172)
+    assert _fr_phase1(**{**t, "scale": torch.empty((e + 1, n), dtype=f32)})[0] == INVALID        # scale_noteq_e (:198)
+    assert _fr_phase1(**{**t, "pts": torch.empty((m + 1,), dtype=f32)})[0] == INVALID            # perTokenScale_noteq_m (:224)
+    assert _fr_phase1(**{**t, "shared": torch.empty((bs + 1, n), dtype=bf)})[0] == INVALID       # shared_input_more_than_bs (:250)
+    assert _fr_phase1(**{**t, "x": torch.empty((0, k), dtype=i8)})[0] == INVALID                 # view_shape_0 (:302)
+    assert _fr_phase1(**{**t, "x": torch.empty((m,), dtype=i8)})[0] == INVALID                   # x12_viewdims_wrong (:328)
+    assert _fr_phase1(**{**t, "shared": torch.empty((bsdp + 1, n + 1), dtype=bf)})[0] == INVALID  # shareinput_outputBS_noeq (:354)
+    assert _fr_phase1(**{**t, "logit": torch.empty((m + 1,), dtype=f32)})[0] == INVALID          # logit_1stdim_noeq_xMdim (:380)
+    assert _fr_phase1(**{**t, "ri": torch.empty((m + 1,), dtype=torch.int64)})[0] == INVALID     # rowindex1stdim_noeq_xMdim (:407)
+    assert _fr_phase1(**{**t, "gl": torch.empty((e + 1,), dtype=torch.int64)})[0] == INVALID     # groupListdim_wrong (:434)
+    assert _fr_phase1(**_fr_tensors(m, k, 224, e, bs, bsdp))[0] == INVALID                       # nvalid (:488, n = 7000 there): n % 32, n >= 256
+    assert _fr_phase1(**{**t, "x": torch.empty((m, 4098), dtype=i8)})[0] == INVALID              # not_support_k_shape (:515)
+    assert _fr_phase1(**{**t, "w": torch.empty((e, n // 32, k // 16, 16, 32), dtype=torch.int32)})[0] == INVALID   # x1_type_not_same_with_x2 (:542)
+    assert _fr_phase1(**{**t, "x": torch.empty((m, k - 1), dtype=i8)})[0] == INVALID             # k_n_not_support_w8a8 (:596)
+
+
 def test_second_phase_host_checks():
     L = _lib.lib()
     assert L.aclnnGroupedMatmulV4(None, 0, None, None) == NULLPTR
