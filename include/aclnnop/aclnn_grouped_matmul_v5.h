@@ -4,8 +4,10 @@
  * Drop-in for the reference's entry points declared at
  *   gmm/grouped_matmul/op_host/op_api/aclnn_grouped_matmul_v5.h:49-69.
  * tuningConfigOptional[0] is the number of rows the caller expects per group; the reference feeds it to its host tiling
- * (aclnn_grouped_matmul.cpp:1336-1360).  Here the tile schedule is built on the device from group_list itself, so the
- * value is validated (no negative entries) and otherwise unused.  Everything else is as in aclnn_grouped_matmul_v4.h.
+ * (aclnn_grouped_matmul.cpp:1336-1360).  Here the tile schedule is built on the device from group_list itself; the value
+ * is validated (no negative entries) and, when positive, replaces M / len(group_list) in the choice between 128-row tiles
+ * and 256-row CTA-pair tiles (pairs from 384 rows per group), which helps when many groups are empty.  Everything else is
+ * as in aclnn_grouped_matmul_v4.h.
  */
 #ifndef B200_ACLNN_GROUPED_MATMUL_V5_H
 #define B200_ACLNN_GROUPED_MATMUL_V5_H

@@ -37,6 +37,7 @@ struct Problem {
     int gl_type = 0;                    // 0 = running total, 1 = per-group count
     int64_t M = 0, K = 0, N = 0, E = 0;
     int w_layout = 0;                   // 0 row major, 1 transposed view, 2 FRACTAL_NZ
+    int64_t rows_per_group_hint = 0;    // > 0: the caller's expected rows per group (tuningConfig), else M / len(group_list) is used
     int act_type = 0;                   // GMMActType: 0 none, 1 relu, 2 gelu (tanh form), 4 fast gelu, 5 silu
     int out_f16 = 0;                    // mode kModeDequantBf16 with a float16 instead of a bfloat16 result
     int mode = kModeDequantBf16;

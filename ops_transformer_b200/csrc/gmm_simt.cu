@@ -227,7 +227,8 @@ void make_plan(const Problem &p, Plan *plan)
     plan->path = sm100_shape_ok(p) ? kPathSm100 : kPathSimt;
     // CTA pairs halve the weight traffic per SM but waste up to 255 rows at the end of every group, so they are
     // used when groups are long on average.  GMM_B200_CTAS=1|2 overrides the choice (for measurements).
-    plan->ctas = (p.gl_len > 0 && p.M / p.gl_len >= 384) ? 2 : 1;
+    const long long avg_rows = p.rows_per_group_hint > 0 ? p.rows_per_group_hint : (p.gl_len > 0 ? p.M / p.gl_len : 0);
+    plan->ctas = avg_rows >= 384 ? 2 : 1;
     if (const char *e = getenv("GMM_B200_CTAS")) {
         if (e[0] == '1') plan->ctas = 1;
         if (e[0] == '2') plan->ctas = 2;

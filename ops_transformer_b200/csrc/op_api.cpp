@@ -156,7 +156,7 @@ void gmmB200SetTimingEvents(void *startEvent, void *stopEvent)
 // Shared first phase of aclnnGroupedMatmulV4 / V5 / WeightNz (aclnnGroupedMatmulGetWorkspaceSizeCommon,
 // gmm/grouped_matmul/op_host/op_api/aclnn_grouped_matmul.cpp:1839-1880).  force_nz: the weight's storage is FRACTAL_NZ
 // whatever its format field says (the WeightNz entry point, :1917-1955).
-static aclnnStatus gmm_phase1(const char *kOp, bool force_nz,
+static aclnnStatus gmm_phase1(const char *kOp, bool force_nz, int64_t rows_hint,
     const aclTensorList *x, const aclTensorList *weight, const aclTensorList *biasOptional,
     const aclTensorList *scaleOptional, const aclTensorList *offsetOptional,
     const aclTensorList *antiquantScaleOptional, const aclTensorList *antiquantOffsetOptional,
@@ -312,6 +312,7 @@ static aclnnStatus gmm_phase1(const char *kOp, bool force_nz,
     p.gl_type = (int)groupListType;
     p.M = M; p.K = K; p.N = N; p.E = E;
     p.w_layout = w_nz ? 2 : (w_trans ? 1 : 0);
+    p.rows_per_group_hint = rows_hint;
     // The reference's test for an activation with an int32 result never fires (aclnn_grouped_matmul.cpp:984-985) and its
     // int32 kernel has no vector stage: the activation is accepted and has no effect.
     p.act_type = int32_out ? 0 : (int)actType;
@@ -333,7 +334,7 @@ aclnnStatus aclnnGroupedMatmulV4GetWorkspaceSize(
     int64_t actType, aclTensorList *out, aclTensorList *activationFeatureOutOptional,
     aclTensorList *dynQuantScaleOutOptional, uint64_t *workspaceSize, aclOpExecutor **executor)
 {
-    return gmm_phase1("aclnnGroupedMatmulV4", false, x, weight, biasOptional, scaleOptional, offsetOptional, antiquantScaleOptional,
+    return gmm_phase1("aclnnGroupedMatmulV4", false, 0, x, weight, biasOptional, scaleOptional, offsetOptional, antiquantScaleOptional,
                       antiquantOffsetOptional, perTokenScaleOptional, groupListOptional, activationInputOptional,
                       activationQuantScaleOptional, activationQuantOffsetOptional, splitItem, groupType, groupListType, actType, out,
                       activationFeatureOutOptional, dynQuantScaleOutOptional, workspaceSize, executor);
@@ -344,13 +345,17 @@ aclnnStatus aclnnGroupedMatmulV4(void *workspace, uint64_t workspaceSize, aclOpE
     return run_executor("aclnnGroupedMatmulV4", workspace, workspaceSize, executor, stream);
 }
 
-// tuningConfigOptional is a hint for the reference's host tiling (expected rows per group,
-// aclnn_grouped_matmul.cpp:1336-1360); the device scheduler here reads group_list itself, so the hint is only validated.
-static aclnnStatus check_tuning_config(const aclIntArray *cfg)
+// tuningConfigOptional[0] is the number of rows the caller expects per group, a hint for the reference's host tiling
+// (aclnn_grouped_matmul.cpp:1336-1360).  The device scheduler here reads group_list itself; the hint only replaces
+// M / len(group_list) in the choice between 128-row tiles and CTA pairs, which matters when many groups are empty.
+static aclnnStatus check_tuning_config(const aclIntArray *cfg, int64_t *rows_hint)
 {
-    if (cfg)
+    *rows_hint = 0;
+    if (cfg) {
         for (int64_t v : cfg->values)
             if (v < 0) return fail(ACLNN_ERR_PARAM_INVALID, "tuningConfig values must not be negative.");
+        if (!cfg->values.empty()) *rows_hint = cfg->values[0];
+    }
     return ACLNN_SUCCESS;
 }
 
@@ -365,8 +370,9 @@ aclnnStatus aclnnGroupedMatmulV5GetWorkspaceSize(
     aclTensorList *dynQuantScaleOutOptional, uint64_t *workspaceSize, aclOpExecutor **executor)
 {
     clear_error();
-    if (check_tuning_config(tuningConfigOptional) != ACLNN_SUCCESS) return ACLNN_ERR_PARAM_INVALID;
-    return gmm_phase1("aclnnGroupedMatmulV5", false, x, weight, biasOptional, scaleOptional, offsetOptional, antiquantScaleOptional,
+    int64_t rows_hint = 0;
+    if (check_tuning_config(tuningConfigOptional, &rows_hint) != ACLNN_SUCCESS) return ACLNN_ERR_PARAM_INVALID;
+    return gmm_phase1("aclnnGroupedMatmulV5", false, rows_hint, x, weight, biasOptional, scaleOptional, offsetOptional, antiquantScaleOptional,
                       antiquantOffsetOptional, perTokenScaleOptional, groupListOptional, activationInputOptional,
                       activationQuantScaleOptional, activationQuantOffsetOptional, splitItem, groupType, groupListType, actType, out,
                       activationFeatureOutOptional, dynQuantScaleOutOptional, workspaceSize, executor);
@@ -389,9 +395,10 @@ aclnnStatus aclnnGroupedMatmulWeightNzGetWorkspaceSize(
     aclOpExecutor **executor)
 {
     clear_error();
-    if (check_tuning_config(tuningConfigOptional) != ACLNN_SUCCESS) return ACLNN_ERR_PARAM_INVALID;
+    int64_t rows_hint = 0;
+    if (check_tuning_config(tuningConfigOptional, &rows_hint) != ACLNN_SUCCESS) return ACLNN_ERR_PARAM_INVALID;
     GMM_REQUIRE(quantGroupSize >= 0, ACLNN_ERR_PARAM_INVALID, "quantGroupSize must not be negative.");
-    return gmm_phase1("aclnnGroupedMatmulWeightNz", true, x, weight, biasOptional, scaleOptional, offsetOptional,
+    return gmm_phase1("aclnnGroupedMatmulWeightNz", true, rows_hint, x, weight, biasOptional, scaleOptional, offsetOptional,
                       antiquantScaleOptional, antiquantOffsetOptional, perTokenScaleOptional, groupListOptional,
                       activationInputOptional, activationQuantScaleOptional, activationQuantOffsetOptional, splitItem, groupType,
                       groupListType, actType, out, activationFeatureOutOptional, dynQuantScaleOutOptional, workspaceSize, executor);

@@ -378,6 +378,7 @@ def test_gmm_v5_tuning_config(oracle):
     counts = [100, 37, 300]
     x, w, ws, xs = make_inputs(437, 512, 768, 3, seed=43)
     check_gmm(oracle, x, w, ws, xs, np.cumsum(counts), 0, api="V5", tuning_config=[146])
+    check_gmm(oracle, x, w, ws, xs, np.cumsum(counts), 0, api="V5", tuning_config=[512])   # the hint selects CTA pairs
     check_gmm(oracle, x, w, ws, xs, np.cumsum(counts), 0, api="V5")
 
 
