@@ -58,6 +58,7 @@ __global__ void __launch_bounds__(kPairsPerBlock) routing_count_kernel(const Rou
     }
     __syncthreads();
     for (int e = threadIdx.x; e < p.range; e += blockDim.x) p.block_hist[(size_t)blockIdx.x * p.range + e] = hist[e];
+    if (blockIdx.x == 0 && threadIdx.x == 0) p.total[1] = 0;  // arrival counter of the scan kernel that follows
 }
 
 // Inclusive scan of one int per thread over a 1024-thread block; returns the inclusive value, *block_sum the total.
@@ -87,14 +88,17 @@ __device__ int block_scan_1024(int v, int *warp_sums, int *block_sum)
     return v;
 }
 
+// Grid: one CTA per 32 active experts.  Part one (all CTAs): per expert the exclusive prefix over the blocks.  Part two
+// (the CTA that arrives last at a counter; nobody waits): the scan over the experts and the counts output.
 __global__ void __launch_bounds__(1024) routing_scan_kernel(const RoutingParams p)
 {
     __shared__ int warp_sums[32];
+    __shared__ int is_last;
     // per expert: exclusive prefix over the blocks, total into expert_first (as a count for now).  One warp per expert,
     // its lanes over 32 blocks at a time.
     {
         const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-        for (int e = warp; e < p.range; e += 32) {
+        for (int e = blockIdx.x * 32 + warp; e < min(p.range, (int)(blockIdx.x + 1) * 32); e += 32) {
             int carry = 0;
             for (int b0 = 0; b0 < p.nb; b0 += 32) {
                 const int b = b0 + lane;
@@ -111,13 +115,18 @@ __global__ void __launch_bounds__(1024) routing_scan_kernel(const RoutingParams 
             if (lane == 0) p.expert_first[e] = carry;
         }
     }
+    __threadfence();
     __syncthreads();
+    if (threadIdx.x == 0) is_last = atomicAdd(p.total + 1, 1) == (int)gridDim.x - 1;
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
     // over the experts, 1024 at a time: first row of every expert, the counts output (count or key-value form)
     int row_carry = 0, nz_carry = 0;
     const int written_pairs = min(p.range + 1, p.expert_num);  // key-value form: entries the operator writes
     for (int base = 0; base < p.range; base += 1024) {
         const int e = base + threadIdx.x;
-        const int c = e < p.range ? p.expert_first[e] : 0;
+        const int c = e < p.range ? __ldcg(p.expert_first + e) : 0;  // written by other CTAs
         int sum_c, sum_nz;
         const int inc_c = block_scan_1024(c, warp_sums, &sum_c);
         const int inc_nz = block_scan_1024(c != 0 ? 1 : 0, warp_sums, &sum_nz);
@@ -524,7 +533,7 @@ cudaError_t init_routing_launch(const InitRoutingProblem &r, void *workspace, si
     p.nb = (int)nb;
     const size_t smem = (size_t)range * 4;
     routing_count_kernel<<<(unsigned)nb, kPairsPerBlock, smem, stream>>>(p);
-    routing_scan_kernel<<<1, 1024, 0, stream>>>(p);
+    routing_scan_kernel<<<(unsigned)((range + 31) / 32), 1024, 0, stream>>>(p);
     if (range <= kWarpTableRange) routing_scatter_kernel<true><<<(unsigned)nb, kPairsPerBlock, smem * (kPairsPerBlock / 32), stream>>>(p);
     else routing_scatter_kernel<false><<<(unsigned)nb, kPairsPerBlock, smem, stream>>>(p);
     const int eb = r.x_dtype == kF32 ? 4 : (r.x_dtype == kI8 ? 1 : 2);
