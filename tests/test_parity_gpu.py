@@ -783,3 +783,61 @@ def test_host_pipelined_pieces_equal_the_whole_call(oracle):
             pipe.run(hx, hxs, counts, h0)
             ref = oracle.gmm_w8a8(x, w, ws, xs, np.cumsum(counts), 0)["y"]
             assert np.array_equal(h0.view(torch.int16).numpy().view(np.uint16), ref)
+
+
+# ----------------------------------------------------------------------------------------------------------
+# seeded random sweep over shapes, group lists, layouts, tile shapes and options
+# ----------------------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("seed", [1, 2, 3])
+def test_random_sweep_of_shapes_and_options(oracle, monkeypatch, seed):
+    rng = np.random.default_rng(seed)
+    for it in range(25):
+        E = int(rng.integers(1, 12))
+        K = int(rng.choice([16, 48, 128, 144, 256, 512, 1040]))
+        N = int(rng.choice([32, 64, 96, 256, 288, 512, 1056]))
+        counts = rng.integers(0, int(rng.choice([3, 140, 300, 700])), size=E).astype(np.int64)
+        counts[rng.random(E) < 0.3] = 0
+        if counts.sum() == 0:
+            counts[0] = 5
+        M = int(counts.sum()) + int(rng.integers(0, 7))
+        x, w, ws, xs = make_inputs(M, K, N, E, seed=1000 * seed + it)
+        monkeypatch.setenv("GMM_B200_CTAS", str(rng.choice(["1", "2"])))
+        monkeypatch.setenv("GMM_B200_HYBRID", str(rng.choice(["0", "1"])))
+        gl_type = int(rng.integers(0, 2))
+        gl = counts if gl_type == 1 else np.cumsum(counts)
+        nz = bool(rng.random() < 0.4)
+        mode = str(rng.choice(["gmm", "gmm_i32", "gmm_f16", "swiglu", "finalize"]))
+        if mode == "gmm":
+            bias = rng.integers(-1000, 1000, size=(E, N)).astype(np.int32) if rng.random() < 0.3 else None
+            check_gmm(oracle, x, w, ws, xs, gl, gl_type, w_nz=nz, bias=bias, act_type=int(rng.choice([0, 1])),
+                      w_trans=(not nz and rng.random() < 0.3))
+        elif mode == "gmm_i32":
+            check_gmm(oracle, x, w, ws, xs, gl, gl_type, w_nz=nz, out_dtype="int32")
+        elif mode == "gmm_f16":
+            check_gmm(oracle, x, w, ws, xs, gl, gl_type, w_nz=nz, out_dtype="f16")
+        elif mode == "swiglu":
+            check_swiglu(oracle, x, w, ws, xs, np.cumsum(counts), w_nz=nz, ws_dtype=str(rng.choice(["f32", "bf16", "f16"])))
+        elif N >= 256:
+            topk = int(rng.choice([1, 2, 4]))
+            rows = (int(counts.sum()) // topk) * topk
+            extra = int(counts.sum()) - rows
+            for i in range(E):
+                d = min(extra, int(counts[i]))
+                counts[i] -= d
+                extra -= d
+            if rows == 0:
+                continue
+            check_finalize(oracle, rows, K, N, E, counts, topk, 2000 * seed + it, shared_rows=max(1, rows // topk // 2),
+                           use_bias=bool(rng.random() < 0.5), idx32=bool(rng.random() < 0.5), use_pts=bool(rng.random() < 0.8),
+                           flat_layout=(int(rng.choice([0, 2])) if rng.random() < 0.5 else None))
+    for it in range(8):
+        E = int(rng.choice([8, 32, 256, 300, 1024]))
+        n, k, h = int(rng.integers(1, 400)), min(int(rng.choice([1, 2, 4, 8])), E), int(rng.choice([16, 20, 64, 100, 512, 1024]))
+        a = int(rng.integers(0, E - 1))
+        b = int(rng.integers(a + 1, E + 1))
+        quant = bool(rng.random() < 0.7)
+        kind = str(rng.choice(["bf16", "f16", "f32"] if quant else ["bf16", "f16", "f32", "int8"]))
+        check_init_routing(oracle, n, k, h, E, (a, b), 3000 * seed + it, quant=quant, x_kind=kind, smooth=bool(quant and rng.random() < 0.5),
+                           row_idx_type=int(rng.integers(0, 2)), count_type=int(rng.integers(1, 3)),
+                           per_token_scale=bool(not quant and rng.random() < 0.5))
