@@ -10,10 +10,13 @@
 //
 // Four launches, no host read in between:
 //   count   - one histogram of the active experts per block of 1024 pairs
-//   scan    - per expert: exclusive prefix over the blocks; over experts: start of every expert's rows, the counts output
-//   scatter - every pair finds its place: expert start + earlier blocks + earlier pairs of its block (warps take turns,
-//             __match_any_sync orders the lanes), which keeps the order of equal keys
-//   gather  - one CTA per output row: read the token row, (quantise,) store
+//   scan    - per expert (one CTA per 32 experts): exclusive prefix over the blocks; the CTA that finishes last then
+//             scans over the experts: start of every expert's rows, the counts output, the number of rows
+//   scatter - every pair finds its place: expert start + earlier blocks + earlier pairs of its block
+//             (__match_any_sync ranks the lanes of a warp; the warps are ranked through a per-warp counter table, or take
+//             turns when the active range is too wide for one), which keeps the order of equal keys
+//   gather  - one CTA per token: the row is read once into registers, (quantised,) and stored at the output row of each
+//             of its k pairs; shapes that do not fit the register tile take one CTA per output row
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
