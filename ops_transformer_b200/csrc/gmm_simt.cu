@@ -2,7 +2,8 @@
 //   * gmm_simt_kernel, swiglu_simt_kernel - complete operators for shapes the TMA path cannot take (K or N not a multiple of
 //                          16 bytes, unaligned pointers).  The reference accepts such shapes (its own unit
 //                          tests use K=5, N=10), so they run here on the GPU instead of being rejected.
-// plus the plan / launch glue shared by both paths.
+//   * combine_init_kernel - the initial contents of the finalize-routing result (weighted shared-expert rows, zeros).
+// plus the plan / launch glue shared by both paths (make_plan: path, tile shape, workspace layout; launch).
 //
 // Arithmetic follows gmm/grouped_matmul/op_kernel/grouped_matmul_quant_mixcore.h:248-315 and
 // gmm/grouped_matmul_swiglu_quant/op_kernel/grouped_matmul_swiglu_quant.h:367-513 step for step: every fp32
