@@ -17,23 +17,38 @@ ACL_FUNC_VISIBILITY int32_t gmmB200Version(void);
 /* The second-phase calls only enqueue work, so a device-side problem (a bounded wait that ran out) cannot be
  * returned by them.  This call waits for `stream`, copies the 4-word status record that the kernels keep at the
  * start of `workspace` and returns ACLNN_SUCCESS when it is clean, ACLNN_ERR_RUNTIME_ERROR otherwise.
- * record[0] = code (0 clean, 1 wait timed out), record[1] = CTA, record[2] = waiting role, record[3] = detail.
+ * record[0] = code (0 clean, 1 wait timed out, 2 bad scatter index), record[1] = CTA, record[2] = waiting role, record[3] = detail.
  * `record` may be null.  Plays the role of the reference's aclrtSynchronizeStream + error query after
  * aclnnGroupedMatmulV4 (gmm/grouped_matmul/examples/test_aclnn_grouped_matmul.cpp:180-196). */
 ACL_FUNC_VISIBILITY aclnnStatus gmmB200CheckStatus(const void *workspace, uint64_t workspaceSize, aclrtStream stream,
                                                   int32_t record[4]);
 
-/* The GEMM kernels are persistent and normally launch one CTA per SM.  A caller that overlaps them with other work on
- * the same GPU (for example the collectives of an expert-parallel layer, whose kernels need a few SMs to make progress)
- * can cap the number of CTAs; 0 restores the default.  Process wide.  No counterpart in the reference, where the
- * AI-core count comes from the platform (gmm/grouped_matmul/op_host/op_tiling/grouped_matmul_tiling.cpp:908-918). */
-ACL_FUNC_VISIBILITY void gmmB200SetSmLimit(int32_t maxCtas);
-
-/* Measurement hook: while both events (cudaEvent_t, created by the caller) are set, every launch records
- * `startEvent` right before and `stopEvent` right after the tensor-core GEMM kernel on the launch stream, so a
- * benchmark can time that kernel alone inside a multi-kernel operator.  Pass null to switch it off.  Process
- * wide and not thread safe; meant for benchmarks.  No counterpart in the reference. */
-ACL_FUNC_VISIBILITY void gmmB200SetTimingEvents(void *startEvent, void *stopEvent);
+/* Per-call launch options.  They belong to one executor (gmmB200SetExecutorOptions, between the two phases of an aclnn
+ * call) or to one flat call (the trailing `options` argument, may be null), never to the process, so threads that launch on
+ * different streams do not see each other's settings.  No counterpart in the reference, where the AI-core count comes from
+ * the platform (gmm/grouped_matmul/op_host/op_tiling/grouped_matmul_tiling.cpp:908-918) and phases are traced with
+ * L2_DFX_PHASE_1/2 (gmm/grouped_matmul/op_host/op_api/aclnn_grouped_matmul.cpp:2005, 2151).
+ *   structSize       sizeof(gmmB200LaunchOptions) as the caller compiled it (fields beyond it read as 0).
+ *   maxCtas          the GEMM kernels are persistent and normally launch one CTA per SM; a caller that overlaps them with
+ *                    other work on the same GPU (the exchange kernels of an expert-parallel layer) can cap the CTAs. 0 = no cap.
+ *   startEvent /     cudaEvent_t handles created by the caller: recorded right before and right after the tensor-core GEMM
+ *   stopEvent        kernel(s) of the call on the launch stream, so a benchmark can time them alone inside a multi-kernel
+ *                    operator.  Null = off.
+ *   waitLimitCycles  bound of every device-side wait (SM clock cycles) before a CTA gives up, records a status and returns;
+ *                    0 = the default of 2^31 cycles (about a second).
+ *   testSkipKBlocks  test only: the copy-issuing warp leaves this many K blocks out of its last tile, so that the bounded wait
+ *                    of the warp that consumes them runs out and the abort path (status record, clean exit) can be exercised
+ *                    without touching memory the call does not own.  Results are then undefined.  0 = off. */
+typedef struct gmmB200LaunchOptions {
+    uint32_t structSize;
+    int32_t maxCtas;
+    void *startEvent;
+    void *stopEvent;
+    int64_t waitLimitCycles;
+    int32_t testSkipKBlocks;
+    int32_t reserved;
+} gmmB200LaunchOptions;
+ACL_FUNC_VISIBILITY aclnnStatus gmmB200SetExecutorOptions(aclOpExecutor *executor, const gmmB200LaunchOptions *options);
 
 /* Flat form of aclnnGroupedMatmulV4 for the W8A8 path (same arithmetic, same validation of sizes).
  * scaleDtype / biasDtype / yDtype use aclDataType codes; bias may be null (biasDtype ignored);
@@ -42,7 +57,9 @@ ACL_FUNC_VISIBILITY void gmmB200SetTimingEvents(void *startEvent, void *stopEven
  * outRowIndex (optional, int64 [m] on the device, may be null): result row r is written to row outRowIndex[r] of y
  * instead of row r, which lets a caller fold the un-permute that follows the down projection of an MoE layer into the
  * GEMM (the row scatter of the reference's GroupedMatmulFinalizeRouting, gmm/grouped_matmul_finalize_routing/README.md:11-14,
- * without its weighting).  The indices must be a permutation onto rows of y; they are not checked.
+ * without its weighting).  The indices must be a permutation onto rows of y.  outRows = the rows of y (and of every
+ * peer buffer): a row whose index is negative, at or beyond outRows, or names a GPU that is no peer is not stored; the
+ * first such row is reported by gmmB200CheckStatus (code 2, record[3] = the source row).  outRows 0 = no upper bound.
  * outPeers / numPeers (optional, bf16 result only): with numPeers in [1, 8], outRowIndex[r] = (gpu << 40) | row and the
  * row is stored into outPeers[gpu] (a [rows, n] bf16 buffer that may live on another GPU of the node, see
  * gmmB200PeerImport) instead of y: the return all-to-all of an expert-parallel layer folded into the GEMM epilogue,
@@ -55,8 +72,9 @@ ACL_FUNC_VISIBILITY aclnnStatus gmmB200GroupedMatmulW8A8(const void *x, const vo
                                                         int32_t biasDtype, const void *groupList, int64_t groupListLen,
                                                         int32_t groupListType, int64_t m, int64_t k, int64_t n, int64_t e,
                                                         int32_t weightTransposed, int32_t actType, const void *outRowIndex,
-                                                        void *const *outPeers, int32_t numPeers, void *y, int32_t yDtype,
-                                                        void *workspace, uint64_t workspaceSize, aclrtStream stream);
+                                                        void *const *outPeers, int32_t numPeers, int64_t outRows, void *y, int32_t yDtype,
+                                                        void *workspace, uint64_t workspaceSize, aclrtStream stream,
+                                                        const gmmB200LaunchOptions *options);
 
 /* Buffers that other GPUs of the node can write into (CUDA IPC).  PeerAlloc/PeerFree own device memory of the calling
  * process; PeerExport fills a 64-byte handle that another process passes to PeerImport to obtain a device pointer to the
@@ -113,7 +131,7 @@ ACL_FUNC_VISIBILITY aclnnStatus gmmB200GroupedMatmulFinalizeRouting(
     const void *perTokenScale, const void *groupList, int64_t groupListLen, int32_t groupListType, const void *sharedInput,
     int64_t sharedRows, int64_t sharedOffset, float sharedWeight, const void *logit, const void *rowIndex, int32_t rowIndexDtype,
     int64_t m, int64_t k, int64_t n, int64_t e, void *y, int64_t yRows, void *workspace, uint64_t workspaceSize,
-    aclrtStream stream);
+    aclrtStream stream, const gmmB200LaunchOptions *options);
 
 /* Flat form of aclnnGroupedMatmulSwigluQuant.  weightLayout: 0 = [e, k, n], 2 = FRACTAL_NZ [e, n/32, k/16, 16, 32]. */
 ACL_FUNC_VISIBILITY aclnnStatus gmmB200GroupedMatmulSwigluQuantWorkspaceSize(int64_t m, int64_t k, int64_t n, int64_t e,
@@ -123,7 +141,8 @@ ACL_FUNC_VISIBILITY aclnnStatus gmmB200GroupedMatmulSwigluQuant(const void *x, c
                                                                const void *groupList, int64_t groupListLen, int64_t m,
                                                                int64_t k, int64_t n, int64_t e, int32_t weightLayout,
                                                                void *output, void *outputScale, void *workspace,
-                                                               uint64_t workspaceSize, aclrtStream stream);
+                                                               uint64_t workspaceSize, aclrtStream stream,
+                                                               const gmmB200LaunchOptions *options);
 
 /* grouped_matmul_swiglu_quant without any device allocation.  This entry point has no counterpart in the reference.
  *
@@ -132,14 +151,19 @@ ACL_FUNC_VISIBILITY aclnnStatus gmmB200GroupedMatmulSwigluQuant(const void *x, c
  * cudaMalloc / cudaFree imply.  The operator's scratch memory is a fixed array of
  * GMM_B200_NO_ALLOC_SCRATCH_BYTES inside the library image, which every GPU that loads the library keeps until the
  * process ends.  Same arguments and results as gmmB200GroupedMatmulSwigluQuant minus the workspace.
- *   - Limit: the scratch needed is about 4*m*(n/2) + 4*m + 4*(m/128 + groupListLen) + 1 KiB bytes; a larger problem is rejected
+ *   - Limit: the scratch needed is 256 + 4*m + 8*(m/128 + 2*groupListLen + 2) + 4*m*(n/2) bytes, each part rounded up to 256; a larger problem is rejected
  *     with ACLNN_ERR_PARAM_INVALID and a message (e.g. at n = 4096, m = 4096 rows fit and m = 8192 do not).
  *   - The first call on each device looks up the array's device address (once, with that device current); make that
  *     first call before any stream capture begins.
  *   - All calls share the one array and it keeps the previous call's contents; the part that must start at zero is
  *     cleared on `stream` by every call.  Two calls that can overlap on the GPU (different streams, no ordering
  *     between them) race on it: order them, or use the workspace variant for one of them.
- * Neither this call nor anything it calls allocates or frees device memory. */
+ * The first call on a device is a warm-up: loading the library's code and the array onto that device, and the first launch
+ * of each kernel variant, may allocate inside the CUDA runtime.  After that neither this call nor anything it calls
+ * allocates or frees device memory.
+ * gmmB200NoAllocCheckStatus: the kernels' status record sits at the start of the built-in array, out of the caller's reach;
+ * this call waits for `stream` and reports it exactly as gmmB200CheckStatus does for a caller-provided workspace (a bounded
+ * device-side wait that ran out gives ACLNN_ERR_RUNTIME_ERROR and fills `record`, which may be null). */
 #define GMM_B200_NO_ALLOC_SCRATCH_BYTES (32u * 1024u * 1024u + 64u * 1024u)
 ACL_FUNC_VISIBILITY uint64_t gmmB200NoAllocScratchBytes(void);
 ACL_FUNC_VISIBILITY aclnnStatus gmmB200GroupedMatmulSwigluQuantNoAlloc(const void *x, const void *weight, const void *weightScale,
@@ -147,6 +171,7 @@ ACL_FUNC_VISIBILITY aclnnStatus gmmB200GroupedMatmulSwigluQuantNoAlloc(const voi
                                                                       const void *groupList, int64_t groupListLen, int64_t m,
                                                                       int64_t k, int64_t n, int64_t e, void *output,
                                                                       void *outputScale, aclrtStream stream);
+ACL_FUNC_VISIBILITY aclnnStatus gmmB200NoAllocCheckStatus(aclrtStream stream, int32_t record[4]);
 
 #ifdef __cplusplus
 }

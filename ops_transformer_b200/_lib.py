@@ -33,11 +33,20 @@ EXPORTED_SYMBOLS = [
     "aclnnMoeInitRoutingV3GetWorkspaceSize", "aclnnMoeInitRoutingV3",
     "aclnnGroupedMatmulSwigluQuantGetWorkspaceSize", "aclnnGroupedMatmulSwigluQuant",
     "aclnnGroupedMatmulSwigluQuantWeightNZGetWorkspaceSize", "aclnnGroupedMatmulSwigluQuantWeightNZ",
-    "gmmB200Version", "gmmB200CheckStatus", "gmmB200SetTimingEvents", "gmmB200SetSmLimit", "gmmB200GroupedMatmulW8A8WorkspaceSize", "gmmB200GroupedMatmulW8A8",
+    "gmmB200Version", "gmmB200CheckStatus", "gmmB200SetExecutorOptions", "gmmB200GroupedMatmulW8A8WorkspaceSize", "gmmB200GroupedMatmulW8A8",
     "gmmB200GroupedMatmulSwigluQuantWorkspaceSize", "gmmB200GroupedMatmulSwigluQuant",
-    "gmmB200NoAllocScratchBytes", "gmmB200GroupedMatmulSwigluQuantNoAlloc",
+    "gmmB200NoAllocScratchBytes", "gmmB200GroupedMatmulSwigluQuantNoAlloc", "gmmB200NoAllocCheckStatus",
     "gmmB200PeerAlloc", "gmmB200PeerFree", "gmmB200PeerExport", "gmmB200PeerImport", "gmmB200PeerRelease", "gmmB200EpDispatch", "gmmB200EpCount", "gmmB200EpRoute",
 ]
+
+
+class LaunchOptions(C.Structure):
+    """gmmB200LaunchOptions (include/gmm_b200.h): per-call CTA cap, timing events, wait bound, abort-path test hook."""
+    _fields_ = [("structSize", C.c_uint32), ("maxCtas", C.c_int32), ("startEvent", C.c_void_p), ("stopEvent", C.c_void_p),
+                ("waitLimitCycles", C.c_int64), ("testSkipKBlocks", C.c_int32), ("reserved", C.c_int32)]
+
+    def __init__(self, max_ctas: int = 0, start_event=None, stop_event=None, wait_limit_cycles: int = 0, test_skip_k_blocks: int = 0):
+        super().__init__(C.sizeof(LaunchOptions), max_ctas, start_event, stop_event, wait_limit_cycles, test_skip_k_blocks, 0)
 
 
 class LibraryMissing(RuntimeError):
@@ -69,26 +78,25 @@ def _load():
     L.aclnnGroupedMatmulWeightNzGetWorkspaceSize.argtypes = [p] * 12 + [i64] * 4 + [p, i64] + [p] * 3 + [C.POINTER(u64), C.POINTER(p)]
     L.aclnnGroupedMatmulWeightNz.argtypes = [p, u64, p, p]
     f32, b8 = C.c_float, C.c_bool
+    po = C.POINTER(LaunchOptions)
     L.aclnnGroupedMatmulFinalizeRoutingWeightNzGetWorkspaceSize.argtypes = [p] * 9 + [i64, f32, i64, b8, b8, i64, p, C.POINTER(u64), C.POINTER(p)]
     L.aclnnGroupedMatmulFinalizeRoutingWeightNz.argtypes = [p, u64, p, p]
     L.aclnnGroupedMatmulFinalizeRoutingWeightNzV2GetWorkspaceSize.argtypes = [p] * 12 + [i64, f32, i64, b8, b8, i64, p, p, C.POINTER(u64), C.POINTER(p)]
     L.aclnnGroupedMatmulFinalizeRoutingWeightNzV2.argtypes = [p, u64, p, p]
     L.aclnnMoeInitRoutingV3GetWorkspaceSize.argtypes = [p] * 4 + [i64] * 5 + [b8, i64, p, i64] + [p] * 4 + [C.POINTER(u64), C.POINTER(p)]
     L.aclnnMoeInitRoutingV3.argtypes = [p, u64, p, p]
-    L.gmmB200GroupedMatmulFinalizeRouting.argtypes = [p, p, i32, p, i32, p, p, p, i64, i32, p, i64, i64, f32, p, p, i32, i64, i64, i64, i64, p, i64, p, u64, p]
+    L.gmmB200GroupedMatmulFinalizeRouting.argtypes = [p, p, i32, p, i32, p, p, p, i64, i32, p, i64, i64, f32, p, p, i32, i64, i64, i64, i64, p, i64, p, u64, p,
+                                                      C.POINTER(LaunchOptions)]
     L.aclnnGroupedMatmulSwigluQuantWeightNZGetWorkspaceSize.argtypes = [p] * 10 + [C.POINTER(u64), C.POINTER(p)]
     L.aclnnGroupedMatmulSwigluQuantWeightNZ.argtypes = [p, u64, p, p]
     L.aclnnGroupedMatmulSwigluQuantGetWorkspaceSize.argtypes = [p] * 10 + [C.POINTER(u64), C.POINTER(p)]
     L.aclnnGroupedMatmulSwigluQuant.argtypes = [p, u64, p, p]
     L.gmmB200CheckStatus.argtypes = [p, u64, p, C.POINTER(i32)]
-    L.gmmB200SetTimingEvents.argtypes = [p, p]
-    L.gmmB200SetTimingEvents.restype = None
-    L.gmmB200SetSmLimit.argtypes = [i32]
-    L.gmmB200SetSmLimit.restype = None
+    L.gmmB200SetExecutorOptions.argtypes = [p, po]
     L.gmmB200GroupedMatmulW8A8WorkspaceSize.argtypes = [i64, i64, i64, i64, i32, C.POINTER(u64)]
-    L.gmmB200GroupedMatmulW8A8.argtypes = [p, p, p, i32, p, p, i32, p, i64, i32, i64, i64, i64, i64, i32, i32, p, p, i32, p, i32, p, u64, p]
+    L.gmmB200GroupedMatmulW8A8.argtypes = [p, p, p, i32, p, p, i32, p, i64, i32, i64, i64, i64, i64, i32, i32, p, p, i32, i64, p, i32, p, u64, p, po]
     L.gmmB200GroupedMatmulSwigluQuantWorkspaceSize.argtypes = [i64, i64, i64, i64, C.POINTER(u64)]
-    L.gmmB200GroupedMatmulSwigluQuant.argtypes = [p, p, p, i32, p, p, i64, i64, i64, i64, i64, i32, p, p, p, u64, p]
+    L.gmmB200GroupedMatmulSwigluQuant.argtypes = [p, p, p, i32, p, p, i64, i64, i64, i64, i64, i32, p, p, p, u64, p, po]
     L.gmmB200PeerAlloc.argtypes = [u64, C.POINTER(p)]
     L.gmmB200PeerFree.argtypes = [p]
     L.gmmB200PeerExport.argtypes = [p, p]
@@ -99,6 +107,7 @@ def _load():
     L.gmmB200EpRoute.argtypes = [p, p, p, i64, i32, i32, i32, i32, i64, i64, i64, p, p, p, p, p, p, p]
     L.gmmB200NoAllocScratchBytes.restype = u64
     L.gmmB200GroupedMatmulSwigluQuantNoAlloc.argtypes = [p, p, p, i32, p, p, i64, i64, i64, i64, i64, p, p, p]
+    L.gmmB200NoAllocCheckStatus.argtypes = [p, C.POINTER(i32)]
     return L
 
 

@@ -14,6 +14,7 @@ from typing import Optional, Sequence
 import torch
 
 from . import _lib
+from ._lib import LaunchOptions  # noqa: F401  (re-exported: the per-call options of include/gmm_b200.h)
 from ._lib import (ACL_BF16, ACL_FLOAT, ACL_FLOAT16, ACL_FORMAT_FRACTAL_NZ, ACL_FORMAT_ND, ACL_INT8, ACL_INT32, ACL_INT64,
                    ACLNN_SUCCESS)
 
@@ -109,7 +110,19 @@ def check_status(workspace: Optional[torch.Tensor], stream=None) -> None:
     size = workspace.numel() if workspace is not None else 0
     rc = _lib.lib().gmmB200CheckStatus(ptr, size, C.c_void_p(_stream_handle(stream)), rec)
     if rc != ACLNN_SUCCESS:
-        raise AclnnError(rc, "gmmB200CheckStatus")
+        err = AclnnError(rc, "gmmB200CheckStatus")
+        err.record = tuple(int(v) for v in rec)   # (code, CTA, waiting role, detail)
+        raise err
+
+
+def _apply_options(executor, options: Optional[LaunchOptions], where: str) -> None:
+    """Attach per-call options to a live executor (between the two phases)."""
+    if options is None:
+        return
+    rc = _lib.lib().gmmB200SetExecutorOptions(executor, C.byref(options))
+    if rc != ACLNN_SUCCESS:
+        _lib.lib().aclDestroyAclOpExecutor(executor)
+        raise AclnnError(rc, where + ": gmmB200SetExecutorOptions")
 
 
 def grouped_matmul_v4(x: torch.Tensor, weight: torch.Tensor, scale: Optional[torch.Tensor],
@@ -119,14 +132,16 @@ def grouped_matmul_v4(x: torch.Tensor, weight: torch.Tensor, scale: Optional[tor
                       out_dtype: torch.dtype = torch.bfloat16, stream=None, workspace: Optional[torch.Tensor] = None,
                       return_workspace: bool = False, out_row_index: Optional[torch.Tensor] = None,
                       out_peers: Optional[Sequence[int]] = None, weight_format: int = ACL_FORMAT_ND,
-                      api: str = "V4", tuning_config: Optional[Sequence[int]] = None, quant_group_size: int = 0):
+                      api: str = "V4", tuning_config: Optional[Sequence[int]] = None, quant_group_size: int = 0,
+                      options: Optional[LaunchOptions] = None, out_rows: int = 0):
     """y = bf16(act((x @ weight[e]) * scale[e] * per_token_scale)) per expert row range (W8A8), a float16 result with
     ``out_dtype`` torch.float16, or the raw int32 accumulators with torch.int32.  Rows not covered by ``group_list``
     keep their contents.  ``weight_format`` ACL_FORMAT_FRACTAL_NZ: ``weight`` is the 5-D storage of ``format_cast_nz``.
     ``api`` picks the entry point: "V4", "V5" (adds ``tuning_config``) or "WeightNz" (adds ``quant_group_size`` and
     treats the weight as FRACTAL_NZ) - aclnn_grouped_matmul_v5.h:49-58, aclnn_grouped_matmul_weight_nz.h:50-59 of the
     reference.  ``out_row_index`` (int64 [M], an extension of this library) scatters result row r to row
-    out_row_index[r]; it goes through the flat entry point gmmB200GroupedMatmulW8A8."""
+    out_row_index[r]; it goes through the flat entry point gmmB200GroupedMatmulW8A8.  ``options``: per-call
+    ``LaunchOptions`` (CTA cap, timing events)."""
     L = _lib.lib()
     nz = weight_format == ACL_FORMAT_FRACTAL_NZ or api == "WeightNz"
     if out is None and not out_peers:
@@ -134,7 +149,7 @@ def grouped_matmul_v4(x: torch.Tensor, weight: torch.Tensor, scale: Optional[tor
         out = torch.empty((x.shape[0], n_out), dtype=out_dtype, device=x.device)
     if out_row_index is not None:
         return _grouped_matmul_flat(x, weight, scale, per_token_scale, group_list, bias, group_list_type, act_type, out,
-                                    out_row_index, stream, workspace, return_workspace, out_peers, nz)
+                                    out_row_index, stream, workspace, return_workspace, out_peers, nz, options, out_rows)
     lists = []
     tuning = None
     try:
@@ -174,6 +189,7 @@ def grouped_matmul_v4(x: torch.Tensor, weight: torch.Tensor, scale: Optional[tor
                 L.aclDestroyAclOpExecutor(ex)
                 raise ValueError(f"workspace of {workspace.numel()} bytes is smaller than the {ws_size.value} required")
             wptr = C.c_void_p(workspace.data_ptr()) if workspace is not None else None
+            _apply_options(ex, options, "aclnnGroupedMatmul" + api)
             rc = getattr(L, "aclnnGroupedMatmul" + api)(wptr, ws_size.value, ex, C.c_void_p(_stream_handle(stream)))
             if rc != ACLNN_SUCCESS:
                 raise AclnnError(rc, "aclnnGroupedMatmul" + api)
@@ -188,9 +204,10 @@ def grouped_matmul_v4(x: torch.Tensor, weight: torch.Tensor, scale: Optional[tor
 
 
 def _grouped_matmul_flat(x, weight, scale, per_token_scale, group_list, bias, group_list_type, act_type, out, out_row_index,
-                         stream, workspace, return_workspace, out_peers=None, nz=False):
+                         stream, workspace, return_workspace, out_peers=None, nz=False, options=None, out_rows=0):
     """Flat entry point.  ``out_peers`` (device addresses, one [rows, N] bf16 buffer per GPU) makes out_row_index hold
-    (gpu << 40) | row; ``out`` may then be None."""
+    (gpu << 40) | row; ``out`` may then be None.  ``out_rows``: rows of ``out`` / of every peer buffer (0 = taken from
+    ``out``, unbounded without it); rows scattered outside are skipped and reported by ``check_status``."""
     L = _lib.lib()
     M, K = x.shape
     if nz and weight.dim() == 5:
@@ -204,6 +221,8 @@ def _grouped_matmul_flat(x, weight, scale, per_token_scale, group_list, bias, gr
     if out_row_index.dtype != torch.int64 or out_row_index.numel() != M:
         raise ValueError("out_row_index must be int64 [M]")
     ydt = _DTYPES[out.dtype] if out is not None else ACL_BF16
+    if not out_rows and out is not None:
+        out_rows = out.shape[0]
     n_peers = len(out_peers) if out_peers else 0
     peers = (C.c_void_p * max(n_peers, 1))(*[C.c_void_p(a) for a in (out_peers or [])])
     size = C.c_uint64(0)
@@ -215,8 +234,8 @@ def _grouped_matmul_flat(x, weight, scale, per_token_scale, group_list, bias, gr
     p = lambda t: C.c_void_p(t.data_ptr()) if t is not None else None  # noqa: E731
     rc = L.gmmB200GroupedMatmulW8A8(p(x), p(weight), p(scale), _DTYPES[scale.dtype] if scale is not None else 0, p(per_token_scale),
                                     p(bias), _DTYPES[bias.dtype] if bias is not None else 0, p(group_list), group_list.numel(),
-                                    group_list_type, M, K, N, E, trans, act_type, p(out_row_index), peers if n_peers else None, n_peers, p(out), ydt, p(workspace),
-                                    workspace.numel(), C.c_void_p(_stream_handle(stream)))
+                                    group_list_type, M, K, N, E, trans, act_type, p(out_row_index), peers if n_peers else None, n_peers, out_rows, p(out), ydt, p(workspace),
+                                    workspace.numel(), C.c_void_p(_stream_handle(stream)), C.byref(options) if options is not None else None)
     if rc != ACLNN_SUCCESS:
         raise AclnnError(rc, "gmmB200GroupedMatmulW8A8")
     return (out, workspace) if return_workspace else out
@@ -227,7 +246,7 @@ def grouped_matmul_swiglu_quant(x: torch.Tensor, weight: torch.Tensor, weight_sc
                                 offset: Optional[torch.Tensor] = None, output: Optional[torch.Tensor] = None,
                                 output_scale: Optional[torch.Tensor] = None, stream=None,
                                 workspace: Optional[torch.Tensor] = None, return_workspace: bool = False,
-                                weight_format: int = ACL_FORMAT_ND, api: str = ""):
+                                weight_format: int = ACL_FORMAT_ND, api: str = "", options: Optional[LaunchOptions] = None):
     """(output int8 [M, N/2], output_scale fp32 [M]) = per-token int8 requant of SwiGLU of the dequantised grouped
     GEMM.  ``group_list`` holds running totals.  Rows at and beyond group_list[-1] keep their contents.
     ``weight_format`` ACL_FORMAT_FRACTAL_NZ: ``weight`` is the 5-D storage of ``format_cast_nz``; ``api`` "WeightNZ"
@@ -264,6 +283,7 @@ def grouped_matmul_swiglu_quant(x: torch.Tensor, weight: torch.Tensor, weight_sc
             L.aclDestroyAclOpExecutor(ex)
             raise ValueError(f"workspace of {workspace.numel()} bytes is smaller than the {ws_size.value} required")
         wptr = C.c_void_p(workspace.data_ptr()) if workspace is not None else None
+        _apply_options(ex, options, name)
         rc = getattr(L, name)(wptr, ws_size.value, ex, C.c_void_p(_stream_handle(stream)))
         if rc != ACLNN_SUCCESS:
             raise AclnnError(rc, name)
@@ -279,7 +299,8 @@ def grouped_matmul_finalize_routing(x: torch.Tensor, weight_nz: torch.Tensor, sc
                                     logit: Optional[torch.Tensor] = None, shared_input_weight: float = 1.0,
                                     shared_input_offset: int = 0, group_list_type: int = 1, out: Optional[torch.Tensor] = None,
                                     view_3d: bool = True, api: str = "", tuning_config: Optional[Sequence[int]] = None,
-                                    stream=None, workspace: Optional[torch.Tensor] = None, return_workspace: bool = False):
+                                    stream=None, workspace: Optional[torch.Tensor] = None, return_workspace: bool = False,
+                                    options: Optional[LaunchOptions] = None):
     """aclnnGroupedMatmulFinalizeRoutingWeightNz (``api`` "") or ...WeightNzV2 (``api`` "V2"): W8A8 grouped GEMM whose fp32
     result rows, weighted by ``logit``, are added into row ``row_index[i]`` of ``out`` [batch, N] on top of the weighted
     ``shared_input`` rows (gmm/grouped_matmul_finalize_routing/op_host/op_api/aclnn_grouped_matmul_finalize_routing_weight_nz.h:48-64
@@ -324,6 +345,7 @@ def grouped_matmul_finalize_routing(x: torch.Tensor, weight_nz: torch.Tensor, sc
             L.aclDestroyAclOpExecutor(ex)
             raise ValueError(f"workspace of {workspace.numel()} bytes is smaller than the {ws_size.value} required")
         wptr = C.c_void_p(workspace.data_ptr()) if workspace is not None else None
+        _apply_options(ex, options, name)
         rc = getattr(L, name)(wptr, ws_size.value, ex, C.c_void_p(_stream_handle(stream)))
         if rc != ACLNN_SUCCESS:
             raise AclnnError(rc, name)
@@ -337,7 +359,7 @@ def grouped_matmul_finalize_routing(x: torch.Tensor, weight_nz: torch.Tensor, sc
 
 def grouped_matmul_finalize_routing_flat(x, weight, weight_layout, scale, group_list, row_index, out, *, bias=None,
                                          pertoken_scale=None, shared_input=None, logit=None, shared_input_weight=1.0,
-                                         shared_input_offset=0, group_list_type=1, stream=None, workspace=None):
+                                         shared_input_offset=0, group_list_type=1, stream=None, workspace=None, options=None):
     """gmmB200GroupedMatmulFinalizeRouting: the same operator without handles; ``weight_layout`` 0 takes the ND [E, K, N]
     weight (the faster layout here), 2 the FRACTAL_NZ storage."""
     L = _lib.lib()
@@ -353,7 +375,8 @@ def grouped_matmul_finalize_routing_flat(x, weight, weight_layout, scale, group_
         p(x), p(weight), weight_layout, p(scale), _DTYPES[scale.dtype], p(bias), p(pertoken_scale), p(group_list),
         group_list.numel(), group_list_type, p(shared_input), 0 if shared_input is None else shared_input.shape[0],
         shared_input_offset, shared_input_weight, p(logit), p(row_index), _DTYPES[row_index.dtype], M, K, N, E, p(out),
-        out.shape[0], p(workspace), workspace.numel(), C.c_void_p(_stream_handle(stream)))
+        out.shape[0], p(workspace), workspace.numel(), C.c_void_p(_stream_handle(stream)),
+        C.byref(options) if options is not None else None)
     if rc != ACLNN_SUCCESS:
         raise AclnnError(rc, "gmmB200GroupedMatmulFinalizeRouting")
     return out

@@ -57,6 +57,12 @@ bool claim_executor(aclOpExecutor *e)
     return g_live_executors.erase(e) == 1;
 }
 
+bool executor_is_live(aclOpExecutor *e)
+{
+    std::lock_guard<std::mutex> lk(g_exec_mu);
+    return g_live_executors.count(e) == 1;
+}
+
 }  // namespace gmm
 
 extern "C" {

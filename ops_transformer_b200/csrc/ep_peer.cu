@@ -21,11 +21,11 @@ struct PeerPtrs {
 constexpr long long kRowMask = (1ll << 40) - 1;
 
 // One warp per row.  dest[i] = (gpu << 40) | row, or negative to skip the row.  A destination row at or beyond
-// `capacity` is not written; the kernel counts such rows in *overflow instead.
+// `capacity`, or a gpu field that names no peer, is not written; the kernel counts such rows in *overflow instead.
 __global__ void __launch_bounds__(256) ep_dispatch_kernel(const int8_t *__restrict__ x, const float *__restrict__ xs,
                                                            const long long *__restrict__ src_token,
                                                            const long long *__restrict__ dest, long long rows, int hidden,
-                                                           long long capacity, PeerPtrs pp, int *overflow,
+                                                           long long capacity, PeerPtrs pp, int num_peers, int *overflow,
                                                            const long long *__restrict__ first_row)
 {
     const int lane = threadIdx.x & 31;
@@ -39,9 +39,10 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const int8_t *__restri
         const long long row = it + rot < rows ? it + rot : it + rot - rows;
         const long long d = dest[row];
         if (d < 0) continue;
-        const int gpu = (int)(d >> 40) & 7;
+        const long long gpu_field = d >> 40;
+        const int gpu = (int)gpu_field;
         const long long drow = d & kRowMask;
-        if (drow >= capacity) {
+        if (gpu_field >= num_peers || drow >= capacity) {
             if (lane == 0) atomicAdd(overflow, 1);
             continue;
         }
@@ -267,7 +268,7 @@ aclnnStatus gmmB200EpDispatch(const void *x, const void *xScale, const void *src
     const int grid = (int)std::min<int64_t>((rows + 7) / 8, (int64_t)sms * 8);
     ep_dispatch_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const int8_t *>(x), static_cast<const float *>(xScale), static_cast<const long long *>(srcToken),
-        static_cast<const long long *>(dest), rows, (int)hidden, capacity, pp, static_cast<int *>(overflowCounter),
+        static_cast<const long long *>(dest), rows, (int)hidden, capacity, pp, numPeers, static_cast<int *>(overflowCounter),
         static_cast<const long long *>(firstRow));
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return gmm::fail(ACLNN_ERR_INNER, "dispatch kernel launch failed: %s", cudaGetErrorString(e));

@@ -22,7 +22,20 @@ enum : int {
 enum : int { kPathSm100 = 0, kPathSimt = 1 };
 
 // Kernel status word (4 x int32 at the start of the workspace).  code 0 = clean.
-enum : int { kStatusOk = 0, kStatusWaitTimeout = 1, kStatusBadSchedule = 2 };
+// kStatusBadIndex: a scattered result row named a GPU that is no peer or a row outside the result; the row was skipped
+// (record[1] = CTA, record[2] = 800, record[3] = the first such source row).
+enum : int { kStatusOk = 0, kStatusWaitTimeout = 1, kStatusBadIndex = 2 };
+
+// Per-call launch options (the internal form of gmmB200LaunchOptions, include/gmm_b200.h).  They travel with the
+// problem description, so two threads launching on two streams never see each other's settings.
+struct LaunchOptions {
+    int max_ctas = 0;                   // cap on the CTAs of the persistent kernels, 0 = one per SM
+    cudaEvent_t ev_start = nullptr;     // recorded right before / after the tensor-core kernel(s) on the launch stream
+    cudaEvent_t ev_stop = nullptr;
+    long long wait_limit_cycles = 0;    // bound of every device-side wait, 0 = the default (about a second)
+    int test_skip_k_blocks = 0;         // test only: the TMA producer leaves out this many K blocks of its last tile, so that
+                                        // the MMA issuer's bounded wait runs out (the abort path); results are undefined
+};
 
 struct Problem {
     const int8_t *x = nullptr;          // [M, K]
@@ -58,6 +71,7 @@ struct Problem {
     int64_t shared_rows = 0;            // float(shared_input) * shared_weight, every other row as 0 (scatter_add only)
     int64_t shared_offset = 0;
     float shared_weight = 1.0f;
+    LaunchOptions opt;
 };
 
 struct Plan {
@@ -103,7 +117,8 @@ struct StagedView {
 };
 cudaError_t view_copy_launch(const StagedView &v, void *contiguous, bool to_contiguous, cudaStream_t stream);
 
-// Host only: choose the kernel path and the workspace layout.  Never touches the device.
+// Host only: choose the kernel path and the workspace layout from the shapes.  Never touches the device (the tile-shape
+// heuristics assume the 148 SMs of a B200; the launch itself asks the device).
 void make_plan(const Problem &p, Plan *plan);
 // Enqueue the operator on `stream`.  Returns cudaSuccess or the first CUDA error.
 cudaError_t launch(const Problem &p, Plan &plan, void *workspace, size_t workspace_bytes, cudaStream_t stream);
@@ -112,16 +127,13 @@ cudaError_t launch(const Problem &p, Plan &plan, void *workspace, size_t workspa
 bool sm100_shape_ok(const Problem &p);
 cudaError_t sm100_encode_maps(const Problem &p, Plan &plan);
 cudaError_t sm100_launch(const Problem &p, Plan &plan, void *workspace, cudaStream_t stream);
-// Optional pair of events recorded right before / after the tensor-core kernel (nullptr = off).
-void set_timing_events(cudaEvent_t start, cudaEvent_t stop);
 // gmm_simt.cu
 // Initial contents of the combined result (PreProcess of grouped_matmul_finalize_routing.h:208-258).
 cudaError_t combine_init_launch(const Problem &p, cudaStream_t stream);
 cudaError_t simt_launch(const Problem &p, Plan &plan, void *workspace, cudaStream_t stream);
 
+// SMs of the current device (cached per device); 0 on error.
 int device_sm_count();
-// Caps the number of CTAs the persistent kernels launch (0 = one per SM).
-void set_sm_limit(int n);
 
 #ifdef __CUDACC__
 // Activations of the dequantising epilogue (ActivationCompute, gmm/grouped_matmul/op_kernel/grouped_matmul_quant_mixcore.h:390-405).

@@ -57,8 +57,8 @@ aclnnStatus gmmB200GroupedMatmulSwigluQuantNoAlloc(const void *x, const void *we
     clear_error();
     if (!(x && weight && weightScale && xScale && groupList && output && outputScale))
         return fail(ACLNN_ERR_PARAM_NULLPTR, "x, weight, weightScale, xScale, groupList, output and outputScale must not be nullptr.");
-    if (!(m >= 0 && k > 0 && n > 0 && e > 0 && k < 65536 && n <= 10240 && n % 2 == 0))
-        return fail(ACLNN_ERR_PARAM_INVALID, "need m >= 0, 0 < k < 65536, 0 < n <= 10240 and even, e > 0.");
+    if (!(m >= 0 && m <= 0x7fffffffll / 2 && k > 0 && n > 0 && e > 0 && k < 65536 && n <= 10240 && n % 2 == 0))
+        return fail(ACLNN_ERR_PARAM_INVALID, "need 0 <= m < 2^30, 0 < k < 65536, 0 < n <= 10240 and even, e > 0.");
     if (!(weightScaleDtype == ACL_FLOAT || weightScaleDtype == ACL_FLOAT16 || weightScaleDtype == ACL_BF16))
         return fail(ACLNN_ERR_PARAM_INVALID, "weightScaleDtype must be float32, float16 or bfloat16.");
     if (!(groupListLen >= 0 && groupListLen <= e && groupListLen <= 1024))
@@ -92,6 +92,19 @@ aclnnStatus gmmB200GroupedMatmulSwigluQuantNoAlloc(const void *x, const void *we
     ce = launch(p, plan, scratch, kNoAllocScratchBytes, static_cast<cudaStream_t>(stream));
     if (ce != cudaSuccess) return fail(ACLNN_ERR_INNER, "kernel launch failed: %s", cudaGetErrorString(ce));
     return ACLNN_SUCCESS;
+}
+
+// The kernels keep their 4-word status record at the start of the scratch array, which a caller of the entry point above
+// cannot address.  This call waits for `stream`, copies the record out (into pageable host memory: no allocation) and
+// reports it like gmmB200CheckStatus does for a caller-provided workspace.
+aclnnStatus gmmB200NoAllocCheckStatus(aclrtStream stream, int32_t record[4])
+{
+    using namespace gmm;
+    clear_error();
+    void *scratch = nullptr;
+    cudaError_t ce = scratch_address(&scratch);
+    if (ce != cudaSuccess) return fail(ACLNN_ERR_RUNTIME_ERROR, "cannot resolve the built-in scratch array: %s", cudaGetErrorString(ce));
+    return gmmB200CheckStatus(scratch, 16, stream, record);
 }
 
 }  // extern "C"

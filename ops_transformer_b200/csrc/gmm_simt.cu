@@ -185,26 +185,47 @@ __global__ void __launch_bounds__(256) combine_init_kernel(float4 *y, const uint
     }
 }
 
+// The same for a result or shared rows that are not 16 / 8-byte aligned (a tensor view with a storage offset) or whose
+// width is not a multiple of 4: one element per thread and step.
+__global__ void __launch_bounds__(256) combine_init_scalar_kernel(float *y, const uint16_t *shared, long long n, long long rows,
+                                                                  long long shared_offset, long long shared_rows, float weight)
+{
+    const long long total = rows * n;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / n;
+        float v = 0.0f;
+        if (r >= shared_offset && r < shared_offset + shared_rows)
+            v = __fmul_rn(__uint_as_float((uint32_t)__ldg(shared + (i - shared_offset * n)) << 16), weight);
+        y[i] = v;
+    }
+}
+
 }  // namespace
 
 cudaError_t combine_init_launch(const Problem &p, cudaStream_t stream)
 {
     if (p.out_rows <= 0 || p.N <= 0) return cudaSuccess;
-    if (p.N % 4 != 0) return cudaErrorInvalidValue;
-    const long long n4 = p.N / 4, total = p.out_rows * n4;
+    if (reinterpret_cast<uintptr_t>(p.out0) & 3) return cudaErrorInvalidValue;
     const int sms = device_sm_count();
-    long long blocks = (total + 255) / 256;
     const long long cap = (long long)(sms > 0 ? sms : 1) * 8;
+    const bool vec = p.N % 4 == 0 && !(reinterpret_cast<uintptr_t>(p.out0) & 15) && !(reinterpret_cast<uintptr_t>(p.shared_input) & 7);
+    if (!vec) {
+        const long long total = p.out_rows * p.N;
+        long long blocks = (total + 255) / 256;
+        if (blocks > cap) blocks = cap;
+        combine_init_scalar_kernel<<<(unsigned)blocks, 256, 0, stream>>>(reinterpret_cast<float *>(p.out0),
+                                                                        reinterpret_cast<const uint16_t *>(p.shared_input), p.N, p.out_rows,
+                                                                        p.shared_offset, p.shared_input ? p.shared_rows : 0, p.shared_weight);
+        return cudaGetLastError();
+    }
+    const long long n4 = p.N / 4, total = p.out_rows * n4;
+    long long blocks = (total + 255) / 256;
     if (blocks > cap) blocks = cap;
     combine_init_kernel<<<(unsigned)blocks, 256, 0, stream>>>(reinterpret_cast<float4 *>(p.out0), reinterpret_cast<const uint2 *>(p.shared_input),
                                                              n4, p.out_rows, p.shared_offset, p.shared_input ? p.shared_rows : 0,
                                                              p.shared_weight);
     return cudaGetLastError();
 }
-
-static int g_sm_limit = 0;
-
-void set_sm_limit(int n) { g_sm_limit = n > 0 ? n : 0; }
 
 int device_sm_count()
 {
@@ -217,7 +238,6 @@ int device_sm_count()
         if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
         cached[dev] = n;
     }
-    if (g_sm_limit > 0 && g_sm_limit < cached[dev]) return g_sm_limit;
     return cached[dev];
 }
 
@@ -239,8 +259,8 @@ void make_plan(const Problem &p, Plan *plan)
     // 5-8 %).  GMM_B200_HYBRID=0|1 overrides.
     {
         const long long n_tiles = p.mode == kModeSwigluQuant ? (p.N / 2 + 127) / 128 : (p.N + 255) / 256;
-        const int sms = device_sm_count();
-        plan->hybrid = plan->ctas == 2 && (long long)p.gl_len * n_tiles >= 16ll * (sms > 0 ? sms : 148);
+        constexpr long long kPlanSms = 148;  // a B200; phase 1 is host only and does not ask the device
+        plan->hybrid = plan->ctas == 2 && (long long)p.gl_len * n_tiles >= 16ll * kPlanSms;
     }
     if (const char *e = getenv("GMM_B200_HYBRID")) plan->hybrid = plan->ctas == 2 && e[0] != '0';
     plan->off_status = 0;
@@ -248,8 +268,8 @@ void make_plan(const Problem &p, Plan *plan)
     plan->off_amax = off;
     if (p.mode == kModeSwigluQuant && plan->path == kPathSm100) {
         off += align_up((size_t)p.M * 4, 256);
-        plan->off_done = off;  // one counter per row block of a tile; every group can add a partial block in each of two launches
-        off += align_up(((size_t)(p.M + 127) / 128 + 2 * (size_t)p.gl_len + 2) * 4, 256);
+        plan->off_done = off;  // two words per row block of a tile; every group can add a partial block in each of two launches
+        off += align_up(((size_t)(p.M + 127) / 128 + 2 * (size_t)p.gl_len + 2) * 8, 256);
         plan->zero_bytes = off;
         plan->off_stage = off;
         off += align_up((size_t)p.M * (size_t)(p.N / 2) * 4, 256);

@@ -28,6 +28,7 @@
 #include <cuda_fp16.h>
 
 #include <cstddef>
+#include <cstdlib>
 
 #include "gmm_common.h"
 
@@ -58,7 +59,14 @@ struct Cfg {
 static_assert(Cfg<1>::kStages == 4 && Cfg<2>::kStages == 6 && Cfg<2>::kStages <= MAX_STAGES, "stage arithmetic");
 constexpr int MAX_GROUPS = 1024;
 constexpr int EPI_WARPS = 8;                 // two warps per TMEM lane quarter, each takes half of the columns
-constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;
+// swiglu_quant only: one publishing warp (one lane: row-block bookkeeping in global memory) and RQ_WARPS warps that
+// requantise finished row slices, all beside the epilogue, so that none of their memory round trips delays the next tile.
+constexpr int RQ_WARPS = 4;
+constexpr int RQ_THREADS = 32 * RQ_WARPS;
+constexpr int RQ_DEPTH = 4;                  // tiles the epilogue may be ahead of the publishing warp
+constexpr int WK_DEPTH = 4;                  // work lists the publishing warp may be ahead of the requantising warps
+constexpr int BASE_THREADS = 64 + 32 * EPI_WARPS;
+__host__ __device__ constexpr int num_threads(int mode) { return BASE_THREADS + (mode == kModeSwigluQuant ? 32 + RQ_THREADS : 0); }
 constexpr int TMEM_COLS = 512;
 constexpr long long WAIT_LIMIT_CYCLES = 1ll << 31;   // about a second
 constexpr long long DRAIN_LIMIT_CYCLES = 1ll << 24;  // a few milliseconds
@@ -67,6 +75,7 @@ constexpr int EPI_THREADS = 32 * EPI_WARPS;
 enum : int { kEpiPlain = 0, kEpiScatter = 1, kEpiGeneric = 2, kEpiCombine = 3 };
 // Weight layouts: [E,K,N]; [E,N,K] (the transposed view); FRACTAL_NZ [E, N/32, K/16, 16, 32] (32-byte runs along N).
 enum : int { kBRowMajor = 0, kBTransposed = 1, kBFractalNz = 2 };
+constexpr int MAX_PENDING = 6;         // unsettled row blocks a CTA keeps track of before it hands its share over
 constexpr int SCALE_BUFS = 3;          // an epilogue thread can run at most two tiles ahead of another one
 constexpr int OUT_STAGE_BYTES = 2048;  // per epilogue warp: 32 rows x 64 bytes of packed bf16
 
@@ -76,11 +85,21 @@ struct Shared {
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
     uint64_t scale_ready[SCALE_BUFS];  // all epilogue threads have stored their column's scale
-    uint64_t tile_sync[2];             // [0] every epilogue thread fenced its stores, [1] an earlier row block is complete
+    uint64_t rq_full[RQ_DEPTH];        // every epilogue thread has stored its part of a tile (swiglu_quant)
+    uint64_t rq_empty[RQ_DEPTH];       // the publishing warp has taken note of it
+    uint64_t wk_full[WK_DEPTH];        // a work list is written
+    uint64_t wk_empty[WK_DEPTH];       // every requantising thread is done with it
     uint32_t tmem_base;
     int abort_flag;
     int total_tiles;
     int pad;
+    long long wait_limit;              // bound of every wait, in cycles
+    // swiglu_quant: row blocks this CTA contributed to and has not yet settled (publishing lane only), and a ring of work
+    // lists: the row ranges to requantise (written by that lane, read by the requantising warps after wk_full)
+    int pend_n;
+    int pend_rb[MAX_PENDING], pend_row0[MAX_PENDING], pend_rows[MAX_PENDING];
+    int n_work[WK_DEPTH];
+    int work_begin[WK_DEPTH][MAX_PENDING + 1], work_end[WK_DEPTH][MAX_PENDING + 1];
     int row_start[MAX_GROUPS];
     int rows[MAX_GROUPS];
     int tile_start[MAX_GROUPS + 1];
@@ -116,12 +135,15 @@ struct KParams {
     int scatter_add;           // 1: atomic adds (shared-expert rows and logits given), 0: plain stores
     long long out_rows;        // rows of the fp32 result; indices outside [0, out_rows) are skipped
     unsigned *amax_bits;  // [M] row max of |S| as float bits (swiglu)
-    int *rb_counter;      // per row block of a tile: number of N tiles that have stored their part (swiglu)
+    int *rb_counter;      // per row block of a tile two words: arrivals + (hand-overs << 16), and the slice claim counter (swiglu)
     int rb_base;          // first counter of this launch (two launches share the array)
     int part;             // 0: all rows; 1: every group without its trailing rows if those are at most 128; 2: only those
     int8_t *q_out;        // int8 [M, N/2] (swiglu)
     float *q_scale_out;   // fp32 [M] (swiglu)
     int *status;
+    long long wait_limit;   // cycles a wait may last before the CTA gives up and records kStatusWaitTimeout
+    int skip_k_blocks;      // test only: K blocks the producer leaves out of its last tile (drives the abort path)
+    int knob_spin, knob_depth;   // EXPERIMENT
 };
 
 // ---------------------------------------------------------------------------------------------------------
@@ -183,7 +205,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, Shared
 {
     const uint32_t a = smem_u32(bar);
     if (mbar_try_wait(a, parity)) return true;
-    return mbar_wait_slow(a, parity, sh, status, who, WAIT_LIMIT_CYCLES);
+    return mbar_wait_slow(a, parity, sh, status, who, sh->wait_limit);
 }
 
 __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int c0, int c1, uint64_t *bar)
@@ -363,7 +385,7 @@ __host__ __device__ constexpr uint32_t make_idesc(bool b_mn_major, int m)
 __device__ void build_schedule(Shared *sh, const KParams &p, int tile_m)
 {
     const int tid = threadIdx.x, L = p.gl_len;
-    for (int g = tid; g < L; g += NUM_THREADS) {
+    for (int g = tid; g < L; g += (int)blockDim.x) {
         const int v = (int)p.group_list[g];
         int start = 0, rows = v;
         if (p.gl_type == 0) {
@@ -482,13 +504,6 @@ __device__ __forceinline__ void red_add_v4(float *p, const float4 v)
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
 
-__device__ __forceinline__ int ld_acquire_gpu(const int *p)
-{
-    int v;
-    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-
 // q = int8(rint(half(S * (1 / (amax / 127)))))  -- CastFp32ToInt8Template,
 // gmm/grouped_matmul_swiglu_quant/op_kernel/grouped_matmul_swiglu_quant_utils.h:308-316; NaN -> 0, saturating.
 __device__ __forceinline__ uint32_t quant1(float s, float rcp)
@@ -505,27 +520,38 @@ __device__ __forceinline__ uint32_t quant4(float4 v, float rcp)
 // Second half of grouped_matmul_swiglu_quant for rows [r_begin, r_end) of a finished row block (all of its N tiles
 // have stored S and the row maxima): per row  qs = amax / 127, r = 1 / qs, q = int8(half(S * r))
 // (gmm/grouped_matmul_swiglu_quant/op_kernel/grouped_matmul_swiglu_quant.h:496-503).  S and amax were written by
-// other SMs, so they are read through L2 (ld.global.cg).  One warp per row, 16 outputs per lane and step.
-__device__ void requant_rows(const KParams &p, int r_begin, int r_end, int te)
+// other SMs, so they are read through L2 (ld.global.cg).  One warp per row; a lane takes pieces of 16 outputs, four pieces
+// (sixteen 16-byte loads) in flight at a time, because these loads wait for L2 under the full load of the GEMM.
+__device__ void requant_rows(const KParams &p, int r_begin, int r_end, int tr)
 {
-    const int warp_e = te >> 5, lane = te & 31;
+    const int warp_r = tr >> 5, lane = tr & 31;
     const int H = p.half_n;
     const int pieces = H >> 4;
     const float *stage = reinterpret_cast<const float *>(p.out);
-    for (int grow = r_begin + warp_e; grow < r_end; grow += EPI_WARPS) {
+    for (int grow = r_begin + warp_r; grow < r_end; grow += RQ_WARPS) {
         const float amax = __uint_as_float(__ldcg(p.amax_bits + grow));
-        const float qs = __fdiv_rn(amax, 127.0f);
-        const float rcp = __fdiv_rn(1.0f, qs);
-        if (lane == 0) p.q_scale_out[grow] = qs;
         const float4 *src = reinterpret_cast<const float4 *>(stage + (size_t)grow * H);
         uint4 *dst = reinterpret_cast<uint4 *>(p.q_out + (size_t)grow * H);
         int c = lane;
-        for (; c + 32 < pieces; c += 64) {  // two pieces (eight 16-byte loads) per lane in flight
-            const float4 a0 = __ldcg(src + c * 4 + 0), a1 = __ldcg(src + c * 4 + 1), a2 = __ldcg(src + c * 4 + 2), a3 = __ldcg(src + c * 4 + 3);
-            const float4 b0 = __ldcg(src + (c + 32) * 4 + 0), b1 = __ldcg(src + (c + 32) * 4 + 1), b2 = __ldcg(src + (c + 32) * 4 + 2),
-                         b3 = __ldcg(src + (c + 32) * 4 + 3);
-            dst[c] = make_uint4(quant4(a0, rcp), quant4(a1, rcp), quant4(a2, rcp), quant4(a3, rcp));
-            dst[c + 32] = make_uint4(quant4(b0, rcp), quant4(b1, rcp), quant4(b2, rcp), quant4(b3, rcp));
+        float4 v[4][4];
+        if (c + 96 < pieces) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) v[u][j] = __ldcg(src + (c + 32 * u) * 4 + j);
+        }
+        const float qs = __fdiv_rn(amax, 127.0f);
+        const float rcp = __fdiv_rn(1.0f, qs);
+        if (lane == 0) p.q_scale_out[grow] = qs;
+        for (; c + 96 < pieces; c += 128) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) dst[c + 32 * u] = make_uint4(quant4(v[u][0], rcp), quant4(v[u][1], rcp), quant4(v[u][2], rcp), quant4(v[u][3], rcp));
+            if (c + 128 + 96 < pieces) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) v[u][j] = __ldcg(src + (c + 128 + 32 * u) * 4 + j);
+            }
         }
         for (; c < pieces; c += 32) {
             const float4 a0 = __ldcg(src + c * 4 + 0), a1 = __ldcg(src + c * 4 + 1), a2 = __ldcg(src + c * 4 + 2), a3 = __ldcg(src + c * 4 + 3);
@@ -534,44 +560,92 @@ __device__ void requant_rows(const KParams &p, int r_begin, int r_end, int te)
     }
 }
 
-// A tile whose SwiGLU part is stored and whose share of the requantisation is still owed.
-struct Pending {
-    int valid, rb, r_begin, r_end;
-};
-
-// Wait (bounded) until every N tile of the row block has stored its part, then requantise this CTA's share of rows.
-// Thread 0 of the epilogue polls the block's counter; the others wait on tile_sync[1].  Returns false on abort.
-__device__ bool settle_pending(const KParams &p, Shared *sh, Pending &pd, uint32_t &settle_it, int te, int target)
+// Who requantises a finished row block, without any CTA ever waiting for another one (so the kernel does not depend on
+// all CTAs being resident at the same time, nor on how many there are).
+//
+// Per row block two words in the workspace: state = arrivals (low 16 bits) + handed-over shares (high 16 bits), and a
+// claim counter.  A block has `shares` contributors (N tiles x CTAs per tile) and is requantised in `shares` row slices.
+//   * A CTA that has stored its part of the block "arrives" (atomic add of 1 after a fence).  The arrival that completes
+//     the block takes one slice for itself plus one for every share handed over so far.
+//   * Every other contributor keeps the block on a short pending list and looks at the state again after each of its
+//     later tiles; once the block is complete it takes one slice.
+//   * A contributor that cannot come back (its last tile is done, or its list is full) hands its share over with an
+//     atomic add of 1 << 16.  If that add finds the block already complete it takes its slice itself; otherwise the
+//     completing arrival, which comes later, sees the hand-over in the value its own add returns.
+// Slices are claimed from the claim counter, so every slice is taken exactly once.
+__device__ __forceinline__ void add_work(Shared *sh, int ws, int row0, int rows, int first, int count, int shares)
 {
-    if (!pd.valid) return true;
-    pd.valid = 0;
-    if (te == 0) {
-        bool ok = true;
-        if (ld_acquire_gpu(p.rb_counter + pd.rb) < target) {
-            const long long t0 = clock64();
-            while (ld_acquire_gpu(p.rb_counter + pd.rb) < target) {
-                if (*(volatile int *)&sh->abort_flag) { ok = false; break; }
-                if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-                    *(volatile int *)&sh->abort_flag = 1;
-                    if (atomicCAS(p.status, kStatusOk, kStatusWaitTimeout) == kStatusOk) {
-                        p.status[1] = (int)blockIdx.x;
-                        p.status[2] = 700;
-                        p.status[3] = pd.rb;
-                    }
-                    ok = false;
-                    break;
-                }
-            }
-        }
-        if (ok) {
-            __threadfence();
-            mbar_arrive(&sh->tile_sync[1]);
+    const int k = sh->n_work[ws]++;
+    sh->work_begin[ws][k] = row0 + (int)((long long)rows * first / shares);
+    sh->work_end[ws][k] = row0 + (int)((long long)rows * (first + count) / shares);
+}
+
+__device__ __forceinline__ int ld_relaxed_gpu(const int *p)
+{
+    int v;
+    asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Publishing lane, after the whole CTA has stored a tile: arrive at block `rb`, look at the pending blocks, fill work list
+// `ws`.  The caller fences before (release of the CTA's stores) and after (acquire of the other CTAs' stores).
+__device__ void publish_and_collect(const KParams &p, Shared *sh, int ws, int rb, int row0, int rows, int shares)
+{
+    sh->n_work[ws] = 0;
+    int *state = p.rb_counter;
+    // the looks at the older blocks and the arrival travel together (one round trip to L2)
+    int seen[MAX_PENDING];
+#pragma unroll
+    for (int i = 0; i < MAX_PENDING; ++i) seen[i] = i < sh->pend_n ? ld_relaxed_gpu(state + 2 * sh->pend_rb[i]) : 0;
+    const int old = atomicAdd(state + 2 * rb, 1);
+    const bool completed = (old & 0xffff) + 1 == shares;
+    // slice claims, again together
+    int first[MAX_PENDING];
+#pragma unroll
+    for (int i = 0; i < MAX_PENDING; ++i)
+        first[i] = (i < sh->pend_n && (seen[i] & 0xffff) == shares) ? atomicAdd(state + 2 * sh->pend_rb[i] + 1, 1) : -1;
+    const int cnt = 1 + (old >> 16);
+    const int mine = completed ? atomicAdd(state + 2 * rb + 1, cnt) : -1;
+    int n = 0;
+#pragma unroll
+    for (int i = 0; i < MAX_PENDING; ++i) {
+        if (i >= sh->pend_n) break;
+        if (first[i] >= 0) {
+            add_work(sh, ws, sh->pend_row0[i], sh->pend_rows[i], first[i], 1, shares);
+        } else {
+            sh->pend_rb[n] = sh->pend_rb[i]; sh->pend_row0[n] = sh->pend_row0[i]; sh->pend_rows[n] = sh->pend_rows[i];
+            ++n;
         }
     }
-    if (!mbar_wait(&sh->tile_sync[1], settle_it & 1u, sh, p.status, 601)) return false;
-    ++settle_it;
-    requant_rows(p, pd.r_begin, pd.r_end, te);
-    return true;
+    sh->pend_n = n;
+    if (completed) {
+        add_work(sh, ws, row0, rows, mine, cnt, shares);
+        return;
+    }
+    if (sh->pend_n == MAX_PENDING) {  // hand the oldest block's share over (or take it, if the block completed meanwhile)
+        const int o = atomicAdd(state + 2 * sh->pend_rb[0], 1 << 16);
+        if ((o & 0xffff) == shares)
+            add_work(sh, ws, sh->pend_row0[0], sh->pend_rows[0], atomicAdd(state + 2 * sh->pend_rb[0] + 1, 1), 1, shares);
+        for (int i = 1; i < MAX_PENDING; ++i) {
+            sh->pend_rb[i - 1] = sh->pend_rb[i]; sh->pend_row0[i - 1] = sh->pend_row0[i]; sh->pend_rows[i - 1] = sh->pend_rows[i];
+        }
+        --sh->pend_n;
+    }
+    const int k = sh->pend_n++;
+    sh->pend_rb[k] = rb; sh->pend_row0[k] = row0; sh->pend_rows[k] = rows;
+}
+
+// Publishing lane, after the CTA's last tile: every block still pending is taken (if complete) or handed over.
+__device__ void release_pending(const KParams &p, Shared *sh, int ws, int shares)
+{
+    sh->n_work[ws] = 0;
+    int *state = p.rb_counter;
+    for (int i = 0; i < sh->pend_n; ++i) {
+        const int o = atomicAdd(state + 2 * sh->pend_rb[i], 1 << 16);
+        if ((o & 0xffff) == shares)
+            add_work(sh, ws, sh->pend_row0[i], sh->pend_rows[i], atomicAdd(state + 2 * sh->pend_rb[i] + 1, 1), 1, shares);
+    }
+    sh->pend_n = 0;
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -583,7 +657,7 @@ __device__ bool settle_pending(const KParams &p, Shared *sh, Pending &pd, uint32
 // result rows scattered through out_row_index, optionally into other GPUs' memory; kEpiGeneric = every option
 // tested at run time.  CTAS: 1 = one CTA per tile, 2 = a cluster of two CTAs per 256-row tile.
 template <int MODE, int BL, int EPI, int CTAS>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(num_threads(MODE), 1)
 gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const KParams p)
 {
     constexpr bool B_MN_MAJOR = BL != kBTransposed;  // [E,K,N] and the fractal layout are N-contiguous
@@ -613,10 +687,18 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             mbar_init(&sh->acc_empty[b], EPI_WARPS * CTAS);  // one arrival per epilogue warp of every CTA of the unit
         }
         for (int b = 0; b < SCALE_BUFS; ++b) mbar_init(&sh->scale_ready[b], EPI_THREADS);
-        mbar_init(&sh->tile_sync[0], EPI_THREADS);
-        mbar_init(&sh->tile_sync[1], 1);
+        for (int b = 0; b < RQ_DEPTH; ++b) {
+            mbar_init(&sh->rq_full[b], EPI_THREADS);
+            mbar_init(&sh->rq_empty[b], 1);
+        }
+        for (int b = 0; b < WK_DEPTH; ++b) {
+            mbar_init(&sh->wk_full[b], 1);
+            mbar_init(&sh->wk_empty[b], RQ_THREADS);
+        }
         sh->abort_flag = 0;
         sh->total_tiles = 0;
+        sh->wait_limit = p.wait_limit;
+        sh->pend_n = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         prefetch_map(&map_x);
         prefetch_map(&map_w);
@@ -649,7 +731,9 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                 if (MODE == kModeSwigluQuant) { n0 = tl.n_idx * (BN / 2); n1 = p.half_n + n0; }
                 else { n0 = tl.n_idx * BN; n1 = n0 + BN / 2; }
                 const int nb = rank == 0 ? n0 : n1;  // pair: the weight box this CTA contributes
-                for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+                // test hook: leaving K blocks out of the last tile makes the MMA issuer's wait run out (nothing else is touched)
+                const int kb_end = p.num_k_blocks - (t + n_units >= total_tiles ? p.skip_k_blocks : 0);
+                for (int kb = 0; kb < kb_end; ++kb) {
                     if (!mbar_wait(&sh->empty[stage], phase ^ 1u, sh, p.status, 100 + stage)) { ok = false; break; }
                     uint8_t *adst = smem + stage * STAGE_BYTES;
                     uint8_t *bdst = adst + A_STAGE;
@@ -740,7 +824,7 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                 if (buf == 0) acc_phase ^= 1u;
             }
         }
-    } else {
+    } else if (warp < 2 + EPI_WARPS) {
         // ------------------------------ epilogue: warp -> (TMEM lane quarter, column half) ------------------------------
         const int quarter = warp & 3;
         const int chalf = (warp - 2) >> 2;
@@ -748,11 +832,9 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         const int r = quarter * 32 + lane;     // row inside the tile == TMEM lane
         uint8_t *my_stage = sh->out_stage[warp - 2];
         int buf = 0, it = 0;
-        uint32_t acc_phase = 0, settle_it = 0;
-        Pending pend = {0, 0, 0, 0};
-        bool ok = true;
+        uint32_t acc_phase = 0;
         const uint32_t acc_empty_rank0 = CTAS == 2 ? map_to_cta(&sh->acc_empty[0], 0) : 0u;
-        for (int t = unit; t < total_tiles && ok; t += n_units, ++it) {
+        for (int t = unit; t < total_tiles; t += n_units, ++it) {
             const Tile tl = decode_tile(sh, t, p.n_tiles, L, C::kTileM);
             const int my_row0 = tl.row0 + (int)rank * BM;                 // this CTA's 128 rows of the tile
             const int my_rows = max(0, min(BM, tl.rows - (int)rank * BM));
@@ -840,7 +922,7 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
 #pragma unroll
                         for (int j4 = 0; j4 < 8; ++j4) {
                             const int col = n0 + c * 32 + j4 * 4;
-                            if (col < p.N && valid) {
+                            if (col < p.N && valid && (!SCATTER || (out_row >= 0 && (p.out_rows <= 0 || out_row < p.out_rows)))) {
                                 int acc[4];
 #pragma unroll
                                 for (int j = 0; j < 4; ++j) {
@@ -973,14 +1055,27 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                                 const uint4 val = *reinterpret_cast<const uint4 *>(my_stage + r16 * 128 + (((pc ^ r16) & 7) << 4));
                                 long long orow = my_row0 + quarter * 32 + rr;
                                 uint16_t *obase = out;
+                                bool in_rows = quarter * 32 + rr < my_rows;
                                 if (SCATTER) {
                                     orow = __shfl_sync(0xffffffffu, out_row, rr);
+                                    long long gpu_field = 0;
                                     if (p.num_peers > 0) {  // high bits: which GPU's buffer, low 40 bits: row in it
-                                        obase = reinterpret_cast<uint16_t *>(p.out_peers[(int)(orow >> 40) & 7]);
+                                        gpu_field = orow >> 40;
                                         orow &= (1ll << 40) - 1;
                                     }
+                                    // an index that names no peer or no row of the result is skipped and reported, not stored
+                                    if (in_rows && (orow < 0 || gpu_field >= (p.num_peers > 0 ? p.num_peers : 1) || (p.out_rows > 0 && orow >= p.out_rows))) {
+                                        if (pc == 0 && c == chalf * 4 && atomicCAS(p.status, kStatusOk, kStatusBadIndex) == kStatusOk) {
+                                            p.status[1] = (int)blockIdx.x;
+                                            p.status[2] = 800;
+                                            p.status[3] = my_row0 + quarter * 32 + rr;
+                                        }
+                                        in_rows = false;
+                                    } else if (p.num_peers > 0) {
+                                        obase = reinterpret_cast<uint16_t *>(p.out_peers[(int)gpu_field]);
+                                    }
                                 }
-                                if (quarter * 32 + rr < my_rows && col < p.N) *reinterpret_cast<uint4 *>(obase + (size_t)orow * p.N + col) = val;
+                                if (in_rows && col < p.N) *reinterpret_cast<uint4 *>(obase + (size_t)orow * p.N + col) = val;
                             }
                             __syncwarp();
                         }
@@ -997,23 +1092,66 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             if (buf == 0) acc_phase ^= 1u;
 
             if (MODE == kModeSwigluQuant) {
-                // Publish this tile's part of its row block, then settle what is owed for the previous tile.
+                // Hand the tile to the requantising warps: they publish it and settle what falls to this CTA, while this
+                // warp goes on with the next tile.  The fence orders this thread's stores and row maxima before the
+                // arrival that the publishing thread observes.
+                const int slot = it % p.knob_depth;
                 __threadfence();
-                mbar_arrive(&sh->tile_sync[0]);
-                if (!mbar_wait(&sh->tile_sync[0], (uint32_t)it & 1u, sh, p.status, 600)) break;
-                if (te == 0) atomicAdd(p.rb_counter + p.rb_base + t / p.n_tiles, 1);
-                const int shares = p.n_tiles * CTAS;  // every CTA that worked on the row block requantises one share of its rows
-                ok = settle_pending(p, sh, pend, settle_it, te, shares);
-                const int share = tl.n_idx * CTAS + (int)rank;
-                pend.valid = 1;
-                pend.rb = p.rb_base + t / p.n_tiles;
-                pend.r_begin = tl.row0 + (int)((long long)tl.rows * share / shares);
-                pend.r_end = tl.row0 + (int)((long long)tl.rows * (share + 1) / shares);
+                if (!mbar_wait(&sh->rq_empty[slot], (((uint32_t)(it / p.knob_depth)) & 1u) ^ 1u, sh, p.status, 610 + slot)) break;
+                mbar_arrive(&sh->rq_full[slot]);
             }
         }
-        if (MODE == kModeSwigluQuant && ok && !*(volatile int *)&sh->abort_flag)
-            settle_pending(p, sh, pend, settle_it, te, p.n_tiles * CTAS);
         if (SCATTER && p.num_peers > 0) __threadfence_system();  // rows stored into other GPUs' memory
+    }
+
+    else if (MODE == kModeSwigluQuant && warp == 2 + EPI_WARPS) {
+        // ------------------------------ publishing warp (swiglu_quant), one lane ------------------------------
+        // Per tile of this unit, in the epilogue's order: wait until the epilogue has stored the tile, arrive at its row
+        // block, collect the row slices that fall to this CTA now (publish_and_collect) into the next work list.  After
+        // the last tile one more list takes or hands over what is still pending.  Nothing here waits for another CTA.
+        if (lane == 0) {
+            const int shares = p.n_tiles * CTAS;
+            int it = 0;
+            bool ok = true;
+            for (int t = unit; t < total_tiles; t += n_units, ++it) {
+                const int slot = it % p.knob_depth, ws = it % WK_DEPTH;
+                if (!mbar_wait(&sh->rq_full[slot], ((uint32_t)(it / p.knob_depth)) & 1u, sh, p.status, 620 + slot)) { ok = false; break; }
+                if (!mbar_wait(&sh->wk_empty[ws], (((uint32_t)(it / WK_DEPTH)) & 1u) ^ 1u, sh, p.status, 630 + ws)) { ok = false; break; }
+                const Tile tl = decode_tile(sh, t, p.n_tiles, L, C::kTileM);
+                if (p.knob_spin > 0 && sh->pend_n > 0) {   // EXPERIMENT: keep the units of a wave together
+                    const int *st = p.rb_counter + 2 * sh->pend_rb[sh->pend_n - 1];
+                    const long long t0 = clock64();
+                    while ((ld_relaxed_gpu(st) & 0xffff) != shares && clock64() - t0 < p.knob_spin) {}
+                }
+                mbar_arrive(&sh->rq_empty[slot]);
+                __threadfence();
+                publish_and_collect(p, sh, ws, p.rb_base + t / p.n_tiles, tl.row0, tl.rows, shares);
+                __threadfence();
+                mbar_arrive(&sh->wk_full[ws]);
+            }
+            if (ok && !*(volatile int *)&sh->abort_flag) {
+                const int ws = it % WK_DEPTH;
+                if (mbar_wait(&sh->wk_empty[ws], (((uint32_t)(it / WK_DEPTH)) & 1u) ^ 1u, sh, p.status, 640 + ws)) {
+                    release_pending(p, sh, ws, shares);
+                    __threadfence();
+                    mbar_arrive(&sh->wk_full[ws]);
+                }
+            }
+        }
+    } else if (MODE == kModeSwigluQuant) {
+        // ------------------------------ requantising warps (swiglu_quant) ------------------------------
+        // One work list per tile of this unit plus the closing one.
+        const int tr = (int)threadIdx.x - BASE_THREADS - 32;  // 0 .. RQ_THREADS-1
+        int it = 0;
+        bool ok = true;
+        for (int t = unit; ok; t += n_units, ++it) {
+            const int ws = it % WK_DEPTH;
+            if (!mbar_wait(&sh->wk_full[ws], ((uint32_t)(it / WK_DEPTH)) & 1u, sh, p.status, 650 + ws)) break;
+            const int n = sh->n_work[ws];
+            for (int k = 0; k < n; ++k) requant_rows(p, sh->work_begin[ws][k], sh->work_end[ws][k], tr);
+            mbar_arrive(&sh->wk_empty[ws]);
+            if (t >= total_tiles) ok = false;  // that was the closing list
+        }
     }
 
     __syncthreads();
@@ -1061,7 +1199,7 @@ cudaError_t launch_variant(const Plan &plan, const KParams &kp, cudaStream_t str
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(CTAS == 2 ? (plan.num_sms & ~1) : plan.num_sms), 1, 1);
-    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.blockDim = dim3(num_threads(MODE), 1, 1);
     cfg.dynamicSmemBytes = SMEM_BYTES;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -1097,15 +1235,7 @@ cudaError_t launch_layout(int layout, int epi, const Plan &plan, const KParams &
     return launch_epi<MODE, kBRowMajor>(epi, plan, kp, stream);
 }
 
-cudaEvent_t g_ev_start = nullptr, g_ev_stop = nullptr;
-
 }  // namespace
-
-void set_timing_events(cudaEvent_t start, cudaEvent_t stop)
-{
-    g_ev_start = start;
-    g_ev_stop = stop;
-}
 
 // The tcgen05 path needs 16-byte aligned row pitches for TMA (K for x; N or K for the weight), 16-byte
 // aligned base pointers and, for SwiGLU, a half width that keeps the second box aligned.
@@ -1172,6 +1302,11 @@ cudaError_t sm100_launch(const Problem &p, Plan &plan, void *workspace, cudaStre
     }
     plan.num_sms = device_sm_count();
     if (plan.num_sms <= 0) return cudaErrorNoDevice;
+    if (p.opt.max_ctas > 0 && p.opt.max_ctas < plan.num_sms) plan.num_sms = p.opt.max_ctas;
+    if (plan.num_sms < 2) {  // a CTA pair needs two CTAs
+        plan.ctas = 1;
+        plan.hybrid = false;
+    }
     uint8_t *ws = static_cast<uint8_t *>(workspace);
     KParams kp;
     kp.group_list = p.group_list;
@@ -1211,7 +1346,15 @@ cudaError_t sm100_launch(const Problem &p, Plan &plan, void *workspace, cudaStre
     kp.num_peers = p.mode == kModeDequantBf16 ? p.num_peers : 0;
     for (int i = 0; i < 8; ++i) kp.out_peers[i] = i < kp.num_peers ? p.out_peers[i] : nullptr;
     if (kp.num_peers > 0 && epi != kEpiScatter) return cudaErrorInvalidValue;
-    if (g_ev_start) cudaEventRecord(g_ev_start, stream);
+    {
+        const char *e1 = getenv("GMM_KNOB_SPIN"), *e2 = getenv("GMM_KNOB_DEPTH");
+        kp.knob_spin = e1 ? atoi(e1) : 0;
+        kp.knob_depth = e2 ? atoi(e2) : RQ_DEPTH;
+        if (kp.knob_depth < 1 || kp.knob_depth > RQ_DEPTH) kp.knob_depth = RQ_DEPTH;
+    }
+    kp.wait_limit = p.opt.wait_limit_cycles > 0 ? p.opt.wait_limit_cycles : WAIT_LIMIT_CYCLES;
+    kp.skip_k_blocks = p.opt.test_skip_k_blocks > 0 ? (p.opt.test_skip_k_blocks < kp.num_k_blocks ? p.opt.test_skip_k_blocks : kp.num_k_blocks) : 0;
+    if (p.opt.ev_start) cudaEventRecord(p.opt.ev_start, stream);
     // Pair tiles for the bulk of every group, then (plan.hybrid) 128-row tiles for the trailing blocks a pair would half waste.
     const int launches = plan.ctas == 2 && plan.hybrid ? 2 : 1;
     Plan one = plan;
@@ -1225,7 +1368,7 @@ cudaError_t sm100_launch(const Problem &p, Plan &plan, void *workspace, cudaStre
         else e = launch_layout<kModeDequantBf16>(p.w_layout, epi, pl, kp, stream);
         if (e != cudaSuccess) break;
     }
-    if (g_ev_stop) cudaEventRecord(g_ev_stop, stream);
+    if (p.opt.ev_stop) cudaEventRecord(p.opt.ev_stop, stream);
     return e;
 }
 

@@ -10,6 +10,9 @@
 //       CheckNotNull :75-105, CheckInputOutDims_A8W8 :108-125, CheckInputOutShape_A8W8 :149-213, CheckDtypeValid :304-324
 // restricted to the int8 x int8 path.  The first phase is host only and never reads group_list; the second
 // phase enqueues on the caller's CUDA stream and returns.
+#include <nvtx3/nvToolsExt.h>
+
+#include <cstdlib>
 #include <cstring>
 #include <type_traits>
 
@@ -26,6 +29,7 @@
 namespace gmm {
 void register_executor(aclOpExecutor *e);
 bool claim_executor(aclOpExecutor *e);
+bool executor_is_live(aclOpExecutor *e);
 
 namespace {
 
@@ -86,6 +90,54 @@ void bind_tensor(aclOpExecutor *e, const aclTensor *t, P *field, bool is_output,
     *field = (P)(uintptr_t)4096;
 }
 
+// Env-gated profiler ranges around both phases of every entry point (GMM_B200_NVTX=1), the counterpart of the
+// reference's L2_DFX_PHASE_1 / L2_DFX_PHASE_2 (gmm/grouped_matmul/op_host/op_api/aclnn_grouped_matmul.cpp:2005, 2151).
+// NVTX is header only and does nothing unless a tool is attached.
+bool nvtx_enabled()
+{
+    static const bool on = [] {
+        const char *e = std::getenv("GMM_B200_NVTX");
+        return e && e[0] && e[0] != '0';
+    }();
+    return on;
+}
+struct PhaseRange {
+    bool on;
+    PhaseRange(const char *op, int phase) : on(nvtx_enabled())
+    {
+        if (!on) return;
+        char name[160];
+        std::snprintf(name, sizeof(name), "%s phase %d", op, phase);
+        nvtxRangePushA(name);
+    }
+    ~PhaseRange()
+    {
+        if (on) nvtxRangePop();
+    }
+};
+
+// Public options -> internal form.  Fields beyond the caller's structSize read as zero.
+aclnnStatus convert_options(const gmmB200LaunchOptions *o, LaunchOptions *out)
+{
+    *out = LaunchOptions();
+    if (!o) return ACLNN_SUCCESS;
+    gmmB200LaunchOptions full;
+    std::memset(&full, 0, sizeof(full));
+    const size_t n = o->structSize < sizeof(full) ? o->structSize : sizeof(full);
+    GMM_REQUIRE(n >= 8, ACLNN_ERR_PARAM_INVALID, "gmmB200LaunchOptions.structSize %u is too small.", o->structSize);
+    std::memcpy(&full, o, n);
+    GMM_REQUIRE(full.maxCtas >= 0 && full.waitLimitCycles >= 0 && full.testSkipKBlocks >= 0, ACLNN_ERR_PARAM_INVALID,
+                "gmmB200LaunchOptions: maxCtas, waitLimitCycles and testSkipKBlocks must not be negative.");
+    GMM_REQUIRE((full.startEvent == nullptr) == (full.stopEvent == nullptr), ACLNN_ERR_PARAM_INVALID,
+                "gmmB200LaunchOptions: startEvent and stopEvent come together or not at all.");
+    out->max_ctas = full.maxCtas;
+    out->ev_start = static_cast<cudaEvent_t>(full.startEvent);
+    out->ev_stop = static_cast<cudaEvent_t>(full.stopEvent);
+    out->wait_limit_cycles = full.waitLimitCycles;
+    out->test_skip_k_blocks = full.testSkipKBlocks;
+    return ACLNN_SUCCESS;
+}
+
 aclnnStatus finish_phase1(aclOpExecutor *e, uint64_t *workspaceSize, aclOpExecutor **executor)
 {
     // kInitRouting stores its size in plan.ws_bytes too
@@ -101,6 +153,7 @@ aclnnStatus run_executor(const char *op_name, void *workspace, uint64_t workspac
                          aclrtStream stream)
 {
     clear_error();
+    PhaseRange phase_range(op_name, 2);
     GMM_REQUIRE(executor != nullptr, ACLNN_ERR_PARAM_NULLPTR, "%s: executor must not be nullptr.", op_name);
     GMM_REQUIRE(claim_executor(executor), ACLNN_ERR_PARAM_INVALID,
                 "%s: executor is not live; an executor can be run once and only after its GetWorkspaceSize call.", op_name);
@@ -146,11 +199,13 @@ extern "C" {
 
 int32_t gmmB200Version(void) { return 100; }
 
-void gmmB200SetSmLimit(int32_t maxCtas) { set_sm_limit(maxCtas); }
-
-void gmmB200SetTimingEvents(void *startEvent, void *stopEvent)
+aclnnStatus gmmB200SetExecutorOptions(aclOpExecutor *executor, const gmmB200LaunchOptions *options)
 {
-    set_timing_events(static_cast<cudaEvent_t>(startEvent), static_cast<cudaEvent_t>(stopEvent));
+    clear_error();
+    GMM_REQUIRE(executor != nullptr, ACLNN_ERR_PARAM_NULLPTR, "executor must not be nullptr.");
+    GMM_REQUIRE(executor_is_live(executor), ACLNN_ERR_PARAM_INVALID,
+                "executor is not live; options are set between GetWorkspaceSize and the second-phase call.");
+    return convert_options(options, &executor->problem.opt);
 }
 
 // Shared first phase of aclnnGroupedMatmulV4 / V5 / WeightNz (aclnnGroupedMatmulGetWorkspaceSizeCommon,
@@ -293,8 +348,9 @@ static aclnnStatus gmm_phase1(const char *kOp, bool force_nz, int64_t rows_hint,
 
     aclOpExecutor *e = new_executor(kOp);
     GMM_REQUIRE(e != nullptr, ACLNN_ERR_INNER_CREATE_EXECUTOR, "cannot create executor.");
-    // Empty tensors: nothing to launch (CheckZeroShape, aclnn_grouped_matmul.cpp:1535-1548).
-    if (M == 0 || N == 0 || glLen == 0) return finish_phase1(e, workspaceSize, executor);
+    // Empty tensors: nothing to launch and a workspace of 0 (CheckZeroShape, aclnn_grouped_matmul.cpp:1535-1548 with its
+    // caller :1770-1772: an x without elements, i.e. M == 0 or K == 0, returns success before anything is built).
+    if (M == 0 || K == 0 || N == 0 || glLen == 0) return finish_phase1(e, workspaceSize, executor);
 
     const bool w_trans = !w_nz && !tw->contiguous() && is_transposed_last_two(tw);
     // Strided views are served through contiguous copies in the workspace (Contiguous / ViewCopy of the reference,
@@ -427,6 +483,7 @@ aclnnStatus aclnnMoeInitRoutingV3GetWorkspaceSize(const aclTensor *x, const aclT
 {
     static const char *kOp = "aclnnMoeInitRoutingV3";
     clear_error();
+    PhaseRange phase_range(kOp, 1);
     GMM_REQUIRE(workspaceSize != nullptr, ACLNN_ERR_PARAM_NULLPTR, "workspaceSize must not be nullptr.");
     GMM_REQUIRE(executor != nullptr, ACLNN_ERR_PARAM_NULLPTR, "executor must not be nullptr.");
     GMM_REQUIRE(x && expertIdx && expandedXOut && expandedRowIdxOut && expertTokensCountOrCumsumOut && expandedScaleOut,
@@ -526,6 +583,7 @@ static aclnnStatus finalize_routing_phase1(const char *kOp, const aclTensor *x1,
                                            aclOpExecutor **executor)
 {
     clear_error();
+    PhaseRange phase_range(kOp, 1);
     GMM_REQUIRE(workspaceSize != nullptr, ACLNN_ERR_PARAM_NULLPTR, "workspaceSize must not be nullptr.");
     GMM_REQUIRE(executor != nullptr, ACLNN_ERR_PARAM_NULLPTR, "executor must not be nullptr.");
     // Two supported scenes: shared input, logit and row index all given (rows are added), or row index alone (rows are stored).
@@ -691,6 +749,7 @@ static aclnnStatus swiglu_phase1(const char *kOp, bool force_nz, const aclTensor
                                  uint64_t *workspaceSize, aclOpExecutor **executor)
 {
     clear_error();
+    PhaseRange phase_range(kOp, 1);
     (void)bias; (void)offset; (void)outputOffset;  // accepted and ignored, as in the reference (:86-104)
     // OP_CHECK_COMM_INPUT + CheckNotNull
     GMM_REQUIRE(workspaceSize != nullptr, ACLNN_ERR_PARAM_NULLPTR, "workspaceSize must not be nullptr.");
@@ -747,6 +806,7 @@ static aclnnStatus swiglu_phase1(const char *kOp, bool force_nz, const aclTensor
     GMM_REQUIRE(!is_private_format(x->format) && !is_private_format(output->format), ACLNN_ERR_PARAM_INVALID,
                 "x / output Format Not support Private Format.");
     GMM_REQUIRE(glLen <= kMaxGroupListLen, ACLNN_ERR_PARAM_INVALID, "groupList longer than %lld.", (long long)kMaxGroupListLen);
+    GMM_REQUIRE(K > 0 || output->empty(), ACLNN_ERR_PARAM_INVALID, "k must be positive (an empty reduction has no row maximum to quantise by).");
 
     aclOpExecutor *e = new_executor(kOp);
     GMM_REQUIRE(e != nullptr, ACLNN_ERR_INNER_CREATE_EXECUTOR, "cannot create executor.");
@@ -828,6 +888,7 @@ aclnnStatus gmmB200CheckStatus(const void *workspace, uint64_t workspaceSize, ac
 static aclnnStatus flat_sizes_ok(int64_t m, int64_t k, int64_t n, int64_t e)
 {
     GMM_REQUIRE(m >= 0 && k > 0 && n > 0 && e > 0, ACLNN_ERR_PARAM_INVALID, "m, k, n, e must be positive (m may be 0).");
+    GMM_REQUIRE(m <= 0x7fffffffll / 2, ACLNN_ERR_PARAM_INVALID, "m must not exceed %lld rows.", 0x7fffffffll / 2);
     GMM_REQUIRE(k <= kMaxInnerAxis && n <= kMaxInnerAxis, ACLNN_ERR_PARAM_INVALID, "k and n must not exceed %lld.", (long long)kMaxInnerAxis);
     return ACLNN_SUCCESS;
 }
@@ -862,15 +923,17 @@ aclnnStatus gmmB200GroupedMatmulW8A8(const void *x, const void *weight, const vo
                                      const void *perTokenScale, const void *bias, int32_t biasDtype, const void *groupList,
                                      int64_t groupListLen, int32_t groupListType, int64_t m, int64_t k, int64_t n, int64_t e,
                                      int32_t weightTransposed, int32_t actType, const void *outRowIndex, void *const *outPeers,
-                                     int32_t numPeers, void *y, int32_t yDtype, void *workspace, uint64_t workspaceSize,
-                                     aclrtStream stream)
+                                     int32_t numPeers, int64_t outRows, void *y, int32_t yDtype, void *workspace, uint64_t workspaceSize,
+                                     aclrtStream stream, const gmmB200LaunchOptions *options)
 {
     clear_error();
+    PhaseRange phase_range("gmmB200GroupedMatmulW8A8", 2);
     GMM_REQUIRE(x && weight && groupList && (y || numPeers > 0), ACLNN_ERR_PARAM_NULLPTR, "x, weight, groupList and y must not be nullptr.");
     aclnnStatus rc = flat_sizes_ok(m, k, n, e);
     if (rc != ACLNN_SUCCESS) return rc;
     GMM_REQUIRE(yDtype == ACL_BF16 || yDtype == ACL_FLOAT16 || yDtype == ACL_INT32, ACLNN_ERR_PARAM_INVALID, "yDtype must be bfloat16, float16 or int32.");
     GMM_REQUIRE(numPeers >= 0 && numPeers <= 8, ACLNN_ERR_PARAM_INVALID, "numPeers must be in [0, 8].");
+    GMM_REQUIRE(outRows >= 0, ACLNN_ERR_PARAM_INVALID, "outRows must not be negative.");
     if (numPeers > 0) {
         GMM_REQUIRE(outPeers && outRowIndex && yDtype == ACL_BF16 && !bias && actType == 0 && perTokenScale, ACLNN_ERR_PARAM_INVALID,
                     "peer output needs outPeers, outRowIndex, a bfloat16 result, a per-token scale, no bias and no activation.");
@@ -906,8 +969,11 @@ aclnnStatus gmmB200GroupedMatmulW8A8(const void *x, const void *weight, const vo
     p.out_f16 = yDtype == ACL_FLOAT16 ? 1 : 0;
     p.out0 = y ? y : outPeers[0];
     p.out_row_index = static_cast<const int64_t *>(outRowIndex);
+    p.out_rows = outRowIndex ? outRows : 0;
     p.num_peers = numPeers;
     for (int i = 0; i < numPeers; ++i) p.out_peers[i] = outPeers[i];
+    rc = convert_options(options, &p.opt);
+    if (rc != ACLNN_SUCCESS) return rc;
     Plan plan;
     make_plan(p, &plan);
     GMM_REQUIRE(workspaceSize >= plan.ws_bytes, ACLNN_ERR_PARAM_INVALID, "workspaceSize %llu is smaller than the %llu bytes required.",
@@ -933,9 +999,11 @@ aclnnStatus gmmB200GroupedMatmulSwigluQuantWorkspaceSize(int64_t m, int64_t k, i
 aclnnStatus gmmB200GroupedMatmulSwigluQuant(const void *x, const void *weight, const void *weightScale, int32_t weightScaleDtype,
                                             const void *xScale, const void *groupList, int64_t groupListLen, int64_t m, int64_t k,
                                             int64_t n, int64_t e, int32_t weightLayout, void *output, void *outputScale,
-                                            void *workspace, uint64_t workspaceSize, aclrtStream stream)
+                                            void *workspace, uint64_t workspaceSize, aclrtStream stream,
+                                            const gmmB200LaunchOptions *options)
 {
     clear_error();
+    PhaseRange phase_range("gmmB200GroupedMatmulSwigluQuant", 2);
     GMM_REQUIRE(x && weight && weightScale && xScale && groupList && output && outputScale, ACLNN_ERR_PARAM_NULLPTR,
                 "x, weight, weightScale, xScale, groupList, output and outputScale must not be nullptr.");
     aclnnStatus rc = flat_sizes_ok(m, k, n, e);
@@ -960,6 +1028,8 @@ aclnnStatus gmmB200GroupedMatmulSwigluQuant(const void *x, const void *weight, c
     p.w_layout = weightLayout;
     p.mode = kModeSwigluQuant;
     p.out0 = output; p.out1 = outputScale;
+    rc = convert_options(options, &p.opt);
+    if (rc != ACLNN_SUCCESS) return rc;
     Plan plan;
     make_plan(p, &plan);
     GMM_REQUIRE(workspaceSize >= plan.ws_bytes, ACLNN_ERR_PARAM_INVALID, "workspaceSize %llu is smaller than the %llu bytes required.",
@@ -975,12 +1045,15 @@ aclnnStatus gmmB200GroupedMatmulFinalizeRouting(const void *x, const void *weigh
                                                 int64_t groupListLen, int32_t groupListType, const void *sharedInput,
                                                 int64_t sharedRows, int64_t sharedOffset, float sharedWeight, const void *logit,
                                                 const void *rowIndex, int32_t rowIndexDtype, int64_t m, int64_t k, int64_t n, int64_t e,
-                                                void *y, int64_t yRows, void *workspace, uint64_t workspaceSize, aclrtStream stream)
+                                                void *y, int64_t yRows, void *workspace, uint64_t workspaceSize, aclrtStream stream,
+                                                const gmmB200LaunchOptions *options)
 {
     clear_error();
+    PhaseRange phase_range("gmmB200GroupedMatmulFinalizeRouting", 2);
     GMM_REQUIRE(x && weight && scale && groupList && rowIndex && y, ACLNN_ERR_PARAM_NULLPTR, "x, weight, scale, groupList, rowIndex and y must not be nullptr.");
     GMM_REQUIRE((sharedInput != nullptr) == (logit != nullptr), ACLNN_ERR_PARAM_NULLPTR, "sharedInput and logit come together or not at all.");
-    GMM_REQUIRE(m > 0 && k > 0 && n > 0 && e > 0 && yRows >= 0 && k <= kMaxInnerAxis && n <= kMaxInnerAxis, ACLNN_ERR_PARAM_INVALID, "bad sizes.");
+    GMM_REQUIRE(m > 0 && m <= 0x7fffffffll / 2 && k > 0 && n > 0 && e > 0 && yRows >= 0 && k <= kMaxInnerAxis && n <= kMaxInnerAxis,
+                ACLNN_ERR_PARAM_INVALID, "bad sizes.");
     GMM_REQUIRE(n % 4 == 0, ACLNN_ERR_PARAM_INVALID, "n must be a multiple of 4.");
     GMM_REQUIRE(weightLayout == 0 || (weightLayout == 2 && k % 16 == 0 && n % 32 == 0), ACLNN_ERR_PARAM_INVALID,
                 "weightLayout must be 0 ([e,k,n]) or 2 (FRACTAL_NZ, k %% 16 == 0, n %% 32 == 0).");
@@ -1008,6 +1081,10 @@ aclnnStatus gmmB200GroupedMatmulFinalizeRouting(const void *x, const void *weigh
     p.scatter_add = sharedInput ? 1 : 0;
     p.out_rows = yRows;
     p.shared_input = sharedInput; p.shared_rows = sharedRows; p.shared_offset = sharedOffset; p.shared_weight = sharedWeight;
+    {
+        aclnnStatus orc = convert_options(options, &p.opt);
+        if (orc != ACLNN_SUCCESS) return orc;
+    }
     Plan plan;
     make_plan(p, &plan);
     GMM_REQUIRE(workspaceSize >= plan.ws_bytes && workspace, ACLNN_ERR_PARAM_INVALID, "workspace of %llu bytes needed.", (unsigned long long)plan.ws_bytes);

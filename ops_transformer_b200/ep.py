@@ -69,8 +69,11 @@ class ExpertParallelFFN:
     """Holds this rank's expert weights and runs the dispatch -> FFN -> return pipeline."""
 
     def __init__(self, n_experts: int, w1, w1_scale, w2, w2_scale, *, group=None, chunks: int = 1,
-                 compute: Optional[Callable] = None):
+                 compute: Optional[Callable] = None, options=None):
+        """``options``: per-call ``LaunchOptions`` for the two GEMM operators, e.g. a CTA cap that leaves a few SMs to the
+        all-to-all kernels running beside them."""
         self.group = group
+        self.options = options
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.n_experts = n_experts
@@ -105,8 +108,9 @@ class ExpertParallelFFN:
         """gate/up GEMM + SwiGLU + requant, then the down GEMM; with ``out_row_index`` the down GEMM scatters its
         result rows (row r -> row out_row_index[r]) so that no separate un-permute pass is needed."""
         from . import acl
-        q, qs = acl.grouped_matmul_swiglu_quant(x, self.w1, self.w1_scale, xs, group_list)
-        return acl.grouped_matmul_v4(q, self.w2, self.w2_scale, qs, group_list, group_list_type=0, out_row_index=out_row_index)
+        q, qs = acl.grouped_matmul_swiglu_quant(x, self.w1, self.w1_scale, xs, group_list, options=self.options)
+        return acl.grouped_matmul_v4(q, self.w2, self.w2_scale, qs, group_list, group_list_type=0, out_row_index=out_row_index,
+                                     options=self.options)
 
     def _a2a(self, out, inp, out_splits, in_splits, async_op=False):
         return dist.all_to_all_single(out, inp, out_splits, in_splits, group=self.group, async_op=async_op)
@@ -268,7 +272,9 @@ class FusedExpertParallelFFN:
       4. a second barrier; every rank then finds its results, in send order, in its own result buffer.
 
     Nothing is read back to the host during a step.  Buffers are sized for `capacity` received rows per rank; rows
-    beyond it are dropped and counted (``overflow``), so capacity must cover the worst expected imbalance.
+    beyond it are dropped and counted, so capacity must cover the worst expected imbalance.  The reference's dispatch is
+    dropless in this mode, so a caller must read the counter: every result dict carries it as ``dropped_rows`` (an int32
+    device tensor, cumulative since construction; anything but 0 means results are missing).
     """
 
     def __init__(self, n_experts: int, hidden: int, hidden_out: int, w1, w1_scale, w2, w2_scale, *, tokens: int, top_k: int,
@@ -395,13 +401,14 @@ class FusedExpertParallelFFN:
             q, qs = acl.grouped_matmul_swiglu_quant(self.act[c], self.w1, self.w1_scale, self.act_scale[c], group_list)
             self._mark(f"swiglu_quant{c}")
             acl.grouped_matmul_v4(q, self.w2, self.w2_scale, qs, group_list, group_list_type=0, out_row_index=ret_dest,
-                                  out_peers=self.buf_y.ptrs, out=None)
+                                  out_peers=self.buf_y.ptrs, out=None, out_rows=self.n_send)
             self._mark(f"down_gemm{c}")
             group_lists.append(group_list)
         self._barrier()   # every rank's results have landed, and everyone is done reading its activation buffers
         self._mark("barrier2")
         chunk_out = [{"y": self.result[self.bounds[c] * k:self.bounds[c + 1] * k], "plan": plans[c]} for c in range(C_)]
-        return {"y": self.result, "plan": plans[0], "group_list": group_lists[0], "group_lists": group_lists, "chunks": chunk_out}
+        return {"y": self.result, "plan": plans[0], "group_list": group_lists[0], "group_lists": group_lists, "chunks": chunk_out,
+                "dropped_rows": self.overflow}
 
     def _forward_kernels(self, x, x_scale, topk_ids):
         """forward() with the routing done by gmmB200EpCount / gmmB200EpRoute."""
@@ -457,13 +464,14 @@ class FusedExpertParallelFFN:
             q, qs = acl.grouped_matmul_swiglu_quant(self.act[c], self.w1, self.w1_scale, self.act_scale[c], r["group_list"])
             self._mark(f"swiglu_quant{c}")
             acl.grouped_matmul_v4(q, self.w2, self.w2_scale, qs, r["group_list"], group_list_type=0, out_row_index=r["ret_dest"],
-                                  out_peers=self.buf_y.ptrs, out=None)
+                                  out_peers=self.buf_y.ptrs, out=None, out_rows=self.n_send)
             self._mark(f"down_gemm{c}")
         self._barrier()   # every rank's results have landed, and everyone is done reading its activation buffers
         self._mark("barrier2")
         group_lists = [self._r[c]["group_list"] for c in range(C_)]
         chunk_out = [{"y": self.result[self.bounds[c] * k:self.bounds[c + 1] * k], "plan": plans[c]} for c in range(C_)]
-        return {"y": self.result, "plan": plans[0], "group_list": group_lists[0], "group_lists": group_lists, "chunks": chunk_out}
+        return {"y": self.result, "plan": plans[0], "group_list": group_lists[0], "group_lists": group_lists, "chunks": chunk_out,
+                "dropped_rows": self.overflow}
 
     def capture(self, x: torch.Tensor, x_scale: torch.Tensor, topk_ids: torch.Tensor):
         """Record one step into a CUDA graph.  Shapes are static (buffers are sized by capacity and nothing is read on
@@ -492,230 +500,3 @@ class FusedExpertParallelFFN:
         self._graph = None
         for b in (self.buf_x, self.buf_s, self.buf_y):
             b.close()
-
-
-# ----------------------------------------------------------------------------------------------------------------
-# benchmark entry (bench.py --gpus N under torchrun, or --workload c5 on one GPU)
-# ----------------------------------------------------------------------------------------------------------------
-
-N_EXPERTS, HIDDEN, INTER, TOP_K = 256, 7168, 2048, 8
-
-
-def default_chunks(world: int) -> int:
-    """Token chunks per step of the NCCL variant: enough rows per local expert and chunk to keep the GEMM tiles full."""
-    return {1: 1, 2: 1, 4: 2}.get(world, 4)
-
-
-def one_gpu_summary(args, dev):
-    """The expert-parallel workload on one GPU (all 256 experts local): tokens/s, ms per step and TOPS."""
-    T = args.ep_tokens
-    d1 = _make_rank_data(dev, 1, 0, T)
-    f1, _, _ = _build_ffn(args, d1, T, 1)
-    ms1, _, rows1 = _timed_steps(f1, d1, max(3, min(args.steps, 10)), 3, 1)
-    out = {"ms_per_step": ms1, "tokens_per_s": T / (ms1 * 1e-3),
-           "tops": rows1 * 2.0 * (HIDDEN * 2 * INTER + INTER * HIDDEN) / (ms1 * 1e-3) / 1e12}
-    if hasattr(f1, "close"):
-        f1.close()
-    del f1, d1
-    torch.cuda.empty_cache()
-    return out
-
-
-def _make_rank_data(dev, world, rank, tokens):
-    """Seeded synthetic weights of this rank's experts and this rank's tokens (DeepSeek-V3 shapes)."""
-    import numpy as np
-
-    from . import synth
-    e_local = N_EXPERTS // world
-    g = torch.Generator(device=dev)
-    g.manual_seed(1234 + rank)
-    d = {}
-    d["w1"] = torch.randint(-127, 128, (e_local, HIDDEN, 2 * INTER), dtype=torch.int8, device=dev, generator=g)
-    d["w2"] = torch.randint(-127, 128, (e_local, INTER, HIDDEN), dtype=torch.int8, device=dev, generator=g)
-    d["w1s"] = torch.empty((e_local, 2 * INTER), dtype=torch.float32, device=dev).uniform_(1e-3, 1e-2, generator=g)
-    d["w2s"] = torch.empty((e_local, HIDDEN), dtype=torch.float32, device=dev).uniform_(1e-3, 1e-2, generator=g)
-    d["x"] = torch.randint(-127, 128, (tokens, HIDDEN), dtype=torch.int8, device=dev, generator=g)
-    d["xs"] = torch.empty((tokens,), dtype=torch.float32, device=dev).uniform_(1e-3, 1e-2, generator=g)
-    _, top = synth.topk_softmax_counts(tokens, N_EXPERTS, TOP_K, seed=rank, idx=7)
-    d["topk"] = torch.from_numpy(top.astype(np.int64)).to(dev)
-    return d
-
-
-def _build_ffn(args, d, tokens, world):
-    if args.ep_impl == "fused":
-        chunks = args.ep_chunks if args.ep_chunks > 0 else 1   # measured on 8 GPUs: 1 chunk 7.1 ms, 2 chunks 7.6 ms, 4 chunks 8.7 ms
-        ffn = FusedExpertParallelFFN(N_EXPERTS, HIDDEN, HIDDEN, d["w1"], d["w1s"], d["w2"], d["w2s"], tokens=tokens, top_k=TOP_K,
-                                     capacity=2 * tokens * TOP_K, chunks=chunks)
-        return ffn, (f"dispatch by peer stores, results stored into the owners' buffers by the down-GEMM epilogue, {chunks} "
-                     "token chunk(s) with the next chunk's dispatch beside the GEMMs"), 3 * chunks
-    chunks = args.ep_chunks if args.ep_chunks > 0 else default_chunks(world)
-    reserve = args.ep_reserve_sms if args.ep_reserve_sms >= 0 else (16 if world > 1 and chunks > 1 else 0)
-    if reserve > 0:
-        # leave a few SMs to the all-to-all kernels so that they can run beside the persistent GEMM kernels
-        from . import _lib
-        n_sm = torch.cuda.get_device_properties(d["x"].device).multi_processor_count
-        _lib.lib().gmmB200SetSmLimit(max(2, n_sm - reserve))
-    ffn = ExpertParallelFFN(N_EXPERTS, d["w1"], d["w1s"], d["w2"], d["w2s"], chunks=chunks)
-    return ffn, f"NCCL all-to-all around the operators, {chunks} chunk(s), {reserve} SMs left to the exchange", 2 * chunks
-
-
-def _rows_of(res):
-    if isinstance(res, dict):
-        return sum(int(g[-1].item()) for g in res["group_lists"])
-    return sum(r["rows_computed"] for r in res)
-
-
-def _timed_steps(ffn, d, steps, warmup, world, use_graph=False):
-    import time
-    if use_graph and hasattr(ffn, "capture"):
-        ffn.capture(d["x"], d["xs"], d["topk"])
-        fwd = ffn.replay
-    else:
-        fwd = ffn.forward
-    for _ in range(max(warmup, 3)):
-        res = fwd(d["x"], d["xs"], d["topk"])
-    torch.cuda.synchronize()
-    rows = _rows_of(res)
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0 = time.perf_counter()
-    ev0.record()
-    for _ in range(steps):
-        fwd(d["x"], d["xs"], d["topk"])
-    ev1.record()
-    torch.cuda.synchronize()
-    wall = (time.perf_counter() - t0) / steps * 1e3
-    return ev0.elapsed_time(ev1) / steps, wall, rows
-
-
-def _e2e_steps(ffn, d, steps):
-    """The same step through the public classes with host buffers: pinned H2D of tokens, scales and routing, the
-    FFN, D2H of the result rows, every step."""
-    import time
-    hx = torch.empty_like(d["x"], device="cpu").pin_memory(); hx.copy_(d["x"])
-    hs = torch.empty_like(d["xs"], device="cpu").pin_memory(); hs.copy_(d["xs"])
-    ht = torch.empty_like(d["topk"], device="cpu").pin_memory(); ht.copy_(d["topk"])
-    dx, ds, dt = torch.empty_like(d["x"]), torch.empty_like(d["xs"]), torch.empty_like(d["topk"])
-    host_out = None
-
-    def step():
-        nonlocal host_out
-        dx.copy_(hx, non_blocking=True); ds.copy_(hs, non_blocking=True); dt.copy_(ht, non_blocking=True)
-        res = ffn.replay(dx, ds, dt) if getattr(ffn, "_graph", None) is not None else ffn.forward(dx, ds, dt)
-        ys = [res["y"]] if isinstance(res, dict) else [r["y"] for r in res]
-        if host_out is None:
-            host_out = [torch.empty_like(y, device="cpu").pin_memory() for y in ys]
-        for h, y in zip(host_out, ys):
-            h.copy_(y, non_blocking=True)
-        torch.cuda.synchronize()
-
-    step()
-    if dist.is_initialized():
-        dist.barrier()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        step()
-    ms = (time.perf_counter() - t0) / steps * 1e3
-    h2d = hx.numel() + hs.numel() * 4 + ht.numel() * 8
-    d2h = sum(h.numel() * h.element_size() for h in host_out)
-    return ms, h2d, d2h
-
-
-def bench_main(args):
-    import json
-    import os as _os
-    import sys as _sys
-
-    _sys.path.insert(0, _os.path.dirname(_os.path.dirname(_os.path.abspath(__file__))))
-    from bench import ClockSampler, cpu_baseline_sample, measured_peaks
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    T = args.ep_tokens
-    ops_per_row = 2.0 * (HIDDEN * 2 * INTER + INTER * HIDDEN)
-
-    # The same workload on one GPU (all 256 experts local, no exchange), measured by rank 0 before the group forms:
-    # the reference point for the scaling of this line.
-    n1 = None
-    if world > 1 and rank == 0 and not args.ep_skip_n1:
-        n1 = one_gpu_summary(args, dev)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-
-    d = _make_rank_data(dev, world, rank, T)
-    ffn, how, launches_per_step = _build_ffn(args, d, T, world)
-    sampler = ClockSampler(local) if rank == 0 else None
-    if sampler:
-        sampler.start()
-        sampler.mark_begin()
-    ms, wall, rows_local = _timed_steps(ffn, d, args.steps, args.warmup, world, use_graph=args.ep_graph and world > 1)
-    if sampler:
-        sampler.mark_end()
-        clocks = sampler.stop()
-    e2e_ms, h2d, d2h = _e2e_steps(ffn, d, 3)
-    dropped = int(ffn.overflow.item()) if hasattr(ffn, "overflow") else 0
-    trace = None
-    if args.ep_phases and hasattr(ffn, "trace"):
-        for _ in range(2):
-            ffn.forward(d["x"], d["xs"], d["topk"])   # eager warm-up (the timed steps may have been graph replays)
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        ffn.trace = []
-        ffn.forward(d["x"], d["xs"], d["topk"])
-        torch.cuda.synchronize()
-        tr = ffn.trace
-        mine = [(b[0], round(a[1].elapsed_time(b[1]), 3)) for a, b in zip(tr[:-1], tr[1:])]
-        ffn.trace = None
-        if world > 1:
-            allt = [None] * world
-            dist.all_gather_object(allt, mine)
-            trace = [(mine[i][0], min(t_[i][1] for t_ in allt), max(t_[i][1] for t_ in allt)) for i in range(len(mine))]
-        else:
-            trace = mine
-    stats = torch.tensor([ms, float(rows_local), float(dropped), e2e_ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        allst = [torch.empty_like(stats) for _ in range(world)]
-        dist.all_gather(allst, stats)
-    else:
-        allst = [stats]
-    ms_max = max(float(s_[0]) for s_ in allst)
-    rows_total = sum(float(s_[1]) for s_ in allst)
-    dropped = sum(float(s_[2]) for s_ in allst)
-    e2e_max = max(float(s_[3]) for s_ in allst)
-    if rank == 0:
-        tops = rows_total * ops_per_row / (ms_max * 1e-3) / 1e12
-        peaks = measured_peaks()
-        int8_peak = 2.0 * peaks["bf16_tflops_sustained"]   # a multi-millisecond step runs under the power cap
-        line = {
-            "metric": "int8 GMM+SwiGLU-quant TOPS", "value": tops, "unit": "TOPS", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_max, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-            "config": {"workload": f"c5 expert-parallel FFN: 256 experts over {world} GPU(s), {T} tokens per GPU, top-8, swiglu_quant "
-                                   f"K=7168 N=4096 then down GEMM K=2048 N=7168; {how}",
-                       "l2": "inputs larger than L2", "tokens_per_s": T * world / (ms_max * 1e-3), "rows_total": rows_total,
-                       "host_ms_per_step": wall, "dropped_rows": dropped, "phase_ms": trace,
-                       "cuda_graph": bool(args.ep_graph and args.ep_impl == "fused" and world > 1)},
-            "roofline": {"bound": "tensor", "achieved": tops / world, "peak": int8_peak, "unit": "TFLOP/s", "frac": tops / world / int8_peak,
-                         "traffic": None, "kernel": "whole step per GPU (dispatch, two GEMM kernels, exchange)",
-                         "peak_basis": f"2 x sustained bf16 of {peaks['source']} ({peaks['bf16_tflops_sustained']} TFLOP/s); int8 ops "
-                                       "counted as 2 per multiply-add"},
-            "e2e": {"value": rows_total * ops_per_row / (e2e_max * 1e-3) / 1e12, "unit": "TOPS", "ms_per_step": e2e_max,
-                    "h2d_bytes_per_step": int(h2d) * world, "d2h_bytes_per_step": int(d2h) * world},
-            "gpu_launches": launches_per_step * args.steps,
-            "clocks": clocks,
-            "ep": {"tokens_per_s": T * world / (ms_max * 1e-3), "one_gpu_same_workload": n1,
-                   "scaling_vs_one_gpu": (T * world / (ms_max * 1e-3)) / n1["tokens_per_s"] if n1 else None},
-        }
-        if world == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_baseline_sample()
-        print(json.dumps(line))
-    if hasattr(ffn, "close"):
-        ffn.close()
-    if world > 1:
-        dist.destroy_process_group()

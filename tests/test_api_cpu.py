@@ -130,6 +130,11 @@ def test_v4_int32_result_needs_no_scales_and_empty_input_needs_no_workspace():
     e = _v4_tensors(M=0)
     rc, size = _v4_phase1(**e)
     assert rc == OK and size == 0
+    # K == 0: x has no elements, so the reference returns success with a workspace of 0 and launches nothing
+    # (CheckZeroShape and its caller, aclnn_grouped_matmul.cpp:1535-1548, 1770-1772)
+    z = _v4_tensors(K=0)
+    rc, size = _v4_phase1(**z)
+    assert rc == OK and size == 0
 
 
 def test_v4_transposed_weight_view_and_unaligned_shapes():
@@ -187,6 +192,37 @@ def test_swiglu_reference_api_ut_case_is_rejected():
     t = _sw_tensors()
     assert _sw_phase1(**{**t, "ws": torch.empty((4, 2048), dtype=torch.int64)})[0] == INVALID
     assert _sw_phase1(**{**t, "q": torch.empty((192, 2048), dtype=torch.int8)})[0] == INVALID
+
+
+def test_swiglu_empty_reduction_is_rejected():
+    # k == 0 leaves no row maximum to quantise by: refused with a message, as the flat entry points do
+    rc, _ = _sw_phase1(**_sw_tensors(k=0))
+    assert rc == INVALID and "k must be positive" in _lib.last_error()
+    size = C.c_uint64(0)
+    assert _lib.lib().gmmB200GroupedMatmulSwigluQuantWorkspaceSize(4, 0, 32, 1, C.byref(size)) == INVALID
+    assert _lib.lib().gmmB200GroupedMatmulW8A8WorkspaceSize(1 << 31, 16, 16, 1, 27, C.byref(size)) == INVALID   # m beyond int range
+
+
+def test_executor_options_are_validated_on_the_host():
+    L = _lib.lib()
+    t = _sw_tensors()
+    hs = {k: acl.create_tensor(v) for k, v in t.items()}
+    size, ex = C.c_uint64(0), C.c_void_p(0)
+    assert L.aclnnGroupedMatmulSwigluQuantGetWorkspaceSize(hs["x"], hs["w"], None, None, hs["ws"], hs["xs"], hs["gl"], hs["q"], hs["qs"],
+                                                           None, C.byref(size), C.byref(ex)) == OK
+    assert L.gmmB200SetExecutorOptions(ex, C.byref(_lib.LaunchOptions(max_ctas=16, wait_limit_cycles=1 << 20))) == OK
+    assert L.gmmB200SetExecutorOptions(ex, None) == OK                                   # null = defaults
+    assert L.gmmB200SetExecutorOptions(ex, C.byref(_lib.LaunchOptions(max_ctas=-1))) == INVALID
+    half = _lib.LaunchOptions(start_event=C.c_void_p(8))                                 # a start event without a stop event
+    assert L.gmmB200SetExecutorOptions(ex, C.byref(half)) == INVALID
+    short = _lib.LaunchOptions(max_ctas=3)
+    short.structSize = 4
+    assert L.gmmB200SetExecutorOptions(ex, C.byref(short)) == INVALID
+    assert L.gmmB200SetExecutorOptions(None, C.byref(short)) == NULLPTR
+    assert L.aclDestroyAclOpExecutor(ex) == OK
+    assert L.gmmB200SetExecutorOptions(ex, C.byref(_lib.LaunchOptions())) == INVALID     # no longer live
+    for h in hs.values():
+        L.aclDestroyTensor(h)
 
 
 def test_swiglu_null_arguments():
@@ -473,7 +509,7 @@ def test_flat_entry_points_validate_on_the_host():
     assert L.gmmB200GroupedMatmulW8A8WorkspaceSize(256, 1024, 2048, 4, _lib.ACL_FLOAT16, C.byref(size)) == OK
     assert L.gmmB200GroupedMatmulW8A8WorkspaceSize(256, 1024, 2048, 4, _lib.ACL_FLOAT, C.byref(size)) == INVALID
     one = C.c_void_p(256)
-    assert L.gmmB200GroupedMatmulW8A8(None, one, one, 0, one, None, 0, one, 1, 0, 1, 16, 16, 1, 0, 0, None, None, 0, one, 27, one, 256, None) == NULLPTR
-    assert L.gmmB200GroupedMatmulW8A8(one, one, one, 0, one, None, 0, one, 2, 0, 1, 16, 16, 1, 0, 0, None, None, 0, one, 27, one, 256, None) == INVALID
-    assert L.gmmB200GroupedMatmulSwigluQuant(one, one, one, 0, one, one, 1, 4, 16, 32, 1, 0, one, one, one, 16, None) == INVALID  # workspace too small
+    assert L.gmmB200GroupedMatmulW8A8(None, one, one, 0, one, None, 0, one, 1, 0, 1, 16, 16, 1, 0, 0, None, None, 0, 0, one, 27, one, 256, None, None) == NULLPTR
+    assert L.gmmB200GroupedMatmulW8A8(one, one, one, 0, one, None, 0, one, 2, 0, 1, 16, 16, 1, 0, 0, None, None, 0, 0, one, 27, one, 256, None, None) == INVALID
+    assert L.gmmB200GroupedMatmulSwigluQuant(one, one, one, 0, one, one, 1, 4, 16, 32, 1, 0, one, one, one, 16, None, None) == INVALID  # workspace too small
     assert "workspaceSize" in _lib.last_error()

@@ -428,7 +428,7 @@ def test_swiglu_fractal_nz_n_multiple_of_32_only(oracle):
 
 def check_finalize(oracle, M, K, N, E, counts, topk, seed, *, shared_rows=0, shared_offset=0, shared_weight=1.0, use_logit=True,
                    use_bias=False, use_pts=True, idx32=False, scale_bf16=False, api="", flat_layout=None, view_3d=True,
-                   batch=None):
+                   batch=None, y_misaligned=False):
     """fp32 sums of up to topk + 1 terms in an order that differs from the oracle's: every element must lie within
     4 ulp-sized steps of the sum of magnitudes (4 * 2^-23 * abs_sum) of the oracle's value."""
     import ops_transformer_b200 as ops
@@ -453,6 +453,11 @@ def check_finalize(oracle, M, K, N, E, counts, topk, seed, *, shared_rows=0, sha
     bf = lambda a: None if a is None else torch.from_numpy(a.view(np.int16)).to(dev).view(torch.bfloat16)  # noqa: E731
     ws_t = bf(ws_o) if scale_bf16 else t(ws)
     out = torch.from_numpy(y0).to(dev)
+    if y_misaligned:  # a result that starts 4 bytes into an allocation: 4-byte but not 16-byte aligned
+        flat = torch.empty(y0.size + 4, dtype=torch.float32, device=dev)
+        out = flat[1:1 + y0.size].view(y_rows, N)
+        out.copy_(torch.from_numpy(y0))
+        assert out.data_ptr() % 16 == 4
     ri_t = t(ri.astype(np.int32)) if idx32 else t(ri)
     kw = dict(bias=bf(bias), pertoken_scale=t(xs) if use_pts else None, shared_input=bf(shared), logit=t(logit),
               shared_input_weight=shared_weight, shared_input_offset=shared_offset)
@@ -502,6 +507,12 @@ def test_finalize_routing_plain_store_scene(oracle):
 @pytest.mark.parametrize("layout", [0, 2])
 def test_finalize_routing_flat_entry_point(oracle, layout):
     check_finalize(oracle, 512, 512, 1024, 4, [128, 200, 0, 184], 8, 65, shared_rows=64, flat_layout=layout, use_bias=True)
+
+
+def test_finalize_routing_result_view_not_16_byte_aligned(oracle):
+    # the tensor-core path needs 16-byte aligned rows; such a view takes the CUDA-core kernels, including the scalar
+    # initialisation of the result
+    check_finalize(oracle, 96, 128, 256, 2, [40, 56], 4, 67, shared_rows=16, shared_offset=3, y_misaligned=True)
 
 
 def test_finalize_routing_batch_smaller_than_rows_per_token(oracle):
