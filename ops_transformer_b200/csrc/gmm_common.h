@@ -81,6 +81,7 @@ struct Plan {
     bool hybrid = false;                // with ctas == 2: a second launch with 128-row tiles takes trailing blocks of <= 128 rows
     size_t ws_bytes = 0;
     size_t off_status = 0, off_amax = 0, off_stage = 0, off_done = 0;
+    size_t off_wave = 0;                // 0 = no pacing counters in this workspace
     size_t zero_bytes = 0;              // leading bytes of the workspace cleared at launch
     bool maps_ready = false;
     alignas(64) CUtensorMap map_x;

@@ -264,12 +264,19 @@ void make_plan(const Problem &p, Plan *plan)
     }
     if (const char *e = getenv("GMM_B200_HYBRID")) plan->hybrid = plan->ctas == 2 && e[0] != '0';
     plan->off_status = 0;
+    plan->off_wave = 0;
     size_t off = 256;
     plan->off_amax = off;
     if (p.mode == kModeSwigluQuant && plan->path == kPathSm100) {
         off += align_up((size_t)p.M * 4, 256);
         plan->off_done = off;  // two words per row block of a tile; every group can add a partial block in each of two launches
         off += align_up(((size_t)(p.M + 127) / 128 + 2 * (size_t)p.gl_len + 2) * 8, 256);
+        // one pacing counter per wave of the tile schedule; at most one wave per tile (a single unit)
+        const size_t max_tiles = ((size_t)(p.M + 127) / 128 + (size_t)p.gl_len) * (size_t)((p.N / 2 + 127) / 128);
+        if (max_tiles <= 262144) {
+            plan->off_wave = off;
+            off += align_up((max_tiles + 1) * 4, 256);
+        }
         plan->zero_bytes = off;
         plan->off_stage = off;
         off += align_up((size_t)p.M * (size_t)(p.N / 2) * 4, 256);

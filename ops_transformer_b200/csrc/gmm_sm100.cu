@@ -59,14 +59,12 @@ struct Cfg {
 static_assert(Cfg<1>::kStages == 4 && Cfg<2>::kStages == 6 && Cfg<2>::kStages <= MAX_STAGES, "stage arithmetic");
 constexpr int MAX_GROUPS = 1024;
 constexpr int EPI_WARPS = 8;                 // two warps per TMEM lane quarter, each takes half of the columns
-// swiglu_quant only: one publishing warp (one lane: row-block bookkeeping in global memory) and RQ_WARPS warps that
-// requantise finished row slices, all beside the epilogue, so that none of their memory round trips delays the next tile.
-constexpr int RQ_WARPS = 4;
-constexpr int RQ_THREADS = 32 * RQ_WARPS;
-constexpr int RQ_DEPTH = 4;                  // tiles the epilogue may be ahead of the publishing warp
-constexpr int WK_DEPTH = 4;                  // work lists the publishing warp may be ahead of the requantising warps
+// swiglu_quant only: one more warp, of which one lane keeps the books of the row blocks in global memory (arrivals, slice
+// claims) beside the epilogue, so that none of its round trips to L2 delays the next tile.  It hands the epilogue warps
+// lists of row ranges to requantise through a small ring.
+constexpr int WK_DEPTH = 4;                  // work lists the publishing lane may be ahead of the epilogue warps
 constexpr int BASE_THREADS = 64 + 32 * EPI_WARPS;
-__host__ __device__ constexpr int num_threads(int mode) { return BASE_THREADS + (mode == kModeSwigluQuant ? 32 + RQ_THREADS : 0); }
+__host__ __device__ constexpr int num_threads(int mode) { return BASE_THREADS + (mode == kModeSwigluQuant ? 32 : 0); }
 constexpr int TMEM_COLS = 512;
 constexpr long long WAIT_LIMIT_CYCLES = 1ll << 31;   // about a second
 constexpr long long DRAIN_LIMIT_CYCLES = 1ll << 24;  // a few milliseconds
@@ -85,17 +83,17 @@ struct Shared {
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
     uint64_t scale_ready[SCALE_BUFS];  // all epilogue threads have stored their column's scale
-    uint64_t rq_full[RQ_DEPTH];        // every epilogue thread has stored its part of a tile (swiglu_quant)
-    uint64_t rq_empty[RQ_DEPTH];       // the publishing warp has taken note of it
-    uint64_t wk_full[WK_DEPTH];        // a work list is written
-    uint64_t wk_empty[WK_DEPTH];       // every requantising thread is done with it
+    uint64_t wk_full[WK_DEPTH];        // a work list is written (swiglu_quant)
+    uint64_t wk_empty[WK_DEPTH];       // every epilogue warp is done with it
     uint32_t tmem_base;
     int abort_flag;
     int total_tiles;
     int pad;
     long long wait_limit;              // bound of every wait, in cycles
-    // swiglu_quant: row blocks this CTA contributed to and has not yet settled (publishing lane only), and a ring of work
-    // lists: the row ranges to requantise (written by that lane, read by the requantising warps after wk_full)
+    // swiglu_quant: how many epilogue threads have stored (and fenced) their part of how many tiles; the row blocks this
+    // CTA contributed to and has not yet settled (publishing lane only); a ring of work lists: the row ranges to requantise
+    // (written by that lane, read by the epilogue warps after wk_full)
+    unsigned stored_count;
     int pend_n;
     int pend_rb[MAX_PENDING], pend_row0[MAX_PENDING], pend_rows[MAX_PENDING];
     int n_work[WK_DEPTH];
@@ -110,6 +108,29 @@ struct Shared {
 constexpr size_t SMEM_BYTES = 1024 + (size_t)PIPE_BYTES + sizeof(Shared);
 static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
 static_assert(offsetof(Shared, scales) % 16 == 0 && offsetof(Shared, out_stage) % 16 == 0, "vector accesses need 16-byte alignment");
+
+// Debug build only (-DGMM_TRACE): clock64 stamps of the roles of a few CTAs, written to a buffer whose address comes from
+// the environment; layout [cta < 4][role < 4][tile < 64][slot < 8].
+#ifdef GMM_TRACE
+#define TRACE(role, tile, slot)                                                                                           \
+    do {                                                                                                                  \
+        if (p.trace && blockIdx.x < 4 && (tile) < 64) p.trace[(((int)blockIdx.x * 4 + (role)) * 64 + (tile)) * 8 + (slot)] = clock64(); \
+    } while (0)
+#define TRACE_ADD(role, tile, slot, v)                                                                                    \
+    do {                                                                                                                  \
+        if (p.trace && blockIdx.x < 4 && (tile) < 64) p.trace[(((int)blockIdx.x * 4 + (role)) * 64 + (tile)) * 8 + (slot)] += (v); \
+    } while (0)
+#define TRACE_GT(role, tile, slot)                                                                                        \
+    do {                                                                                                                  \
+        unsigned long long gt_;                                                                                           \
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt_));                                                           \
+        if (p.trace && blockIdx.x < 4 && (tile) < 64) p.trace[(((int)blockIdx.x * 4 + (role)) * 64 + (tile)) * 8 + (slot)] = (long long)gt_; \
+    } while (0)
+#else
+#define TRACE_GT(role, tile, slot) do {} while (0)
+#define TRACE(role, tile, slot) do {} while (0)
+#define TRACE_ADD(role, tile, slot, v) do {} while (0)
+#endif
 
 struct KParams {
     const int64_t *group_list;
@@ -143,7 +164,11 @@ struct KParams {
     int *status;
     long long wait_limit;   // cycles a wait may last before the CTA gives up and records kStatusWaitTimeout
     int skip_k_blocks;      // test only: K blocks the producer leaves out of its last tile (drives the abort path)
-    int knob_spin, knob_depth;   // EXPERIMENT
+    int *wave_cnt;          // optional: per wave (round of the static tile schedule) the units that have started it
+    int pace_cycles;        // how long a producer waits for the other units to have started the previous wave
+#ifdef GMM_TRACE
+    long long *trace;
+#endif
 };
 
 // ---------------------------------------------------------------------------------------------------------
@@ -520,42 +545,34 @@ __device__ __forceinline__ uint32_t quant4(float4 v, float rcp)
 // Second half of grouped_matmul_swiglu_quant for rows [r_begin, r_end) of a finished row block (all of its N tiles
 // have stored S and the row maxima): per row  qs = amax / 127, r = 1 / qs, q = int8(half(S * r))
 // (gmm/grouped_matmul_swiglu_quant/op_kernel/grouped_matmul_swiglu_quant.h:496-503).  S and amax were written by
-// other SMs, so they are read through L2 (ld.global.cg).  One warp per row; a lane takes pieces of 16 outputs, four pieces
-// (sixteen 16-byte loads) in flight at a time, because these loads wait for L2 under the full load of the GEMM.
-__device__ void requant_rows(const KParams &p, int r_begin, int r_end, int tr)
+// other SMs, so they are read through L2 (ld.global.cg).  One warp per row.  Consecutive lanes read consecutive 16-byte
+// pieces (a load instruction covers 512 contiguous bytes, a store 128): the tensor cores read their operands through the
+// same shared-memory / L1 data path, so every extra line these accesses touch is taken from the MMAs.  Sixteen loads
+// per lane are in flight at a time, because they wait for L2 under the full load of the GEMM.
+__device__ void requant_rows(const KParams &p, int r_begin, int r_end, int warp_r, int lane)
 {
-    const int warp_r = tr >> 5, lane = tr & 31;
     const int H = p.half_n;
-    const int pieces = H >> 4;
+    const int nf = H >> 2;  // 16-byte pieces per row
     const float *stage = reinterpret_cast<const float *>(p.out);
-    for (int grow = r_begin + warp_r; grow < r_end; grow += RQ_WARPS) {
+    for (int grow = r_begin + warp_r; grow < r_end; grow += EPI_WARPS) {
         const float amax = __uint_as_float(__ldcg(p.amax_bits + grow));
         const float4 *src = reinterpret_cast<const float4 *>(stage + (size_t)grow * H);
-        uint4 *dst = reinterpret_cast<uint4 *>(p.q_out + (size_t)grow * H);
-        int c = lane;
-        float4 v[4][4];
-        if (c + 96 < pieces) {
+        uint32_t *dst = reinterpret_cast<uint32_t *>(p.q_out + (size_t)grow * H);
+        float4 v[16];
+        int f = lane;
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
-#pragma unroll
-                for (int j = 0; j < 4; ++j) v[u][j] = __ldcg(src + (c + 32 * u) * 4 + j);
-        }
+        for (int u = 0; u < 16; ++u) v[u] = f + 32 * u < nf ? __ldcg(src + f + 32 * u) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         const float qs = __fdiv_rn(amax, 127.0f);
         const float rcp = __fdiv_rn(1.0f, qs);
         if (lane == 0) p.q_scale_out[grow] = qs;
-        for (; c + 96 < pieces; c += 128) {
+        while (true) {
 #pragma unroll
-            for (int u = 0; u < 4; ++u) dst[c + 32 * u] = make_uint4(quant4(v[u][0], rcp), quant4(v[u][1], rcp), quant4(v[u][2], rcp), quant4(v[u][3], rcp));
-            if (c + 128 + 96 < pieces) {
+            for (int u = 0; u < 16; ++u)
+                if (f + 32 * u < nf) dst[f + 32 * u] = quant4(v[u], rcp);
+            f += 512;
+            if (f - lane >= nf) break;
 #pragma unroll
-                for (int u = 0; u < 4; ++u)
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) v[u][j] = __ldcg(src + (c + 128 + 32 * u) * 4 + j);
-            }
-        }
-        for (; c < pieces; c += 32) {
-            const float4 a0 = __ldcg(src + c * 4 + 0), a1 = __ldcg(src + c * 4 + 1), a2 = __ldcg(src + c * 4 + 2), a3 = __ldcg(src + c * 4 + 3);
-            dst[c] = make_uint4(quant4(a0, rcp), quant4(a1, rcp), quant4(a2, rcp), quant4(a3, rcp));
+            for (int u = 0; u < 16; ++u) v[u] = f + 32 * u < nf ? __ldcg(src + f + 32 * u) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         }
     }
 }
@@ -648,6 +665,30 @@ __device__ void release_pending(const KParams &p, Shared *sh, int ws, int shares
     sh->pend_n = 0;
 }
 
+// Epilogue warp: requantise the row ranges of the next work list(s).  Every warp consumes every list, in order, and takes
+// the rows warp, warp + EPI_WARPS, ... of each range.  With `blocking` unset only lists that are already written are
+// taken; otherwise the call waits (bounded) for the next one.  Returns false when a wait gave up.
+__device__ __forceinline__ bool consume_work(const KParams &p, Shared *sh, int &lists_done, int warp_e, int lane, bool blocking)
+{
+    while (true) {
+        const int ws = lists_done % WK_DEPTH;
+        const uint32_t parity = ((uint32_t)(lists_done / WK_DEPTH)) & 1u;
+        int ready = 0;
+        if (lane == 0) {
+            ready = mbar_try_wait(smem_u32(&sh->wk_full[ws]), parity) ? 1 : 0;
+            if (!ready && blocking) ready = mbar_wait(&sh->wk_full[ws], parity, sh, p.status, 650 + ws) ? 1 : -1;
+        }
+        ready = __shfl_sync(0xffffffffu, ready, 0);
+        if (ready <= 0) return ready == 0;
+        const int n = sh->n_work[ws];
+        for (int k = 0; k < n; ++k) requant_rows(p, sh->work_begin[ws][k], sh->work_end[ws][k], warp_e, lane);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh->wk_empty[ws]);
+        ++lists_done;
+        if (blocking) return true;
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------------------------------------
@@ -687,14 +728,11 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             mbar_init(&sh->acc_empty[b], EPI_WARPS * CTAS);  // one arrival per epilogue warp of every CTA of the unit
         }
         for (int b = 0; b < SCALE_BUFS; ++b) mbar_init(&sh->scale_ready[b], EPI_THREADS);
-        for (int b = 0; b < RQ_DEPTH; ++b) {
-            mbar_init(&sh->rq_full[b], EPI_THREADS);
-            mbar_init(&sh->rq_empty[b], 1);
-        }
         for (int b = 0; b < WK_DEPTH; ++b) {
             mbar_init(&sh->wk_full[b], 1);
-            mbar_init(&sh->wk_empty[b], RQ_THREADS);
+            mbar_init(&sh->wk_empty[b], EPI_WARPS);
         }
+        sh->stored_count = 0;
         sh->abort_flag = 0;
         sh->total_tiles = 0;
         sh->wait_limit = p.wait_limit;
@@ -724,9 +762,28 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             bool ok = true;
             // pair: rank 0's full barriers as shared::cluster addresses (barriers are 8 bytes apart)
             const uint32_t full_rank0 = CTAS == 2 ? map_to_cta(&sh->full[0], 0) : 0u;
-            for (int t = unit; t < total_tiles && ok; t += n_units) {
+            // Pacing: the units of a wave (one round of the static schedule) share their operands through L2 - the N tiles
+            // of a row block read the same rows of x, the row blocks of an expert the same weight boxes - and one launch
+            // streams many times the L2's capacity, so a unit that drifts a tile or two away from the others finds the
+            // shared data evicted and fetches it from DRAM again.  Every unit therefore announces the wave it starts and
+            // waits, for at most about one tile's duration, until all units have started the wave before.  It is a hint,
+            // never needed for correctness: when the wait runs out (units not resident together) pacing is switched off.
+            bool pace = p.wave_cnt != nullptr && rank == 0;
+            int wave = 0;
+            for (int t = unit; t < total_tiles && ok; t += n_units, ++wave) {
                 const Tile tl = decode_tile(sh, t, p.n_tiles, L, C::kTileM);
                 const int my_row0 = tl.row0 + (int)rank * BM;
+                if (pace) {
+                    if (wave > 0) {
+                        const int expected = min(n_units, total_tiles - (wave - 1) * n_units);
+                        const long long t0 = clock64();
+                        while (ld_relaxed_gpu(p.wave_cnt + wave - 1) < expected) {
+                            if (clock64() - t0 > p.pace_cycles) { pace = false; break; }
+                            __nanosleep(500);
+                        }
+                    }
+                    asm volatile("red.relaxed.gpu.global.add.s32 [%0], 1;" ::"l"(p.wave_cnt + wave) : "memory");
+                }
                 int n0, n1;
                 if (MODE == kModeSwigluQuant) { n0 = tl.n_idx * (BN / 2); n1 = p.half_n + n0; }
                 else { n0 = tl.n_idx * BN; n1 = n0 + BN / 2; }
@@ -785,12 +842,22 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             bool ok = true;
             const uint32_t empty_peer = CTAS == 2 ? map_to_cta(&sh->empty[0], 1) : 0u;       // the partner's barriers
             const uint32_t acc_full_peer = CTAS == 2 ? map_to_cta(&sh->acc_full[0], 1) : 0u;
-            for (int t = unit; t < total_tiles && ok; t += n_units) {
+            int ti = 0;
+            TRACE_GT(0, 0, 0);
+            for (int t = unit; t < total_tiles && ok; t += n_units, ++ti) {
+                TRACE(1, ti, 0);
                 if (!mbar_wait(&sh->acc_empty[buf], acc_phase ^ 1u, sh, p.status, 200 + buf)) { ok = false; break; }
+                TRACE(1, ti, 1);
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)buf * BN;
                 for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+#ifdef GMM_TRACE
+                    const long long tw0 = clock64();
+#endif
                     if (!mbar_wait(&sh->full[stage], phase, sh, p.status, 300 + stage)) { ok = false; break; }
+#ifdef GMM_TRACE
+                    TRACE_ADD(1, ti, 3, clock64() - tw0);
+#endif
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(smem + stage * STAGE_BYTES);
                     const uint32_t b_addr = a_addr + A_STAGE;
@@ -814,6 +881,8 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
                 if (!ok) break;
+                TRACE(1, ti, 2);
+                TRACE_GT(0, 0, 1);
                 if (CTAS == 1) {
                     umma_commit(&sh->acc_full[buf]);
                 } else {
@@ -833,6 +902,7 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         uint8_t *my_stage = sh->out_stage[warp - 2];
         int buf = 0, it = 0;
         uint32_t acc_phase = 0;
+        int lists_done = 0, lists_total = 0;
         const uint32_t acc_empty_rank0 = CTAS == 2 ? map_to_cta(&sh->acc_empty[0], 0) : 0u;
         for (int t = unit; t < total_tiles; t += n_units, ++it) {
             const Tile tl = decode_tile(sh, t, p.n_tiles, L, C::kTileM);
@@ -871,8 +941,10 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                     if (p.logit) lg = __ldg(p.logit + grow);
                 }
             } else if (MODE != kModeSwigluQuant && SCATTER && p.out_row_index && valid) out_row = __ldg(p.out_row_index + grow);
+            if (te == 0) TRACE(2, it, 0);
             if (MODE != kModeInt32 && !mbar_wait(&sh->scale_ready[sb], (uint32_t)(it / SCALE_BUFS) & 1u, sh, p.status, 500 + sb)) break;
             if (!mbar_wait(&sh->acc_full[buf], acc_phase, sh, p.status, 400 + buf)) break;
+            if (te == 0) TRACE(2, it, 1);
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * BN;
             const float *tsc = sh->scales[sb];
@@ -880,7 +952,7 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             if (warp_has_rows) {
                 if (MODE == kModeSwigluQuant) {
                     float amax = 0.0f;
-                    float *srow = reinterpret_cast<float *>(p.out) + (size_t)grow * p.half_n;
+                    float *sout = reinterpret_cast<float *>(p.out);
 #pragma unroll 1
                     for (int c = chalf * 2; c < chalf * 2 + 2; ++c) {
                         if (n0 + c * 32 >= p.half_n) break;
@@ -890,25 +962,44 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                         tmem_ld_wait();
 #pragma unroll
                         for (int j4 = 0; j4 < 8; ++j4) {
-                            const int col = n0 + c * 32 + j4 * 4;
-                            if (col < p.half_n) {
-                                const float4 sa = *reinterpret_cast<const float4 *>(tsc + c * 32 + j4 * 4);
-                                const float4 sg = *reinterpret_cast<const float4 *>(tsc + BN / 2 + c * 32 + j4 * 4);
-                                const float sav[4] = {sa.x, sa.y, sa.z, sa.w}, sgv[4] = {sg.x, sg.y, sg.z, sg.w};
-                                float o[4];
+                            const float4 sa = *reinterpret_cast<const float4 *>(tsc + c * 32 + j4 * 4);
+                            const float4 sg = *reinterpret_cast<const float4 *>(tsc + BN / 2 + c * 32 + j4 * 4);
+                            const float sav[4] = {sa.x, sa.y, sa.z, sa.w}, sgv[4] = {sg.x, sg.y, sg.z, sg.w};
 #pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    // (acc * x_scale) * w_scale, then S = gate * (act / (1 + exp(-act)))
-                                    const float a = __fmul_rn(__fmul_rn(__int2float_rn((int)va[j4 * 4 + j]), xs), sav[j]);
-                                    const float b = __fmul_rn(__fmul_rn(__int2float_rn((int)vb[j4 * 4 + j]), xs), sgv[j]);
-                                    const float den = __fadd_rn(1.0f, expf(-a));
-                                    const float sw = __fdiv_rn(a, den);
-                                    const float sv = __fmul_rn(b, sw);
-                                    o[j] = sv;
-                                    amax = fmaxf(amax, fabsf(sv));
-                                }
-                                if (valid) *reinterpret_cast<float4 *>(srow + col) = make_float4(o[0], o[1], o[2], o[3]);
+                            for (int j = 0; j < 4; ++j) {
+                                // (acc * x_scale) * w_scale, then S = gate * (act / (1 + exp(-act)))
+                                const float a = __fmul_rn(__fmul_rn(__int2float_rn((int)va[j4 * 4 + j]), xs), sav[j]);
+                                const float b = __fmul_rn(__fmul_rn(__int2float_rn((int)vb[j4 * 4 + j]), xs), sgv[j]);
+                                const float den = __fadd_rn(1.0f, expf(-a));
+                                const float sw = __fdiv_rn(a, den);
+                                const float sv = __fmul_rn(b, sw);
+                                va[j4 * 4 + j] = __float_as_uint(sv);
+                                if (n0 + c * 32 + j4 * 4 + j < p.half_n) amax = fmaxf(amax, fabsf(sv));
                             }
+                        }
+                        // Transpose through shared memory, 16 rows per round, so that eight lanes store 128 contiguous bytes
+                        // of one row of S: a store instruction then touches 4 lines instead of 32 (the shared-memory / L1
+                        // data path is the one the tensor cores read their operands through).
+                        const int pc = lane & 7;
+                        const int col = n0 + c * 32 + pc * 4;
+#pragma unroll
+                        for (int round = 0; round < 2; ++round) {
+                            if ((lane >> 4) == round) {
+#pragma unroll
+                                for (int q8 = 0; q8 < 8; ++q8)
+                                    *reinterpret_cast<uint4 *>(my_stage + (lane & 15) * 128 + (((q8 ^ lane) & 7) << 4)) =
+                                        make_uint4(va[q8 * 4], va[q8 * 4 + 1], va[q8 * 4 + 2], va[q8 * 4 + 3]);
+                            }
+                            __syncwarp();
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int r16 = i * 4 + (lane >> 3);
+                                const int rr = quarter * 32 + round * 16 + r16;
+                                const float4 val = *reinterpret_cast<const float4 *>(my_stage + r16 * 128 + (((pc ^ r16) & 7) << 4));
+                                if (rr < my_rows && col < p.half_n)
+                                    *reinterpret_cast<float4 *>(sout + (size_t)(my_row0 + rr) * p.half_n + col) = val;
+                            }
+                            __syncwarp();
                         }
                     }
                     if (valid) atomicMax(p.amax_bits + grow, __float_as_uint(amax));
@@ -1082,6 +1173,7 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                     }
                 }
             }
+            if (te == 0) TRACE(2, it, 2);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {  // the accumulator buffer may be overwritten once every epilogue warp of the unit has read it
@@ -1092,41 +1184,67 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             if (buf == 0) acc_phase ^= 1u;
 
             if (MODE == kModeSwigluQuant) {
-                // Hand the tile to the requantising warps: they publish it and settle what falls to this CTA, while this
-                // warp goes on with the next tile.  The fence orders this thread's stores and row maxima before the
-                // arrival that the publishing thread observes.
-                const int slot = it % p.knob_depth;
+                // Tell the publishing lane that this thread's part of the tile is stored (the fence orders the stores and
+                // the row maximum before the count), then take the work list it writes for this tile.  That list comes
+                // within a few round trips to L2 (the lane waits for no other CTA) and names the row blocks that are
+                // complete by now - normally the block of this unit's previous tile, whose rows are then read while
+                // they are still in L2; one tile later they would have been evicted.
                 __threadfence();
-                if (!mbar_wait(&sh->rq_empty[slot], (((uint32_t)(it / p.knob_depth)) & 1u) ^ 1u, sh, p.status, 610 + slot)) break;
-                mbar_arrive(&sh->rq_full[slot]);
+                if (te == 0) TRACE(2, it, 3);
+                atomicAdd(&sh->stored_count, 1u);
+                if (!consume_work(p, sh, lists_done, warp - 2, lane, true)) break;
+                if (te == 0) { TRACE(2, it, 4); TRACE_ADD(2, it, 5, lists_done); }
             }
+        }
+        if (MODE == kModeSwigluQuant && !*(volatile int *)&sh->abort_flag) {
+            // one list per tile of this unit plus the closing one: wait (bounded) for those not seen yet
+            lists_total = it + 1;
+            while (lists_done < lists_total)
+                if (!consume_work(p, sh, lists_done, warp - 2, lane, true)) break;
         }
         if (SCATTER && p.num_peers > 0) __threadfence_system();  // rows stored into other GPUs' memory
     }
 
-    else if (MODE == kModeSwigluQuant && warp == 2 + EPI_WARPS) {
-        // ------------------------------ publishing warp (swiglu_quant), one lane ------------------------------
-        // Per tile of this unit, in the epilogue's order: wait until the epilogue has stored the tile, arrive at its row
-        // block, collect the row slices that fall to this CTA now (publish_and_collect) into the next work list.  After
-        // the last tile one more list takes or hands over what is still pending.  Nothing here waits for another CTA.
+    else if (MODE == kModeSwigluQuant) {
+        // ------------------------------ publishing lane (swiglu_quant) ------------------------------
+        // Per tile of this unit, in the epilogue's order: wait until every epilogue thread has stored the tile, arrive at its
+        // row block, collect the row slices that fall to this CTA now (publish_and_collect) into the next work list.  After
+        // the last tile one more list takes or hands over what is still pending.  Nothing here waits for another CTA; the
+        // only back-pressure is the ring of work lists, which the epilogue warps empty after every tile.
         if (lane == 0) {
             const int shares = p.n_tiles * CTAS;
             int it = 0;
             bool ok = true;
-            for (int t = unit; t < total_tiles; t += n_units, ++it) {
-                const int slot = it % p.knob_depth, ws = it % WK_DEPTH;
-                if (!mbar_wait(&sh->rq_full[slot], ((uint32_t)(it / p.knob_depth)) & 1u, sh, p.status, 620 + slot)) { ok = false; break; }
+            for (int t = unit; t < total_tiles && ok; t += n_units, ++it) {
+                const int ws = it % WK_DEPTH;
+                const unsigned need = (unsigned)(it + 1) * EPI_THREADS;
+                if (*(volatile unsigned *)&sh->stored_count < need) {
+                    const long long t0 = clock64();
+                    while (*(volatile unsigned *)&sh->stored_count < need) {
+                        __nanosleep(200);
+                        if (*(volatile int *)&sh->abort_flag) { ok = false; break; }
+                        if (clock64() - t0 > sh->wait_limit) {
+                            *(volatile int *)&sh->abort_flag = 1;
+                            if (atomicCAS(p.status, kStatusOk, kStatusWaitTimeout) == kStatusOk) {
+                                p.status[1] = (int)blockIdx.x;
+                                p.status[2] = 620;
+                                p.status[3] = it;
+                            }
+                            ok = false;
+                            break;
+                        }
+                    }
+                    if (!ok) break;
+                }
+                TRACE(3, it, 0);
                 if (!mbar_wait(&sh->wk_empty[ws], (((uint32_t)(it / WK_DEPTH)) & 1u) ^ 1u, sh, p.status, 630 + ws)) { ok = false; break; }
                 const Tile tl = decode_tile(sh, t, p.n_tiles, L, C::kTileM);
-                if (p.knob_spin > 0 && sh->pend_n > 0) {   // EXPERIMENT: keep the units of a wave together
-                    const int *st = p.rb_counter + 2 * sh->pend_rb[sh->pend_n - 1];
-                    const long long t0 = clock64();
-                    while ((ld_relaxed_gpu(st) & 0xffff) != shares && clock64() - t0 < p.knob_spin) {}
-                }
-                mbar_arrive(&sh->rq_empty[slot]);
+                TRACE(3, it, 1);
                 __threadfence();
                 publish_and_collect(p, sh, ws, p.rb_base + t / p.n_tiles, tl.row0, tl.rows, shares);
                 __threadfence();
+                TRACE(3, it, 2);
+                TRACE_ADD(3, it, 3, sh->n_work[ws]);
                 mbar_arrive(&sh->wk_full[ws]);
             }
             if (ok && !*(volatile int *)&sh->abort_flag) {
@@ -1137,20 +1255,6 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                     mbar_arrive(&sh->wk_full[ws]);
                 }
             }
-        }
-    } else if (MODE == kModeSwigluQuant) {
-        // ------------------------------ requantising warps (swiglu_quant) ------------------------------
-        // One work list per tile of this unit plus the closing one.
-        const int tr = (int)threadIdx.x - BASE_THREADS - 32;  // 0 .. RQ_THREADS-1
-        int it = 0;
-        bool ok = true;
-        for (int t = unit; ok; t += n_units, ++it) {
-            const int ws = it % WK_DEPTH;
-            if (!mbar_wait(&sh->wk_full[ws], ((uint32_t)(it / WK_DEPTH)) & 1u, sh, p.status, 650 + ws)) break;
-            const int n = sh->n_work[ws];
-            for (int k = 0; k < n; ++k) requant_rows(p, sh->work_begin[ws][k], sh->work_end[ws][k], tr);
-            mbar_arrive(&sh->wk_empty[ws]);
-            if (t >= total_tiles) ok = false;  // that was the closing list
         }
     }
 
@@ -1346,11 +1450,15 @@ cudaError_t sm100_launch(const Problem &p, Plan &plan, void *workspace, cudaStre
     kp.num_peers = p.mode == kModeDequantBf16 ? p.num_peers : 0;
     for (int i = 0; i < 8; ++i) kp.out_peers[i] = i < kp.num_peers ? p.out_peers[i] : nullptr;
     if (kp.num_peers > 0 && epi != kEpiScatter) return cudaErrorInvalidValue;
-    {
-        const char *e1 = getenv("GMM_KNOB_SPIN"), *e2 = getenv("GMM_KNOB_DEPTH");
-        kp.knob_spin = e1 ? atoi(e1) : 0;
-        kp.knob_depth = e2 ? atoi(e2) : RQ_DEPTH;
-        if (kp.knob_depth < 1 || kp.knob_depth > RQ_DEPTH) kp.knob_depth = RQ_DEPTH;
+    // Pacing (see the producer): needs one zeroed word per wave; the plan reserves them only where it pays.
+    kp.wave_cnt = plan.off_wave ? reinterpret_cast<int *>(ws + plan.off_wave) : nullptr;
+    kp.pace_cycles = kp.num_k_blocks * 1200 + 20000;   // about one tile's duration
+#ifdef GMM_TRACE
+    kp.trace = getenv("GMM_TRACE_PTR") ? reinterpret_cast<long long *>(strtoull(getenv("GMM_TRACE_PTR"), nullptr, 0)) : nullptr;
+#endif
+    if (const char *e = getenv("GMM_B200_PACE")) {
+        if (e[0] == '0') kp.wave_cnt = nullptr;
+        else if (atoi(e) > 1) kp.pace_cycles = atoi(e);
     }
     kp.wait_limit = p.opt.wait_limit_cycles > 0 ? p.opt.wait_limit_cycles : WAIT_LIMIT_CYCLES;
     kp.skip_k_blocks = p.opt.test_skip_k_blocks > 0 ? (p.opt.test_skip_k_blocks < kp.num_k_blocks ? p.opt.test_skip_k_blocks : kp.num_k_blocks) : 0;
@@ -1362,7 +1470,10 @@ cudaError_t sm100_launch(const Problem &p, Plan &plan, void *workspace, cudaStre
         kp.part = launches == 2 ? i + 1 : 0;
         kp.rb_base = i == 0 ? 0 : (int)((p.M + 2 * BM - 1) / (2 * BM)) + p.gl_len + 1;
         const Plan &pl = i == 0 ? plan : one;
-        if (i == 1) one.ctas = 1;
+        if (i == 1) {
+            one.ctas = 1;
+            kp.wave_cnt = nullptr;  // the pacing counters belong to the first launch
+        }
         if (p.mode == kModeSwigluQuant) e = launch_layout<kModeSwigluQuant>(p.w_layout, epi, pl, kp, stream);
         else if (p.mode == kModeInt32) e = launch_layout<kModeInt32>(p.w_layout, epi, pl, kp, stream);
         else e = launch_layout<kModeDequantBf16>(p.w_layout, epi, pl, kp, stream);
