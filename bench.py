@@ -713,6 +713,8 @@ def main():
     ap.add_argument("--no-ep", action="store_true", help="N=1: skip the one-GPU run of the expert-parallel workload")
     ap.add_argument("--ep-tokens", type=int, default=16384, help="tokens per GPU of the expert-parallel workload")
     ap.add_argument("--ep-chunks", type=int, default=0, help="token chunks pipelined against the exchange (0 = by world size)")
+    ap.add_argument("--ep-parts", type=int, default=0,
+                    help="fused variant: expert ranges per rank pipelined against the exchange (0 = default, one range)")
     ap.add_argument("--ep-reserve-sms", type=int, default=-1, help="SMs left free for the exchange kernels (-1 = automatic)")
     ap.add_argument("--ep-impl", default="fused", choices=["fused", "nccl"],
                     help="fused: rows move by peer stores inside our kernels; nccl: NCCL all-to-all around the operators")

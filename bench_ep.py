@@ -47,10 +47,15 @@ def build_ffn(args, d, tokens, world):
     from ops_transformer_b200 import ep
     if args.ep_impl == "fused":
         chunks = args.ep_chunks if args.ep_chunks > 0 else 1   # measured on 8 GPUs: 1 chunk 7.1 ms, 2 chunks 7.6 ms, 4 chunks 8.7 ms
+        parts = getattr(args, "ep_parts", 0)
+        if parts <= 0:
+            parts = 1   # expert ranges (--ep-parts 2: the second range is dispatched beside the GEMMs of the first); on 2 GPUs, where
+                        # half of the rows stay local, the split costs more than the overlap gains (6.81 vs 6.48 ms per step)
         ffn = ep.FusedExpertParallelFFN(N_EXPERTS, HIDDEN, HIDDEN, d["w1"], d["w1s"], d["w2"], d["w2s"], tokens=tokens, top_k=TOP_K,
-                                        capacity=2 * tokens * TOP_K, chunks=chunks)
+                                        capacity=2 * tokens * TOP_K, chunks=chunks, expert_parts=parts)
+        pieces = max(chunks, parts)
         return ffn, (f"dispatch by peer stores, results stored into the owners' buffers by the down-GEMM epilogue, {chunks} "
-                     "token chunk(s) with the next chunk's dispatch beside the GEMMs"), 3 * chunks
+                     f"token chunk(s), {parts} expert range(s) per rank with the next piece's dispatch beside the GEMMs"), 3 * pieces
     chunks = args.ep_chunks if args.ep_chunks > 0 else default_chunks(world)
     reserve = args.ep_reserve_sms if args.ep_reserve_sms >= 0 else (16 if world > 1 and chunks > 1 else 0)
     options = None
@@ -136,41 +141,49 @@ def verify_returned_rows(res, d, dev, world, rank, tokens, experts_checked=4, ro
     O.build()
     O.use_all_cores()
     chunks = res["chunks"] if isinstance(res, dict) else res
-    if len(chunks) != 1:
-        return {"rows": 0, "mismatches": 0, "note": "row check needs a single token chunk"}
-    plan = chunks[0]["plan"]
-    y = chunks[0]["y"]
     topk_flat = d["topk"].reshape(-1)
-    order = plan.order.to(torch.int64)
-    src_token = plan.src_token.to(torch.int64)
-    expert_of_row = topk_flat[order]                               # global expert of every send row (rows are grouped by expert)
     owner = (rank + 1) % world
     e_local = N_EXPERTS // world
     dw = d if owner == rank else make_rank_data(dev, world, owner, tokens)   # the owner's weights, from their seed
     rng = np.random.default_rng(seed + rank)
     local_ids = sorted(set([0, e_local - 1] + [int(v) for v in rng.integers(0, e_local, size=max(experts_checked - 2, 0))]))
-    sel_rows, sel_counts = [], []
+    # every piece (token chunk or expert range) holds its own send order and result rows
+    pieces = []
+    tok_off = 0
+    for ch in chunks:
+        plan = ch["plan"]
+        order = plan.order.to(torch.int64)
+        n_use = int(ch["rows_in_use"].item()) if "rows_in_use" in ch else int(order.shape[0])
+        if isinstance(res, dict):
+            pair, tok = order[:n_use], plan.src_token.to(torch.int64)[:n_use]
+        else:   # the NCCL variant numbers pairs and tokens inside its token chunk
+            pair, tok = order[:n_use] + tok_off * TOP_K, plan.src_token.to(torch.int64)[:n_use] + tok_off
+            tok_off += int(ch.get("tokens", 0))
+        pieces.append((topk_flat[pair], tok, ch["y"]))           # global expert of every send row, its token, the results
+    sel_x, sel_xs, sel_y, sel_counts = [], [], [], []
     for le in local_ids:
-        pos = torch.nonzero(expert_of_row == owner * e_local + le).reshape(-1)
-        if pos.numel() == 0:
-            sel_counts.append(0)
-            continue
-        n = int(pos.numel())
-        pick = sorted(set([0, n - 1] + [int(v) for v in rng.integers(0, n, size=rows_per_expert)]))
-        sel_rows.append(pos[torch.tensor(pick, device=pos.device)])
-        sel_counts.append(len(pick))
+        n_le = 0
+        for expert_of_row, tok, y in pieces:
+            pos = torch.nonzero(expert_of_row == owner * e_local + le).reshape(-1)
+            if pos.numel() == 0:
+                continue
+            n = int(pos.numel())
+            pick = sorted(set([0, n - 1] + [int(v) for v in rng.integers(0, n, size=rows_per_expert)]))
+            pos = pos[torch.tensor(pick, device=pos.device)]
+            sel_x.append(d["x"][tok[pos]]); sel_xs.append(d["xs"][tok[pos]]); sel_y.append(y[pos])
+            n_le += len(pick)
+        sel_counts.append(n_le)
+    sel_rows = sel_x
     if not sel_rows:
         return {"rows": 0, "mismatches": 0, "note": "no rows for the sampled experts"}
-    sel = torch.cat(sel_rows)
-    tok = src_token[sel]
-    x_rows = d["x"][tok].cpu().numpy()
-    xs_rows = d["xs"][tok].cpu().numpy()
+    x_rows = torch.cat(sel_x).cpu().numpy()
+    xs_rows = torch.cat(sel_xs).cpu().numpy()
     idx = torch.tensor(local_ids, device=dev)
     w1 = dw["w1"][idx].cpu().numpy(); w1s = dw["w1s"][idx].cpu().numpy()
     w2 = dw["w2"][idx].cpu().numpy(); w2s = dw["w2s"][idx].cpu().numpy()
     gl = np.cumsum(np.asarray(sel_counts, np.int64))
     r1 = O.swiglu_quant(x_rows, w1, w1s, xs_rows, gl)
-    got = y[sel].view(torch.int16).cpu().numpy().view(np.uint16)
+    got = torch.cat(sel_y).view(torch.int16).cpu().numpy().view(np.uint16)
     out = SC.check_gmm_rows(r1["q"], w2, w2s, r1["q_scale"], np.asarray(sel_counts, np.int64), got)
     out["experts_of_rank"] = owner
     del dw

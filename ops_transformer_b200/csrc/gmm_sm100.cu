@@ -851,13 +851,7 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)buf * BN;
                 for (int kb = 0; kb < p.num_k_blocks; ++kb) {
-#ifdef GMM_TRACE
-                    const long long tw0 = clock64();
-#endif
                     if (!mbar_wait(&sh->full[stage], phase, sh, p.status, 300 + stage)) { ok = false; break; }
-#ifdef GMM_TRACE
-                    TRACE_ADD(1, ti, 3, clock64() - tw0);
-#endif
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(smem + stage * STAGE_BYTES);
                     const uint32_t b_addr = a_addr + A_STAGE;

@@ -140,7 +140,7 @@ class ExpertParallelFFN:
                 group_list = torch.cumsum(p.send_counts.reshape(-1), 0).to(torch.int64)
                 y = self.compute(sx, ss, group_list, None)
                 t = self._tick("gemms", t)
-                results.append({"y": y, "plan": p, "rows_computed": int(sx.shape[0])})
+                results.append({"y": y, "plan": p, "rows_computed": int(sx.shape[0]), "tokens": bounds[c + 1] - bounds[c]})
             return results
 
         # counts of all chunks in one small exchange; the split sizes are needed on the host
@@ -199,7 +199,8 @@ class ExpertParallelFFN:
                 w3.wait()
             t = self._tick("a2a_return", t)
             returns.append(w3)
-            results.append({"y": out, "plan": p, "rows_computed": n_rows, "keep": (y_back, sx, ss, xs_sorted, ss_sorted)})
+            results.append({"y": out, "plan": p, "rows_computed": n_rows, "tokens": bounds[c + 1] - bounds[c],
+                            "keep": (y_back, sx, ss, xs_sorted, ss_sorted)})
         for c, w in enumerate(returns):
             if w is not None:
                 w.wait()
@@ -271,6 +272,11 @@ class FusedExpertParallelFFN:
          down projection's epilogue stores each result row into the buffer of the GPU that sent the token,
       4. a second barrier; every rank then finds its results, in send order, in its own result buffer.
 
+    Two ways to overlap the exchange with the GEMMs, both as "pieces" whose dispatch runs on a second stream beside the
+    GEMMs of the piece before: ``chunks`` splits the tokens (rows per expert shrink with it, which costs tile efficiency),
+    ``expert_parts`` splits every rank's experts into ranges (groups keep their length: piece p holds the pairs routed to
+    the p-th range of local experts of every rank, its rows are dispatched while the GEMMs of range p-1 run).
+
     Nothing is read back to the host during a step.  Buffers are sized for `capacity` received rows per rank; rows
     beyond it are dropped and counted, so capacity must cover the worst expected imbalance.  The reference's dispatch is
     dropless in this mode, so a caller must read the counter: every result dict carries it as ``dropped_rows`` (an int32
@@ -278,9 +284,10 @@ class FusedExpertParallelFFN:
     """
 
     def __init__(self, n_experts: int, hidden: int, hidden_out: int, w1, w1_scale, w2, w2_scale, *, tokens: int, top_k: int,
-                 capacity: int, group=None, chunks: int = 1):
-        """capacity: rows this rank can receive per step (all chunks together).  chunks > 1 splits the tokens; the
-        dispatch of chunk c+1 then runs on a second stream beside the GEMMs of chunk c."""
+                 capacity: int, group=None, chunks: int = 1, expert_parts: int = 1):
+        """capacity: rows this rank can receive per step (all pieces together).  chunks > 1 splits the tokens,
+        expert_parts > 1 the local experts of every rank (not both); the dispatch of piece c+1 then runs on a second
+        stream beside the GEMMs of piece c."""
         import ctypes as C
 
         from .peer import PeerBuffer
@@ -290,18 +297,39 @@ class FusedExpertParallelFFN:
         self.n_experts, self.e_local = n_experts, n_experts // self.world
         self.hidden, self.hidden_out = hidden, hidden_out
         self.w1, self.w1_scale, self.w2, self.w2_scale = w1, w1_scale, w2, w2_scale
-        self.tokens, self.top_k, self.chunks = tokens, top_k, chunks
-        self.bounds = [tokens * c // chunks for c in range(chunks + 1)]
+        self.tokens, self.top_k = tokens, top_k
+        self.parts = expert_parts
+        if expert_parts > 1:
+            if chunks != 1 or self.e_local % expert_parts:
+                raise ValueError("expert_parts needs chunks == 1 and a number of local experts it divides")
+            chunks = expert_parts                               # one piece per expert range
+        self.chunks = chunks
         self.n_send = tokens * top_k
+        if self.parts > 1:
+            # every piece sees all tokens; its pairs are those routed to its expert range, at most all of them
+            self.bounds = [0] * (chunks + 1)
+            self.e_piece = self.e_local // self.parts           # local experts per piece
+            self.piece_pairs = [self.n_send] * chunks
+            self.token_base = [0] * chunks
+            self.result_base = [c * self.n_send for c in range(chunks)]
+            result_rows = chunks * self.n_send
+        else:
+            self.bounds = [tokens * c // chunks for c in range(chunks + 1)]
+            self.e_piece = self.e_local
+            self.piece_pairs = [(self.bounds[c + 1] - self.bounds[c]) * top_k for c in range(chunks)]
+            self.token_base = self.bounds[:-1]
+            self.result_base = [self.bounds[c] * top_k for c in range(chunks)]
+            result_rows = self.n_send
+        self.result_rows = result_rows
         self.capacity = capacity
-        self.cap_c = (capacity + chunks - 1) // chunks          # rows per chunk buffer
+        self.cap_c = (capacity + chunks - 1) // chunks          # rows per piece buffer
         self.buf_x = PeerBuffer(chunks * self.cap_c * hidden, group)
         self.buf_s = PeerBuffer(chunks * self.cap_c * 4, group)
-        self.buf_y = PeerBuffer(self.n_send * hidden_out * 2, group)
+        self.buf_y = PeerBuffer(result_rows * hidden_out * 2, group)
         dev = torch.device("cuda", torch.cuda.current_device())
         self.act = self.buf_x.view(torch.int8, (chunks, self.cap_c, hidden))
         self.act_scale = self.buf_s.view(torch.float32, (chunks, self.cap_c))
-        self.result = self.buf_y.view(torch.bfloat16, (self.n_send, hidden_out))
+        self.result = self.buf_y.view(torch.bfloat16, (result_rows, hidden_out))
         # per chunk: every rank's activation / scale buffer of that chunk
         self._x_ptrs = [(C.c_void_p * self.world)(*[C.c_void_p(p + c * self.cap_c * hidden) for p in self.buf_x.ptrs])
                         for c in range(chunks)]
@@ -315,12 +343,12 @@ class FusedExpertParallelFFN:
         i64 = dict(dtype=torch.int64, device=dev)
         self._r = []
         for c in range(chunks):
-            n_c = (self.bounds[c + 1] - self.bounds[c]) * top_k
-            self._r.append(dict(n=n_c, hist=torch.empty(((n_c + 1023) // 1024, n_experts), dtype=torch.int32, device=dev),
-                                src_token=torch.empty(n_c, **i64), order=torch.empty(n_c, **i64), send_dest=torch.empty(n_c, **i64),
-                                ret_dest=torch.empty(self.cap_c, **i64), group_list=torch.empty(self.e_local, **i64),
+            n_c = self.piece_pairs[c]
+            self._r.append(dict(n=n_c, hist=torch.empty(((n_c + 1023) // 1024, self.world * self.e_piece), dtype=torch.int32, device=dev),
+                                src_token=torch.zeros(n_c, **i64), order=torch.zeros(n_c, **i64), send_dest=torch.empty(n_c, **i64),
+                                ret_dest=torch.empty(self.cap_c, **i64), group_list=torch.empty(self.e_piece, **i64),
                                 first_row=torch.empty(1, **i64)))
-        self._totals = torch.empty((chunks, self.world, self.e_local), **i64)
+        self._totals = torch.empty((chunks, self.world, self.e_piece), **i64)
         self._side = torch.cuda.Stream() if chunks > 1 else None
         self._graph = None
         self.trace = None   # set to a list to collect (label, CUDA event) marks without synchronising
@@ -356,6 +384,8 @@ class FusedExpertParallelFFN:
         self._mark("start")
         if self.route_kernels:
             return self._forward_kernels(x, x_scale, topk_ids)
+        if self.parts > 1:
+            raise ValueError("expert_parts needs the routing kernels (route_kernels = True)")
         # routing plans and row maps of all chunks first (small kernels), one count exchange for all chunks
         plans = [dispatch_plan(topk_ids[self.bounds[c]:self.bounds[c + 1]], self.n_experts, G) for c in range(C_)]
         self._mark("plan")
@@ -401,7 +431,7 @@ class FusedExpertParallelFFN:
             q, qs = acl.grouped_matmul_swiglu_quant(self.act[c], self.w1, self.w1_scale, self.act_scale[c], group_list)
             self._mark(f"swiglu_quant{c}")
             acl.grouped_matmul_v4(q, self.w2, self.w2_scale, qs, group_list, group_list_type=0, out_row_index=ret_dest,
-                                  out_peers=self.buf_y.ptrs, out=None, out_rows=self.n_send)
+                                  out_peers=self.buf_y.ptrs, out=None, out_rows=self.result_rows)
             self._mark(f"down_gemm{c}")
             group_lists.append(group_list)
         self._barrier()   # every rank's results have landed, and everyone is done reading its activation buffers
@@ -420,24 +450,36 @@ class FusedExpertParallelFFN:
         p = lambda t: C.c_void_p(t.data_ptr())  # noqa: E731
         st = lambda: C.c_void_p(torch.cuda.current_stream().cuda_stream)  # noqa: E731
         topk_ids = topk_ids.contiguous()
-        tk = [topk_ids[self.bounds[c]:self.bounds[c + 1]] for c in range(C_)]
+        Ep = self.e_piece
+        if self.parts > 1:
+            # piece c = the pairs routed to local experts [c*Ep, (c+1)*Ep) of any rank, renumbered rank*Ep + (local - c*Ep);
+            # the other pairs read as -1, which the count and route kernels skip
+            flat = topk_ids.reshape(-1)
+            owner, local = flat // E, flat % E
+            piece_of = local // Ep
+            renum = owner * Ep + (local - piece_of * Ep)
+            tk = [torch.where(piece_of == c, renum, torch.full_like(renum, -1)) for c in range(C_)]
+        else:
+            tk = [topk_ids[self.bounds[c]:self.bounds[c + 1]] for c in range(C_)]
         for c in range(C_):
-            rc = L.gmmB200EpCount(p(tk[c]), self._r[c]["n"], self.n_experts, p(self._r[c]["hist"]), p(self._totals[c]), st())
+            rc = L.gmmB200EpCount(p(tk[c]), self._r[c]["n"], G * Ep, p(self._r[c]["hist"]), p(self._totals[c]), st())
             if rc != 0:
                 raise acl.AclnnError(rc, "gmmB200EpCount")
         self._mark("plan")
         if G > 1:
-            allc = torch.empty((G, C_, G, E), dtype=torch.int64, device=x.device)
+            allc = torch.empty((G, C_, G, Ep), dtype=torch.int64, device=x.device)
             dist.all_gather_into_tensor(allc, self._totals, group=self.group)
         else:
-            allc = self._totals.reshape(1, C_, 1, E)
+            allc = self._totals.reshape(1, C_, 1, Ep)
         self._mark("counts_gathered")
         plans = []
         for c in range(C_):
             r = self._r[c]
             ac = allc[:, c].contiguous()
-            rc = L.gmmB200EpRoute(p(tk[c]), p(r["hist"]), p(ac), r["n"], k, G, E, self.rank, self.cap_c, self.bounds[c],
-                                  self.bounds[c] * k, p(r["src_token"]), p(r["order"]), p(r["send_dest"]), p(r["ret_dest"]),
+            if self.parts > 1:
+                r["send_dest"].fill_(-1)   # positions beyond the piece's pairs must read as "no row"
+            rc = L.gmmB200EpRoute(p(tk[c]), p(r["hist"]), p(ac), r["n"], k, G, Ep, self.rank, self.cap_c, self.token_base[c],
+                                  self.result_base[c], p(r["src_token"]), p(r["order"]), p(r["send_dest"]), p(r["ret_dest"]),
                                   p(r["group_list"]), p(r["first_row"]), st())
             if rc != 0:
                 raise acl.AclnnError(rc, "gmmB200EpRoute")
@@ -461,15 +503,19 @@ class FusedExpertParallelFFN:
                     self._barrier()
                     landed[c + 1] = torch.cuda.Event()
                     landed[c + 1].record()
-            q, qs = acl.grouped_matmul_swiglu_quant(self.act[c], self.w1, self.w1_scale, self.act_scale[c], r["group_list"])
+            e0, e1 = (c * Ep, (c + 1) * Ep) if self.parts > 1 else (0, E)
+            q, qs = acl.grouped_matmul_swiglu_quant(self.act[c], self.w1[e0:e1], self.w1_scale[e0:e1], self.act_scale[c], r["group_list"])
             self._mark(f"swiglu_quant{c}")
-            acl.grouped_matmul_v4(q, self.w2, self.w2_scale, qs, r["group_list"], group_list_type=0, out_row_index=r["ret_dest"],
-                                  out_peers=self.buf_y.ptrs, out=None, out_rows=self.n_send)
+            acl.grouped_matmul_v4(q, self.w2[e0:e1], self.w2_scale[e0:e1], qs, r["group_list"], group_list_type=0,
+                                  out_row_index=r["ret_dest"], out_peers=self.buf_y.ptrs, out=None, out_rows=self.result_rows)
             self._mark(f"down_gemm{c}")
         self._barrier()   # every rank's results have landed, and everyone is done reading its activation buffers
         self._mark("barrier2")
         group_lists = [self._r[c]["group_list"] for c in range(C_)]
-        chunk_out = [{"y": self.result[self.bounds[c] * k:self.bounds[c + 1] * k], "plan": plans[c]} for c in range(C_)]
+        # per piece: its result rows (in its send order), the plan, and how many of the rows are in use (a device scalar;
+        # with expert_parts a piece holds only the pairs routed to its expert range)
+        chunk_out = [{"y": self.result[self.result_base[c]:self.result_base[c] + self.piece_pairs[c]], "plan": plans[c],
+                      "rows_in_use": self._totals[c].sum()} for c in range(C_)]
         return {"y": self.result, "plan": plans[0], "group_list": group_lists[0], "group_lists": group_lists, "chunks": chunk_out,
                 "dropped_rows": self.overflow}
 

@@ -64,17 +64,41 @@ def test_single_rank_ffn_matches_oracle(oracle, chunks):
     _check(oracle, res, chunks, x, xs, topk, w1, s1, w2, s2)
 
 
-def _run_fused(O, dev, rank, world, w1, s1, w2, s2, x, xs, topk, chunks=1, route_kernels=True):
+def _check_parts(O, res, x, xs, topk, w1, s1, w2, s2):
+    """Expert-range pieces: every piece holds, in its own send order, the pairs routed to its range of local experts."""
+    seen = 0
+    for ch in res["chunks"]:
+        n = int(ch["rows_in_use"].item())
+        order = ch["plan"].order.cpu().numpy()[:n]
+        tok = ch["plan"].src_token.cpu().numpy()[:n]
+        experts = topk.reshape(-1)[order]
+        assert (tok == order // TOP_K).all() and (np.diff(experts) >= 0).all()
+        gl = np.cumsum(np.bincount(experts, minlength=N_EXPERTS))
+        q = O.swiglu_quant(x[tok], w1, s1, xs[tok], gl)
+        exp = O.gmm_w8a8(q["q"], w2, s2, q["q_scale"], gl, 0)["y"]
+        got = ch["y"][:n].view(torch.int16).cpu().numpy().view(np.uint16)
+        a, b = O.bf16_bits_to_f32(got), O.bf16_bits_to_f32(exp)
+        bad = np.abs(a - b) > 1e-2 + 4e-3 * np.abs(b)
+        assert bad.mean() < 1e-3 and (got == exp).mean() > 0.995
+        seen += n
+    assert seen == T * TOP_K, "the pieces together hold every (token, slot) pair once"
+
+
+def _run_fused(O, dev, rank, world, w1, s1, w2, s2, x, xs, topk, chunks=1, route_kernels=True, parts=1):
     el = N_EXPERTS // world
     lo, hi = rank * el, (rank + 1) * el
     t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)  # noqa: E731
     ffn = ep.FusedExpertParallelFFN(N_EXPERTS, H, H, t(w1[lo:hi]), t(s1[lo:hi]), t(w2[lo:hi]), t(s2[lo:hi]), tokens=T, top_k=TOP_K,
-                                    capacity=2 * T * TOP_K, chunks=chunks)
+                                    capacity=2 * T * TOP_K, chunks=chunks, expert_parts=parts)
     ffn.route_kernels = route_kernels
     for _ in range(2):  # twice: the second step runs over the first one's buffers
         res = ffn.forward(t(x), t(xs), t(topk))
     torch.cuda.synchronize()
     assert int(ffn.overflow.item()) == 0
+    if parts > 1:
+        _check_parts(O, res, x, xs, topk, w1, s1, w2, s2)
+        ffn.close()
+        return
     outs = []
     for c, ch in enumerate(res["chunks"]):  # _check expects chunk-local token numbers in the plan
         pl = ch["plan"]
@@ -98,6 +122,15 @@ def test_single_rank_fused_ffn_matches_oracle(oracle, chunks):
     _run_fused(oracle, torch.device("cuda:0"), 0, 1, w1, s1, w2, s2, x, xs, topk, chunks=chunks, route_kernels=False)
 
 
+@pytest.mark.parametrize("parts", [2, 4])
+def test_single_rank_fused_ffn_expert_ranges(oracle, parts):
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    w1, w2, s1, s2 = _weights()
+    x, xs, topk = _inputs(0)
+    _run_fused(oracle, torch.device("cuda:0"), 0, 1, w1, s1, w2, s2, x, xs, topk, parts=parts)
+
+
 def _rank_main():
     import torch.distributed as dist
     from oracle import oracle as O
@@ -118,6 +151,7 @@ def _rank_main():
     _run_fused(O, dev, rank, world, w1, s1, w2, s2, x, xs, topk)
     _run_fused(O, dev, rank, world, w1, s1, w2, s2, x, xs, topk, chunks=2)
     _run_fused(O, dev, rank, world, w1, s1, w2, s2, x, xs, topk, route_kernels=False)
+    _run_fused(O, dev, rank, world, w1, s1, w2, s2, x, xs, topk, parts=2)
     dist.barrier()
     dist.destroy_process_group()
     print(f"rank {rank} ok")
