@@ -652,11 +652,30 @@ __device__ void publish_and_collect(const KParams &p, Shared *sh, int ws, int rb
     sh->pend_rb[k] = rb; sh->pend_row0[k] = row0; sh->pend_rows[k] = rows;
 }
 
-// Publishing lane, after the CTA's last tile: every block still pending is taken (if complete) or handed over.
-__device__ void release_pending(const KParams &p, Shared *sh, int ws, int shares)
+// Publishing lane, after the CTA's last tile: every block still pending is taken once it is complete.  The other units
+// are finishing at the same time, so the lane first looks on for up to `patience` cycles (nothing else is left to do;
+// handing the share over at once would leave the last arrival of every block of the final wave with all of its slices,
+// a serial tail of tens of microseconds); what is still incomplete after that is handed over, so the kernel never
+// depends on the other CTAs being resident.
+__device__ void release_pending(const KParams &p, Shared *sh, int ws, int shares, long long patience)
 {
     sh->n_work[ws] = 0;
     int *state = p.rb_counter;
+    const long long t0 = clock64();
+    while (sh->pend_n > 0) {
+        int n = 0;
+        for (int i = 0; i < sh->pend_n; ++i) {
+            if ((ld_relaxed_gpu(state + 2 * sh->pend_rb[i]) & 0xffff) == shares) {
+                add_work(sh, ws, sh->pend_row0[i], sh->pend_rows[i], atomicAdd(state + 2 * sh->pend_rb[i] + 1, 1), 1, shares);
+            } else {
+                sh->pend_rb[n] = sh->pend_rb[i]; sh->pend_row0[n] = sh->pend_row0[i]; sh->pend_rows[n] = sh->pend_rows[i];
+                ++n;
+            }
+        }
+        sh->pend_n = n;
+        if (n == 0 || clock64() - t0 > patience) break;
+        __nanosleep(500);
+    }
     for (int i = 0; i < sh->pend_n; ++i) {
         const int o = atomicAdd(state + 2 * sh->pend_rb[i], 1 << 16);
         if ((o & 0xffff) == shares)
@@ -1244,7 +1263,7 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             if (ok && !*(volatile int *)&sh->abort_flag) {
                 const int ws = it % WK_DEPTH;
                 if (mbar_wait(&sh->wk_empty[ws], (((uint32_t)(it / WK_DEPTH)) & 1u) ^ 1u, sh, p.status, 640 + ws)) {
-                    release_pending(p, sh, ws, shares);
+                    release_pending(p, sh, ws, shares, 2ll * p.pace_cycles);
                     __threadfence();
                     mbar_arrive(&sh->wk_full[ws]);
                 }
