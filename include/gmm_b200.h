@@ -95,11 +95,13 @@ ACL_FUNC_VISIBILITY aclnnStatus gmmB200PeerRelease(void *devPtr);
  * destination is beyond `capacity` are dropped and counted in *overflowCounter (int32 on the device, cleared by the
  * caller).  firstRow (optional, int64 on the device): the send row the kernel starts with, wrapping around; giving every
  * rank the first row of a different destination keeps the ranks from all storing into one GPU at a time.
+ * maxBlocks (0 = no cap): most blocks of 256 threads the kernel launches; 8 fit an SM, so 8 * s keeps it on about s SMs
+ * when it runs beside a GEMM whose CTAs were capped accordingly (gmmB200LaunchOptions.maxCtas).
  * The caller orders the GPUs (a barrier) before the receivers read. */
 ACL_FUNC_VISIBILITY aclnnStatus gmmB200EpDispatch(const void *x, const void *xScale, const void *srcToken, const void *dest,
                                                  int64_t rows, int64_t hidden, int64_t capacity, void *const *peerX,
                                                  void *const *peerScale, int32_t numPeers, void *overflowCounter,
-                                                 const void *firstRow, aclrtStream stream);
+                                                 const void *firstRow, int32_t maxBlocks, aclrtStream stream);
 
 /* Routing for the expert-parallel dispatch, in two launches around the all-gather of the per-expert counts, without any
  * read on the host.  topk: int64 [nPairs] global expert of every (token, slot) pair (pair i belongs to token i / topK).

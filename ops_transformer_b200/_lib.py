@@ -102,7 +102,7 @@ def _load():
     L.gmmB200PeerExport.argtypes = [p, p]
     L.gmmB200PeerImport.argtypes = [p, C.POINTER(p)]
     L.gmmB200PeerRelease.argtypes = [p]
-    L.gmmB200EpDispatch.argtypes = [p, p, p, p, i64, i64, i64, C.POINTER(p), C.POINTER(p), i32, p, p, p]
+    L.gmmB200EpDispatch.argtypes = [p, p, p, p, i64, i64, i64, C.POINTER(p), C.POINTER(p), i32, p, p, i32, p]
     L.gmmB200EpCount.argtypes = [p, i64, i32, p, p, p]
     L.gmmB200EpRoute.argtypes = [p, p, p, i64, i32, i32, i32, i32, i64, i64, i64, p, p, p, p, p, p, p]
     L.gmmB200NoAllocScratchBytes.restype = u64

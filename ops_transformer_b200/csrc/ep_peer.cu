@@ -247,7 +247,7 @@ aclnnStatus gmmB200PeerRelease(void *devPtr)
 
 aclnnStatus gmmB200EpDispatch(const void *x, const void *xScale, const void *srcToken, const void *dest, int64_t rows,
                               int64_t hidden, int64_t capacity, void *const *peerX, void *const *peerScale, int32_t numPeers,
-                              void *overflowCounter, const void *firstRow, aclrtStream stream)
+                              void *overflowCounter, const void *firstRow, int32_t maxBlocks, aclrtStream stream)
 {
     gmm::clear_error();
     if (!x || !xScale || !srcToken || !dest || !peerX || !peerScale || !overflowCounter)
@@ -265,7 +265,8 @@ aclnnStatus gmmB200EpDispatch(const void *x, const void *xScale, const void *src
     }
     int sms = gmm::device_sm_count();
     if (sms <= 0) sms = 148;
-    const int grid = (int)std::min<int64_t>((rows + 7) / 8, (int64_t)sms * 8);
+    int grid = (int)std::min<int64_t>((rows + 7) / 8, (int64_t)sms * 8);
+    if (maxBlocks > 0 && grid > maxBlocks) grid = maxBlocks;   // leave the other SMs to a GEMM running beside the dispatch
     ep_dispatch_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const int8_t *>(x), static_cast<const float *>(xScale), static_cast<const long long *>(srcToken),
         static_cast<const long long *>(dest), rows, (int)hidden, capacity, pp, numPeers, static_cast<int *>(overflowCounter),

@@ -284,10 +284,14 @@ class FusedExpertParallelFFN:
     """
 
     def __init__(self, n_experts: int, hidden: int, hidden_out: int, w1, w1_scale, w2, w2_scale, *, tokens: int, top_k: int,
-                 capacity: int, group=None, chunks: int = 1, expert_parts: int = 1):
+                 capacity: int, group=None, chunks: int = 1, expert_parts: int = 1, reserve_sms: int = 0):
         """capacity: rows this rank can receive per step (all pieces together).  chunks > 1 splits the tokens,
         expert_parts > 1 the local experts of every rank (not both); the dispatch of piece c+1 then runs on a second
-        stream beside the GEMMs of piece c."""
+        stream beside the GEMMs of piece c.  reserve_sms > 0: with expert_parts, the SMs that dispatch is confined to, the
+        gate/up GEMM running beside it being capped to the others.  Measured: neither form of the overlap pays on this
+        hardware (8 GPUs: 9.1 ms per step with two expert ranges against 6.75 ms with one; 2 GPUs: 6.8 ms, with 16 reserved
+        SMs 9.4 ms, against 6.5 ms) - the dispatch kernel and the persistent GEMM queue for the same SMs, and a dispatch
+        confined to a few SMs cannot keep NVLink busy - so one piece is the default."""
         import ctypes as C
 
         from .peer import PeerBuffer
@@ -298,6 +302,7 @@ class FusedExpertParallelFFN:
         self.hidden, self.hidden_out = hidden, hidden_out
         self.w1, self.w1_scale, self.w2, self.w2_scale = w1, w1_scale, w2, w2_scale
         self.tokens, self.top_k = tokens, top_k
+        self.reserve_sms = reserve_sms
         self.parts = expert_parts
         if expert_parts > 1:
             if chunks != 1 or self.e_local % expert_parts:
@@ -365,7 +370,7 @@ class FusedExpertParallelFFN:
         if self.world > 1:
             dist.all_reduce(self._token, group=self.group)
 
-    def _dispatch(self, c, x, x_scale, plan, send_dest, first_row):
+    def _dispatch(self, c, x, x_scale, plan, send_dest, first_row, max_blocks=0):
         import ctypes as C
 
         from . import _lib, acl
@@ -373,7 +378,8 @@ class FusedExpertParallelFFN:
         stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
         n = int(plan.src_token.shape[0])
         rc = _lib.lib().gmmB200EpDispatch(p(x), p(x_scale), p(plan.src_token), p(send_dest), n, self.hidden, self.cap_c,
-                                          self._x_ptrs[c], self._s_ptrs[c], self.world, p(self.overflow), p(first_row), stream)
+                                          self._x_ptrs[c], self._s_ptrs[c], self.world, p(self.overflow), p(first_row),
+                                          max_blocks, stream)
         if rc != 0:
             raise acl.AclnnError(rc, "gmmB200EpDispatch")
 
@@ -496,15 +502,22 @@ class FusedExpertParallelFFN:
                 self._mark("barrier1")
             else:
                 main.wait_event(landed[c])
+            beside = None
             if c + 1 < C_:
+                cap = self.parts > 1 and self.reserve_sms > 0
                 self._side.wait_stream(main)
                 with torch.cuda.stream(self._side):
-                    self._dispatch(c + 1, x, x_scale, plans[c + 1], self._r[c + 1]["send_dest"], self._r[c + 1]["first_row"])
+                    self._dispatch(c + 1, x, x_scale, plans[c + 1], self._r[c + 1]["send_dest"], self._r[c + 1]["first_row"],
+                                   max_blocks=8 * self.reserve_sms if cap else 0)
                     self._barrier()
                     landed[c + 1] = torch.cuda.Event()
                     landed[c + 1].record()
+                if cap:
+                    n_sm = torch.cuda.get_device_properties(x.device).multi_processor_count
+                    beside = acl.LaunchOptions(max_ctas=max(2, n_sm - self.reserve_sms))
             e0, e1 = (c * Ep, (c + 1) * Ep) if self.parts > 1 else (0, E)
-            q, qs = acl.grouped_matmul_swiglu_quant(self.act[c], self.w1[e0:e1], self.w1_scale[e0:e1], self.act_scale[c], r["group_list"])
+            q, qs = acl.grouped_matmul_swiglu_quant(self.act[c], self.w1[e0:e1], self.w1_scale[e0:e1], self.act_scale[c], r["group_list"],
+                                                    options=beside)
             self._mark(f"swiglu_quant{c}")
             acl.grouped_matmul_v4(q, self.w2[e0:e1], self.w2_scale[e0:e1], qs, r["group_list"], group_list_type=0,
                                   out_row_index=r["ret_dest"], out_peers=self.buf_y.ptrs, out=None, out_rows=self.result_rows)

@@ -104,7 +104,7 @@ def test_dispatch_skips_and_counts_rows_with_a_bad_destination():
     overflow = torch.zeros(1, dtype=torch.int32, device=dev)
     px, ps = (C.c_void_p * 1)(bx.data_ptr()), (C.c_void_p * 1)(bs.data_ptr())
     p = lambda t: C.c_void_p(t.data_ptr())  # noqa: E731
-    rc = L.gmmB200EpDispatch(p(x), p(xs), p(src), p(dest), rows, hidden, cap, px, ps, 1, p(overflow), None,
+    rc = L.gmmB200EpDispatch(p(x), p(xs), p(src), p(dest), rows, hidden, cap, px, ps, 1, p(overflow), None, 0,
                              C.c_void_p(torch.cuda.current_stream().cuda_stream))
     assert rc == 0, _lib.last_error()
     torch.cuda.synchronize()
