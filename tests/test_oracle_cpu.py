@@ -315,3 +315,51 @@ def test_golden_fixtures(oracle):
         else:
             r = oracle.swiglu_quant(x, w, ws, xs, gl)
             assert np.array_equal(r["q"], d["q"]) and np.array_equal(r["q_scale"], d["q_scale"])
+
+
+# ---------------------------------------------------------------------------------------------------------
+# Row-sampled checks of full-size launches (oracle/sampled_check.py): the sampling itself and the row-independence
+# the method rests on
+# ---------------------------------------------------------------------------------------------------------
+
+def test_sample_rows_covers_edges_of_every_expert():
+    from oracle import sampled_check as SC
+    counts = np.array([300, 0, 1, 513, 129], np.int64)
+    rows = SC.sample_rows(counts, n_random=4, seed=3)
+    starts = np.concatenate([[0], np.cumsum(counts)[:-1]])
+    assert (np.diff(rows) > 0).all() and rows.min() >= 0 and rows.max() < counts.sum()
+    for s, r in zip(starts, counts):
+        if r == 0:
+            continue
+        must = {s, s + r - 1} | {s + m + d for m in range(128, r, 128) for d in (-1, 0)}
+        assert must <= set(rows.tolist())
+    assert (SC.counts_of_sample(rows, counts) <= counts).all() and SC.counts_of_sample(rows, counts).sum() == len(rows)
+    assert (SC.counts_of_sample(rows, counts)[[1]] == 0).all()
+    # few rows: everything is taken
+    assert np.array_equal(SC.sample_rows([3, 0, 5], max_rows_all=16), np.arange(8))
+
+
+def test_oracle_on_sampled_rows_equals_sampled_rows_of_the_oracle(oracle):
+    """Both operators treat every row on its own: the oracle on a subset of rows (same weights) reproduces those rows."""
+    from oracle import sampled_check as SC
+    from ops_transformer_b200 import synth
+    counts = np.array([70, 0, 33, 140], np.int64)
+    M, K, N, E = int(counts.sum()), 96, 64, 4
+    x, w = synth.int8_tensor((M, K), 7, 1), synth.int8_tensor((E, K, N), 7, 2)
+    ws, xs = synth.scale_tensor((E, N), 7, 3), synth.scale_tensor((M,), 7, 4)
+    gl = np.cumsum(counts)
+    full_s = oracle.swiglu_quant(x, w, ws, xs, gl)
+    full_g = oracle.gmm_w8a8(x, w, ws, xs, gl, 0)["y"]
+    rows = SC.sample_rows(counts, n_random=5, seed=1)
+    sc = SC.counts_of_sample(rows, counts)
+    r = SC.check_swiglu_rows(x[rows], w, ws, xs[rows], sc, full_s["q"][rows], full_s["q_scale"][rows])
+    assert r["mismatches"] == 0 and r["int8_off_by_one"] == 0 and r["rows"] == len(rows)
+    g = SC.check_gmm_rows(x[rows], w, ws, xs[rows], sc, full_g[rows])
+    assert g["mismatches"] == 0 and g["not_bit_identical"] == 0
+    # a wrong row is caught
+    bad = full_g[rows].copy()
+    bad[3] ^= 0x0040
+    assert SC.check_gmm_rows(x[rows], w, ws, xs[rows], sc, bad)["not_bit_identical"] > 0
+    qbad = full_s["q"][rows].copy()
+    qbad[2, :] = np.where(qbad[2, :] > 100, qbad[2, :] - 3, qbad[2, :] + 3)
+    assert SC.check_swiglu_rows(x[rows], w, ws, xs[rows], sc, qbad, full_s["q_scale"][rows])["mismatches"] > 0
