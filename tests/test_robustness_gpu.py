@@ -135,6 +135,36 @@ def test_cta_cap_per_call_swiglu_quant(oracle, monkeypatch, max_ctas, ctas):
     assert d.max() <= 1 and np.count_nonzero(d) / d.size <= 1e-4
 
 
+def test_two_swiglu_calls_overlapping_on_two_streams(oracle):
+    """Two persistent launches that each want every SM: their CTAs are not all resident together.  Nothing in the kernel
+    waits for another CTA (the wave pacing is a bounded hint), so both calls finish without a timeout and are correct."""
+    import ops_transformer_b200 as ops
+    dev = _dev()
+    counts = np.array([700, 300, 0, 1100, 520], np.int64)
+    M, K, N, E = int(counts.sum()), 1024, 2048, 5
+    gl = torch.from_numpy(np.cumsum(counts)).to(dev)
+    sets = [_gmm_inputs(dev, M, K, N, E, 44 + i) for i in range(2)]
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    outs = []
+    torch.cuda.synchronize()
+    for rep in range(3):
+        outs = []
+        for (host, devt), st in zip(sets, streams):
+            with torch.cuda.stream(st):
+                wsb = torch.empty(64 << 20, dtype=torch.uint8, device=dev)   # one workspace per call
+                q, qs, wsb = ops.grouped_matmul_swiglu_quant(*devt, gl, stream=st, workspace=wsb, return_workspace=True,
+                                                             options=ops.LaunchOptions(wait_limit_cycles=400_000_000))
+                outs.append((q, qs, wsb, st))
+        for q, qs, wsb, st in outs:
+            ops.check_status(wsb, stream=st)
+    for (host, _), (q, qs, _, _) in zip(sets, outs):
+        ref = oracle.swiglu_quant(*host, np.cumsum(counts))
+        rel = np.abs(qs.cpu().numpy() - ref["q_scale"]) / np.abs(ref["q_scale"])
+        assert rel.max() <= 1e-6
+        d = np.abs(q.cpu().numpy().astype(np.int32) - ref["q"].astype(np.int32))
+        assert d.max() <= 1 and np.count_nonzero(d) / d.size <= 1e-4
+
+
 def test_options_are_per_executor_and_need_a_live_executor(gmm_lib):
     _dev()
     opts = _lib.LaunchOptions(max_ctas=4)
