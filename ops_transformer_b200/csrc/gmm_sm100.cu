@@ -795,7 +795,11 @@ gmm_w8a8_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             int wave = 0;
             for (int t = unit; t < total_tiles && ok; t += n_units, ++wave) {
                 const Tile tl = decode_tile(sh, t, p.n_tiles, L, C::kTileM);
-                const int my_row0 = tl.row0 + (int)rank * BM;
+                // A CTA none of whose 128 rows belong to the group (the second CTA of a pair on a trailing block of at most
+                // 128 rows) loads from beyond the last row of x instead: TMA then fills the box with zeros without touching
+                // memory, and the tensor core multiplies zeros instead of the next group's rows (less traffic, less power;
+                // the results of those rows are discarded either way).
+                const int my_row0 = tl.rows > (int)rank * BM ? tl.row0 + (int)rank * BM : p.M;
                 if (pace) {
                     if (wave > 0) {
                         const int expected = min(n_units, total_tiles - (wave - 1) * n_units);
