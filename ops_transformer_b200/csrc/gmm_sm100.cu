@@ -12,18 +12,24 @@
 //   grouped_matmul       : the 256 columns are 256 consecutive output columns.
 //   swiglu_quant         : columns [0,128) come from weight columns n0.. (activated half), columns [128,256)
 //                          from N/2+n0.. (linear half), so SwiGLU is tile-local and a tile yields 128 outputs.
-// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2-9 = epilogue.
+// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2-9 = epilogue; swiglu_quant
+// adds warp 10, one lane of which keeps the books of the row blocks in global memory.
 // CTA pairs (cluster of 2, tcgen05 cta_group::2) compute 256-row tiles when groups are long; each CTA then stages its own
 // 128 rows of x and half of the weight columns.  Weight layouts: [E,K,N] (MN-major operand, 128-byte swizzle), the
 // transposed view [E,N,K] (K-major) and FRACTAL_NZ [E,N/32,K/16,16,32] (MN-major, 32-byte swizzle, 5-D tensor map).
 // Epilogue: the tile's per-column scales are staged in shared memory while the MMAs run; bf16 / fp16 results are
 // transposed through shared memory so that stores cover whole 128-byte row segments (optionally scattered by a row
 // index, also into other GPUs' buffers); the finalize-routing variant adds weighted fp32 rows into token rows with
-// 16-byte vector reductions; SwiGLU values go to an fp32 staging buffer with a per-row atomic max, and once all N tiles of a
-// 128-row block have done so (a counter per block) every CTA that worked on the block requantises its share of
-// the block's rows to int8, one tile later, while the data is still in L2.
+// 16-byte vector reductions; SwiGLU values go to an fp32 staging buffer (transposed the same way) with a per-row atomic
+// max, and a finished row block is requantised to int8 in row slices that the CTAs which worked on it claim from a
+// counter - no CTA ever waits for another one (see publish_and_collect).
+// What bounds the MMA loop is the shared-memory / L1 data path (TMA writes, operand reads of both CTAs of a pair, and
+// every load, store and shuffle of the epilogue), not the tensor pipe and not the feed: memory instructions of the
+// epilogue are kept wide and contiguous for that reason.  The producers pace themselves wave by wave so that the units
+// which share x rows and weight boxes through L2 stay together (a bounded hint).
 // Every wait on an mbarrier is bounded; on expiry the CTA records a status word, all roles leave their loops,
 // outstanding copies are drained with a second bounded wait, TMEM is released and the kernel returns.
+// -DGMM_TRACE builds in clock64 / globaltimer stamps of the roles of a few CTAs (a buffer address comes from the environment).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 

@@ -20,6 +20,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+
 #include "gmm_common.h"
 
 namespace gmm {
@@ -49,9 +51,35 @@ struct RoutingParams {
     int nb;
 };
 
+// Programmatic dependent launch.  The kernels of one call form a chain (count -> scatter -> gather) in which the next
+// kernel has work that does not depend on the previous one: the gather kernel loads and quantises its token before it needs
+// the row positions.  A kernel that calls pdl_release() lets the next launch of the stream (if it was made with launch_pdl)
+// start while this one still runs; that next kernel calls pdl_wait() before it touches anything this one writes, and the
+// wait returns when this grid has ended and its writes are visible.  Without the launch attribute both are no-ops.
+__device__ __forceinline__ void pdl_release() { asm volatile("griddepcontrol.launch_dependents;"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), unsigned grid, unsigned block, size_t smem, cudaStream_t stream, bool overlap,
+                       Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(block);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = overlap ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 __global__ void __launch_bounds__(kPairsPerBlock) routing_count_kernel(const RoutingParams p)
 {
     extern __shared__ int hist[];
+    pdl_release();
     for (int e = threadIdx.x; e < p.range; e += blockDim.x) hist[e] = 0;
     __syncthreads();
     const long long j = (long long)blockIdx.x * kPairsPerBlock + threadIdx.x;
@@ -158,12 +186,59 @@ constexpr int kWarpTableRange = 256;  // up to this many active experts the scat
 
 // PER_WARP: shared memory holds [32 warps][range] counters, all warps count at once and a scan over the warps gives every
 // warp its start; otherwise one counter per expert and the warps take turns.
-template <bool PER_WARP>
+// FOLD (small tables: at most kWarpTableRange active experts and kFoldTable counters): the scan kernel is left out and
+// every block derives what it needs from the block histograms itself - the rows of the earlier blocks and the first row
+// of every expert - while block 0 also writes the counts output.  One launch less per call.
+constexpr int kFoldTable = 8192;
+template <bool PER_WARP, bool FOLD = false>
 __global__ void __launch_bounds__(kPairsPerBlock) routing_scatter_kernel(const RoutingParams p)
 {
     extern __shared__ int running[];
+    __shared__ int s_first[FOLD ? kWarpTableRange : 1], s_off[FOLD ? kWarpTableRange : 1], s_tot[FOLD ? kWarpTableRange : 1];
     const int slots = PER_WARP ? p.range * (kPairsPerBlock / 32) : p.range;
+    pdl_release();
     for (int e = threadIdx.x; e < slots; e += blockDim.x) running[e] = 0;
+    pdl_wait();  // the block histograms (or the scan's tables) are complete
+    if (FOLD) {
+        for (int e = threadIdx.x; e < p.range; e += blockDim.x) {
+            int before = 0, total = 0;
+            for (int b = 0; b < p.nb; ++b) {
+                const int h = __ldg(p.block_hist + (size_t)b * p.range + e);
+                if (b < (int)blockIdx.x) before += h;
+                total += h;
+            }
+            s_off[e] = before;
+            s_tot[e] = total;
+        }
+        __syncthreads();
+        for (int e = threadIdx.x; e < p.range; e += blockDim.x) {
+            int first = 0, nz = 0;
+            for (int e2 = 0; e2 < e; ++e2) {
+                first += s_tot[e2];
+                nz += s_tot[e2] != 0;
+            }
+            s_first[e] = first;
+            if (blockIdx.x == 0) {  // the counts output, in count or key-value form (as the scan kernel writes it)
+                const int c = s_tot[e];
+                if (p.count_type == 1) {
+                    p.counts_out[e] = c;
+                } else if (c != 0) {
+                    p.counts_out[2 * (size_t)nz] = e + p.e_start;
+                    p.counts_out[2 * (size_t)nz + 1] = c;
+                }
+                if (e == p.range - 1) {
+                    *p.total = first + c;
+                    if (p.count_type == 2) {  // the compact list ends in zero entries
+                        const int written_pairs = min(p.range + 1, p.expert_num);
+                        for (int i = nz + (c != 0); i < written_pairs; ++i) {
+                            p.counts_out[2 * (size_t)i] = 0;
+                            p.counts_out[2 * (size_t)i + 1] = 0;
+                        }
+                    }
+                }
+            }
+        }
+    }
     const long long j = (long long)blockIdx.x * kPairsPerBlock + threadIdx.x;
     int e = -1;
     if (j < p.pairs) {
@@ -211,7 +286,8 @@ __global__ void __launch_bounds__(kPairsPerBlock) routing_scatter_kernel(const R
         if (p.row_idx_type == 0) p.expanded_row_idx[j] = -1;
         return;
     }
-    const int pos = p.expert_first[e] + p.block_off[(size_t)blockIdx.x * p.range + e] + before;
+    const int pos = FOLD ? s_first[e] + s_off[e] + before
+                         : p.expert_first[e] + p.block_off[(size_t)blockIdx.x * p.range + e] + before;
     p.sorted_row[pos] = (int)j;
     p.pair_pos[j] = pos;
     if (p.row_idx_type == 1) p.expanded_row_idx[pos] = (int)j;
@@ -360,9 +436,11 @@ __device__ __forceinline__ void unpack16<__half>(const uint4 &u, float *f)
 // stays in registers; without a smooth scale it is quantised once and the int8 row is stored at the output row of each
 // of the token's k pairs; with one, every pair is scaled, reduced and quantised from the registers.  DRAM traffic is the
 // algorithmic minimum: x once, every output row once.  Needs h a multiple of the 16-byte vector, h <= THREADS * NCH * VEC
-// and 16-byte aligned pointers; other shapes take routing_quant_kernel.
-template <typename T, int NCH, int THREADS>
-__global__ void __launch_bounds__(THREADS, 3) routing_quant_token_kernel(const RoutingParams p)
+// and 16-byte aligned pointers; other shapes take routing_quant_kernel.  MINB CTAs per SM: the 16-bit inputs run with 4
+// (64 registers): 66 instead of 73 us per call on 4096 x 7168 bf16 tokens, because a CTA is a chain of load, block
+// reduction and stores, and only other CTAs fill the gaps.
+template <typename T, int NCH, int THREADS, int MINB = 3>
+__global__ void __launch_bounds__(THREADS, MINB) routing_quant_token_kernel(const RoutingParams p)
 {
     constexpr int VEC = 16 / (int)sizeof(T);
     constexpr int G = 16 / VEC;  // 16-byte loads that make one 16-byte store of int8: a thread owns G adjacent ones
@@ -400,6 +478,7 @@ __global__ void __launch_bounds__(THREADS, 3) routing_quant_token_kernel(const R
                 w[i][e4 / 4] = pack4(quant_fast(v[i][e4], scale, rcp), quant_fast(v[i][e4 + 1], scale, rcp),
                                      quant_fast(v[i][e4 + 2], scale, rcp), quant_fast(v[i][e4 + 3], scale, rcp));
     }
+    pdl_wait();  // the row positions are complete
     for (int s = 0; s < p.k; ++s) {
         const long long j = (long long)token * p.k + s;
         const int pos = p.pair_pos[j];
@@ -535,24 +614,30 @@ cudaError_t init_routing_launch(const InitRoutingProblem &r, void *workspace, si
     p.pair_pos = reinterpret_cast<int *>(ws + off);
     p.nb = (int)nb;
     const size_t smem = (size_t)range * 4;
+    // GMM_B200_PDL=0 turns the overlap of the chain's kernels off (plain stream order)
+    const char *pdl_env = getenv("GMM_B200_PDL");
+    const bool overlap = !(pdl_env && pdl_env[0] == '0');
     routing_count_kernel<<<(unsigned)nb, kPairsPerBlock, smem, stream>>>(p);
-    routing_scan_kernel<<<(unsigned)((range + 31) / 32), 1024, 0, stream>>>(p);
-    if (range <= kWarpTableRange) routing_scatter_kernel<true><<<(unsigned)nb, kPairsPerBlock, smem * (kPairsPerBlock / 32), stream>>>(p);
-    else routing_scatter_kernel<false><<<(unsigned)nb, kPairsPerBlock, smem, stream>>>(p);
+    if (range <= kWarpTableRange && (long long)nb * range <= kFoldTable) {
+        launch_pdl(routing_scatter_kernel<true, true>, (unsigned)nb, kPairsPerBlock, smem * (kPairsPerBlock / 32), stream, overlap, p);
+    } else {
+        routing_scan_kernel<<<(unsigned)((range + 31) / 32), 1024, 0, stream>>>(p);
+        if (range <= kWarpTableRange) routing_scatter_kernel<true><<<(unsigned)nb, kPairsPerBlock, smem * (kPairsPerBlock / 32), stream>>>(p);
+        else routing_scatter_kernel<false><<<(unsigned)nb, kPairsPerBlock, smem, stream>>>(p);
+    }
     const int eb = r.x_dtype == kF32 ? 4 : (r.x_dtype == kI8 ? 1 : 2);
     const bool aligned = ((reinterpret_cast<uintptr_t>(r.x) | reinterpret_cast<uintptr_t>(r.expanded_x) | reinterpret_cast<uintptr_t>(r.scale)) & 15) == 0;
     if (r.quant) {
         // token-major kernels hold 32 values per thread (256 threads): h <= 8192, and h a multiple of 16 for the 16-byte stores
-        const int vec = 16 / eb;
         const bool fast = aligned && r.h % 16 == 0 && r.h <= 8192 && r.n <= 0x7fffffffll;
         if (r.x_dtype == kF32) {
-            if (fast) routing_quant_token_kernel<float, 8, 256><<<(unsigned)r.n, 256, 0, stream>>>(p);
+            if (fast) launch_pdl(routing_quant_token_kernel<float, 8, 256>, (unsigned)r.n, 256, 0, stream, overlap, p);
             else routing_quant_kernel<float><<<(unsigned)pairs, 128, 0, stream>>>(p);
         } else if (r.x_dtype == kF16) {
-            if (fast) routing_quant_token_kernel<__half, 4, 256><<<(unsigned)r.n, 256, 0, stream>>>(p);
+            if (fast) launch_pdl(routing_quant_token_kernel<__half, 4, 256, 4>, (unsigned)r.n, 256, 0, stream, overlap, p);
             else routing_quant_kernel<__half><<<(unsigned)pairs, 128, 0, stream>>>(p);
         } else if (r.x_dtype == kBF16) {
-            if (fast) routing_quant_token_kernel<__nv_bfloat16, 4, 256><<<(unsigned)r.n, 256, 0, stream>>>(p);
+            if (fast) launch_pdl(routing_quant_token_kernel<__nv_bfloat16, 4, 256, 4>, (unsigned)r.n, 256, 0, stream, overlap, p);
             else routing_quant_kernel<__nv_bfloat16><<<(unsigned)pairs, 128, 0, stream>>>(p);
         } else {
             return cudaErrorInvalidValue;
