@@ -170,18 +170,22 @@ __global__ void __launch_bounds__(256) swiglu_simt_kernel(const SimtParams p)
 __global__ void __launch_bounds__(256) combine_init_kernel(float4 *y, const uint2 *shared, long long n4, long long rows,
                                                            long long shared_offset, long long shared_rows, float weight)
 {
-    const long long total = rows * n4;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-        const long long r = i / n4;
-        float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
+        float4 *dst = y + r * n4;
         if (r >= shared_offset && r < shared_offset + shared_rows) {
-            const uint2 b = __ldg(shared + (i - shared_offset * n4));  // four bf16
-            v.x = __fmul_rn(__uint_as_float(b.x << 16), weight);
-            v.y = __fmul_rn(__uint_as_float(b.x & 0xffff0000u), weight);
-            v.z = __fmul_rn(__uint_as_float(b.y << 16), weight);
-            v.w = __fmul_rn(__uint_as_float(b.y & 0xffff0000u), weight);
+            const uint2 *src = shared + (r - shared_offset) * n4;
+            for (long long c = threadIdx.x; c < n4; c += blockDim.x) {
+                const uint2 b = __ldg(src + c);  // four bf16
+                float4 v;
+                v.x = __fmul_rn(__uint_as_float(b.x << 16), weight);
+                v.y = __fmul_rn(__uint_as_float(b.x & 0xffff0000u), weight);
+                v.z = __fmul_rn(__uint_as_float(b.y << 16), weight);
+                v.w = __fmul_rn(__uint_as_float(b.y & 0xffff0000u), weight);
+                dst[c] = v;
+            }
+        } else {
+            for (long long c = threadIdx.x; c < n4; c += blockDim.x) dst[c] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         }
-        y[i] = v;
     }
 }
 
@@ -218,8 +222,8 @@ cudaError_t combine_init_launch(const Problem &p, cudaStream_t stream)
                                                                         p.shared_offset, p.shared_input ? p.shared_rows : 0, p.shared_weight);
         return cudaGetLastError();
     }
-    const long long n4 = p.N / 4, total = p.out_rows * n4;
-    long long blocks = (total + 255) / 256;
+    const long long n4 = p.N / 4;
+    long long blocks = p.out_rows;  // whole rows per block
     if (blocks > cap) blocks = cap;
     combine_init_kernel<<<(unsigned)blocks, 256, 0, stream>>>(reinterpret_cast<float4 *>(p.out0), reinterpret_cast<const uint2 *>(p.shared_input),
                                                              n4, p.out_rows, p.shared_offset, p.shared_input ? p.shared_rows : 0,
