@@ -42,10 +42,10 @@ FALLBACK_BF16_TFLOPS = 1590.0
 # The full-size launches are too large to capture, so the reduced cases are scaled by the units processed (rows, or non-empty
 # experts for the weight-streaming decode case); traffic grows in proportion to them.  name -> (bytes, source file).
 NCU_DRAM_BYTES_PER_LAUNCH = {
-    "c2_small": (504.7e6, "profiles/ncu_gmm_kernel_c2_small_swiglu_quant.md"),
-    "c2": (4 * 504.7e6, "profiles/ncu_gmm_kernel_c2_small_swiglu_quant.md, x4 by rows"),
-    "c3_small": (216.7e6, "profiles/ncu_gmm_kernel_c3_small_w8a8_bf16.md"),
-    "c3": (4 * 216.7e6, "profiles/ncu_gmm_kernel_c3_small_w8a8_bf16.md, x4 by rows"),
+    "c2_small": (486.3e6, "profiles/ncu_gmm_kernel_c2_small_swiglu_quant.md"),
+    "c2": (4 * 486.3e6, "profiles/ncu_gmm_kernel_c2_small_swiglu_quant.md, x4 by rows"),
+    "c3_small": (217.8e6, "profiles/ncu_gmm_kernel_c3_small_w8a8_bf16.md"),
+    "c3": (4 * 217.8e6, "profiles/ncu_gmm_kernel_c3_small_w8a8_bf16.md, x4 by rows"),
     "c4_swiglu_small": (859.8e6, "profiles/ncu_gmm_kernel_c4_small_decode_swiglu_quant.md"),
     "c4_swiglu": (859.8e6 * 165 / 29, "profiles/ncu_gmm_kernel_c4_small_decode_swiglu_quant.md, x165/29 by non-empty experts"),
 }
@@ -700,7 +700,7 @@ def bench_init_routing(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=400)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, help="c2 (default at N=1), c3, c4_swiglu, c4_down, c3_finalize, init_routing")

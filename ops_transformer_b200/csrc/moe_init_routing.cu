@@ -619,7 +619,8 @@ cudaError_t init_routing_launch(const InitRoutingProblem &r, void *workspace, si
     const bool overlap = !(pdl_env && pdl_env[0] == '0');
     routing_count_kernel<<<(unsigned)nb, kPairsPerBlock, smem, stream>>>(p);
     if (range <= kWarpTableRange && (long long)nb * range <= kFoldTable) {
-        launch_pdl(routing_scatter_kernel<true, true>, (unsigned)nb, kPairsPerBlock, smem * (kPairsPerBlock / 32), stream, overlap, p);
+        const cudaError_t e = launch_pdl(routing_scatter_kernel<true, true>, (unsigned)nb, kPairsPerBlock, smem * (kPairsPerBlock / 32), stream, overlap, p);
+        if (e != cudaSuccess) return e;
     } else {
         routing_scan_kernel<<<(unsigned)((range + 31) / 32), 1024, 0, stream>>>(p);
         if (range <= kWarpTableRange) routing_scatter_kernel<true><<<(unsigned)nb, kPairsPerBlock, smem * (kPairsPerBlock / 32), stream>>>(p);
@@ -627,17 +628,18 @@ cudaError_t init_routing_launch(const InitRoutingProblem &r, void *workspace, si
     }
     const int eb = r.x_dtype == kF32 ? 4 : (r.x_dtype == kI8 ? 1 : 2);
     const bool aligned = ((reinterpret_cast<uintptr_t>(r.x) | reinterpret_cast<uintptr_t>(r.expanded_x) | reinterpret_cast<uintptr_t>(r.scale)) & 15) == 0;
+    cudaError_t launch_err = cudaSuccess;
     if (r.quant) {
         // token-major kernels hold 32 values per thread (256 threads): h <= 8192, and h a multiple of 16 for the 16-byte stores
         const bool fast = aligned && r.h % 16 == 0 && r.h <= 8192 && r.n <= 0x7fffffffll;
         if (r.x_dtype == kF32) {
-            if (fast) launch_pdl(routing_quant_token_kernel<float, 8, 256>, (unsigned)r.n, 256, 0, stream, overlap, p);
+            if (fast) launch_err = launch_pdl(routing_quant_token_kernel<float, 8, 256>, (unsigned)r.n, 256, 0, stream, overlap, p);
             else routing_quant_kernel<float><<<(unsigned)pairs, 128, 0, stream>>>(p);
         } else if (r.x_dtype == kF16) {
-            if (fast) launch_pdl(routing_quant_token_kernel<__half, 4, 256, 4>, (unsigned)r.n, 256, 0, stream, overlap, p);
+            if (fast) launch_err = launch_pdl(routing_quant_token_kernel<__half, 4, 256, 4>, (unsigned)r.n, 256, 0, stream, overlap, p);
             else routing_quant_kernel<__half><<<(unsigned)pairs, 128, 0, stream>>>(p);
         } else if (r.x_dtype == kBF16) {
-            if (fast) launch_pdl(routing_quant_token_kernel<__nv_bfloat16, 4, 256, 4>, (unsigned)r.n, 256, 0, stream, overlap, p);
+            if (fast) launch_err = launch_pdl(routing_quant_token_kernel<__nv_bfloat16, 4, 256, 4>, (unsigned)r.n, 256, 0, stream, overlap, p);
             else routing_quant_kernel<__nv_bfloat16><<<(unsigned)pairs, 128, 0, stream>>>(p);
         } else {
             return cudaErrorInvalidValue;
@@ -649,6 +651,7 @@ cudaError_t init_routing_launch(const InitRoutingProblem &r, void *workspace, si
         else
             routing_copy_kernel<<<(unsigned)pairs, 128, 0, stream>>>(p, eb);
     }
+    if (launch_err != cudaSuccess) return launch_err;
     return cudaGetLastError();
 }
 
