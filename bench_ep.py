@@ -40,6 +40,8 @@ def make_rank_data(dev, world, rank, tokens):
     d["xs"] = torch.empty((tokens,), dtype=torch.float32, device=dev).uniform_(1e-3, 1e-2, generator=g)
     _, top = synth.topk_softmax_counts(tokens, N_EXPERTS, TOP_K, seed=rank, idx=7)
     d["topk"] = torch.from_numpy(top.astype(np.int64)).to(dev)
+    wts = torch.empty((tokens, TOP_K), dtype=torch.float32, device=dev).uniform_(0.05, 1.0, generator=g)
+    d["topk_w"] = wts / wts.sum(dim=1, keepdim=True)   # routing weights of the combine (they sum to 1 per token)
     return d
 
 
@@ -99,24 +101,35 @@ def timed_steps(ffn, d, steps, warmup, world, use_graph=False):
 
 
 def e2e_steps(ffn, d, steps):
-    """The same step through the public classes with host buffers: pinned H2D of tokens, scales and routing, the
-    FFN, D2H of the result rows, every step."""
+    """The same step through the public classes with host buffers, every step: pinned H2D of tokens, scales, routing (and
+    routing weights), the FFN, D2H of the result.  The fused layer returns what a caller of the reference's
+    dispatch -> FFN -> combine chain gets back, one combined bf16 row per token (the weighted sum of its top-k result
+    rows, FusedExpertParallelFFN.combine); the NCCL variant has no combine and returns all result rows."""
+    combine = hasattr(ffn, "combine")
     hx = torch.empty_like(d["x"], device="cpu").pin_memory(); hx.copy_(d["x"])
     hs = torch.empty_like(d["xs"], device="cpu").pin_memory(); hs.copy_(d["xs"])
     ht = torch.empty_like(d["topk"], device="cpu").pin_memory(); ht.copy_(d["topk"])
-    dx, ds, dt = torch.empty_like(d["x"]), torch.empty_like(d["xs"]), torch.empty_like(d["topk"])
+    hw = torch.empty_like(d["topk_w"], device="cpu").pin_memory(); hw.copy_(d["topk_w"])
+    dx, ds, dt, dw = torch.empty_like(d["x"]), torch.empty_like(d["xs"]), torch.empty_like(d["topk"]), torch.empty_like(d["topk_w"])
     host_out = None
+    last = {}
 
     def step():
         nonlocal host_out
         dx.copy_(hx, non_blocking=True); ds.copy_(hs, non_blocking=True); dt.copy_(ht, non_blocking=True)
+        if combine:
+            dw.copy_(hw, non_blocking=True)
         res = ffn.replay(dx, ds, dt) if getattr(ffn, "_graph", None) is not None else ffn.forward(dx, ds, dt)
-        ys = [res["y"]] if isinstance(res, dict) else [r["y"] for r in res]
+        if combine:
+            ys = [ffn.combine(res, dw)]
+        else:
+            ys = [res["y"]] if isinstance(res, dict) else [r["y"] for r in res]
         if host_out is None:
             host_out = [torch.empty_like(y, device="cpu").pin_memory() for y in ys]
         for h, y in zip(host_out, ys):
             h.copy_(y, non_blocking=True)
         torch.cuda.synchronize()
+        last["res"], last["out"] = res, ys
 
     step()
     if dist.is_initialized():
@@ -125,9 +138,32 @@ def e2e_steps(ffn, d, steps):
     for _ in range(steps):
         step()
     ms = (time.perf_counter() - t0) / steps * 1e3
-    h2d = hx.numel() + hs.numel() * 4 + ht.numel() * 8
+    h2d = hx.numel() + hs.numel() * 4 + ht.numel() * 8 + (hw.numel() * 4 if combine else 0)
     d2h = sum(h.numel() * h.element_size() for h in host_out)
-    return ms, h2d, d2h
+    checked = verify_combined(ffn, last["res"], d, host_out[0]) if combine else None
+    return ms, h2d, d2h, checked
+
+
+def verify_combined(ffn, res, d, host_combined, n_tokens=64, seed=0):
+    """Combined rows of a token sample (as they arrived on the host) against the oracle's combine of the returned rows
+    (which verify_returned_rows checks against the oracle FFN): bit for bit."""
+    from oracle import oracle as O
+    k = ffn.top_k
+    pair_row = np.full(ffn.tokens * k, -1, np.int64)
+    for c, ch in enumerate(res["chunks"]):
+        n = int(ch["rows_in_use"].item())
+        order = ch["plan"].order[:n].cpu().numpy()
+        pair0 = 0 if ffn.parts > 1 else ffn.bounds[c] * k
+        pair_row[pair0 + order] = ffn.result_base[c] + np.arange(n)
+    rng = np.random.default_rng(seed + ffn.rank)
+    toks = np.unique(np.concatenate([[0, ffn.tokens - 1], rng.integers(0, ffn.tokens, size=n_tokens)]))
+    rows = pair_row.reshape(ffn.tokens, k)[toks]                       # [n, k] rows of the result buffer
+    flat = torch.from_numpy(np.maximum(rows, 0).reshape(-1)).to(res["y"].device)
+    y_sel = res["y"][flat].view(torch.int16).cpu().numpy().view(np.uint16)
+    local = np.where(rows >= 0, np.arange(rows.size).reshape(rows.shape), -1)
+    want = O.ep_combine(y_sel, local, d["topk_w"][torch.from_numpy(toks).to(res["y"].device)].cpu().numpy())
+    got = host_combined[torch.from_numpy(toks)].view(torch.int16).numpy().view(np.uint16)
+    return {"tokens": int(toks.size), "mismatches": int((got != want).any(axis=1).sum())}
 
 
 def verify_returned_rows(res, d, dev, world, rank, tokens, experts_checked=4, rows_per_expert=24, seed=0):
@@ -240,7 +276,7 @@ def bench_main(args, ClockSampler, cpu_baseline_sample, measured_peaks, extra_c2
     if not args.no_verify:
         torch.cuda.synchronize()
         verified = verify_returned_rows(res, d, dev, world, rank, T)
-    e2e_ms, h2d, d2h = e2e_steps(ffn, d, 3)
+    e2e_ms, h2d, d2h, combined_checked = e2e_steps(ffn, d, 3)
     dropped = int(ffn.overflow.item()) if hasattr(ffn, "overflow") else 0
     trace = None
     if args.ep_phases and hasattr(ffn, "trace"):
@@ -262,7 +298,8 @@ def bench_main(args, ClockSampler, cpu_baseline_sample, measured_peaks, extra_c2
         else:
             trace = mine
     stats = torch.tensor([ms, float(rows_local), float(dropped), e2e_ms, float(verified["rows"]), float(verified["mismatches"]),
-                          float(verified.get("not_bit_identical", 0))], dtype=torch.float64, device=dev)
+                          float(verified.get("not_bit_identical", 0)), float(combined_checked["tokens"] if combined_checked else 0),
+                          float(combined_checked["mismatches"] if combined_checked else 0)], dtype=torch.float64, device=dev)
     if world > 1:
         allst = [torch.empty_like(stats) for _ in range(world)]
         dist.all_gather(allst, stats)
@@ -294,7 +331,13 @@ def bench_main(args, ClockSampler, cpu_baseline_sample, measured_peaks, extra_c2
                          "peak_basis": f"2 x sustained bf16 of {peaks['source']} ({peaks['bf16_tflops_sustained']} TFLOP/s); int8 ops "
                                        "counted as 2 per multiply-add"},
             "e2e": {"value": rows_total * ops_per_row / (e2e_max * 1e-3) / 1e12, "unit": "TOPS", "ms_per_step": e2e_max,
-                    "h2d_bytes_per_step": int(h2d) * world, "d2h_bytes_per_step": int(d2h) * world},
+                    "h2d_bytes_per_step": int(h2d) * world, "d2h_bytes_per_step": int(d2h) * world,
+                    "result": ("one combined bf16 row per token (weighted sum of its top-k result rows, on the device after the "
+                               "step)" if combined_checked else "all result rows"),
+                    "combined_verified": ({"tokens": int(sum(float(s_[7]) for s_ in allst)),
+                                           "mismatches": int(sum(float(s_[8]) for s_ in allst)),
+                                           "bar": "bit-identical to the oracle's combine of the returned rows"}
+                                          if combined_checked else None)},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
             "ep": {"tokens_per_s": T * world / (ms_max * 1e-3), "one_gpu_same_workload": n1,

@@ -123,6 +123,22 @@ ACL_FUNC_VISIBILITY aclnnStatus gmmB200EpRoute(const void *topk, const void *blo
                                               int64_t tokenBase, int64_t resultBase, void *srcToken, void *order, void *sendDest,
                                               void *retDest, void *groupList, void *firstRow, aclrtStream stream);
 
+/* The consumer of the expert-parallel path: every token's result rows, which the down GEMM's epilogue stored into this
+ * GPU's result buffer in send order, weighted and summed into one row per token - the last step of the reference's
+ * MoeDistributeCombineV2, xOut = Sum(expertScales * ataOut) (mc2/moe_distribute_combine_v2/README.md:12-17; fp32 Muls and
+ * Add per slot in slot order, CAST_RINT to bf16 at the end: op_kernel/moe_distribute_combine_v2.h:1130-1134, 1195-1258).
+ *   gmmB200EpInverseMap: pairRow[order[i]] = resultBase + i for i < min(*rowsInUse, maxRows).  order (int64, from
+ *                   gmmB200EpRoute) and rowsInUse (int64[1]) are on the device; pairRow is int32 [nPairs], which the caller
+ *                   has filled with -1 (pairs without a row - dropped or outside this piece - stay -1); entries of order
+ *                   outside [0, nPairs) are skipped and counted in *badCounter (int32 on the device).
+ *   gmmB200EpCombine: out[t] = bf16(sum over s < topK with pairRow[t*topK+s] >= 0 of float(y[pairRow[t*topK+s]]) * weights[t*topK+s]).
+ *                   y bf16 [yRows, hidden], weights fp32 [tokens, topK], out bf16 [tokens, hidden]; hidden a multiple of 8.
+ * The caller orders the GPUs (a barrier) between the down GEMM and the combine. */
+ACL_FUNC_VISIBILITY aclnnStatus gmmB200EpInverseMap(const void *order, const void *rowsInUse, int64_t maxRows, int64_t resultBase,
+                                                   int64_t nPairs, void *pairRow, void *badCounter, aclrtStream stream);
+ACL_FUNC_VISIBILITY aclnnStatus gmmB200EpCombine(const void *y, const void *pairRow, const void *weights, void *out, int64_t tokens,
+                                                int32_t topK, int64_t hidden, int64_t yRows, aclrtStream stream);
+
 /* Flat form of aclnnGroupedMatmulFinalizeRoutingWeightNz (include/aclnnop/aclnn_grouped_matmul_finalize_routing_weight_nz.h),
  * with two freedoms the aclnn form lacks: weightLayout 0 ([e, k, n], the faster layout on B200) besides 2 (FRACTAL_NZ), and
  * groupListType 0 (running totals) besides 1.  sharedInput and logit are given together (rows are added to y, which the

@@ -36,7 +36,7 @@ EXPORTED_SYMBOLS = [
     "gmmB200Version", "gmmB200CheckStatus", "gmmB200SetExecutorOptions", "gmmB200GroupedMatmulW8A8WorkspaceSize", "gmmB200GroupedMatmulW8A8",
     "gmmB200GroupedMatmulSwigluQuantWorkspaceSize", "gmmB200GroupedMatmulSwigluQuant",
     "gmmB200NoAllocScratchBytes", "gmmB200GroupedMatmulSwigluQuantNoAlloc", "gmmB200NoAllocCheckStatus",
-    "gmmB200PeerAlloc", "gmmB200PeerFree", "gmmB200PeerExport", "gmmB200PeerImport", "gmmB200PeerRelease", "gmmB200EpDispatch", "gmmB200EpCount", "gmmB200EpRoute",
+    "gmmB200PeerAlloc", "gmmB200PeerFree", "gmmB200PeerExport", "gmmB200PeerImport", "gmmB200PeerRelease", "gmmB200EpDispatch", "gmmB200EpCount", "gmmB200EpRoute", "gmmB200EpInverseMap", "gmmB200EpCombine",
 ]
 
 
@@ -105,6 +105,8 @@ def _load():
     L.gmmB200EpDispatch.argtypes = [p, p, p, p, i64, i64, i64, C.POINTER(p), C.POINTER(p), i32, p, p, i32, p]
     L.gmmB200EpCount.argtypes = [p, i64, i32, p, p, p]
     L.gmmB200EpRoute.argtypes = [p, p, p, i64, i32, i32, i32, i32, i64, i64, i64, p, p, p, p, p, p, p]
+    L.gmmB200EpInverseMap.argtypes = [p, p, i64, i64, i64, p, p, p]
+    L.gmmB200EpCombine.argtypes = [p, p, p, p, i64, i32, i64, i64, p]
     L.gmmB200NoAllocScratchBytes.restype = u64
     L.gmmB200GroupedMatmulSwigluQuantNoAlloc.argtypes = [p, p, p, i32, p, p, i64, i64, i64, i64, i64, p, p, p]
     L.gmmB200NoAllocCheckStatus.argtypes = [p, C.POINTER(i32)]

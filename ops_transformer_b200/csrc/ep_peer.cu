@@ -5,6 +5,8 @@
 // (mc2/moe_distribute_dispatch_v2/docs/MoeDistributeDispatch-Combine算子设计介绍.md:40-66) followed by MoeReRouting
 // (moe/moe_re_routing/README.md:12-26) for rows that are already quantised.
 // Only plain stores to peer memory are used; no bulk-tensor copies touch another GPU's memory.
+#include <cuda_bf16.h>
+
 #include <algorithm>
 #include <cstring>
 
@@ -195,6 +197,51 @@ __global__ void __launch_bounds__(256) ep_route_kernel(const RouteParams p)
 
 }  // namespace
 
+// Inverse of the send order: pair_row[order[i]] = result_base + i for the rows in use.
+__global__ void __launch_bounds__(256) ep_inverse_map_kernel(const long long *order, const long long *rows_in_use, long long max_rows,
+                                                             long long result_base, int n_pairs, int *pair_row, int *bad)
+{
+    const long long n = min(*rows_in_use, max_rows);
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long pair = order[i];
+        if (pair >= 0 && pair < n_pairs) pair_row[pair] = (int)(result_base + i);
+        else atomicAdd(bad, 1);   // a send position that names no pair: skipped and counted
+    }
+}
+
+// One CTA per token: out[token] = bf16( sum over the token's slots, in slot order, of float(y[row]) * weight ), every product
+// and every sum rounded on its own (Muls then Add on fp32, CAST_RINT at the end:
+// mc2/moe_distribute_combine_v2/op_kernel/moe_distribute_combine_v2.h:1130-1134, 1195, 1258).  Slots without a row are left out.
+__global__ void __launch_bounds__(256) ep_combine_kernel(const uint4 *y, const int *pair_row, const float *weights, uint4 *out,
+                                                         int top_k, int h8, long long y_rows)
+{
+    const long long token = blockIdx.x;
+    for (int c = threadIdx.x; c < h8; c += blockDim.x) {
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+        for (int s = 0; s < top_k; ++s) {
+            const int row = pair_row[token * top_k + s];
+            if (row < 0 || row >= y_rows) continue;
+            const float w = weights[token * top_k + s];
+            const uint4 v = y[(size_t)row * h8 + c];   // written by other GPUs before the barrier: a plain (coherent) load
+            const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                acc[2 * j] = __fadd_rn(acc[2 * j], __fmul_rn(__uint_as_float(u[j] << 16), w));
+                acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], __fmul_rn(__uint_as_float(u[j] & 0xffff0000u), w));
+            }
+        }
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const __nv_bfloat162 b = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+            o[j] = *reinterpret_cast<const uint32_t *>(&b);
+        }
+        out[(size_t)token * h8 + c] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
 extern "C" {
 
 aclnnStatus gmmB200PeerAlloc(uint64_t bytes, void **devPtr)
@@ -317,6 +364,43 @@ aclnnStatus gmmB200EpRoute(const void *topk, const void *blockHist, const void *
     ep_route_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return gmm::fail(ACLNN_ERR_INNER, "route kernel launch failed: %s", cudaGetErrorString(e));
+    return ACLNN_SUCCESS;
+}
+
+aclnnStatus gmmB200EpInverseMap(const void *order, const void *rowsInUse, int64_t maxRows, int64_t resultBase, int64_t nPairs,
+                                void *pairRow, void *badCounter, aclrtStream stream)
+{
+    gmm::clear_error();
+    if (!order || !rowsInUse || !pairRow || !badCounter)
+        return gmm::fail(ACLNN_ERR_PARAM_NULLPTR, "order, rowsInUse, pairRow and badCounter must not be nullptr.");
+    if (maxRows < 0 || nPairs <= 0 || nPairs > 0x7fffffff || resultBase < 0 || resultBase + maxRows > 0x7fffffff)
+        return gmm::fail(ACLNN_ERR_PARAM_INVALID, "need 0 < nPairs < 2^31, maxRows >= 0 and resultBase + maxRows < 2^31.");
+    if (maxRows == 0) return ACLNN_SUCCESS;
+    int sms = gmm::device_sm_count();
+    if (sms <= 0) sms = 148;
+    const int grid = (int)std::min<int64_t>((maxRows + 255) / 256, (int64_t)sms * 8);
+    ep_inverse_map_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const long long *>(order), static_cast<const long long *>(rowsInUse), maxRows, resultBase, (int)nPairs,
+        static_cast<int *>(pairRow), static_cast<int *>(badCounter));
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return gmm::fail(ACLNN_ERR_INNER, "inverse map kernel launch failed: %s", cudaGetErrorString(e));
+    return ACLNN_SUCCESS;
+}
+
+aclnnStatus gmmB200EpCombine(const void *y, const void *pairRow, const void *weights, void *out, int64_t tokens, int32_t topK,
+                             int64_t hidden, int64_t yRows, aclrtStream stream)
+{
+    gmm::clear_error();
+    if (!y || !pairRow || !weights || !out) return gmm::fail(ACLNN_ERR_PARAM_NULLPTR, "y, pairRow, weights and out must not be nullptr.");
+    if (tokens < 0 || tokens > 0x7fffffff || topK <= 0 || hidden <= 0 || hidden % 8 != 0 || yRows < 0 ||
+        ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(out)) & 15))
+        return gmm::fail(ACLNN_ERR_PARAM_INVALID, "hidden must be a positive multiple of 8, y and out 16-byte aligned, tokens < 2^31.");
+    if (tokens == 0) return ACLNN_SUCCESS;
+    ep_combine_kernel<<<(unsigned)tokens, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4 *>(y), static_cast<const int *>(pairRow), static_cast<const float *>(weights), static_cast<uint4 *>(out),
+        topK, (int)(hidden / 8), yRows);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return gmm::fail(ACLNN_ERR_INNER, "combine kernel launch failed: %s", cudaGetErrorString(e));
     return ACLNN_SUCCESS;
 }
 

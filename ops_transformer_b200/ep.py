@@ -354,6 +354,11 @@ class FusedExpertParallelFFN:
                                 ret_dest=torch.empty(self.cap_c, **i64), group_list=torch.empty(self.e_piece, **i64),
                                 first_row=torch.empty(1, **i64)))
         self._totals = torch.empty((chunks, self.world, self.e_piece), **i64)
+        # for the combine (forward(..., topk_weights=...)): the row of every (token, slot) pair in the result buffer, the
+        # combined tokens, and a counter of send positions that named no pair
+        self._pair_row = torch.empty(self.n_send, dtype=torch.int32, device=dev)
+        self.combined = None
+        self.bad_pairs = torch.zeros(1, dtype=torch.int32, device=dev)
         self._side = torch.cuda.Stream() if chunks > 1 else None
         self._graph = None
         self.trace = None   # set to a list to collect (label, CUDA event) marks without synchronising
@@ -383,13 +388,18 @@ class FusedExpertParallelFFN:
         if rc != 0:
             raise acl.AclnnError(rc, "gmmB200EpDispatch")
 
-    def forward(self, x: torch.Tensor, x_scale: torch.Tensor, topk_ids: torch.Tensor):
+    def forward(self, x: torch.Tensor, x_scale: torch.Tensor, topk_ids: torch.Tensor, topk_weights: Optional[torch.Tensor] = None):
+        """topk_weights (fp32 [tokens, top_k], optional): also combine every token's result rows into one row,
+        result["combined"] = bf16(sum_s weights[t, s] * y[row of (t, s)]) - the last step of the reference's
+        MoeDistributeCombineV2 (mc2/moe_distribute_combine_v2/README.md:12-17).  Dropped rows are left out of the sum."""
         from . import acl
         G, E, C_ = self.world, self.e_local, self.chunks
         k = self.top_k
         self._mark("start")
         if self.route_kernels:
-            return self._forward_kernels(x, x_scale, topk_ids)
+            return self._forward_kernels(x, x_scale, topk_ids, topk_weights)
+        if topk_weights is not None:
+            raise ValueError("the combine needs the routing kernels (route_kernels = True)")
         if self.parts > 1:
             raise ValueError("expert_parts needs the routing kernels (route_kernels = True)")
         # routing plans and row maps of all chunks first (small kernels), one count exchange for all chunks
@@ -446,7 +456,40 @@ class FusedExpertParallelFFN:
         return {"y": self.result, "plan": plans[0], "group_list": group_lists[0], "group_lists": group_lists, "chunks": chunk_out,
                 "dropped_rows": self.overflow}
 
-    def _forward_kernels(self, x, x_scale, topk_ids):
+    def combine(self, res: dict, topk_weights: torch.Tensor) -> torch.Tensor:
+        """The combine on the result of a forward() or replay(): the row of every pair from the send orders of all pieces,
+        then one weighted sum per token (bf16 [tokens, hidden_out]).  forward(..., topk_weights=...) calls it itself."""
+        plans = [ch["plan"] for ch in res["chunks"]]
+        import ctypes as C
+
+        from . import _lib, acl
+        L = _lib.lib()
+        p = lambda t: C.c_void_p(t.data_ptr())  # noqa: E731
+        st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        w = topk_weights.to(torch.float32).contiguous()
+        if tuple(w.shape) != (self.tokens, self.top_k):
+            raise ValueError(f"topk_weights must be [{self.tokens}, {self.top_k}]")
+        if self.combined is None:
+            self.combined = torch.empty((self.tokens, self.hidden_out), dtype=torch.bfloat16, device=w.device)
+        self._pair_row.fill_(-1)
+        in_use = []
+        for c in range(self.chunks):
+            # expert ranges number their pairs over all tokens; token chunks inside the chunk
+            pair0 = 0 if self.parts > 1 else self.bounds[c] * self.top_k
+            n_pairs = self.n_send if self.parts > 1 else self.piece_pairs[c]
+            rows = self._totals[c].sum().reshape(1)
+            in_use.append(rows)
+            rc = L.gmmB200EpInverseMap(p(plans[c].order), p(rows), self.piece_pairs[c], self.result_base[c], n_pairs,
+                                       C.c_void_p(self._pair_row.data_ptr() + 4 * pair0), p(self.bad_pairs), st)
+            if rc != 0:
+                raise acl.AclnnError(rc, "gmmB200EpInverseMap")
+        rc = L.gmmB200EpCombine(p(self.result), p(self._pair_row), p(w), p(self.combined), self.tokens, self.top_k, self.hidden_out,
+                                self.result_rows, st)
+        if rc != 0:
+            raise acl.AclnnError(rc, "gmmB200EpCombine")
+        return self.combined
+
+    def _forward_kernels(self, x, x_scale, topk_ids, topk_weights=None):
         """forward() with the routing done by gmmB200EpCount / gmmB200EpRoute."""
         import ctypes as C
 
@@ -529,29 +572,39 @@ class FusedExpertParallelFFN:
         # with expert_parts a piece holds only the pairs routed to its expert range)
         chunk_out = [{"y": self.result[self.result_base[c]:self.result_base[c] + self.piece_pairs[c]], "plan": plans[c],
                       "rows_in_use": self._totals[c].sum()} for c in range(C_)]
-        return {"y": self.result, "plan": plans[0], "group_list": group_lists[0], "group_lists": group_lists, "chunks": chunk_out,
-                "dropped_rows": self.overflow}
+        out = {"y": self.result, "plan": plans[0], "group_list": group_lists[0], "group_lists": group_lists, "chunks": chunk_out,
+               "dropped_rows": self.overflow}
+        if topk_weights is not None:
+            out["combined"] = self.combine(out, topk_weights)
+            out["bad_pairs"] = self.bad_pairs
+            self._mark("combine")
+        return out
 
-    def capture(self, x: torch.Tensor, x_scale: torch.Tensor, topk_ids: torch.Tensor):
+    def capture(self, x: torch.Tensor, x_scale: torch.Tensor, topk_ids: torch.Tensor, topk_weights: Optional[torch.Tensor] = None):
         """Record one step into a CUDA graph.  Shapes are static (buffers are sized by capacity and nothing is read on
         the host), so the whole step - routing plan, count exchange, row maps, dispatch, both GEMMs, barriers - replays
         with one launch and no Python in between.  Inputs are copied into fixed tensors before every replay."""
         self._gx, self._gs, self._gt = torch.empty_like(x), torch.empty_like(x_scale), torch.empty_like(topk_ids)
         self._gx.copy_(x); self._gs.copy_(x_scale); self._gt.copy_(topk_ids)
+        self._gw = None
+        if topk_weights is not None:
+            self._gw = topk_weights.to(torch.float32).contiguous().clone()
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             for _ in range(2):   # warm-up outside capture: lazy initialisation of kernels, NCCL and the workspace pool
-                self.forward(self._gx, self._gs, self._gt)
+                self.forward(self._gx, self._gs, self._gt, self._gw)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         self._graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self._graph):
-            self._graph_out = self.forward(self._gx, self._gs, self._gt)
+            self._graph_out = self.forward(self._gx, self._gs, self._gt, self._gw)
         return self
 
-    def replay(self, x: torch.Tensor, x_scale: torch.Tensor, topk_ids: torch.Tensor):
+    def replay(self, x: torch.Tensor, x_scale: torch.Tensor, topk_ids: torch.Tensor, topk_weights: Optional[torch.Tensor] = None):
         self._gx.copy_(x, non_blocking=True); self._gs.copy_(x_scale, non_blocking=True); self._gt.copy_(topk_ids, non_blocking=True)
+        if self._gw is not None and topk_weights is not None:
+            self._gw.copy_(topk_weights, non_blocking=True)
         self._graph.replay()
         return self._graph_out
 

@@ -255,6 +255,26 @@ def bf16_bits_to_f32(b) -> np.ndarray:
     return (np.ascontiguousarray(b, np.uint16).astype(np.uint32) << 16).view(np.float32)
 
 
+def ep_combine(y_bits, pair_row, weights) -> np.ndarray:
+    """The combine that ends the expert-parallel path: per token, sum = 0; for every slot in slot order
+    sum = sum + float(row) * weight (fp32 Muls, then fp32 Add: mc2/moe_distribute_combine_v2/op_kernel/
+    moe_distribute_combine_v2.h:1130-1134, 1195); the result is cast to bf16 with round-to-nearest-even (:1258).
+    y_bits: uint16 [rows, h] bf16 bit patterns; pair_row: int [tokens, k] row of every (token, slot) pair, negative or
+    beyond the rows = no row; weights: fp32 [tokens, k].  Returns uint16 [tokens, h]."""
+    y_bits = np.ascontiguousarray(y_bits, np.uint16)
+    pair_row = np.asarray(pair_row)
+    weights = np.asarray(weights, np.float32)
+    tokens, k = pair_row.shape
+    acc = np.zeros((tokens, y_bits.shape[1]), np.float32)
+    for s in range(k):
+        rows = pair_row[:, s]
+        ok = (rows >= 0) & (rows < y_bits.shape[0])
+        v = bf16_bits_to_f32(y_bits[np.where(ok, rows, 0)])
+        prod = (v * weights[:, s:s + 1]).astype(np.float32)      # one rounding
+        acc = np.where(ok[:, None], (acc + prod).astype(np.float32), acc)   # one rounding
+    return f32_to_bf16_bits(acc)
+
+
 # --------------------------------------------------------------------------------------------------
 # Independent numpy formulation (slow; small cases only).  Written separately from the C code: int64
 # matmul for the accumulators, numpy float32 element-wise ops (each one separately rounded), numpy's own

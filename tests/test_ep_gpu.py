@@ -84,6 +84,22 @@ def _check_parts(O, res, x, xs, topk, w1, s1, w2, s2):
     assert seen == T * TOP_K, "the pieces together hold every (token, slot) pair once"
 
 
+def _check_combined(O, ffn, res, wts):
+    """res["combined"] against the oracle's combine of the returned rows, bit for bit; the pair -> row map is rebuilt here
+    from the pieces' send orders."""
+    pair_row = np.full(T * TOP_K, -1, np.int64)
+    for c, ch in enumerate(res["chunks"]):
+        n = int(ch["rows_in_use"].item()) if "rows_in_use" in ch else int(ch["plan"].order.shape[0])
+        order = ch["plan"].order.cpu().numpy()[:n]
+        pair0 = 0 if ffn.parts > 1 else ffn.bounds[c] * TOP_K
+        pair_row[pair0 + order] = ffn.result_base[c] + np.arange(n)
+    assert (pair_row >= 0).all() and int(res["bad_pairs"].item()) == 0
+    y_bits = res["y"].view(torch.int16).cpu().numpy().view(np.uint16)
+    want = O.ep_combine(y_bits, pair_row.reshape(T, TOP_K), wts)
+    got = res["combined"].view(torch.int16).cpu().numpy().view(np.uint16)
+    assert got.shape == want.shape and np.array_equal(got, want)
+
+
 def _run_fused(O, dev, rank, world, w1, s1, w2, s2, x, xs, topk, chunks=1, route_kernels=True, parts=1):
     el = N_EXPERTS // world
     lo, hi = rank * el, (rank + 1) * el
@@ -91,10 +107,13 @@ def _run_fused(O, dev, rank, world, w1, s1, w2, s2, x, xs, topk, chunks=1, route
     ffn = ep.FusedExpertParallelFFN(N_EXPERTS, H, H, t(w1[lo:hi]), t(s1[lo:hi]), t(w2[lo:hi]), t(s2[lo:hi]), tokens=T, top_k=TOP_K,
                                     capacity=2 * T * TOP_K, chunks=chunks, expert_parts=parts)
     ffn.route_kernels = route_kernels
+    wts = np.random.default_rng(97 + rank).uniform(0.05, 1.0, size=(T, TOP_K)).astype(np.float32) if route_kernels else None
     for _ in range(2):  # twice: the second step runs over the first one's buffers
-        res = ffn.forward(t(x), t(xs), t(topk))
+        res = ffn.forward(t(x), t(xs), t(topk), None if wts is None else t(wts))
     torch.cuda.synchronize()
     assert int(ffn.overflow.item()) == 0
+    if wts is not None:
+        _check_combined(O, ffn, res, wts)
     if parts > 1:
         _check_parts(O, res, x, xs, topk, w1, s1, w2, s2)
         ffn.close()

@@ -363,3 +363,19 @@ def test_oracle_on_sampled_rows_equals_sampled_rows_of_the_oracle(oracle):
     qbad = full_s["q"][rows].copy()
     qbad[2, :] = np.where(qbad[2, :] > 100, qbad[2, :] - 3, qbad[2, :] + 3)
     assert SC.check_swiglu_rows(x[rows], w, ws, xs[rows], sc, qbad, full_s["q_scale"][rows])["mismatches"] > 0
+
+
+def test_ep_combine_weighted_sum_in_slot_order(oracle):
+    """Two tokens, three slots: products and sums rounded one at a time in slot order, missing rows left out, bf16 RNE."""
+    y = np.array([[1.0, 3.0], [0.5, -2.0], [4.0, 1.0], [8.0, 8.0]], np.float32)
+    pair_row = np.array([[0, 2, 1], [3, -1, 99]])
+    w = np.array([[0.5, 0.25, 2.0], [0.125, 7.0, 7.0]], np.float32)
+    got = oracle.bf16_bits_to_f32(oracle.ep_combine(oracle.f32_to_bf16_bits(y), pair_row, w))
+    want = np.array([[0.5 + 1.0 + 1.0, 1.5 + 0.25 - 4.0], [1.0, 1.0]], np.float32)
+    assert np.array_equal(got, want)
+    # the order of the additions is the slot order: a sum that depends on it
+    big = oracle.f32_to_bf16_bits(np.array([[2.0 ** 24], [1.0], [-(2.0 ** 24)]], np.float32))
+    r = oracle.bf16_bits_to_f32(oracle.ep_combine(big, np.array([[0, 1, 2]]), np.ones((1, 3), np.float32)))
+    assert r[0, 0] == 0.0      # (2^24 + 1) rounds to 2^24, then - 2^24
+    r = oracle.bf16_bits_to_f32(oracle.ep_combine(big, np.array([[0, 2, 1]]), np.ones((1, 3), np.float32)))
+    assert r[0, 0] == 1.0
