@@ -701,7 +701,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, help="c2 (default at N=1), c3, c4_swiglu, c4_down, c3_finalize, init_routing")
     ap.add_argument("--weight-format", default="nd", choices=["nd", "nz"], help="N=1: weight layout [E,K,N] or FRACTAL_NZ")
