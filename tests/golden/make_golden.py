@@ -73,8 +73,18 @@ def main():
     cases.append(dict(file="finalize_routing_small.npz", op="grouped_matmul_finalize_routing", M=M, K=K, N=N, E=E, batch=M // topk,
                       shared_offset=4, shared_weight=0.5, group_list_type=1,
                       note="y is the sum in row order; an unordered fp32 sum may differ by 4 * 2^-23 * abs_sum"))
+    # the combine that ends the expert-parallel path: weighted sum of a token's result rows in slot order
+    tokens, k, h, rows = 20, 4, 64, 70
+    yb = O.f32_to_bf16_bits(rng.uniform(-300, 300, size=(rows, h)).astype(np.float32))
+    pair_row = rng.permutation(tokens * k)[:tokens * k].reshape(tokens, k) % rows
+    pair_row[3, 1] = -1            # a dropped row
+    pair_row[7] = -1               # a token none of whose rows came back
+    wts = rng.uniform(0.05, 1.0, size=(tokens, k)).astype(np.float32)
+    np.savez_compressed(os.path.join(HERE, "ep_combine_small.npz"), y_bf16_bits=yb, pair_row=pair_row.astype(np.int32), weights=wts,
+                        out_bf16_bits=O.ep_combine(yb, pair_row, wts))
+    cases.append(dict(file="ep_combine_small.npz", op="ep_combine", tokens=tokens, k=k, h=h, rows=rows))
     with open(os.path.join(HERE, "manifest.json"), "w") as f:
-        json.dump(dict(source="oracle/gmm_oracle.c (the reference has no golden vectors for these operators)",
+        json.dump(dict(source="oracle/gmm_oracle.c, oracle/oracle.py (the reference has no golden vectors for these operators)",
                        cases=cases), f, indent=1)
 
 

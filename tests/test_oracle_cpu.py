@@ -302,6 +302,9 @@ def test_golden_fixtures(oracle):
                 assert np.array_equal(r[key], d[key]), key
             assert r["rows"] == int(d["rows"])
             continue
+        if case["op"] == "ep_combine":
+            assert np.array_equal(oracle.ep_combine(d["y_bf16_bits"], d["pair_row"], d["weights"]), d["out_bf16_bits"])
+            continue
         x, w, ws, xs, gl = d["x"], d["w"], d["w_scale"], d["x_scale"], d["group_list"]
         if case["op"] == "grouped_matmul_finalize_routing":
             r = oracle.gmm_finalize_routing(x, w, ws, xs, gl, d["row_index"], case["batch"], bias=d["bias_bf16_bits"],

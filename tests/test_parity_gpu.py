@@ -741,6 +741,19 @@ def test_golden_fixtures_on_the_gpu():
             for got, key in zip(outs, ("expanded_x", "expanded_row_idx", "counts", "expanded_scale")):
                 assert np.array_equal(got.cpu().numpy(), d[key]), (case["file"], key)
             continue
+        if case["op"] == "ep_combine":
+            import ctypes as C
+
+            from ops_transformer_b200 import _lib
+            y_dev, rows_dev, w_dev = bf(d["y_bf16_bits"]), t(d["pair_row"]), t(d["weights"])
+            out = torch.full((case["tokens"], case["h"]), -1.0, dtype=torch.bfloat16, device=dev)
+            p = lambda a: C.c_void_p(a.data_ptr())  # noqa: E731
+            rc = _lib.lib().gmmB200EpCombine(p(y_dev), p(rows_dev), p(w_dev), p(out), case["tokens"], case["k"], case["h"], case["rows"],
+                                             C.c_void_p(torch.cuda.current_stream().cuda_stream))
+            assert rc == 0
+            torch.cuda.synchronize()
+            assert np.array_equal(_bf16_bits(out), d["out_bf16_bits"]), case["file"]
+            continue
         x, w, ws, xs, gl = d["x"], d["w"], d["w_scale"], d["x_scale"], d["group_list"]
         if case["op"] == "grouped_matmul_finalize_routing":
             y = ops.grouped_matmul_finalize_routing(t(x), t(nd_to_nz(w)), t(ws), t(gl), t(d["row_index"]), case["batch"],
@@ -765,7 +778,8 @@ def test_golden_fixtures_on_the_gpu():
             rel = np.abs(qs.cpu().numpy()[:rows] - d["q_scale"][:rows]) / d["q_scale"][:rows]
             dd = np.abs(q.cpu().numpy()[:rows].astype(np.int32) - d["q"][:rows].astype(np.int32))
             assert rel.max() <= QSCALE_RTOL and dd.max() <= 1 and np.count_nonzero(dd) <= max(1, int(Q_LSB_FRACTION * dd.size)), case["file"]
-    assert seen == {"grouped_matmul", "grouped_matmul_swiglu_quant", "moe_init_routing_v3", "grouped_matmul_finalize_routing"}
+    assert seen == {"grouped_matmul", "grouped_matmul_swiglu_quant", "moe_init_routing_v3", "grouped_matmul_finalize_routing",
+                    "ep_combine"}
 
 
 def test_host_pipelined_pieces_equal_the_whole_call(oracle):
