@@ -42,8 +42,8 @@ FALLBACK_BF16_TFLOPS = 1590.0
 # The full-size launches are too large to capture, so the reduced cases are scaled by the units processed (rows, or non-empty
 # experts for the weight-streaming decode case); traffic grows in proportion to them.  name -> (bytes, source file).
 NCU_DRAM_BYTES_PER_LAUNCH = {
-    "c2_small": (486.3e6, "profiles/ncu_gmm_kernel_c2_small_swiglu_quant.md"),
-    "c2": (4 * 486.3e6, "profiles/ncu_gmm_kernel_c2_small_swiglu_quant.md, x4 by rows"),
+    "c2_small": (454.0e6, "profiles/ncu_gmm_kernel_c2_small_swiglu_quant.md"),
+    "c2": (4 * 454.0e6, "profiles/ncu_gmm_kernel_c2_small_swiglu_quant.md, x4 by rows"),
     "c3_small": (217.8e6, "profiles/ncu_gmm_kernel_c3_small_w8a8_bf16.md"),
     "c3": (4 * 217.8e6, "profiles/ncu_gmm_kernel_c3_small_w8a8_bf16.md, x4 by rows"),
     "c4_swiglu_small": (859.8e6, "profiles/ncu_gmm_kernel_c4_small_decode_swiglu_quant.md"),
