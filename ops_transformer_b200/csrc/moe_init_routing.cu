@@ -200,42 +200,48 @@ __global__ void __launch_bounds__(kPairsPerBlock) routing_scatter_kernel(const R
     for (int e = threadIdx.x; e < slots; e += blockDim.x) running[e] = 0;
     pdl_wait();  // the block histograms (or the scan's tables) are complete
     if (FOLD) {
+        __shared__ int warp_sums[32];
         for (int e = threadIdx.x; e < p.range; e += blockDim.x) {
-            int before = 0, total = 0;
-            for (int b = 0; b < p.nb; ++b) {
-                const int h = __ldg(p.block_hist + (size_t)b * p.range + e);
-                if (b < (int)blockIdx.x) before += h;
-                total += h;
-            }
-            s_off[e] = before;
-            s_tot[e] = total;
+            s_off[e] = 0;
+            s_tot[e] = 0;
         }
         __syncthreads();
-        for (int e = threadIdx.x; e < p.range; e += blockDim.x) {
-            int first = 0, nz = 0;
-            for (int e2 = 0; e2 < e; ++e2) {
-                first += s_tot[e2];
-                nz += s_tot[e2] != 0;
+        // all threads share the table (one round trip to L2): per expert the total and the rows of the earlier blocks
+        const int entries = p.nb * p.range;
+        for (int i = threadIdx.x; i < entries; i += blockDim.x) {
+            const int h = __ldg(p.block_hist + i);
+            if (h != 0) {
+                const int b = i / p.range, e = i - b * p.range;
+                atomicAdd(&s_tot[e], h);
+                if (b < (int)blockIdx.x) atomicAdd(&s_off[e], h);
             }
-            s_first[e] = first;
-            if (blockIdx.x == 0) {  // the counts output, in count or key-value form (as the scan kernel writes it)
-                const int c = s_tot[e];
-                if (p.count_type == 1) {
-                    p.counts_out[e] = c;
-                } else if (c != 0) {
-                    p.counts_out[2 * (size_t)nz] = e + p.e_start;
-                    p.counts_out[2 * (size_t)nz + 1] = c;
-                }
-                if (e == p.range - 1) {
-                    *p.total = first + c;
-                    if (p.count_type == 2) {  // the compact list ends in zero entries
-                        const int written_pairs = min(p.range + 1, p.expert_num);
-                        for (int i = nz + (c != 0); i < written_pairs; ++i) {
-                            p.counts_out[2 * (size_t)i] = 0;
-                            p.counts_out[2 * (size_t)i + 1] = 0;
-                        }
+        }
+        __syncthreads();
+        // scan over the experts (range <= 256 <= blockDim): first row of every expert, and the counts output from block 0
+        {
+            const int e = threadIdx.x;
+            const int c = e < p.range ? s_tot[e] : 0;
+            int sum_c, sum_nz;
+            const int inc_c = block_scan_1024(c, warp_sums, &sum_c);
+            const int inc_nz = block_scan_1024(c != 0 ? 1 : 0, warp_sums, &sum_nz);
+            if (e < p.range) s_first[e] = inc_c - c;
+            if (blockIdx.x == 0) {  // in count or key-value form (as the scan kernel writes it)
+                if (e < p.range) {
+                    if (p.count_type == 1) {
+                        p.counts_out[e] = c;
+                    } else if (c != 0) {
+                        p.counts_out[2 * (size_t)(inc_nz - 1)] = e + p.e_start;
+                        p.counts_out[2 * (size_t)(inc_nz - 1) + 1] = c;
                     }
                 }
+                if (p.count_type == 2) {  // the compact list ends in zero entries (moe_v3_expert_tokens_count.h:126-128, 255-257)
+                    const int written_pairs = min(p.range + 1, p.expert_num);
+                    for (int i = sum_nz + threadIdx.x; i < written_pairs; i += blockDim.x) {
+                        p.counts_out[2 * (size_t)i] = 0;
+                        p.counts_out[2 * (size_t)i + 1] = 0;
+                    }
+                }
+                if (threadIdx.x == 0) *p.total = sum_c;
             }
         }
     }
