@@ -584,8 +584,9 @@ def test_init_routing_many_blocks_keep_pair_order(oracle):
     # 40000 pairs = 40 blocks of 1024: the order of equal experts must hold across warps and blocks
     check_init_routing(oracle, 5000, 8, 64, 32, (0, 32), 74)
     check_init_routing(oracle, 5000, 8, 64, 2048, (100, 1900), 75, count_type=2)
-    check_init_routing(oracle, 5000, 8, 64, 256, (0, 256), 79, count_type=2)   # table too large for the folded scan
-    check_init_routing(oracle, 4000, 8, 64, 256, (3, 250), 80, count_type=2)   # folded scan, key-value counts
+    check_init_routing(oracle, 4000, 8, 64, 256, (3, 250), 80, count_type=2)   # scan folded into the scatter kernel, key-value counts
+    check_init_routing(oracle, 9000, 8, 64, 256, (0, 256), 79, count_type=2)   # table too large for the folded scan
+    check_init_routing(oracle, 9000, 8, 64, 32, (1, 31), 82, count_type=2)     # folded scan over 71 blocks
 
 
 def test_init_routing_without_quantisation(oracle):
