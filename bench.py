@@ -447,7 +447,7 @@ def measure_workload(args, name, steps, weight_format="nd", with_e2e=False, veri
         ho1 = torch.empty_like(out1, device="cpu").pin_memory() if out1 is not None else None
         dx, dxs, dgl = torch.empty_like(x), torch.empty_like(xs), torch.empty_like(gl)
         pipe = None
-        if not finalize and args.e2e_pieces > 1 and weight_format == "nd":   # the pipelined helper slices an [E, K, N] weight
+        if not finalize and args.e2e_pieces > 1:   # the pipelined helper slices the weight by experts, in either layout
             # the call a user with host-resident rows makes: the operator split by experts into a copy-in / operator /
             # copy-out pipeline (ops_transformer_b200/hostio.py); every piece goes through the aclnn entry points
             from ops_transformer_b200.hostio import HostPipelinedGroupedOp

@@ -30,7 +30,12 @@ class HostPipelinedGroupedOp:
         self.op = op
         self.w, self.ws = weight, weight_scale
         self.dev = weight.device
-        self.E, self.K, self.N = weight.shape
+        if weight.dim() == 5:   # FRACTAL_NZ [E, N/32, K/16, 16, 32] (acl.format_cast_nz); pieces slice it by experts all the same
+            self.E, self.N, self.K = int(weight.shape[0]), int(weight.shape[1]) * 32, int(weight.shape[2]) * 16
+            self.wkw = {"weight_format": _lib.ACL_FORMAT_FRACTAL_NZ}
+        else:
+            self.E, self.K, self.N = (int(v) for v in weight.shape)
+            self.wkw = {}
         self.pieces = max(1, min(pieces, self.E))
         self.s_in, self.s_op, self.s_out = (torch.cuda.Stream(self.dev) for _ in range(3))
         self.dx = torch.empty((max_rows, self.K), dtype=torch.int8, device=self.dev)
@@ -86,11 +91,11 @@ class HostPipelinedGroupedOp:
                 if self.op == "swiglu_quant":
                     acl.grouped_matmul_swiglu_quant(
                         self.dx[r0:r1], self.w[e0:e1], self.ws[e0:e1], self.dxs[r0:r1], self.dgl[e0:e1], output=self.out0[r0:r1],
-                        output_scale=self.out1[r0:r1], stream=self.s_op, workspace=self.workspace)
+                        output_scale=self.out1[r0:r1], stream=self.s_op, workspace=self.workspace, **self.wkw)
                 else:
                     acl.grouped_matmul_v4(
                         self.dx[r0:r1], self.w[e0:e1], self.ws[e0:e1], self.dxs[r0:r1], self.dgl[e0:e1], out=self.out0[r0:r1],
-                        stream=self.s_op, workspace=self.workspace)
+                        stream=self.s_op, workspace=self.workspace, **self.wkw)
                 ev_op = torch.cuda.Event()
                 ev_op.record(self.s_op)
             with torch.cuda.stream(self.s_out):

@@ -811,6 +811,14 @@ def test_host_pipelined_pieces_equal_the_whole_call(oracle):
             pipe.run(hx, hxs, counts, h0)
             ref = oracle.gmm_w8a8(x, w, ws, xs, np.cumsum(counts), 0)["y"]
             assert np.array_equal(h0.view(torch.int16).numpy().view(np.uint16), ref)
+    # the same pipeline over a FRACTAL_NZ weight (the 5-D storage is sliced by experts like the 3-D one)
+    pipe = HostPipelinedGroupedOp("swiglu_quant", ops.format_cast_nz(t(w)), t(ws), M, pieces=3)
+    h0 = torch.zeros((M, 256), dtype=torch.int8).pin_memory()
+    h1 = torch.zeros((M,), dtype=torch.float32).pin_memory()
+    pipe.run(hx, hxs, counts, h0, h1)
+    q, qs = ops.grouped_matmul_swiglu_quant(t(x), t(w), t(ws), t(xs), t(np.cumsum(counts)))
+    torch.cuda.synchronize()
+    assert np.array_equal(h1.numpy(), qs.cpu().numpy()) and np.array_equal(h0.numpy(), q.cpu().numpy())
 
 
 # ----------------------------------------------------------------------------------------------------------
